@@ -1,0 +1,278 @@
+// C ABI of the library: argument checks, buffer layout, launch parameters. No torch types, no exceptions.
+#include <cuda_runtime.h>
+#include <cstdio>
+#include <cstring>
+#include <cmath>
+
+#include "../../include/megamoe_b200.h"
+#include "mm_kernel.cuh"
+#include "mm_frontend.cuh"
+
+namespace {
+
+thread_local char g_cuda_error[256] = "";
+
+int cuda_fail(cudaError_t e, const char* what) {
+    snprintf(g_cuda_error, sizeof(g_cuda_error), "%s: %s", what, cudaGetErrorString(e));
+    return MM_ERR_CUDA;
+}
+#define MM_CUDA(call) do { cudaError_t e_ = (call); if (e_ != cudaSuccess) return cuda_fail(e_, #call); } while (0)
+
+inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+int sf_vec_of(int fmt) { return fmt == MM_FMT_NVFP4 ? 16 : 32; }
+
+int check_config(const mm_config_t* c) {
+    if (c == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (c->num_ranks < 1 || c->num_ranks > mm::kMaxRanks || c->rank < 0 || c->rank >= c->num_ranks) return MM_ERR_INVALID_ARGUMENT;
+    if (c->num_experts <= 0 || c->num_experts % c->num_ranks != 0) return MM_ERR_INVALID_ARGUMENT;
+    if (c->num_experts / c->num_ranks > mm::kMaxLocalExperts) return MM_ERR_UNSUPPORTED;
+    if (c->num_topk < 1 || c->num_topk > 32 || c->num_max_tokens_per_rank < 1 || c->num_max_tokens_per_rank > 32768) return MM_ERR_INVALID_ARGUMENT;
+    if (c->hidden <= 0 || c->hidden % 512 != 0 || c->hidden > 4096) return MM_ERR_UNSUPPORTED;
+    if (c->intermediate <= 0 || c->intermediate % 256 != 0 || c->intermediate > 4096) return MM_ERR_UNSUPPORTED;
+    if (c->act_format != MM_FMT_MXFP4 && c->act_format != MM_FMT_NVFP4) return MM_ERR_UNSUPPORTED;
+    return MM_OK;
+}
+
+int grid_size(const mm_config_t* cfg, int* out) {
+    int g = cfg->num_sms;
+    if (g <= 0) {
+        int dev = 0;
+        MM_CUDA(cudaGetDevice(&dev));
+        MM_CUDA(cudaDeviceGetAttribute(&g, cudaDevAttrMultiProcessorCount, dev));
+    }
+    if (g > 256 || g < cfg->num_ranks) return MM_ERR_UNSUPPORTED;
+    *out = g;
+    return MM_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* mm_status_string(int s) {
+    switch (s) {
+        case MM_OK: return "ok";
+        case MM_ERR_INVALID_ARGUMENT: return "invalid argument";
+        case MM_ERR_UNSUPPORTED: return "unsupported configuration";
+        case MM_ERR_CUDA: return "CUDA runtime error";
+        case MM_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+        case MM_ERR_DEVICE_CAPACITY: return "device-side table capacity exceeded";
+        default: return "unknown status";
+    }
+}
+
+const char* mm_last_cuda_error(void) { return g_cuda_error; }
+
+int32_t mm_get_token_alignment(void) { return 16; }
+
+int mm_get_weight_geometry(int32_t act_format, mm_weight_geometry_t* out) {
+    if (out == nullptr || (act_format != MM_FMT_MXFP4 && act_format != MM_FMT_NVFP4)) return MM_ERR_INVALID_ARGUMENT;
+    const int vec = sf_vec_of(act_format);
+    out->tile_rows = mm::kTileRows;
+    out->unit_k = mm::kUnitK;
+    out->unit_weight_bytes = mm::kUnitWBytes;
+    out->unit_sf_bytes = (mm::kUnitK / (4 * vec)) * 512;
+    out->unit_bytes = out->unit_weight_bytes + out->unit_sf_bytes;
+    out->sf_vec = vec;
+    return MM_OK;
+}
+
+int mm_get_layout(const mm_config_t* c, mm_layout_t* out) {
+    const int st = check_config(c);
+    if (st != MM_OK) return st;
+    if (out == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    memset(out, 0, sizeof(*out));
+    const int vec = sf_vec_of(c->act_format);
+    const int64_t e_local = c->num_experts / c->num_ranks;
+    const int64_t t_max = c->num_max_tokens_per_rank;
+    out->sf_vec = vec;
+    out->x_row_bytes = c->hidden / 2;
+    out->x_sf_row_bytes = c->hidden / vec;
+    out->rx_row_bytes = out->x_row_bytes + out->x_sf_row_bytes + 16;
+    out->rx_cap_rows = t_max * (c->num_topk < e_local ? c->num_topk : e_local);
+    out->mid_rows = out->rx_cap_rows * c->num_ranks + mm::kTileTokens * e_local;
+    out->mid_row_bytes = c->intermediate / 2;
+    out->mid_sf_row_bytes = align_up(c->intermediate / vec, 16);
+    int64_t off = 0;
+    auto take = [&](int64_t bytes) { const int64_t o = off; off = align_up(off + bytes, 1024); return o; };
+    out->off_ctrl = take(mm::kCtrlBytes);
+    out->off_flags = take(mm::kFlagBytes);
+    out->off_x = take(t_max * out->x_row_bytes);
+    out->off_x_sf = take(t_max * out->x_sf_row_bytes);
+    out->off_topk_idx = take(t_max * c->num_topk * 8);
+    out->off_topk_weights = take(t_max * c->num_topk * 4);
+    out->off_rx = take(2 * c->num_ranks * out->rx_cap_rows * out->rx_row_bytes);
+    out->off_mid = take(out->mid_rows * out->mid_row_bytes);
+    out->off_mid_sf = take(out->mid_rows * out->mid_sf_row_bytes);
+    out->off_comb = take(t_max * c->num_topk * c->hidden * 2);
+    out->total_bytes = off;
+    return MM_OK;
+}
+
+int mm_reset(const mm_config_t* cfg, void* buffer, void* stream) {
+    mm_layout_t L;
+    const int st = mm_get_layout(cfg, &L);
+    if (st != MM_OK) return st;
+    if (buffer == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_ctrl, 0, L.off_x - L.off_ctrl, static_cast<cudaStream_t>(stream)));
+    return MM_OK;
+}
+
+int mm_read_device_status(const mm_config_t* cfg, const void* buffer, uint32_t out_words[16], void* stream) {
+    mm_layout_t L;
+    const int st = mm_get_layout(cfg, &L);
+    if (st != MM_OK) return st;
+    if (buffer == nullptr || out_words == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    MM_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    MM_CUDA(cudaMemcpy(out_words, static_cast<const uint8_t*>(buffer) + L.off_ctrl + mm::kCtrlStatus, 64, cudaMemcpyDeviceToHost));
+    const uint32_t code = out_words[0] & 0xFFu;
+    if (code == 0) return MM_OK;
+    return (code == mm::kErrMetaCapacity || code == mm::kErrTaskCapacity) ? MM_ERR_DEVICE_CAPACITY : MM_ERR_DEVICE_TIMEOUT;
+}
+
+int mm_read_phase_stamps(const mm_config_t* cfg, const void* buffer, uint64_t out_stamps[32], void* stream) {
+    mm_layout_t L;
+    const int st = mm_get_layout(cfg, &L);
+    if (st != MM_OK) return st;
+    if (buffer == nullptr || out_stamps == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    MM_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    MM_CUDA(cudaMemcpy(out_stamps, static_cast<const uint8_t*>(buffer) + L.off_ctrl + mm::kCtrlStamps, 256, cudaMemcpyDeviceToHost));
+    return MM_OK;
+}
+
+}  // extern "C"
+
+static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KParams* P, int* grid, size_t* smem_bytes) {
+    mm_layout_t L;
+    int st = mm_get_layout(cfg, &L);
+    if (st != MM_OK) return st;
+    if (a == nullptr || a->buffer == nullptr || a->peer_buffers == nullptr || a->l1_weights == nullptr || a->l2_weights == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (a->num_tokens < 0 || a->num_tokens > cfg->num_max_tokens_per_rank) return MM_ERR_INVALID_ARGUMENT;
+    if (a->num_tokens > 0 && a->y == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (a->peer_buffers[cfg->rank] != a->buffer) return MM_ERR_INVALID_ARGUMENT;
+    st = grid_size(cfg, grid);
+    if (st != MM_OK) return st;
+    mm_weight_geometry_t wg;
+    mm_get_weight_geometry(cfg->act_format, &wg);
+    mm::KParams& p = *P;
+    memset(&p, 0, sizeof(p));
+    p.R = cfg->num_ranks; p.rank = cfg->rank; p.e_local = cfg->num_experts / cfg->num_ranks; p.topk = cfg->num_topk;
+    p.H = cfg->hidden; p.I = cfg->intermediate; p.T = a->num_tokens; p.cap = static_cast<int>(L.rx_cap_rows);
+    p.n1_tiles = 2 * p.I / mm::kTileRows; p.n2_tiles = p.H / mm::kTileRows;
+    p.k1_units = p.H / mm::kUnitK; p.k2_units = p.I / mm::kUnitK;
+    if (p.n1_tiles > 255 || p.n2_tiles > 255) return MM_ERR_UNSUPPORTED;
+    p.unit_bytes = wg.unit_bytes;
+    p.x_row_bytes = static_cast<int>(L.x_row_bytes); p.x_sf_row_bytes = static_cast<int>(L.x_sf_row_bytes);
+    p.rx_row_bytes = static_cast<int>(L.rx_row_bytes);
+    p.mid_row_bytes = static_cast<int>(L.mid_row_bytes); p.mid_sf_row_bytes = static_cast<int>(L.mid_sf_row_bytes);
+    p.has_clamp = (a->activation_clamp >= 0.f && std::isfinite(a->activation_clamp)) ? 1 : 0;
+    p.clamp = a->activation_clamp; p.fast_math = a->fast_math;
+    const float xg = a->x_global_scale > 0.f ? a->x_global_scale : 1.f, g1 = a->l1_global_scale > 0.f ? a->l1_global_scale : 1.f;
+    const float g2 = a->l2_global_scale > 0.f ? a->l2_global_scale : 1.f, gm = a->mid_global_scale > 0.f ? a->mid_global_scale : 1.f;
+    p.l1_scale = xg * g1; p.l2_scale = g2 * gm; p.mid_gs = gm;
+    for (int r = 0; r < p.R; ++r) {
+        if (a->peer_buffers[r] == nullptr) return MM_ERR_INVALID_ARGUMENT;
+        p.peer[r] = static_cast<uint8_t*>(a->peer_buffers[r]);
+    }
+    p.w1 = static_cast<const uint8_t*>(a->l1_weights); p.w2 = static_cast<const uint8_t*>(a->l2_weights);
+    p.y = static_cast<__nv_bfloat16*>(a->y); p.stats = a->cumulative_local_expert_recv_stats;
+    p.off_ctrl = L.off_ctrl; p.off_flags = L.off_flags; p.off_x = L.off_x; p.off_x_sf = L.off_x_sf;
+    p.off_topk_idx = L.off_topk_idx; p.off_topk_w = L.off_topk_weights; p.off_rx = L.off_rx;
+    p.off_mid = L.off_mid; p.off_mid_sf = L.off_mid_sf; p.off_comb = L.off_comb;
+    const double tmo = a->timeout_ms > 0.f ? a->timeout_ms : 2000.0;
+    p.timeout_ns = static_cast<unsigned long long>(tmo * 1e6);
+    p.debug_acc = static_cast<float*>(a->debug_accumulators); p.debug_tasks = a->debug_accumulators ? a->debug_num_tasks : 0;
+    // shared memory plan: [stages][2 x token tiles][2 x token scale chunks][output tile]
+    const int kmax = p.H > p.I ? p.H : p.I;
+    const int vec = sf_vec_of(cfg->act_format);
+    p.act_bytes = mm::kTileTokens * kmax / 2;
+    p.asf_bytes = static_cast<uint32_t>(align_up(kmax / vec, 16) / 16 * 512);
+    if ((kmax / mm::kUnitK) * (mm::kUnitK / (4 * vec)) > 96) return MM_ERR_UNSUPPORTED;
+    const size_t fixed = 2 * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes;
+    const size_t budget = 232448 - sizeof(mm::Ctl) - 1024 /* alignment slack */ - 512;
+    int nstage = static_cast<int>((budget - fixed) / p.unit_bytes);
+    if (nstage > mm::kMaxStages) nstage = mm::kMaxStages;
+    if (nstage < 2) return MM_ERR_UNSUPPORTED;
+    p.nstage = nstage;
+    p.sm_act = nstage * p.unit_bytes;
+    p.sm_asf = p.sm_act + 2 * p.act_bytes;
+    p.sm_otile = p.sm_asf + 2 * p.asf_bytes;
+    *smem_bytes = p.sm_otile + mm::kOtileBytes + 1024;
+    if (static_cast<size_t>(p.T) * p.topk * 4 > 2 * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
+    return MM_OK;
+}
+
+template <int kVec, bool kUmma>
+static int launch_variant(const mm::KParams& p, int grid, size_t smem_bytes, cudaStream_t stream) {
+    auto kern = mm::mega_moe_kernel<kVec, kUmma>;
+    MM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
+    kern<<<grid, mm::kThreads, smem_bytes, stream>>>(p);
+    MM_CUDA(cudaGetLastError());
+    return MM_OK;
+}
+
+extern "C" {
+
+int mm_mega_moe_launch(const mm_config_t* cfg, const mm_launch_args_t* a, void* stream) {
+    mm::KParams p;
+    int grid = 0;
+    size_t smem_bytes = 0;
+    const int st = fill_params(cfg, a, &p, &grid, &smem_bytes);
+    if (st != MM_OK) return st;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool umma = a->engine == MM_ENGINE_UMMA;
+    if (cfg->act_format == MM_FMT_MXFP4)
+        return umma ? launch_variant<32, true>(p, grid, smem_bytes, s) : launch_variant<32, false>(p, grid, smem_bytes, s);
+    return umma ? launch_variant<16, true>(p, grid, smem_bytes, s) : launch_variant<16, false>(p, grid, smem_bytes, s);
+}
+
+int64_t mm_frontend_workspace_bytes(const mm_config_t* cfg) {
+    if (cfg == nullptr) return -1;
+    return static_cast<int64_t>(cfg->num_max_tokens_per_rank) * cfg->num_experts * 4 + 256;
+}
+
+int mm_frontend_launch(const mm_config_t* cfg, void* buffer, const mm_frontend_args_t* fe, void* stream) {
+    mm_layout_t L;
+    int st = mm_get_layout(cfg, &L);
+    if (st != MM_OK) return st;
+    if (buffer == nullptr || fe == nullptr || fe->hidden_states == nullptr || fe->router_weight == nullptr || fe->workspace == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (fe->num_tokens < 0 || fe->num_tokens > cfg->num_max_tokens_per_rank) return MM_ERR_INVALID_ARGUMENT;
+    if (cfg->num_topk != 8 || cfg->num_experts > 1024) return MM_ERR_UNSUPPORTED;
+    if (fe->score_mode == 1 && fe->expert_bias == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (fe->num_tokens == 0) return MM_OK;
+    int grid = 0;
+    st = grid_size(cfg, &grid);
+    if (st != MM_OK) return st;
+    mm::FeParams q;
+    memset(&q, 0, sizeof(q));
+    q.hidden = static_cast<const __nv_bfloat16*>(fe->hidden_states);
+    q.router_w = static_cast<const __nv_bfloat16*>(fe->router_weight);
+    q.bias = fe->expert_bias;
+    q.logits = reinterpret_cast<float*>(static_cast<uint8_t*>(fe->workspace) + 256);
+    q.arrive = reinterpret_cast<uint32_t*>(fe->workspace);
+    q.T = fe->num_tokens; q.H = cfg->hidden; q.E = cfg->num_experts; q.topk = cfg->num_topk;
+    q.score_mode = fe->score_mode; q.fmt = cfg->act_format;
+    q.x_gs = fe->x_global_scale > 0.f ? fe->x_global_scale : 1.f;
+    uint8_t* b = static_cast<uint8_t*>(buffer);
+    q.x = b + L.off_x; q.x_sf = b + L.off_x_sf;
+    q.topk_idx = reinterpret_cast<long long*>(b + L.off_topk_idx);
+    q.topk_w = reinterpret_cast<float*>(b + L.off_topk_weights);
+    q.x_row_bytes = static_cast<int>(L.x_row_bytes); q.x_sf_row_bytes = static_cast<int>(L.x_sf_row_bytes);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    mm::frontend_logits_kernel<<<grid, 256, 0, s>>>(q);
+    MM_CUDA(cudaGetLastError());
+    const int sel_blocks = (q.T + 3) / 4;
+    mm::frontend_select_quant_kernel<<<sel_blocks, 128, q.E * 4 * 4, s>>>(q);
+    MM_CUDA(cudaGetLastError());
+    return MM_OK;
+}
+
+int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_t* args, const mm_frontend_args_t* fe, void* stream) {
+    if (args == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    int st = mm_frontend_launch(cfg, args->buffer, fe, stream);
+    if (st != MM_OK) return st;
+    return mm_mega_moe_launch(cfg, args, stream);
+}
+
+}  // extern "C"

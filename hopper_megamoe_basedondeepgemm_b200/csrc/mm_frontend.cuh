@@ -1,0 +1,166 @@
+// Router frontend: bf16 router GEMM (fp32 accumulate, one bf16 rounding), top-8 selection with the
+// (score descending, expert id ascending) order, routing weights, and token quantisation into the layer's input views.
+//
+// Reduction order of a logit (fixed, so that a CPU restatement can reproduce it bit for bit): lane l of a warp owns the
+// 8-element chunks l, l + 32, l + 64, ... of the K axis and runs one fused multiply-add chain over them in order; the 32
+// partial sums are combined by a butterfly (xor 16, 8, 4, 2, 1); the sum is rounded to bf16 once.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cstdint>
+#include "mm_ptx.cuh"
+
+namespace mm {
+
+struct FeParams {
+    const __nv_bfloat16* hidden; const __nv_bfloat16* router_w; const float* bias;
+    float* logits; uint32_t* arrive;
+    uint8_t* x; uint8_t* x_sf; long long* topk_idx; float* topk_w;
+    int T, H, E, topk, score_mode, fmt, x_row_bytes, x_sf_row_bytes;
+    float x_gs;
+};
+
+__device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+    #pragma unroll
+    for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
+}
+
+// one warp per (expert, block of up to 4 tokens)
+__global__ void __launch_bounds__(256) frontend_logits_kernel(const FeParams q) {
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nwarps = gridDim.x * (blockDim.x >> 5);
+    const uint32_t tblocks = (q.T + 3) / 4, nchunk = q.H / 8;
+    for (uint32_t item = warp; item < static_cast<uint32_t>(q.E) * tblocks; item += nwarps) {
+        const uint32_t e = item % q.E, t0 = (item / q.E) * 4;
+        const uint32_t nt = min(4u, static_cast<uint32_t>(q.T) - t0);
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        const uint4* wrow = reinterpret_cast<const uint4*>(q.router_w + static_cast<size_t>(e) * q.H);
+        for (uint32_t ch = lane; ch < nchunk; ch += 32) {
+            float w[8];
+            unpack_bf16x8(__ldg(wrow + ch), w);
+            #pragma unroll
+            for (uint32_t t = 0; t < 4; ++t) {
+                if (t < nt) {
+                    float x[8];
+                    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(q.hidden + static_cast<size_t>(t0 + t) * q.H) + ch), x);
+                    #pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[t] = fmaf(x[k], w[k], acc[t]);
+                }
+            }
+        }
+        #pragma unroll
+        for (uint32_t t = 0; t < 4; ++t) {
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc[t] += __shfl_xor_sync(0xffffffffu, acc[t], o);
+            if (lane == 0 && t < nt) q.logits[static_cast<size_t>(t0 + t) * q.E + e] = bf16_round(acc[t]) + 0.0f;
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t orderable_f32(float v) {
+    const uint32_t b = __float_as_uint(v);
+    return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+        v = other > v ? other : v;
+    }
+    return v;
+}
+
+// one warp per token: top-8 + weights, then the token's quantisation
+__global__ void __launch_bounds__(128) frontend_select_quant_kernel(const FeParams q) {
+    extern __shared__ float fe_scores[];                 // [4 warps][E]
+    const uint32_t lane = threadIdx.x & 31u, w = threadIdx.x >> 5;
+    const uint32_t t = blockIdx.x * 4 + w;
+    if (t >= static_cast<uint32_t>(q.T)) return;
+    float* sc = fe_scores + w * q.E;
+    const float* lg = q.logits + static_cast<size_t>(t) * q.E;
+    for (int e = lane; e < q.E; e += 32) {
+        const float v = lg[e];
+        sc[e] = q.score_mode == 1 ? (1.0f / (1.0f + expf(-v))) + q.bias[e] : v;
+    }
+    __syncwarp();
+
+    // ---- quantise the token (and learn whether the row is all zero)
+    const int vec = q.fmt == 1 ? 16 : 32, lanes_per_group = vec / 8;
+    const __nv_bfloat16* xrow = q.hidden + static_cast<size_t>(t) * q.H;
+    uint8_t* qrow = q.x + static_cast<size_t>(t) * q.x_row_bytes;
+    uint8_t* sfrow = q.x_sf + static_cast<size_t>(t) * q.x_sf_row_bytes;
+    bool nonzero = false;
+    for (int k0 = lane * 8; k0 < q.H; k0 += 256) {
+        float x[8];
+        unpack_bf16x8(*reinterpret_cast<const uint4*>(xrow + k0), x);
+        float local = 0.f;
+        #pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            nonzero |= x[j] != 0.f;
+            if (q.fmt == 1) x[j] = __fdiv_rn(x[j], q.x_gs);
+            local = fmaxf(local, fabsf(x[j]));
+        }
+        local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, 1));
+        if (lanes_per_group == 4) local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, 2));
+        const float v = fmaxf(local, 1.0e-30f) * (1.0f / 6.0f);
+        uint32_t sf_byte; float sf;
+        if (q.fmt == 1) {
+            sf_byte = cvt_e4m3x2(v, 0.f) & 0xFFu;
+            if (sf_byte == 0u) sf_byte = 1u;
+            sf = e4m3_to_float(sf_byte);
+        } else {
+            sf_byte = ceil_pow2_exp(v);
+            sf = __uint_as_float(sf_byte << 23);
+        }
+        if ((lane % lanes_per_group) == 0) sfrow[k0 / vec] = static_cast<uint8_t>(sf_byte);
+        const float inv = 1.0f / sf;
+        uint32_t packed = 0u;
+        #pragma unroll
+        for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(x[2 * j] * inv, x[2 * j + 1] * inv) << (8 * j);
+        *reinterpret_cast<uint32_t*>(qrow + k0 / 2) = packed;
+    }
+    nonzero = __any_sync(0xffffffffu, nonzero);
+
+    // ---- top-8: eight rounds of a warp-wide maximum over 64-bit keys (score, then smaller expert id)
+    unsigned long long chosen = 0ull;
+    for (int k = 0; k < 8; ++k) {
+        unsigned long long best = 0ull;
+        for (int e = lane; e < q.E; e += 32) {
+            const float s = sc[e];
+            if (s == -INFINITY) continue;
+            const unsigned long long key = (static_cast<unsigned long long>(orderable_f32(s + 0.0f)) << 32) | (0xFFFFFFFFu - static_cast<uint32_t>(e));
+            best = key > best ? key : best;
+        }
+        best = warp_max_u64(best);
+        const uint32_t e_best = 0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFull);
+        if (lane == 0) sc[e_best] = -INFINITY;
+        if (static_cast<int>(lane) == k) chosen = e_best;
+        __syncwarp();
+    }
+    const int e_sel = static_cast<int>(chosen);
+    const float v_sel = lane < 8 ? lg[e_sel] : -INFINITY;
+    float wgt;
+    if (q.score_mode == 1) {
+        const float s = lane < 8 ? 1.0f / (1.0f + expf(-v_sel)) : 0.f;
+        float sum = 0.f;
+        #pragma unroll
+        for (int k = 0; k < 8; ++k) sum += __shfl_sync(0xffffffffu, s, k);
+        wgt = s / sum;
+    } else {
+        float mx = v_sel;
+        #pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+        const float ex = lane < 8 ? expf(v_sel - mx) : 0.f;
+        float sum = 0.f;
+        #pragma unroll
+        for (int k = 0; k < 8; ++k) sum += __shfl_sync(0xffffffffu, ex, k);
+        wgt = ex / sum;
+    }
+    if (lane < 8) {
+        q.topk_idx[static_cast<size_t>(t) * 8 + lane] = nonzero ? e_sel : -1;
+        q.topk_w[static_cast<size_t>(t) * 8 + lane] = nonzero ? wgt : 0.f;
+    }
+}
+
+}  // namespace mm

@@ -1,0 +1,717 @@
+// The fused expert-parallel MoE layer as one persistent sm_100a kernel.
+//
+//   dispatch  : SM d (< ranks) packs this rank's routed rows for rank d and stores them, densely and in (token, slot)
+//               order, into a region of rank d's receive pool that only this rank writes; one release store of
+//               (epoch, row count) then tells rank d that the rows are complete. No ticket atomics, no collective.
+//   schedule  : every SM reads the R flags, scans the received rows' expert ids and derives the same task list
+//               (L1 tiles of all active experts, then L2 tiles); its own tasks are those of a closed-form owner map.
+//   L1 GEMM   : 128 weight rows x 16 tokens per task, swap-AB block-scaled tcgen05 MMA, accumulators in TMEM. Weights
+//               arrive as pre-tiled 128 B-swizzled units with their scale planes by one bulk async copy per stage.
+//   L1 epilog : SwiGLU * top-k weight, requantise to E2M1 (+ scale byte), store to the local intermediate pool,
+//               release-add on the expert's arrival counter.
+//   L2 GEMM   : acquires that counter, same main loop on W2, epilogue stores bf16 rows straight into the source
+//               rank's combine buffer over NVLink.
+//   combine   : after all ranks' "L2 done" flags, each token's routes are summed in slot order (fp32) and written to y.
+//
+// Every wait is bounded by a deadline; on expiry the SM records a status word, raises a CTA-wide abort flag and all
+// roles fall through to the common exit (TMEM is always released).
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cstdint>
+#include "mm_ptx.cuh"
+
+namespace mm {
+
+constexpr int kThreads = 256;
+constexpr int kMaxRanks = 8;
+constexpr int kMaxLocalExperts = 64;
+constexpr int kMaxTasks = 256;          // tasks one SM can own in one launch
+constexpr int kMetaCap = 4096;          // rows one rank can receive in one launch
+constexpr int kMaxStages = 12;
+constexpr int kTileRows = 128;          // UMMA M: weight rows per task
+constexpr int kTileTokens = 16;         // UMMA N: token rows per task
+constexpr int kUnitK = 256;             // K elements per streamed unit (one 128 B swizzle atom of packed E2M1)
+constexpr int kUnitWBytes = kTileRows * 128;
+constexpr int kNumEpiThreads = 128, kNumStagerThreads = 64, kNumDispatchThreads = 192;
+constexpr uint32_t kBarEpi = 1, kBarStager = 2, kBarDispatch = 3;
+constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kOtileBytes = 4096;
+
+// control-block offsets (bytes from off_ctrl)
+constexpr int kCtrlEpoch = 0;           // u32[256] one launch counter per SM
+constexpr int kCtrlStatus = 1024;       // u32[16]
+constexpr int kCtrlL2Done = 1088;       // u32 SMs that finished their L2 tasks
+constexpr int kCtrlFeArrive = 1092;     // u32 SMs that published their router logits
+constexpr int kCtrlL1Done = 1152;       // u32[2][64] L1 tiles finished per (parity, local expert)
+constexpr int kCtrlStamps = 2048;       // u64[32] phase stamps
+constexpr int kCtrlBytes = 4096;
+// flag-block offsets (bytes from off_flags); written by the peers
+constexpr int kFlagDispatch = 0;        // u64[2][8]: (epoch + 1) << 32 | rows
+constexpr int kFlagCombine = 256;       // u32[2][8]: epoch + 1
+constexpr int kFlagBytes = 1024;
+
+// device status codes (low byte of status word 0)
+enum : uint32_t {
+    kErrWaitEmpty = 1, kErrWaitFull = 2, kErrWaitActsFull = 3, kErrWaitActsEmpty = 4, kErrWaitTmemFull = 5,
+    kErrWaitTmemEmpty = 6, kErrWaitDispatchFlag = 7, kErrWaitL1Done = 8, kErrWaitCombineFlag = 9,
+    kErrMetaCapacity = 10, kErrTaskCapacity = 11, kErrWaitFrontend = 12
+};
+// phase stamp slots (SM 0 unless noted)
+enum : int {
+    kStampEntry = 0, kStampDispatched = 1, kStampFlagsSeen = 2, kStampScheduled = 3, kStampTasksDone = 4,
+    kStampL2Signalled = 5, kStampCombineFlags = 6, kStampExit = 7, kStampLastExit = 8 /* max over SMs */,
+    kStampFrontend = 9
+};
+
+struct RowMeta { int32_t src, token, slot; float weight; };
+
+struct KParams {
+    int R, rank, e_local, topk, H, I, T, cap;
+    int n1_tiles, n2_tiles, k1_units, k2_units;
+    int nstage;
+    uint32_t unit_bytes;                 // weights + scale planes of one streamed unit
+    int x_row_bytes, x_sf_row_bytes, rx_row_bytes, mid_row_bytes, mid_sf_row_bytes;
+    float clamp; int has_clamp, fast_math;
+    float l1_scale, l2_scale, mid_gs;
+    uint8_t* peer[kMaxRanks];
+    const uint8_t* w1; const uint8_t* w2;
+    __nv_bfloat16* y; int* stats;
+    long long off_ctrl, off_flags, off_x, off_x_sf, off_topk_idx, off_topk_w, off_rx, off_mid, off_mid_sf, off_comb;
+    uint32_t sm_act, sm_asf, sm_otile;   // dynamic shared memory offsets (stages start at 0)
+    uint32_t act_bytes, asf_bytes;
+    unsigned long long timeout_ns;
+    float* debug_acc; int debug_tasks;   // optional diagnostics: raw accumulators of SM 0's first tasks [task][token][row]
+};
+
+struct Ctl {
+    uint64_t full[kMaxStages], empty[kMaxStages];
+    uint64_t acts_full[2], acts_empty[2], tmem_full[2], tmem_empty[2];
+    uint32_t tmem_base, epoch, abort_flag, ntasks;
+    uint32_t rx_count[kMaxRanks], rx_prefix[kMaxRanks + 1];
+    uint32_t exp_count[kMaxLocalExperts], mid_base[kMaxLocalExperts];
+    uint32_t tb1[kMaxLocalExperts], tb2[kMaxLocalExperts];
+    uint32_t nt1, nt2, dcount, pad0;
+    uint32_t tasks[kMaxTasks];
+    RowMeta row_meta[4][kTileTokens];
+    RowMeta epi_meta[2][kTileTokens];
+    uint32_t nvalid[4];
+    uint32_t rowref[kTileTokens];
+    uint32_t rowidx[kTileTokens];
+    float amax_x[4][kTileTokens];
+    uint8_t meta_e[kMetaCap];
+};
+
+__device__ __forceinline__ uint32_t task_pack(uint32_t type, uint32_t e, uint32_t mt, uint32_t j) {
+    return (type << 28) | (e << 20) | (mt << 8) | j;
+}
+
+struct Ctx {
+    const KParams& p;
+    Ctl& c;
+    uint8_t* buf;         // this rank's buffer
+    uint8_t* smem;        // dynamic shared memory (1024 B aligned)
+    uint64_t deadline;
+    uint32_t par;         // launch parity: which half of the receive pool / flags this launch uses
+    __device__ __forceinline__ bool aborted() const { return *reinterpret_cast<volatile uint32_t*>(&c.abort_flag) != 0u; }
+    __device__ __forceinline__ void fail(uint32_t code, uint32_t detail = 0) const {
+        uint32_t* st = reinterpret_cast<uint32_t*>(buf + p.off_ctrl + kCtrlStatus);
+        atomicCAS(st, 0u, code | (blockIdx.x << 8) | (detail << 16));
+        *reinterpret_cast<volatile uint32_t*>(&c.abort_flag) = 1u;
+    }
+    __device__ __forceinline__ bool expired() const { return globaltimer_ns() > deadline; }
+    __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, uint32_t code) const {
+        uint32_t it = 0;
+        while (!mbar_try_wait(bar, parity)) {
+            if ((++it & 0xFFu) == 0u) {
+                if (aborted()) return false;
+                if (expired()) { fail(code); return false; }
+            }
+        }
+        return true;
+    }
+    __device__ __forceinline__ void stamp(int slot) const {
+        reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[slot] = globaltimer_ns();
+    }
+    __device__ __forceinline__ uint8_t* rx_row(uint32_t src_rank, uint32_t i) const {
+        return buf + p.off_rx + (static_cast<size_t>(par * p.R + src_rank) * p.cap + i) * p.rx_row_bytes;
+    }
+};
+
+// position of 16 B chunk `c` of row `r` inside a 128 B-swizzled [rows x 128 B] tile
+__device__ __forceinline__ uint32_t sw128_off(uint32_t r, uint32_t c) {
+    return (r >> 3) * 1024u + (r & 7u) * 128u + ((c ^ (r & 7u)) << 4);
+}
+// E2M1 code -> value: the three magnitude bits become the low exponent bit pair and top mantissa bit of an fp16 (x 2^14)
+__device__ __forceinline__ float e2m1_value(uint32_t code) {
+    const uint32_t h = ((code & 7u) << 9) | ((code & 8u) << 12);
+    return __half2float(__ushort_as_half(static_cast<unsigned short>(h))) * 16384.0f;
+}
+template <int kVec>
+__device__ __forceinline__ float sf_value(uint32_t byte) {
+    if constexpr (kVec == 32) return __uint_as_float((byte & 0xFFu) << 23);
+    else return e4m3_to_float(byte);
+}
+
+// ============================================================================================= weight loader
+__device__ void role_loader(const Ctx& cx) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    uint32_t it = 0;
+    for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
+        const uint32_t t = c.tasks[ti];
+        const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, j = t & 0xFF;
+        const int ntiles = type ? p.n2_tiles : p.n1_tiles, kunits = type ? p.k2_units : p.k1_units;
+        const uint8_t* src = (type ? p.w2 : p.w1) + (static_cast<size_t>(e) * ntiles + j) * kunits * p.unit_bytes;
+        for (int u = 0; u < kunits; ++u, ++it) {
+            const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
+            if (!cx.wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
+            mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
+            bulk_g2s(cx.smem + static_cast<size_t>(s) * p.unit_bytes, src + static_cast<size_t>(u) * p.unit_bytes,
+                     p.unit_bytes, &c.full[s]);
+        }
+    }
+}
+
+// ============================================================================================= MMA issuer
+template <int kVec>
+__device__ void role_mma(const Ctx& cx, uint32_t lane) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    constexpr uint32_t kPlanes = kUnitK / (4 * kVec);           // scale words per row per unit
+    constexpr uint32_t kIdesc = idesc_block_scaled(kFmtMxf4E2M1, kFmtMxf4E2M1, kTileRows, kTileTokens, kVec == 32 ? 1u : 0u);
+    const uint32_t tm = c.tmem_base;
+    const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 96
+    uint32_t it = 0;
+    for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
+        const uint32_t t = c.tasks[ti];
+        const uint32_t type = t >> 28;
+        const int kunits = type ? p.k2_units : p.k1_units;
+        const uint32_t ab = ti & 1u, acc = ti & 1u, use = (ti >> 1) & 1u;
+        if (!__all_sync(0xffffffffu, cx.wait(&c.acts_full[ab], use, kErrWaitActsFull))) return;
+        if (!__all_sync(0xffffffffu, cx.wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty))) return;
+        tc_fence_after();
+        if (lane == 0) {
+            // token scale bytes of the whole K: chunk q carries scale words 4q..4q+3 of every token row (lane = row)
+            const uint32_t nq = (static_cast<uint32_t>(kunits) * kPlanes + 3u) / 4u;
+            const uint32_t asf = smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes);
+            for (uint32_t q = 0; q < nq; ++q)
+                utccp_32x128b_warpx4(tm + sfb_col + ab * 96u + q * 4u, smem_desc(asf + q * 512u, 128u, kLayoutNone));
+        }
+        const uint32_t act = smem_u32(cx.smem + p.sm_act + ab * p.act_bytes);
+        for (int u = 0; u < kunits; ++u, ++it) {
+            const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
+            if (!__all_sync(0xffffffffu, cx.wait(&c.full[s], ph, kErrWaitFull))) return;
+            tc_fence_after();
+            if (lane == 0) {
+                const uint32_t wsm = smem_u32(cx.smem + static_cast<size_t>(s) * p.unit_bytes);
+                const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u;
+                #pragma unroll
+                for (uint32_t pl = 0; pl < kPlanes; ++pl)
+                    utccp_32x128b_warpx4(sfa + pl * 4u, smem_desc(wsm + kUnitWBytes + pl * 512u, 128u, kLayoutNone));
+                const uint32_t bsm = act + static_cast<uint32_t>(u) * (kTileTokens * 128u);
+                #pragma unroll
+                for (uint32_t ks = 0; ks < kUnitK / 64; ++ks) {
+                    const uint32_t pl = (ks * 64u) / (4u * kVec), sf_id = ((ks * 64u) % (4u * kVec)) / kVec;
+                    const uint64_t adesc = smem_desc(wsm + ks * 32u, 1024u, kLayoutSw128);
+                    const uint64_t bdesc = smem_desc(bsm + ks * 32u, 1024u, kLayoutSw128);
+                    const uint32_t idesc = idesc_with_sf(kIdesc, sf_id, sf_id);
+                    const uint32_t sfb = tm + sfb_col + ab * 96u + static_cast<uint32_t>(u) * kPlanes + pl;
+                    const uint32_t accum = (u > 0 || ks > 0) ? 1u : 0u;
+                    if constexpr (kVec == 32)
+                        umma_mxf4_block32(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb, accum);
+                    else
+                        umma_nvf4_block16(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb, accum);
+                }
+                tc_commit(&c.empty[s]);
+            }
+            __syncwarp();
+        }
+        if (lane == 0) {
+            tc_commit(&c.tmem_full[acc]);
+            tc_commit(&c.acts_empty[ab]);
+        }
+        __syncwarp();
+    }
+}
+
+// ============================================================================================= activation stagers
+// Rows [16 mt, 16 mt + 16) of local expert e in canonical (source rank, token, slot) order -> c.rowref (flat receive
+// index). Executed by one full warp.
+__device__ __forceinline__ void find_rows(Ctl& c, uint32_t total, uint32_t e, uint32_t mt, uint32_t lane) {
+    const uint32_t lo = mt * kTileTokens, hi = lo + kTileTokens;
+    uint32_t seen = 0;
+    for (uint32_t base = 0; base < total && seen < hi; base += 32) {
+        const uint32_t f = base + lane;
+        const bool m = f < total && c.meta_e[f] == e;
+        const uint32_t b = __ballot_sync(0xffffffffu, m);
+        const uint32_t rank = seen + __popc(b & ((1u << lane) - 1u));
+        if (m && rank >= lo && rank < hi) c.rowref[rank - lo] = f;
+        seen += __popc(b);
+    }
+}
+
+__device__ void role_stager(const Ctx& cx, uint32_t stid) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    const uint32_t lane = stid & 31u;
+    const uint32_t total = c.rx_prefix[p.R];
+    uint32_t* l1_done = reinterpret_cast<uint32_t*>(cx.buf + p.off_ctrl + kCtrlL1Done) + cx.par * kMaxLocalExperts;
+    for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
+        const uint32_t t = c.tasks[ti];
+        const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
+        const uint32_t ab = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u;
+        if (bar_red_or(kBarStager, kNumStagerThreads, !cx.wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty))) return;
+        if (stid < 32) {
+            find_rows(c, total, e, mt, lane);
+            if (lane == 0) {
+                const uint32_t left = c.exp_count[e] - mt * kTileTokens;
+                c.nvalid[ring] = left < kTileTokens ? left : kTileTokens;
+            }
+        }
+        bar_sync(kBarStager, kNumStagerThreads);
+        const uint32_t nv = c.nvalid[ring];
+        if (stid < nv) {
+            const uint32_t f = c.rowref[stid];
+            uint32_t r = 0;
+            while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
+            const uint32_t i = f - c.rx_prefix[r];
+            const uint4 m = ld_cg_v4(cx.rx_row(r, i) + p.rx_row_bytes - 16);
+            c.row_meta[ring][stid] = RowMeta{static_cast<int32_t>(r), static_cast<int32_t>(m.y), static_cast<int32_t>(m.z), __uint_as_float(m.w)};
+            c.rowidx[stid] = (r << 24) | i;
+        }
+        if (type == 1u && stid == 0) {
+            const uint32_t need = static_cast<uint32_t>(p.n1_tiles) * ((c.exp_count[e] + kTileTokens - 1) / kTileTokens);
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(l1_done + e) < need) {
+                if ((++spins & 0x3Fu) == 0u) {
+                    if (cx.aborted()) break;
+                    if (cx.expired()) { cx.fail(kErrWaitL1Done, e); break; }
+                }
+            }
+        }
+        if (bar_red_or(kBarStager, kNumStagerThreads, cx.aborted())) return;
+        uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
+        uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
+        const uint32_t nchunk = (type ? p.I : p.H) / 32;                       // 16 B chunks of one packed row
+        const uint32_t sfchunk = (type ? p.mid_sf_row_bytes : p.x_sf_row_bytes) / 16;
+        const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
+        for (uint32_t idx = stid; idx < nv * nchunk; idx += kNumStagerThreads) {
+            const uint32_t n = idx / nchunk, ci = idx % nchunk;
+            const uint8_t* src = type ? cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes
+                                      : cx.rx_row(c.rowidx[n] >> 24, c.rowidx[n] & 0xFFFFFFu);
+            const uint4 v = ld_cg_v4(src + ci * 16u);
+            *reinterpret_cast<uint4*>(act + (ci >> 3) * (kTileTokens * 128u) + sw128_off(n, ci & 7u)) = v;
+        }
+        for (uint32_t idx = stid; idx < nv * sfchunk; idx += kNumStagerThreads) {
+            const uint32_t n = idx / sfchunk, q = idx % sfchunk;
+            const uint8_t* src = type ? cx.buf + p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes
+                                      : cx.rx_row(c.rowidx[n] >> 24, c.rowidx[n] & 0xFFFFFFu) + p.x_row_bytes;
+            const uint4 v = ld_cg_v4(src + q * 16u);
+            *reinterpret_cast<uint4*>(asf + q * 512u + n * 16u) = v;
+        }
+        fence_proxy_async_smem();
+        bar_sync(kBarStager, kNumStagerThreads);
+        if (stid == 0) mbar_arrive(&c.acts_full[ab]);
+    }
+}
+
+// ============================================================================================= epilogue
+// CUDA-core evaluation of one streamed unit for one weight row (the on-device cross-check of the tensor-core path):
+// v[n] += sum_k w[row][k] a[n][k] with both operands' block scales applied.
+template <int kVec>
+__device__ __forceinline__ void check_accumulate(const Ctx& cx, const uint8_t* wsm, const uint8_t* act, const uint8_t* asf,
+                                                 uint32_t u, uint32_t row, uint32_t nv, float (&v)[kTileTokens]) {
+    constexpr uint32_t kPlanes = kUnitK / (4 * kVec);
+    constexpr uint32_t kBlockBytes = kVec / 2;
+    const uint8_t* wrow = wsm + (row >> 3) * 1024u + (row & 7u) * 128u;
+    const uint32_t* wsf = reinterpret_cast<const uint32_t*>(wsm + kUnitWBytes);
+    #pragma unroll
+    for (uint32_t pl = 0; pl < kPlanes; ++pl) {
+        const uint32_t wword = wsf[pl * 128u + (row & 31u) * 4u + (row >> 5)];
+        const uint32_t g = u * kPlanes + pl;
+        #pragma unroll
+        for (uint32_t sb = 0; sb < 4; ++sb) {
+            const float sw = sf_value<kVec>((wword >> (8 * sb)) & 0xFFu);
+            const uint32_t byte0 = (pl * 4u + sb) * kBlockBytes;            // byte offset inside the 128 B row
+            const uint32_t ci = byte0 >> 4, in = byte0 & 15u;
+            uint32_t wq[kBlockBytes / 4];
+            #pragma unroll
+            for (uint32_t w4 = 0; w4 < kBlockBytes / 4; ++w4)
+                wq[w4] = *reinterpret_cast<const uint32_t*>(wrow + ((ci ^ (row & 7u)) << 4) + in + w4 * 4u);
+            #pragma unroll
+            for (uint32_t n = 0; n < kTileTokens; ++n) {
+                if (n < nv) {
+                    const uint8_t* arow = act + u * (kTileTokens * 128u) + (n >> 3) * 1024u + (n & 7u) * 128u + ((ci ^ (n & 7u)) << 4) + in;
+                    const uint32_t aword = *reinterpret_cast<const uint32_t*>(asf + (g >> 2) * 512u + n * 16u + (g & 3u) * 4u);
+                    const float sa = sf_value<kVec>((aword >> (8 * sb)) & 0xFFu);
+                    float dot = 0.f;
+                    #pragma unroll
+                    for (uint32_t w4 = 0; w4 < kBlockBytes / 4; ++w4) {
+                        const uint32_t aq = *reinterpret_cast<const uint32_t*>(arow + w4 * 4u);
+                        #pragma unroll
+                        for (uint32_t k = 0; k < 8; ++k)
+                            dot += e2m1_value((wq[w4] >> (4 * k)) & 0xFu) * e2m1_value((aq >> (4 * k)) & 0xFu);
+                    }
+                    v[n] += dot * sw * sa;
+                }
+            }
+        }
+    }
+}
+
+template <int kVec, bool kUmma>
+__device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    const uint32_t ew = etid >> 5, lane = etid & 31u, row = etid;
+    uint8_t* otile = cx.smem + p.sm_otile;
+    uint32_t* l1_done = reinterpret_cast<uint32_t*>(cx.buf + p.off_ctrl + kCtrlL1Done) + cx.par * kMaxLocalExperts;
+    uint32_t it = 0;
+    for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
+        const uint32_t t = c.tasks[ti];
+        const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF, j = t & 0xFF;
+        const uint32_t ab = ti & 1u, acc = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u;
+        bar_sync(kBarEpi, kNumEpiThreads);        // the previous task's output tile and metas are no longer in use
+        float v[kTileTokens];
+        uint32_t nv;
+        if constexpr (kUmma) {
+            if (bar_red_or(kBarEpi, kNumEpiThreads, !cx.wait(&c.tmem_full[acc], use, kErrWaitTmemFull))) return;
+            tc_fence_after();
+            if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
+            nv = c.nvalid[ring];
+            uint32_t raw[kTileTokens];
+            tmem_ld_32x32b_x16(c.tmem_base + ((ew * 32u) << 16) + acc * 16u, raw);
+            tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(&c.tmem_empty[acc]);
+            #pragma unroll
+            for (int n = 0; n < kTileTokens; ++n) v[n] = __uint_as_float(raw[n]);
+        } else {
+            if (bar_red_or(kBarEpi, kNumEpiThreads, !cx.wait(&c.acts_full[ab], use, kErrWaitActsFull))) return;
+            if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
+            nv = c.nvalid[ring];
+            #pragma unroll
+            for (int n = 0; n < kTileTokens; ++n) v[n] = 0.f;
+            const int kunits = type ? p.k2_units : p.k1_units;
+            const uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
+            const uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
+            for (int u = 0; u < kunits; ++u, ++it) {
+                const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
+                if (bar_red_or(kBarEpi, kNumEpiThreads, !cx.wait(&c.full[s], ph, kErrWaitFull))) return;
+                check_accumulate<kVec>(cx, cx.smem + static_cast<size_t>(s) * p.unit_bytes, act, asf, u, row, nv, v);
+                mbar_arrive(&c.empty[s]);
+            }
+            mbar_arrive(&c.acts_empty[ab]);
+        }
+        bar_sync(kBarEpi, kNumEpiThreads);        // epi_meta visible
+        if (p.debug_acc != nullptr && blockIdx.x == 0 && ti < static_cast<uint32_t>(p.debug_tasks)) {
+            #pragma unroll
+            for (int n = 0; n < kTileTokens; ++n) p.debug_acc[(static_cast<size_t>(ti) * kTileTokens + n) * kTileRows + row] = v[n];
+        }
+        const RowMeta* meta = c.epi_meta[acc];
+        const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
+
+        if (type == 0u) {
+            // ---- L1: rows come in groups of 16 = 8 gate rows then the 8 matching up rows
+            const bool is_up = (lane & 8u) != 0u;
+            float actv[kTileTokens];
+            #pragma unroll
+            for (int n = 0; n < kTileTokens; ++n) {
+                actv[n] = 0.f;
+                if (n < static_cast<int>(nv)) {
+                    const float mine = bf16_round(v[n] * p.l1_scale);
+                    const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+                    float gate = is_up ? other : mine, up = is_up ? mine : other;
+                    if (p.has_clamp) { gate = fminf(gate, p.clamp); up = fminf(fmaxf(up, -p.clamp), p.clamp); }
+                    const float sig = p.fast_math ? __frcp_rn(1.0f + __expf(-gate)) : 1.0f / (1.0f + expf(-gate));
+                    actv[n] = gate * sig * up * meta[n].weight;
+                    if constexpr (kVec == 16) actv[n] = __fdiv_rn(actv[n], p.mid_gs);
+                    float a = fabsf(actv[n]);
+                    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+                    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+                    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+                    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+                    if (lane == 0) c.amax_x[ew][n] = a;
+                }
+            }
+            bar_sync(kBarEpi, kNumEpiThreads);
+            #pragma unroll
+            for (int n = 0; n < kTileTokens; ++n) {
+                if (n < static_cast<int>(nv)) {
+                    float amax = c.amax_x[ew][n];
+                    if constexpr (kVec == 32) amax = fmaxf(amax, c.amax_x[ew ^ 1u][n]);
+                    amax = fmaxf(amax, 1e-30f);
+                    uint32_t sf_byte; float scaled;
+                    if constexpr (kVec == 32) {
+                        sf_byte = ceil_pow2_exp(__fdiv_rn(amax, 6.0f));
+                        scaled = __fdiv_rn(actv[n], __uint_as_float(sf_byte << 23));
+                    } else {
+                        sf_byte = cvt_e4m3x2(__fdiv_rn(amax, 6.0f), 0.f) & 0xFFu;
+                        const float sf = e4m3_to_float(sf_byte);
+                        scaled = sf > 0.f ? __fdiv_rn(actv[n], sf) : (actv[n] == 0.f ? 0.f : copysignf(6.0f, actv[n]));
+                    }
+                    const float nb = __shfl_down_sync(0xffffffffu, scaled, 1);
+                    if (!is_up && (lane & 1u) == 0u)
+                        otile[n * 32 + ew * 8u + (lane >> 4) * 4u + ((lane & 7u) >> 1)] = static_cast<uint8_t>(cvt_e2m1x2(scaled, nb));
+                    if (lane == 0 && (kVec == 16 || (ew & 1u) == 0u)) {
+                        const uint32_t sfi = kVec == 32 ? 2u * j + (ew >> 1) : 4u * j + ew;
+                        cx.buf[p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes + sfi] = static_cast<uint8_t>(sf_byte);
+                    }
+                }
+            }
+            bar_sync(kBarEpi, kNumEpiThreads);
+            if (etid < nv * 2u) {
+                const uint32_t n = etid >> 1, half = etid & 1u;
+                const uint4 val = *reinterpret_cast<const uint4*>(otile + n * 32u + half * 16u);
+                st_global_v4(cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes + j * 32u + half * 16u, val);
+            }
+            __threadfence();
+            bar_sync(kBarEpi, kNumEpiThreads);
+            if (etid == 0) red_release_gpu_add(l1_done + e, 1u);
+        } else {
+            // ---- L2: bf16 rows back to the token's source rank
+            __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(otile);
+            #pragma unroll
+            for (int n = 0; n < kTileTokens; ++n)
+                if (n < static_cast<int>(nv)) ot[n * kTileRows + row] = __float2bfloat16_rn(v[n] * p.l2_scale);
+            bar_sync(kBarEpi, kNumEpiThreads);
+            for (uint32_t idx = etid; idx < nv * 16u; idx += kNumEpiThreads) {
+                const uint32_t n = idx >> 4, ch = idx & 15u;
+                const uint4 val = *reinterpret_cast<const uint4*>(otile + n * 256u + ch * 16u);
+                uint8_t* dst = p.peer[meta[n].src] + p.off_comb +
+                    ((static_cast<size_t>(meta[n].token) * p.topk + meta[n].slot) * p.H + j * kTileRows) * 2u + ch * 16u;
+                st_global_v4(dst, val);
+            }
+        }
+    }
+}
+
+// ============================================================================================= the kernel
+template <int kVec, bool kUmma>
+__global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_constant__ KParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ Ctl c;
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023u));
+    const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, bid = blockIdx.x, G = gridDim.x;
+    uint8_t* buf = p.peer[p.rank];
+    uint32_t* ctrl32 = reinterpret_cast<uint32_t*>(buf + p.off_ctrl);
+
+    // ---- prologue
+    if (tid == 0) {
+        const uint32_t ep = ctrl32[kCtrlEpoch / 4 + bid];
+        ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
+        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u;
+        for (int s = 0; s < p.nstage; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kUmma ? 1 : kNumEpiThreads); }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(&c.acts_full[i], 1); mbar_init(&c.acts_empty[i], kUmma ? 1 : kNumEpiThreads);
+            mbar_init(&c.tmem_full[i], 1); mbar_init(&c.tmem_empty[i], kNumEpiThreads);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) { tmem_alloc(&c.tmem_base, kTmemCols); tmem_relinquish(); tc_fence_before(); }
+    if (tid < kMaxLocalExperts) c.exp_count[tid] = 0u;
+    __syncthreads();
+    tc_fence_after();
+    Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, c.epoch & 1u};
+    const uint32_t epoch = c.epoch, par = cx.par;
+    if (bid == 0 && tid == 0) { ctrl32[kCtrlStatus / 4 + 1] = epoch + 1u; cx.stamp(kStampEntry); }
+
+    // ---- dispatch: SM d pushes this rank's rows for rank d
+    if (bid < static_cast<uint32_t>(p.R) && tid >= 64) {
+        const uint32_t d = bid, dtid = tid - 64;
+        uint32_t* dlist = reinterpret_cast<uint32_t*>(smem + p.sm_act);
+        if (warp == 2) {
+            const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
+            const uint32_t n = static_cast<uint32_t>(p.T) * p.topk;
+            uint32_t cnt = 0;
+            for (uint32_t base = 0; base < n; base += 32) {
+                const uint32_t i = base + lane;
+                const long long ex = i < n ? tk[i] : -1;
+                const bool m = ex >= 0 && static_cast<uint32_t>(ex / p.e_local) == d;
+                const uint32_t b = __ballot_sync(0xffffffffu, m);
+                if (m) dlist[cnt + __popc(b & ((1u << lane) - 1u))] = ((i / p.topk) << 16) | ((i % p.topk) << 8) | static_cast<uint32_t>(ex % p.e_local);
+                cnt += __popc(b);
+            }
+            if (lane == 0) c.dcount = cnt;
+        }
+        bar_sync(kBarDispatch, kNumDispatchThreads);
+        const uint32_t cnt = c.dcount;
+        const uint32_t nchunk = p.rx_row_bytes / 16, xq = p.x_row_bytes / 16, xs = p.x_sf_row_bytes / 16;
+        uint8_t* dst_base = p.peer[d] + p.off_rx + static_cast<size_t>(par * p.R + p.rank) * p.cap * p.rx_row_bytes;
+        const float* tw = reinterpret_cast<const float*>(buf + p.off_topk_w);
+        for (uint32_t idx = dtid; idx < cnt * nchunk; idx += kNumDispatchThreads) {
+            const uint32_t i = idx / nchunk, ci = idx % nchunk, ent = dlist[i];
+            const uint32_t tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
+            uint4 v;
+            if (ci < xq) v = *reinterpret_cast<const uint4*>(buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes + ci * 16u);
+            else if (ci < xq + xs) v = *reinterpret_cast<const uint4*>(buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes + (ci - xq) * 16u);
+            else v = make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot]));
+            st_global_v4(dst_base + static_cast<size_t>(i) * p.rx_row_bytes + ci * 16u, v);
+        }
+        __threadfence_system();
+        bar_sync(kBarDispatch, kNumDispatchThreads);
+        if (dtid == 0) {
+            uint64_t* flag = reinterpret_cast<uint64_t*>(p.peer[d] + p.off_flags + kFlagDispatch) + par * kMaxRanks + p.rank;
+            st_release_sys64(flag, (static_cast<uint64_t>(epoch + 1u) << 32) | cnt);
+        }
+    }
+    __syncthreads();
+    if (bid == 0 && tid == 0) cx.stamp(kStampDispatched);
+
+    // ---- the staging buffers start from zero: rows beyond a task's valid tokens only ever hold finite bytes
+    for (uint32_t off = tid * 16u; off < 2u * (p.act_bytes + p.asf_bytes); off += kThreads * 16u)
+        *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
+
+    // ---- receive: wait for every source rank's flag, then scan the rows' expert ids
+    if (tid < static_cast<uint32_t>(p.R)) {
+        const uint64_t* flag = reinterpret_cast<const uint64_t*>(buf + p.off_flags + kFlagDispatch) + par * kMaxRanks + tid;
+        uint32_t spins = 0; uint64_t f;
+        while (((f = ld_acquire_sys64(flag)) >> 32) != epoch + 1u) {
+            if ((++spins & 0x3Fu) == 0u) {
+                if (cx.aborted()) break;
+                if (cx.expired()) { cx.fail(kErrWaitDispatchFlag, tid); break; }
+            }
+        }
+        c.rx_count[tid] = static_cast<uint32_t>(f & 0xFFFFFFFFu);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t s = 0;
+        for (int r = 0; r < p.R; ++r) { c.rx_prefix[r] = s; s += c.rx_count[r]; }
+        c.rx_prefix[p.R] = s;
+        if (s > kMetaCap) cx.fail(kErrMetaCapacity, s >> 4);
+        if (bid == 0) cx.stamp(kStampFlagsSeen);
+    }
+    __syncthreads();
+    if (!cx.aborted()) {
+        const uint32_t total = c.rx_prefix[p.R];
+        for (uint32_t f = tid; f < total; f += kThreads) {
+            uint32_t r = 0;
+            while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
+            const uint32_t e = ld_cg_u32(cx.rx_row(r, f - c.rx_prefix[r]) + p.rx_row_bytes - 16) & 0xFFu;
+            c.meta_e[f] = static_cast<uint8_t>(e);
+            atomicAdd(&c.exp_count[e < kMaxLocalExperts ? e : 0], 1u);
+        }
+    }
+    __syncthreads();
+
+    // ---- schedule: L1 tiles of every active expert, then L2 tiles; SM g owns L1 task i when i % G == g. L2 tasks go
+    //      first (two rounds) to the SMs that own one L1 task fewer, then round-robin over all SMs.
+    if (warp == 0 && !cx.aborted()) {
+        if (lane == 0) {
+            uint32_t a1 = 0, a2 = 0, mb = 0;
+            for (int e = 0; e < p.e_local; ++e) {
+                const uint32_t mtiles = (c.exp_count[e] + kTileTokens - 1) / kTileTokens;
+                c.tb1[e] = a1; c.tb2[e] = a2; c.mid_base[e] = mb;
+                a1 += mtiles * p.n1_tiles; a2 += mtiles * p.n2_tiles; mb += mtiles * kTileTokens;
+            }
+            c.nt1 = a1; c.nt2 = a2;
+        }
+        __syncwarp();
+        const uint32_t nt1 = c.nt1, r1 = nt1 % G, g2 = (r1 == 0u) ? G : G - r1;
+        uint32_t nmine = 0;
+        for (uint32_t type = 0; type < 2; ++type) {
+            const uint32_t ntile = type ? p.n2_tiles : p.n1_tiles;
+            for (int e = 0; e < p.e_local; ++e) {
+                const uint32_t mtiles = (c.exp_count[e] + kTileTokens - 1) / kTileTokens;
+                for (uint32_t mt = 0; mt < mtiles; ++mt) {
+                    for (uint32_t j0 = 0; j0 < ntile; j0 += 32) {
+                        const uint32_t j = j0 + lane;
+                        const uint32_t gi = (type ? c.tb2[e] : c.tb1[e]) + mt * ntile + j;
+                        uint32_t owner;
+                        if (type == 0u) owner = gi % G;
+                        else if (r1 != 0u && gi < 2u * g2) owner = r1 + gi % g2;
+                        else owner = (gi - (r1 != 0u ? 2u * g2 : 0u)) % G;
+                        const bool m = j < ntile && owner == bid;
+                        const uint32_t b = __ballot_sync(0xffffffffu, m);
+                        const uint32_t pos = nmine + __popc(b & ((1u << lane) - 1u));
+                        if (m && pos < kMaxTasks) c.tasks[pos] = task_pack(type, e, mt, j);
+                        nmine += __popc(b);
+                    }
+                }
+            }
+        }
+        if (lane == 0) {
+            if (nmine > kMaxTasks) cx.fail(kErrTaskCapacity, nmine);
+            else c.ntasks = nmine;
+        }
+    }
+    __syncthreads();
+    if (bid == 0 && tid == 0) cx.stamp(kStampScheduled);
+    if (bid == 0 && tid < static_cast<uint32_t>(p.e_local) && p.stats != nullptr && !cx.aborted())
+        p.stats[tid] += static_cast<int>(c.exp_count[tid]);
+    // the other parity's L1 counters are idle during this launch: clear them for the next one
+    if (bid == G - 1 && tid < kMaxLocalExperts) ctrl32[kCtrlL1Done / 4 + (par ^ 1u) * kMaxLocalExperts + tid] = 0u;
+
+    // ---- roles
+    if (!cx.aborted()) {
+        if (warp == 0) { if (lane == 0) role_loader(cx); }
+        else if (warp == 1) { if constexpr (kUmma) role_mma<kVec>(cx, lane); }
+        else if (warp < 4) role_stager(cx, tid - 64);
+        else role_epilogue<kVec, kUmma>(cx, tid - 128);
+    }
+    __syncthreads();
+    if (bid == 0 && tid == 0) cx.stamp(kStampTasksDone);
+
+    // ---- tell every rank that this rank's expert outputs have been written
+    if (tid == 0 && !cx.aborted()) {
+        __threadfence_system();
+        const uint32_t old = atom_acq_rel_gpu_add(&ctrl32[kCtrlL2Done / 4], 1u);
+        if (old == G - 1) {
+            ctrl32[kCtrlL2Done / 4] = 0u;
+            __threadfence_system();
+            for (int r = 0; r < p.R; ++r)
+                st_release_sys(reinterpret_cast<uint32_t*>(p.peer[r] + p.off_flags + kFlagCombine) + par * kMaxRanks + p.rank, epoch + 1u);
+            cx.stamp(kStampL2Signalled);
+        }
+    }
+    // ---- combine: wait for every rank's flag, then sum each token's routes in slot order
+    if (tid < static_cast<uint32_t>(p.R) && !cx.aborted()) {
+        const uint32_t* flag = reinterpret_cast<const uint32_t*>(buf + p.off_flags + kFlagCombine) + par * kMaxRanks + tid;
+        uint32_t spins = 0;
+        while (ld_acquire_sys(flag) != epoch + 1u) {
+            if ((++spins & 0x3Fu) == 0u) {
+                if (cx.aborted()) break;
+                if (cx.expired()) { cx.fail(kErrWaitCombineFlag, tid); break; }
+            }
+        }
+    }
+    __syncthreads();
+    if (bid == 0 && tid == 0) cx.stamp(kStampCombineFlags);
+    if (!cx.aborted()) {
+        const uint32_t chunks_per_row = p.H / 8;
+        const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
+        for (uint32_t idx = bid * kThreads + tid; idx < static_cast<uint32_t>(p.T) * chunks_per_row; idx += G * kThreads) {
+            const uint32_t tok = idx / chunks_per_row, ch = idx % chunks_per_row;
+            float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            for (int s = 0; s < p.topk; ++s) {
+                if (tk[tok * p.topk + s] < 0) continue;
+                const uint4 v = ld_cg_v4(buf + p.off_comb + ((static_cast<size_t>(tok) * p.topk + s) * p.H) * 2u + ch * 16u);
+                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+                #pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    acc[2 * k] += __uint_as_float(w[k] << 16);
+                    acc[2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
+                }
+            }
+            uint4 o;
+            uint32_t* ow = &o.x;
+            #pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * k]));
+                const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * k + 1]));
+                ow[k] = lo | (hi << 16);
+            }
+            *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.y) + (static_cast<size_t>(tok) * p.H) * 2u + ch * 16u) = o;
+        }
+    }
+
+    // ---- exit: an aborted SM lets its bulk copies in flight land before the shared memory goes away
+    if (cx.aborted()) { for (int i = 0; i < 64; ++i) __nanosleep(1000); }
+    __syncthreads();
+    if (warp == 1) { tc_fence_after(); tmem_dealloc(c.tmem_base, kTmemCols); }
+    if (tid == 0) {
+        if (bid == 0) cx.stamp(kStampExit);
+        atomicMax(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps) + kStampLastExit, globaltimer_ns());
+    }
+}
+
+}  // namespace mm

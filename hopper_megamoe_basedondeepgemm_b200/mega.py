@@ -1,0 +1,233 @@
+"""Host-side mirror of the reference's mega-MoE operator surface (`sm100_b200/mega___init__.py`).
+
+Same names, argument meaning and error behaviour (RuntimeError on a failed check); the work is done by the
+sm_100a library behind the C ABI of `include/megamoe_b200.h`. PyTorch supplies device memory, the current stream and
+the symmetric-memory rendezvous only.
+"""
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import _lib
+from .quant import SF_VEC, interleave_gate_up, pretile_weights
+
+
+def _align(x: int, y: int) -> int:
+    return (x + y - 1) // y * y
+
+
+def get_token_alignment_for_mega_moe() -> int:
+    return int(_lib.load().mm_get_token_alignment())
+
+
+class SymmBuffer:
+    """The per-rank symmetric buffer and its input views (`sm100_b200/mega___init__.py:16-60`).
+
+    `group` may be None or a one-rank group for a single GPU; then the buffer is plain device memory.
+    """
+
+    def __init__(self, group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int,
+                 hidden: int, intermediate_hidden: int, use_fp8_dispatch: bool = True,
+                 activation: str = 'swiglu', act_format: str = 'fp8', num_sms: int = 0):
+        assert act_format in ('fp8', 'mxfp4', 'nvfp4')
+        if activation != 'swiglu':
+            raise RuntimeError('only the swiglu activation is supported')
+        lib = _lib.load()
+        self.act_format = act_format
+        self.act_sf_vec_size = {'fp8': 0, 'mxfp4': 32, 'nvfp4': 16}[act_format]
+        self.group = group
+        self.num_ranks = 1 if group is None else group.size()
+        self.rank = 0 if group is None else group.rank()
+        self.num_experts = num_experts
+        self.num_max_tokens_per_rank = num_max_tokens_per_rank
+        self.num_topk = num_topk
+        self.hidden = hidden
+        self.intermediate_hidden = intermediate_hidden
+        self.cfg = _lib.MMConfig(self.num_ranks, self.rank, num_experts, num_max_tokens_per_rank, num_topk, hidden,
+                                 intermediate_hidden, _lib.FMT[act_format], num_sms)
+        self.layout = _lib.MMLayout()
+        _lib.check(lib.mm_get_layout(ctypes.byref(self.cfg), ctypes.byref(self.layout)), 'get_symm_buffer_for_mega_moe')
+        nbytes = int(self.layout.total_bytes)
+        self.handle = None
+        if self.num_ranks > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+            self.buffer = symm_mem.empty(nbytes, dtype=torch.int8, device='cuda')
+            self.handle = symm_mem.rendezvous(self.buffer, group=group)
+            self.buffer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
+        else:
+            self.buffer = torch.empty(nbytes, dtype=torch.int8, device='cuda')
+            self.buffer_ptrs = [self.buffer.data_ptr()]
+        self.buffer.zero_()
+        if self.num_ranks > 1:
+            self.group.barrier()
+        torch.cuda.synchronize()
+        self._peer_array = (ctypes.c_void_p * self.num_ranks)(*self.buffer_ptrs)
+        L, t = self.layout, num_max_tokens_per_rank
+        vec = int(L.sf_vec)
+
+        def view(off, nbytes_, dtype, shape):
+            return self.buffer[off:off + nbytes_].view(dtype).view(*shape)
+        self.x = view(L.off_x, t * L.x_row_bytes, torch.int8, (t, int(L.x_row_bytes)))
+        self.x_sf = view(L.off_x_sf, t * L.x_sf_row_bytes, torch.int32, (t, hidden // (4 * vec)))
+        self.topk_idx = view(L.off_topk_idx, t * num_topk * 8, torch.int64, (t, num_topk))
+        self.topk_weights = view(L.off_topk_weights, t * num_topk * 4, torch.float32, (t, num_topk))
+        # receive pool: [parity][source rank][row][packed tokens | scale bytes | 16 B (expert, token, slot, weight)]
+        self.l1_acts = view(L.off_rx, 2 * self.num_ranks * L.rx_cap_rows * L.rx_row_bytes, torch.uint8,
+                            (2, self.num_ranks, int(L.rx_cap_rows), int(L.rx_row_bytes)))
+        self.l1_acts_sf = self.l1_acts[..., int(L.x_row_bytes):int(L.x_row_bytes + L.x_sf_row_bytes)]
+        self.l2_acts = view(L.off_mid, L.mid_rows * L.mid_row_bytes, torch.uint8, (int(L.mid_rows), int(L.mid_row_bytes)))
+        self.l2_acts_sf = view(L.off_mid_sf, L.mid_rows * L.mid_sf_row_bytes, torch.uint8,
+                               (int(L.mid_rows), int(L.mid_sf_row_bytes)))
+        self.combine = view(L.off_comb, t * num_topk * hidden * 2, torch.bfloat16, (t, num_topk, hidden))
+
+    def reset(self):
+        """Zero the control block and the flags (after an aborted launch). All ranks call it together."""
+        lib = _lib.load()
+        torch.cuda.synchronize()
+        if self.num_ranks > 1:
+            self.group.barrier()
+        _lib.check(lib.mm_reset(ctypes.byref(self.cfg), self.buffer.data_ptr(),
+                                torch.cuda.current_stream().cuda_stream), 'reset')
+        torch.cuda.synchronize()
+        if self.num_ranks > 1:
+            self.group.barrier()
+
+    def device_status(self):
+        """(status code, 16 status words) of the launches so far; synchronises the current stream."""
+        lib = _lib.load()
+        words = (ctypes.c_uint32 * 16)()
+        st = lib.mm_read_device_status(ctypes.byref(self.cfg), self.buffer.data_ptr(), words,
+                                       torch.cuda.current_stream().cuda_stream)
+        return st, list(words)
+
+    def phase_stamps(self):
+        lib = _lib.load()
+        stamps = (ctypes.c_uint64 * 32)()
+        _lib.check(lib.mm_read_phase_stamps(ctypes.byref(self.cfg), self.buffer.data_ptr(), stamps,
+                                            torch.cuda.current_stream().cuda_stream), 'phase_stamps')
+        return list(stamps)
+
+    def destroy(self):
+        self.handle = None
+        self.buffer = None
+        self.group = None
+        self.x = None
+        self.x_sf = None
+
+
+def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int,
+                                 hidden: int, intermediate_hidden: int, use_fp8_dispatch: bool = True,
+                                 activation: str = 'swiglu', act_format: str = 'fp8', num_sms: int = 0) -> SymmBuffer:
+    """`sm100_b200/mega___init__.py:63-78`: the token count is rounded up to the operator's alignment."""
+    num_max_tokens_per_rank = _align(num_max_tokens_per_rank, get_token_alignment_for_mega_moe())
+    return SymmBuffer(group, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
+                      use_fp8_dispatch, activation, act_format, num_sms)
+
+
+def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor],
+                                   l2_weights: Tuple[torch.Tensor, torch.Tensor]):
+    """Load-time weight transform (`sm100_b200/mega___init__.py:102-111`).
+
+    Inputs as the reference takes them: `(packed int8 [E, N, K/2], scales int32 [E, N, K/(4 vec)] MN-major)`.
+    L1 gets the 8-row gate/up interleave; both layers are then pre-tiled into the stream the kernel copies verbatim
+    (see `quant.pretile_weights`). Each result is `(stream uint8 [E, N/128, K/256, unit_bytes], shape int64 [N, K, vec])`.
+    """
+    def one(wt, interleave):
+        w, sf = wt
+        e, n, kh = w.shape
+        vec = (kh * 2) // (sf.shape[-1] * 4)
+        if vec not in (16, 32):
+            raise RuntimeError('weight scale tensor must hold one byte per 16 or 32 elements')
+        if interleave:
+            w, sf = interleave_gate_up(w), interleave_gate_up(sf)
+        return pretile_weights(w, sf, vec), torch.tensor([n, kh * 2, vec], dtype=torch.int64)
+    return one(l1_weights, True), one(l2_weights, False)
+
+
+def _launch(y, l1_weights, l2_weights, sym_buffer: SymmBuffer, stats, recipe, activation, activation_clamp, fast_math,
+            engine='umma', global_scales=(1.0, 1.0, 1.0, 1.0), timeout_ms=0.0, debug_accumulators=None):
+    lib = _lib.load()
+    if activation != 'swiglu':
+        raise RuntimeError('only the swiglu activation is supported')
+    b = sym_buffer
+    vec = b.act_sf_vec_size
+    if tuple(recipe) != (1, 1, vec):
+        raise RuntimeError(f'recipe {recipe} does not match the buffer format {b.act_format}')
+    if y.dtype != torch.bfloat16 or y.dim() != 2 or y.size(1) != b.hidden or not y.is_contiguous():
+        raise RuntimeError('y must be a contiguous bf16 [num_tokens, hidden] tensor')
+    if y.size(0) > b.num_max_tokens_per_rank:
+        raise RuntimeError('more tokens than the buffer was created for')
+    e_local = b.num_experts // b.num_ranks
+    (w1, s1), (w2, s2) = l1_weights, l2_weights
+    if w1.dtype != torch.uint8 or w1.dim() != 4 or w2.dtype != torch.uint8 or w2.dim() != 4:
+        raise RuntimeError('weights must come from transform_weights_for_mega_moe')
+    if s1.tolist() != [2 * b.intermediate_hidden, b.hidden, vec] or s2.tolist() != [b.hidden, b.intermediate_hidden, vec]:
+        raise RuntimeError('weight shapes do not match the buffer')
+    if w1.size(0) != e_local or w2.size(0) != e_local or not (w1.is_contiguous() and w2.is_contiguous()):
+        raise RuntimeError('expected one contiguous weight stream per local expert')
+    if stats is not None and (stats.dtype != torch.int32 or stats.numel() != e_local):
+        raise RuntimeError('cumulative_local_expert_recv_stats must be int32 [num_local_experts]')
+    args = _lib.MMLaunchArgs(
+        b.buffer.data_ptr(), b._peer_array, w1.data_ptr(), w2.data_ptr(), y.data_ptr() if y.numel() else None,
+        y.size(0), _lib.ENGINE[engine], stats.data_ptr() if stats is not None else None,
+        float(activation_clamp) if activation_clamp is not None else -1.0, int(bool(fast_math)),
+        *[float(g) for g in global_scales], float(timeout_ms),
+        debug_accumulators.data_ptr() if debug_accumulators is not None else None,
+        debug_accumulators.size(0) if debug_accumulators is not None else 0, 0)
+    _lib.check(lib.mm_mega_moe_launch(ctypes.byref(b.cfg), ctypes.byref(args), torch.cuda.current_stream().cuda_stream),
+               'mega_moe launch')
+
+
+def fp4_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
+                     cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
+                     recipe: Optional[Tuple[int, int, int]] = None, activation: str = 'swiglu',
+                     activation_clamp: Optional[float] = None, fast_math: bool = True, *,
+                     x_global_scale: float = 1.0, l1_global_scale: float = 1.0, l2_global_scale: float = 1.0,
+                     mid_global_scale: float = 1.0, engine: str = 'umma', timeout_ms: float = 0.0,
+                     debug_accumulators: Optional[torch.Tensor] = None):
+    """W4A4 MegaMoE, packed E2M1 activations and weights (`sm100_b200/mega___init__.py:244-274`).
+
+    The caller has written `x`, `x_sf`, `topk_idx`, `topk_weights[:y.size(0)]` into the buffer views; the launch is
+    asynchronous on the current CUDA stream and every rank of the group must make the same call. The keyword-only
+    arguments are additions: NVFP4 per-tensor scales (default 1.0 = the reference's behaviour), `engine='check'`
+    (the same kernel with CUDA-core dot products, used as an on-device cross-check) and the device wait budget.
+    """
+    assert sym_buffer.act_format in ('mxfp4', 'nvfp4'), 'buffer must be created with act_format mxfp4/nvfp4'
+    if recipe is None:
+        recipe = (1, 1, sym_buffer.act_sf_vec_size)
+    assert recipe[2] == sym_buffer.act_sf_vec_size
+    _launch(y, l1_weights, l2_weights, sym_buffer, cumulative_local_expert_recv_stats, recipe, activation,
+            activation_clamp, fast_math, engine, (x_global_scale, l1_global_scale, l2_global_scale, mid_global_scale),
+            timeout_ms, debug_accumulators)
+
+
+def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
+                     cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
+                     recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = 'swiglu',
+                     activation_clamp: Optional[float] = None, fast_math: bool = True):
+    """W-MXFP4 x A-FP8 MegaMoE (`sm100_b200/mega___init__.py:221-241`)."""
+    raise RuntimeError('fp8_fp4_mega_moe: the FP8-activation variant is not built yet')
+
+
+def fe_workspace_bytes(sym_buffer: SymmBuffer) -> int:
+    return int(_lib.load().mm_frontend_workspace_bytes(ctypes.byref(sym_buffer.cfg)))
+
+
+def fe_forward(hidden: torch.Tensor, router_weight: torch.Tensor, sym_buffer: SymmBuffer, workspace: torch.Tensor,
+               score_mode: int = 0, expert_bias: Optional[torch.Tensor] = None, x_global_scale: float = 1.0):
+    """Router frontend (`sm100_b200/fe_sm100/fe_binding.cpp:8-35`): router GEMM, top-8, routing weights and the token
+    quantisation, written into `sym_buffer.x / x_sf / topk_idx / topk_weights[:hidden.size(0)]`."""
+    lib = _lib.load()
+    b = sym_buffer
+    if hidden.dtype != torch.bfloat16 or router_weight.dtype != torch.bfloat16:
+        raise RuntimeError('hidden states and router weight must be bf16')
+    if hidden.size(1) != b.hidden or tuple(router_weight.shape) != (b.num_experts, b.hidden):
+        raise RuntimeError('router shapes do not match the buffer')
+    if workspace.numel() * workspace.element_size() < fe_workspace_bytes(b):
+        raise RuntimeError('frontend workspace too small')
+    args = _lib.MMFrontendArgs(hidden.data_ptr(), router_weight.data_ptr(),
+                               expert_bias.data_ptr() if expert_bias is not None else None,
+                               hidden.size(0), score_mode, workspace.data_ptr(), float(x_global_scale))
+    _lib.check(lib.mm_frontend_launch(ctypes.byref(b.cfg), b.buffer.data_ptr(), ctypes.byref(args),
+                                      torch.cuda.current_stream().cuda_stream), 'fe_forward')

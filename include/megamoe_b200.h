@@ -1,0 +1,135 @@
+/* C ABI of the B200 (sm_100a) expert-parallel MegaMoE layer.
+ *
+ * Plain pointers and sizes only; every function returns an `mm_status` code and never throws.
+ * The library is what a host binding (ctypes, pybind, cgo ...) loads in place of the reference's
+ * `deep_gemm._C` mega-MoE entry points. File:line citations name the reference interface that
+ * each entry point replaces (paths relative to the reference project's root).
+ */
+#ifndef MEGAMOE_B200_H_
+#define MEGAMOE_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum mm_status {
+    MM_OK = 0,
+    MM_ERR_INVALID_ARGUMENT = 1,   /* shape / pointer check failed (reference: DG_HOST_ASSERT -> RuntimeError) */
+    MM_ERR_UNSUPPORTED = 2,        /* a limit of this build (hidden size, experts per rank, ...) */
+    MM_ERR_CUDA = 3,               /* a CUDA runtime call failed; see mm_last_cuda_error() */
+    MM_ERR_DEVICE_TIMEOUT = 4,     /* a bounded device-side wait expired; see mm_read_device_status() */
+    MM_ERR_DEVICE_CAPACITY = 5     /* a device-side table overflowed (rows received / tasks per SM) */
+};
+
+enum mm_act_format { MM_FMT_MXFP4 = 0, MM_FMT_NVFP4 = 1, MM_FMT_FP8 = 2 };
+enum mm_engine { MM_ENGINE_UMMA = 0 /* tcgen05 block-scaled MMA */, MM_ENGINE_CHECK = 1 /* same kernel, CUDA-core dot products: on-device cross-check */ };
+
+/* Static description of one layer instance; identical on every rank except `rank`. */
+typedef struct mm_config {
+    int32_t num_ranks;                 /* expert-parallel group size, 1..8 */
+    int32_t rank;
+    int32_t num_experts;               /* global; num_experts / num_ranks experts live on each rank (<= 64) */
+    int32_t num_max_tokens_per_rank;
+    int32_t num_topk;
+    int32_t hidden;                    /* multiple of 512, <= 4096 */
+    int32_t intermediate;              /* multiple of 256 */
+    int32_t act_format;                /* enum mm_act_format */
+    int32_t num_sms;                   /* persistent grid size; 0 = all SMs of the current device */
+} mm_config_t;
+
+/* Byte offsets of the regions inside one rank's symmetric buffer.
+ * Replaces `get_symm_buffer_size_for_mega_moe` + its slicing lambda (sm100_b200/apis_mega.hpp:23-171). */
+typedef struct mm_layout {
+    int64_t total_bytes;
+    int64_t off_ctrl;          /* per-SM epochs, device status words, local counters, phase stamps */
+    int64_t off_flags;         /* dispatch / combine arrival flags written by the peers */
+    int64_t off_x;             /* [T_max][x_row_bytes]   quantised tokens (caller or frontend writes) */
+    int64_t off_x_sf;          /* [T_max][x_sf_row_bytes] one scale byte per `vec` elements, K-major */
+    int64_t off_topk_idx;      /* [T_max][topk] int64, -1 = masked slot */
+    int64_t off_topk_weights;  /* [T_max][topk] float */
+    int64_t off_rx;            /* [2 parities][num_ranks sources][rx_cap_rows][rx_row_bytes] receive pool */
+    int64_t off_mid;           /* [mid_rows][mid_row_bytes] requantised SwiGLU output (local) */
+    int64_t off_mid_sf;        /* [mid_rows][mid_sf_row_bytes] */
+    int64_t off_comb;          /* [T_max][topk][hidden] bf16 expert outputs written back by the peers */
+    int64_t x_row_bytes, x_sf_row_bytes;
+    int64_t rx_row_bytes, rx_cap_rows;
+    int64_t mid_rows, mid_row_bytes, mid_sf_row_bytes;
+    int32_t sf_vec;            /* elements per scale byte of the activation format */
+    int32_t reserved;
+} mm_layout_t;
+
+/* Geometry of the pre-tiled weight stream produced by the load-time transform.
+ * Replaces the layout contract of `transform_weights_for_mega_moe` (sm100_b200/mega___init__.py:81-111). */
+typedef struct mm_weight_geometry {
+    int32_t tile_rows;         /* 128 weight rows per tile */
+    int32_t unit_k;            /* K elements per streamed unit */
+    int32_t unit_weight_bytes; /* swizzled weight bytes of one unit */
+    int32_t unit_sf_bytes;     /* scale planes of one unit */
+    int32_t unit_bytes;        /* stride between units */
+    int32_t sf_vec;            /* elements per weight scale byte */
+} mm_weight_geometry_t;
+
+typedef struct mm_launch_args {
+    void* buffer;                    /* this rank's symmetric buffer (mm_layout.total_bytes) */
+    void* const* peer_buffers;       /* num_ranks device pointers, peer_buffers[rank] == buffer */
+    const void* l1_weights;          /* pre-tiled stream [E_local][2I/128][H/unit_k][unit_bytes] */
+    const void* l2_weights;          /* pre-tiled stream [E_local][H/128][I/unit_k][unit_bytes] */
+    void* y;                         /* bf16 [num_tokens][hidden], caller-owned */
+    int32_t num_tokens;              /* tokens of this rank in this call (rows of y) */
+    int32_t engine;                  /* enum mm_engine */
+    int32_t* cumulative_local_expert_recv_stats;   /* optional int32 [E_local], += rows received */
+    float activation_clamp;          /* < 0 or inf: no clamp */
+    int32_t fast_math;               /* 1: __expf + approximate reciprocal in the SwiGLU */
+    float x_global_scale, l1_global_scale, l2_global_scale, mid_global_scale;   /* NVFP4 per-tensor scales; 1.0 otherwise */
+    float timeout_ms;                /* budget of every device-side wait; <= 0: 2000 ms */
+    void* debug_accumulators;        /* optional diagnostics: float [debug_num_tasks][16][128], the raw fp32 accumulators
+                                        of the first tasks of SM 0 (meaningful with num_sms = 1); NULL in production */
+    int32_t debug_num_tasks;
+    int32_t reserved;
+} mm_launch_args_t;
+
+/* Router frontend: bf16 router GEMM, top-k selection, token quantisation into the buffer views.
+ * Replaces `launch_router_quant_topk_frontend` (sm100_b200/fe_sm100/fable_frontend.h:48-52). */
+typedef struct mm_frontend_args {
+    const void* hidden_states;       /* bf16 [num_tokens][hidden] */
+    const void* router_weight;       /* bf16 [num_experts][hidden] */
+    const float* expert_bias;        /* optional float [num_experts] (score_mode 1) */
+    int32_t num_tokens;
+    int32_t score_mode;              /* 0: softmax over the selected logits; 1: sigmoid + bias selection, renormalised */
+    void* workspace;                 /* mm_frontend_workspace_bytes() bytes of device memory */
+    float x_global_scale;
+} mm_frontend_args_t;
+
+/* sm100_b200/apis_mega.hpp:23-171 (buffer sizing) */
+int mm_get_layout(const mm_config_t* cfg, mm_layout_t* out);
+/* sm100_b200/mega___init__.py:81-111 (weight layout contract) */
+int mm_get_weight_geometry(int32_t act_format, mm_weight_geometry_t* out);
+/* sm100_b200/apis_mega.hpp:544-552 (`get_token_alignment_for_mega_moe`) */
+int32_t mm_get_token_alignment(void);
+/* sm100_b200/apis_mega.hpp:173-358 (`fp8_fp4_mega_moe`, `fp4_fp4_mega_moe`): asynchronous launch on `stream` */
+int mm_mega_moe_launch(const mm_config_t* cfg, const mm_launch_args_t* args, void* stream);
+/* sm100_b200/fe_sm100/fable_frontend.h:48-52 (`launch_router_quant_topk_frontend`) */
+int mm_frontend_launch(const mm_config_t* cfg, void* buffer, const mm_frontend_args_t* args, void* stream);
+/* sm100_b200/fe_sm100/fe_binding.cpp:8-35 (`fe_workspace_bytes`) */
+int64_t mm_frontend_workspace_bytes(const mm_config_t* cfg);
+/* Router frontend and layer as ONE persistent kernel (the frontend's outputs still land in the buffer views). */
+int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_t* args,
+                                   const mm_frontend_args_t* fe, void* stream);
+/* Zero the control block and the arrival flags (after an aborted launch or at creation). The reference's
+ * only remedy is re-creating the buffer (sm100_b200/mega___init__.py:43-47). Callers synchronise the ranks around it. */
+int mm_reset(const mm_config_t* cfg, void* buffer, void* stream);
+/* Synchronises `stream`, then copies the 16 device status words: [0] first failure (0 = none; code | sm << 8 |
+ * detail << 16), [1] launches seen, [2..] diagnostics. The reference traps instead (sm100_b200/layout_mega_moe.cuh:13-19). */
+int mm_read_device_status(const mm_config_t* cfg, const void* buffer, uint32_t out_words[16], void* stream);
+/* Synchronises `stream`, then copies the 32 phase stamps (globaltimer ns) of the last launch.
+ * Replaces the `DG_SM100_PHASE_STAMPS_PTR` facility (sm100_b200/sm100_fp4_fp4_mega_moe.cuh:97-128). */
+int mm_read_phase_stamps(const mm_config_t* cfg, const void* buffer, uint64_t out_stamps[32], void* stream);
+const char* mm_status_string(int status);
+const char* mm_last_cuda_error(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* MEGAMOE_B200_H_ */

@@ -1,0 +1,105 @@
+"""CPU-side checks: the library loads and exports the declared C ABI, the buffer layout, the weight pre-tiling."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+import hopper_megamoe_basedondeepgemm_b200 as mm
+from hopper_megamoe_basedondeepgemm_b200 import _lib, quant
+from oracle import megamoe_oracle as O
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    header = open(os.path.join(ROOT, 'include', 'megamoe_b200.h')).read()
+    declared = set(re.findall(r'\b(mm_[a-z0-9_]+)\s*\(', header))
+    assert declared == set(_lib.EXPORTS)
+    for name in declared:
+        assert getattr(lib, name) is not None
+
+
+def _layout(**kw):
+    lib = _lib.load()
+    cfg = _lib.MMConfig(kw.get('ranks', 8), kw.get('rank', 0), kw.get('experts', 384), kw.get('tmax', 128), 8,
+                        kw.get('hidden', 3072), kw.get('inter', 1280), _lib.FMT[kw.get('fmt', 'mxfp4')], 148)
+    L = _lib.MMLayout()
+    return lib.mm_get_layout(ctypes.byref(cfg), ctypes.byref(L)), L
+
+
+def test_layout_regions_are_ordered_and_sized():
+    st, L = _layout()
+    assert st == 0
+    offs = [L.off_ctrl, L.off_flags, L.off_x, L.off_x_sf, L.off_topk_idx, L.off_topk_weights, L.off_rx, L.off_mid,
+            L.off_mid_sf, L.off_comb, L.total_bytes]
+    assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs)
+    assert L.x_row_bytes == 1536 and L.x_sf_row_bytes == 96 and L.rx_row_bytes == 1536 + 96 + 16
+    assert L.rx_cap_rows == 128 * 8 and L.mid_row_bytes == 640 and L.mid_sf_row_bytes == 48
+    assert L.off_mid - L.off_rx >= 2 * 8 * L.rx_cap_rows * L.rx_row_bytes
+    st, L2 = _layout(fmt='nvfp4')
+    assert st == 0 and L2.x_sf_row_bytes == 192 and L2.mid_sf_row_bytes == 80 and L2.sf_vec == 16
+
+
+def test_layout_rejects_bad_shapes():
+    assert _layout(hidden=3000)[0] == 2        # unsupported
+    assert _layout(experts=385)[0] == 1        # invalid: not divisible by ranks
+    assert _layout(ranks=16, experts=384)[0] == 1
+    assert _layout(ranks=1, experts=384)[0] == 2   # more than 64 local experts
+    assert _layout(fmt='fp8')[0] in (0, 2)
+
+
+@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4'])
+def test_pretiled_stream_decodes_back_to_the_weights(fmt):
+    """Walk the stream with the address arithmetic the kernel uses and recover every weight byte and scale byte."""
+    vec = quant.SF_VEC[fmt]
+    torch.manual_seed(0)
+    e, n, k = 2, 256, 512
+    w = (torch.randn(e, n, k) * 0.05).to(torch.bfloat16)
+    q, sf_mn = quant.cast_grouped_weights_to_fp4(w, fmt)
+    stream = quant.pretile_weights(q, sf_mn, vec)
+    planes = 256 // (4 * vec)
+    assert stream.shape == (e, n // 128, k // 256, 16384 + planes * 512)
+    qb = q.view(torch.uint8)
+    sfb = sf_mn.contiguous().view(torch.uint8).reshape(e, n, k // vec)
+    for ex in range(e):
+        for j in range(n // 128):
+            for u in range(k // 256):
+                unit = stream[ex, j, u]
+                for r in (0, 1, 7, 8, 37, 64, 127):
+                    for ci in range(8):
+                        off = (r >> 3) * 1024 + (r & 7) * 128 + ((ci ^ (r & 7)) << 4)
+                        assert torch.equal(unit[off:off + 16], qb[ex, 128 * j + r, u * 128 + ci * 16:u * 128 + ci * 16 + 16])
+                    for pl in range(planes):
+                        off = 16384 + pl * 512 + ((r & 31) * 4 + (r >> 5)) * 4
+                        g = u * planes + pl
+                        assert torch.equal(unit[off:off + 4], sfb[ex, 128 * j + r, 4 * g:4 * g + 4])
+
+
+def test_product_quantiser_matches_oracle():
+    torch.manual_seed(1)
+    t = (torch.randn(8, 512) * 0.3).to(torch.bfloat16)
+    for fmt in ('mxfp4', 'nvfp4'):
+        p, sf, words = quant.cast_rows_to_fp4(t, fmt)
+        po, sfo, sfbo = O.quant_fp4_rows(t, fmt, rounding='rne', sf_rule='div')
+        assert torch.equal(p.view(torch.uint8), po) and torch.equal(sf, sfo)
+        assert torch.equal(words.view(torch.uint8).reshape(8, -1), sfbo)
+
+
+def test_interleave_matches_reference_rule():
+    t = torch.arange(2 * 32).reshape(2, 32, 1)
+    out = quant.interleave_gate_up(t)
+    # [gate 0..7, up 0..7, gate 8..15, up 8..15]
+    assert out[0, :, 0].tolist() == list(range(0, 8)) + list(range(16, 24)) + list(range(8, 16)) + list(range(24, 32))
+
+
+def test_transform_weights_shapes():
+    torch.manual_seed(2)
+    w1 = (torch.randn(2, 512, 512) * 0.05).to(torch.bfloat16)
+    w2 = (torch.randn(2, 512, 256) * 0.05).to(torch.bfloat16)
+    l1, l2 = mm.transform_weights_for_mega_moe(quant.cast_grouped_weights_to_fp4(w1, 'mxfp4'),
+                                               quant.cast_grouped_weights_to_fp4(w2, 'mxfp4'))
+    assert l1[0].shape == (2, 4, 2, 17408) and l1[1].tolist() == [512, 512, 32]
+    assert l2[0].shape == (2, 4, 1, 17408) and l2[1].tolist() == [512, 256, 32]

@@ -68,7 +68,7 @@ def test_layer_matches_reference_torch_moe(fmt):
     y = torch.cat([v.float() for v in res.y])
     y_ref = g['y_ref']
     # the oracle returns bf16; the reference sum is fp32: compare after the same final rounding
-    assert torch.equal(y.to(torch.bfloat16), y_ref.to(torch.bfloat16)) or O.rel_rmse(y, y_ref) < 2e-3
+    assert torch.equal(y.to(torch.bfloat16), y_ref.to(torch.bfloat16))
     # the kernel-faithful variant (per-route bf16, RNE) stays inside the parity tolerance of the fused kernel
     res2 = O.moe_layer_reference(inputs, weights, fmt, num_experts, clamp=10.0, faithful=True, rounding='rne')
     y2 = torch.cat([v.float() for v in res2.y])

@@ -187,10 +187,9 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     const int kmax = p.H > p.I ? p.H : p.I;
     const int vec = sf_vec_of(cfg->act_format);
     p.act_bytes = mm::kTileTokens * kmax / 2;
-    p.asf_bytes = static_cast<uint32_t>(align_up(kmax / vec, 16) / 16 * 512);
-    if ((kmax / mm::kUnitK) * (mm::kUnitK / (4 * vec)) > 96) return MM_ERR_UNSUPPORTED;
+    p.asf_bytes = static_cast<uint32_t>(align_up(kmax / vec, 16) / 4 * 256);     // 256 B per scale word of the K axis
     const size_t fixed = 2 * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes;
-    const size_t budget = 232448 - sizeof(mm::Ctl) - 1024 /* alignment slack */ - 512;
+    const size_t budget = 232448 - sizeof(mm::Ctl) - 1024 /* alignment slack */ - 768;
     int nstage = static_cast<int>((budget - fixed) / p.unit_bytes);
     if (nstage > mm::kMaxStages) nstage = mm::kMaxStages;
     if (nstage < 2) return MM_ERR_UNSUPPORTED;
@@ -198,7 +197,7 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.sm_act = nstage * p.unit_bytes;
     p.sm_asf = p.sm_act + 2 * p.act_bytes;
     p.sm_otile = p.sm_asf + 2 * p.asf_bytes;
-    *smem_bytes = p.sm_otile + mm::kOtileBytes + 1024;
+    *smem_bytes = p.sm_otile + mm::kOtileBytes + 1024 + 256;
     if (static_cast<size_t>(p.T) * p.topk * 4 > 2 * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
     return MM_OK;
 }

@@ -36,7 +36,7 @@ constexpr int kUnitK = 256;             // K elements per streamed unit (one 128
 constexpr int kUnitWBytes = kTileRows * 128;
 constexpr int kNumEpiThreads = 128, kNumStagerThreads = 64, kNumDispatchThreads = 192;
 constexpr uint32_t kBarEpi = 1, kBarStager = 2, kBarDispatch = 3;
-constexpr uint32_t kTmemCols = 256;
+constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kOtileBytes = 4096;
 
 // control-block offsets (bytes from off_ctrl)
@@ -180,7 +180,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     constexpr uint32_t kPlanes = kUnitK / (4 * kVec);           // scale words per row per unit
     constexpr uint32_t kIdesc = idesc_block_scaled(kFmtMxf4E2M1, kFmtMxf4E2M1, kTileRows, kTileTokens, kVec == 32 ? 1u : 0u);
     const uint32_t tm = c.tmem_base;
-    const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 96
+    const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 16
     uint32_t it = 0;
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
@@ -190,13 +190,6 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         if (!__all_sync(0xffffffffu, cx.wait(&c.acts_full[ab], use, kErrWaitActsFull))) return;
         if (!__all_sync(0xffffffffu, cx.wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty))) return;
         tc_fence_after();
-        if (lane == 0) {
-            // token scale bytes of the whole K: chunk q carries scale words 4q..4q+3 of every token row (lane = row)
-            const uint32_t nq = (static_cast<uint32_t>(kunits) * kPlanes + 3u) / 4u;
-            const uint32_t asf = smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes);
-            for (uint32_t q = 0; q < nq; ++q)
-                utccp_32x128b_warpx4(tm + sfb_col + ab * 96u + q * 4u, smem_desc(asf + q * 512u, 128u, kLayoutNone));
-        }
         const uint32_t act = smem_u32(cx.smem + p.sm_act + ab * p.act_bytes);
         for (int u = 0; u < kunits; ++u, ++it) {
             const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
@@ -204,10 +197,15 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
             tc_fence_after();
             if (lane == 0) {
                 const uint32_t wsm = smem_u32(cx.smem + static_cast<size_t>(s) * p.unit_bytes);
-                const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u;
+                const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u, sfb = tm + sfb_col + (it & 1u) * 16u;
+                const uint32_t asf = smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes) + static_cast<uint32_t>(u) * kPlanes * 256u;
                 #pragma unroll
-                for (uint32_t pl = 0; pl < kPlanes; ++pl)
+                for (uint32_t pl = 0; pl < kPlanes; ++pl) {
+                    // one scale word (4 scale bytes, K span 4 * vec) per row: lane = row % 32, column = row / 32.
+                    // Token rows fill lanes 0..15 of a plane; lanes 16..31 receive the next plane's bytes and are never read.
                     utccp_32x128b_warpx4(sfa + pl * 4u, smem_desc(wsm + kUnitWBytes + pl * 512u, 128u, kLayoutNone));
+                    utccp_32x128b_warpx4(sfb + pl * 4u, smem_desc(asf + pl * 256u, 128u, kLayoutNone));
+                }
                 const uint32_t bsm = act + static_cast<uint32_t>(u) * (kTileTokens * 128u);
                 #pragma unroll
                 for (uint32_t ks = 0; ks < kUnitK / 64; ++ks) {
@@ -215,12 +213,11 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
                     const uint64_t adesc = smem_desc(wsm + ks * 32u, 1024u, kLayoutSw128);
                     const uint64_t bdesc = smem_desc(bsm + ks * 32u, 1024u, kLayoutSw128);
                     const uint32_t idesc = idesc_with_sf(kIdesc, sf_id, sf_id);
-                    const uint32_t sfb = tm + sfb_col + ab * 96u + static_cast<uint32_t>(u) * kPlanes + pl;
                     const uint32_t accum = (u > 0 || ks > 0) ? 1u : 0u;
                     if constexpr (kVec == 32)
-                        umma_mxf4_block32(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb, accum);
+                        umma_mxf4_block32(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
                     else
-                        umma_nvf4_block16(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb, accum);
+                        umma_nvf4_block16(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
                 }
                 tc_commit(&c.empty[s]);
             }
@@ -292,7 +289,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t stid) {
         uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
         uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
         const uint32_t nchunk = (type ? p.I : p.H) / 32;                       // 16 B chunks of one packed row
-        const uint32_t sfchunk = (type ? p.mid_sf_row_bytes : p.x_sf_row_bytes) / 16;
+        const uint32_t sfwords = (type ? p.mid_sf_row_bytes : p.x_sf_row_bytes) / 4;   // scale words of one row
         const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
         for (uint32_t idx = stid; idx < nv * nchunk; idx += kNumStagerThreads) {
             const uint32_t n = idx / nchunk, ci = idx % nchunk;
@@ -301,12 +298,11 @@ __device__ void role_stager(const Ctx& cx, uint32_t stid) {
             const uint4 v = ld_cg_v4(src + ci * 16u);
             *reinterpret_cast<uint4*>(act + (ci >> 3) * (kTileTokens * 128u) + sw128_off(n, ci & 7u)) = v;
         }
-        for (uint32_t idx = stid; idx < nv * sfchunk; idx += kNumStagerThreads) {
-            const uint32_t n = idx / sfchunk, q = idx % sfchunk;
+        for (uint32_t idx = stid; idx < nv * sfwords; idx += kNumStagerThreads) {
+            const uint32_t n = idx / sfwords, g = idx % sfwords;
             const uint8_t* src = type ? cx.buf + p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes
                                       : cx.rx_row(c.rowidx[n] >> 24, c.rowidx[n] & 0xFFFFFFu) + p.x_row_bytes;
-            const uint4 v = ld_cg_v4(src + q * 16u);
-            *reinterpret_cast<uint4*>(asf + q * 512u + n * 16u) = v;
+            *reinterpret_cast<uint32_t*>(asf + g * 256u + n * 16u) = ld_cg_u32(src + g * 4u);
         }
         fence_proxy_async_smem();
         bar_sync(kBarStager, kNumStagerThreads);
@@ -341,7 +337,7 @@ __device__ __forceinline__ void check_accumulate(const Ctx& cx, const uint8_t* w
             for (uint32_t n = 0; n < kTileTokens; ++n) {
                 if (n < nv) {
                     const uint8_t* arow = act + u * (kTileTokens * 128u) + (n >> 3) * 1024u + (n & 7u) * 128u + ((ci ^ (n & 7u)) << 4) + in;
-                    const uint32_t aword = *reinterpret_cast<const uint32_t*>(asf + (g >> 2) * 512u + n * 16u + (g & 3u) * 4u);
+                    const uint32_t aword = *reinterpret_cast<const uint32_t*>(asf + g * 256u + n * 16u);
                     const float sa = sf_value<kVec>((aword >> (8 * sb)) & 0xFFu);
                     float dot = 0.f;
                     #pragma unroll

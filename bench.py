@@ -1,0 +1,241 @@
+"""Benchmark of the fused MegaMoE layer: kernel microseconds per layer (max over ranks) and HBM roofline fraction.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--tokens-per-rank T] [--format mxfp4|nvfp4]
+
+N = 1 runs the single-GPU configuration (48 local experts, the per-rank work of the 8-rank global-M=8 case: 8 routed
+rows on 8 experts). Under torchrun (N > 1) every rank owns 48 experts and feeds T tokens (default 1), i.e. the
+8-rank run is the reference's headline case E=384 / H=3072 / I=1280 / top-8 / global M=8. One JSON line on rank 0.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN, INTER, TOPK, E_LOCAL = 3072, 1280, 8, 48
+PUBLISHED_US = {}          # BASELINE.json `published` is empty: no number measured for this exact metric
+
+
+def peaks():
+    path = os.path.join(ROOT, 'MEASURED_PEAKS.json')
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)['hbm_gbs']), 'measured (MEASURED_PEAKS.json)'
+    return 6650.0, 'fallback'
+
+
+class ClockSampler:
+    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
+             'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, gpu_index):
+        self.gpu_index, self.proc = gpu_index, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits',
+                                          '-lms', '100', '-i', str(self.gpu_index)], stdout=subprocess.PIPE, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        self.proc.terminate()
+        out, _ = self.proc.communicate(timeout=10)
+        sm, mx, reasons = [], [], set()
+        for line in out.strip().splitlines():
+            f = [v.strip() for v in line.split(',')]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1])); mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), f[5:9]):
+                if v.lower().startswith('active'):
+                    reasons.add(name)
+        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
+                'reasons': sorted(reasons), 'samples': len(sm)}
+
+
+def cpu_reference_us(tokens, fmt, reps, threads=None):
+    """The reference's pure-torch quantised MoE (the CPU oracle port) on the host cores: microseconds per layer."""
+    import torch
+    from oracle import megamoe_oracle as O
+    from tests import util_moe as U
+    if threads:
+        torch.set_num_threads(threads)
+    w, gs1, gs2 = O.make_expert_weights(E_LOCAL, HIDDEN, INTER, fmt, seed=0, std=0.02)
+    idx, tw = O.balanced_routing(tokens, 0, 1, E_LOCAL, TOPK)
+    _, inp, _ = U.make_rank_inputs(tokens, HIDDEN, fmt, 1, idx, tw)
+    times = []
+    for i in range(reps + 1):
+        t0 = time.perf_counter()
+        O.moe_layer_reference([inp], [w], fmt, E_LOCAL, clamp=10.0, w1_global_scale=gs1, w2_global_scale=gs2)
+        if i:
+            times.append((time.perf_counter() - t0) * 1e6)
+    return statistics.median(times), torch.get_num_threads()
+
+
+def run_reference(args):
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    us, cores = cpu_reference_us(args.tokens_per_rank, args.format, max(args.steps, 3))
+    sample = (f'{max(args.steps, 3)} repetitions (after 1 warm-up) of one rank\'s layer: {args.tokens_per_rank} token(s) x top-8 '
+              f'over 48 experts, H=3072, I=1280, {args.format}; weights dequantised inside the timed call')
+    line = {'impl': 'reference', 'metric': 'moe_layer_kernel_us', 'value': us, 'unit': 'us', 'n_gpus': args.gpus,
+            'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': us / 1e3, 'higher_is_better': False,
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp4 (e2m1) x fp4, fp32 accumulate', 'data': 'synthetic',
+            'config': workload_config(args, args.gpus),
+            'cpu_baseline': {'value': us, 'unit': 'us', 'cores': cores, 'kind': 'port', 'sample': sample},
+            'e2e': {'value': us, 'unit': 'us', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}
+    print(json.dumps(line))
+
+
+def workload_config(args, n):
+    return {'workload': f'EP{n} W4A4 {args.format.upper()} MegaMoE layer, E={E_LOCAL * n} ({E_LOCAL}/rank), H={HIDDEN}, '
+                        f'I={INTER}, top-{TOPK}, forced-balanced routing, {args.tokens_per_rank} token(s) per rank '
+                        f'(global M={args.tokens_per_rank * n}), weights ~N(0,0.02)',
+            'l2': 'flushed by a 256 MiB write before every timed step', 'parallelism': f'ep{n}'}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument('--gpus', type=int, default=1)
+    ap.add_argument('--steps', type=int, default=30)
+    ap.add_argument('--warmup', type=int, default=5)
+    ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
+    ap.add_argument('--tokens-per-rank', type=int, default=1)
+    ap.add_argument('--format', default='mxfp4', choices=['mxfp4', 'nvfp4'])
+    ap.add_argument('--no-cpu-baseline', action='store_true')
+    ap.add_argument('--num-sms', type=int, default=0)
+    args = ap.parse_args()
+    if args.impl == 'reference':
+        return run_reference(args)
+
+    import torch
+    import torch.distributed as dist
+    import hopper_megamoe_basedondeepgemm_b200 as mm
+    from hopper_megamoe_basedondeepgemm_b200 import workload as W
+
+    rank, world = int(os.environ.get('RANK', '0')), int(os.environ.get('WORLD_SIZE', '1'))
+    local = int(os.environ.get('LOCAL_RANK', '0'))
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        dist.init_process_group('nccl', device_id=torch.device('cuda', local))
+        group = dist.group.WORLD
+    n, fmt, T = world, args.format, args.tokens_per_rank
+    num_experts = E_LOCAL * n
+    W_WARM = max(args.warmup, 3)
+
+    buf = mm.get_symm_buffer_for_mega_moe(group, num_experts, max(T, 16), TOPK, HIDDEN, INTER, act_format=fmt,
+                                          num_sms=args.num_sms)
+    l1, l2, (gs1, gs2) = W.make_layer_weights(E_LOCAL, HIDDEN, INTER, fmt, seed=1000 + rank)
+    x_gs, mid_gs = (1.0 / 64.0, 1.0 / 512.0) if fmt == 'nvfp4' else (1.0, 1.0)
+    _, xq, xsf = W.make_tokens(T, HIDDEN, fmt, seed=2000 + rank, global_scale=x_gs)
+    idx, tw = W.balanced_routing(T, rank, n, num_experts, TOPK, device='cuda')
+    all_idx = [W.balanced_routing(T, r, n, num_experts, TOPK)[0] for r in range(n)]
+    active = W.active_experts_per_rank(all_idx, num_experts, n)
+    y = torch.empty((T, HIDDEN), dtype=torch.bfloat16, device='cuda')
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device='cuda')
+    align = torch.ones(1, device='cuda')
+    # pinned host copies for the end-to-end leg
+    h_x, h_sf = xq.cpu().pin_memory(), xsf.cpu().pin_memory()
+    h_idx, h_w = idx.cpu().pin_memory(), tw.cpu().pin_memory()
+    h_y = torch.empty((T, HIDDEN), dtype=torch.bfloat16).pin_memory()
+
+    def write_inputs_from_device():
+        if T:
+            buf.x[:T].copy_(xq); buf.x_sf[:T].copy_(xsf); buf.topk_idx[:T].copy_(idx); buf.topk_weights[:T].copy_(tw)
+
+    def launch():
+        mm.fp4_fp4_mega_moe(y, l1, l2, buf, activation_clamp=10.0, fast_math=True, x_global_scale=x_gs,
+                            l1_global_scale=gs1, l2_global_scale=gs2, mid_global_scale=mid_gs)
+
+    def timed(step_fn, steps, warm):
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        spans = []
+        for i in range(warm + steps):
+            flush.zero_()
+            if world > 1:
+                dist.all_reduce(align)             # aligns the ranks on the stream, as the reference's streamed replay does
+            if i >= warm:
+                starts[i - warm].record()
+            step_fn()
+            if i >= warm:
+                ends[i - warm].record()
+        torch.cuda.synchronize()
+        return [s.elapsed_time(e) * 1e3 for s, e in zip(starts, ends)]
+
+    write_inputs_from_device()
+    sampler = ClockSampler(local)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    if rank == 0:
+        sampler.start()
+    t_wall0 = time.perf_counter()
+    ks = timed(launch, args.steps, W_WARM)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t_wall = time.perf_counter() - t_wall0
+    clocks = sampler.stop() if rank == 0 else None
+    stamps = buf.phase_stamps()
+    span_us = (stamps[8] - stamps[0]) / 1e3
+    st, words = buf.device_status()
+    if st != 0:
+        raise RuntimeError(f'device status {st}: {[hex(v) for v in words[:4]]}')
+
+    def e2e_step():
+        if T:
+            buf.x[:T].copy_(h_x, non_blocking=True); buf.x_sf[:T].copy_(h_sf, non_blocking=True)
+            buf.topk_idx[:T].copy_(h_idx, non_blocking=True); buf.topk_weights[:T].copy_(h_w, non_blocking=True)
+        launch()
+        h_y.copy_(y, non_blocking=True)
+    es = timed(e2e_step, args.steps, 3)
+
+    mean_us, e2e_us = sum(ks) / len(ks), sum(es) / len(es)
+    t = torch.tensor([mean_us, e2e_us, statistics.median(ks), span_us], device='cuda', dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    mean_us, e2e_us, med_us, span_us = t.tolist()
+    if rank == 0:
+        peak, peak_src = peaks()
+        a_max = max(active)
+        alg_bytes = a_max * W.weight_bytes_per_expert(HIDDEN, INTER, fmt)
+        achieved = alg_bytes / (mean_us * 1e-6) / 1e9
+        line = {'metric': 'moe_layer_kernel_us', 'value': mean_us, 'unit': 'us', 'n_gpus': n, 'steps': args.steps,
+                'warmup': W_WARM, 'ms_per_step': mean_us / 1e3, 'higher_is_better': False, 'scaling': 'weak',
+                'vs_baseline': None, 'dtype': 'fp4 (e2m1) x fp4, fp32 accumulate', 'data': 'synthetic',
+                'config': workload_config(args, n), 'timing': 'CUDA events around each launch, mean of the timed steps, max over ranks',
+                'median_us': med_us, 'device_span_us_last_step': span_us, 'wall_s': t_wall,
+                'clocks': clocks, 'gpu_launches': args.steps,
+                'e2e': {'value': e2e_us, 'unit': 'us',
+                        'h2d_bytes_per_step': int(h_x.numel() + h_sf.numel() * 4 + h_idx.numel() * 8 + h_w.numel() * 4),
+                        'd2h_bytes_per_step': int(h_y.numel() * 2)},
+                'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
+                             'traffic': None, 'peak_source': peak_src,
+                             'algorithmic_bytes_per_launch': alg_bytes, 'active_experts_per_rank': active}}
+        if not args.no_cpu_baseline and n == 1:
+            us, cores = cpu_reference_us(T, fmt, 5)
+            line['cpu_baseline'] = {'value': us, 'unit': 'us', 'cores': cores, 'kind': 'port',
+                                    'sample': f'5 repetitions (after 1 warm-up) of the same layer ({T} token(s) x top-8 over 48 '
+                                              'experts) in the pure-torch oracle, weights dequantised inside the timed call'}
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

@@ -18,8 +18,8 @@ class MMConfig(ctypes.Structure):
 class MMLayout(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int64) for n in (
         'total_bytes', 'off_ctrl', 'off_flags', 'off_x', 'off_x_sf', 'off_topk_idx', 'off_topk_weights', 'off_rx',
-        'off_mid', 'off_mid_sf', 'off_comb', 'x_row_bytes', 'x_sf_row_bytes', 'rx_row_bytes', 'rx_cap_rows',
-        'mid_rows', 'mid_row_bytes', 'mid_sf_row_bytes')] + [('sf_vec', ctypes.c_int32), ('reserved', ctypes.c_int32)]
+        'off_mid', 'off_mid_sf', 'off_comb', 'off_red', 'off_cnt', 'x_row_bytes', 'x_sf_row_bytes', 'rx_row_bytes', 'rx_cap_rows',
+        'mid_rows', 'mid_row_bytes', 'mid_sf_row_bytes', 'cnt_per_phase')] + [('sf_vec', ctypes.c_int32), ('reserved', ctypes.c_int32)]
 
 
 class MMWeightGeometry(ctypes.Structure):
@@ -37,7 +37,7 @@ class MMLaunchArgs(ctypes.Structure):
         ('x_global_scale', ctypes.c_float), ('l1_global_scale', ctypes.c_float),
         ('l2_global_scale', ctypes.c_float), ('mid_global_scale', ctypes.c_float),
         ('timeout_ms', ctypes.c_float), ('debug_accumulators', ctypes.c_void_p),
-        ('debug_num_tasks', ctypes.c_int32), ('reserved', ctypes.c_int32)]
+        ('debug_num_tasks', ctypes.c_int32), ('reserved', ctypes.c_int32), ('debug_trace', ctypes.c_void_p)]
 
 
 class MMFrontendArgs(ctypes.Structure):

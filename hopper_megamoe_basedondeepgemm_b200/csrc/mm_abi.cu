@@ -3,6 +3,7 @@
 #include <cstdio>
 #include <cstring>
 #include <cmath>
+#include <cstdlib>
 
 #include "../../include/megamoe_b200.h"
 #include "mm_kernel.cuh"
@@ -106,6 +107,10 @@ int mm_get_layout(const mm_config_t* c, mm_layout_t* out) {
     out->off_mid = take(out->mid_rows * out->mid_row_bytes);
     out->off_mid_sf = take(out->mid_rows * out->mid_sf_row_bytes);
     out->off_comb = take(t_max * c->num_topk * c->hidden * 2);
+    const int64_t n_max = (2 * c->intermediate > c->hidden ? 2 * c->intermediate : c->hidden) / mm::kTileRows;
+    out->cnt_per_phase = (out->mid_rows / mm::kTileTokens) * n_max;
+    out->off_red = take(256 /* SMs */ * 2 /* phases */ * 2 /* slots */ * mm::kTileTokens * mm::kTileRows * 4);
+    out->off_cnt = take(2 * out->cnt_per_phase * 4);
     out->total_bytes = off;
     return MM_OK;
 }
@@ -116,6 +121,7 @@ int mm_reset(const mm_config_t* cfg, void* buffer, void* stream) {
     if (st != MM_OK) return st;
     if (buffer == nullptr) return MM_ERR_INVALID_ARGUMENT;
     MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_ctrl, 0, L.off_x - L.off_ctrl, static_cast<cudaStream_t>(stream)));
+    MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_cnt, 0, L.total_bytes - L.off_cnt, static_cast<cudaStream_t>(stream)));
     return MM_OK;
 }
 
@@ -180,15 +186,18 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.off_ctrl = L.off_ctrl; p.off_flags = L.off_flags; p.off_x = L.off_x; p.off_x_sf = L.off_x_sf;
     p.off_topk_idx = L.off_topk_idx; p.off_topk_w = L.off_topk_weights; p.off_rx = L.off_rx;
     p.off_mid = L.off_mid; p.off_mid_sf = L.off_mid_sf; p.off_comb = L.off_comb;
+    p.off_red = L.off_red; p.off_cnt = L.off_cnt; p.cnt_per_phase = static_cast<int>(L.cnt_per_phase);
     const double tmo = a->timeout_ms > 0.f ? a->timeout_ms : 2000.0;
     p.timeout_ns = static_cast<unsigned long long>(tmo * 1e6);
+    p.trace = static_cast<unsigned long long*>(a->debug_trace);
+    { const char* d = getenv("MM_DBG"); p.dbg = d ? atoi(d) : 0; }
     p.debug_acc = static_cast<float*>(a->debug_accumulators); p.debug_tasks = a->debug_accumulators ? a->debug_num_tasks : 0;
     // shared memory plan: [stages][2 x token tiles][2 x token scale chunks][output tile]
     const int kmax = p.H > p.I ? p.H : p.I;
     const int vec = sf_vec_of(cfg->act_format);
     p.act_bytes = mm::kTileTokens * kmax / 2;
     p.asf_bytes = static_cast<uint32_t>(align_up(kmax / vec, 16) / 4 * 256);     // 256 B per scale word of the K axis
-    const size_t fixed = 2 * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes;
+    const size_t fixed = 2 * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes + mm::kVtBytes;
     const size_t budget = 232448 - sizeof(mm::Ctl) - 1024 /* alignment slack */ - 768;
     int nstage = static_cast<int>((budget - fixed) / p.unit_bytes);
     if (nstage > mm::kMaxStages) nstage = mm::kMaxStages;
@@ -197,7 +206,8 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.sm_act = nstage * p.unit_bytes;
     p.sm_asf = p.sm_act + 2 * p.act_bytes;
     p.sm_otile = p.sm_asf + 2 * p.asf_bytes;
-    *smem_bytes = p.sm_otile + mm::kOtileBytes + 1024 + 256;
+    p.sm_vt = p.sm_otile + mm::kOtileBytes;
+    *smem_bytes = p.sm_vt + mm::kVtBytes + 1024 + 256;
     if (static_cast<size_t>(p.T) * p.topk * 4 > 2 * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
     return MM_OK;
 }

@@ -30,6 +30,8 @@ constexpr int kMaxLocalExperts = 64;
 constexpr int kMaxTasks = 256;          // tasks one SM can own in one launch
 constexpr int kMetaCap = 4096;          // rows one rank can receive in one launch
 constexpr int kMaxStages = 12;
+constexpr int kMetaSmemRows = 256;      // received rows whose (token, slot, weight) records are cached in shared memory
+constexpr int kMaxMTiles = kMetaCap / 16 + kMaxLocalExperts;   // 16-token tiles over all local experts
 constexpr int kTileRows = 128;          // UMMA M: weight rows per task
 constexpr int kTileTokens = 16;         // UMMA N: token rows per task
 constexpr int kUnitK = 256;             // K elements per streamed unit (one 128 B swizzle atom of packed E2M1)
@@ -38,6 +40,7 @@ constexpr int kNumEpiThreads = 128, kNumStagerThreads = 64, kNumDispatchThreads 
 constexpr uint32_t kBarEpi = 1, kBarStager = 2, kBarDispatch = 3;
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kOtileBytes = 4096;
+constexpr uint32_t kVtBytes = kTileTokens * kTileRows * 4;   // fp32 accumulators of one task, token-major
 
 // control-block offsets (bytes from off_ctrl)
 constexpr int kCtrlEpoch = 0;           // u32[256] one launch counter per SM
@@ -78,11 +81,14 @@ struct KParams {
     uint8_t* peer[kMaxRanks];
     const uint8_t* w1; const uint8_t* w2;
     __nv_bfloat16* y; int* stats;
-    long long off_ctrl, off_flags, off_x, off_x_sf, off_topk_idx, off_topk_w, off_rx, off_mid, off_mid_sf, off_comb;
-    uint32_t sm_act, sm_asf, sm_otile;   // dynamic shared memory offsets (stages start at 0)
+    long long off_ctrl, off_flags, off_x, off_x_sf, off_topk_idx, off_topk_w, off_rx, off_mid, off_mid_sf, off_comb, off_red, off_cnt;
+    int cnt_per_phase;
+    uint32_t sm_act, sm_asf, sm_otile, sm_vt;   // dynamic shared memory offsets (stages start at 0)
     uint32_t act_bytes, asf_bytes;
     unsigned long long timeout_ns;
     float* debug_acc; int debug_tasks;   // optional diagnostics: raw accumulators of SM 0's first tasks [task][token][row]
+    unsigned long long* trace;           // optional diagnostics: 16 globaltimer stamps per SM
+    int dbg;
 };
 
 struct Ctl {
@@ -91,15 +97,20 @@ struct Ctl {
     uint32_t tmem_base, epoch, abort_flag, ntasks;
     uint32_t rx_count[kMaxRanks], rx_prefix[kMaxRanks + 1];
     uint32_t exp_count[kMaxLocalExperts], mid_base[kMaxLocalExperts];
-    uint32_t tb1[kMaxLocalExperts], tb2[kMaxLocalExperts];
     uint32_t nt1, nt2, dcount, pad0;
-    uint32_t tasks[kMaxTasks];
+    uint32_t tasks[kMaxTasks];           // type << 28 | expert << 20 | token tile << 8 | weight tile
+    uint32_t tasks2[kMaxTasks];          // first unit | end unit << 8 | parts of the tile << 16 | first contributing SM << 24
+    uint32_t tasks3[kMaxTasks];          // tile index inside its phase (counter slot)
+    uint32_t sk_q[2], sk_rem[2];         // unit ranges of the phases: the first `rem` SMs own q + 1 units, the others q
+    uint32_t red_old;
     RowMeta row_meta[4][kTileTokens];
     RowMeta epi_meta[2][kTileTokens];
     uint32_t nvalid[4];
-    uint32_t rowref[kTileTokens];
-    uint32_t rowidx[kTileTokens];
+    uint32_t rowref[2][kTileTokens];
+    uint32_t rowidx[2][kTileTokens];
     float amax_x[4][kTileTokens];
+    uint32_t mtl[kMaxMTiles];            // (expert << 16 | token tile) of every 16-token tile, expert-major
+    RowMeta rx_meta[kMetaSmemRows];
     uint8_t meta_e[kMetaCap];
 };
 
@@ -131,6 +142,9 @@ struct Ctx {
         }
         return true;
     }
+    __device__ __forceinline__ void trace(int slot) const {
+        if (p.trace != nullptr) p.trace[blockIdx.x * 32 + slot] = globaltimer_ns();
+    }
     __device__ __forceinline__ void stamp(int slot) const {
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[slot] = globaltimer_ns();
     }
@@ -138,6 +152,13 @@ struct Ctx {
         return buf + p.off_rx + (static_cast<size_t>(par * p.R + src_rank) * p.cap + i) * p.rx_row_bytes;
     }
 };
+
+// unit ranges: SM g owns units [sk_lo(g), sk_lo(g + 1)) of a phase
+__device__ __forceinline__ uint32_t sk_lo(uint32_t g, uint32_t q, uint32_t rem) { return g * q + (g < rem ? g : rem); }
+__device__ __forceinline__ uint32_t sk_owner(uint32_t unit, uint32_t q, uint32_t rem) {
+    const uint32_t head = rem * (q + 1u);
+    return unit < head ? unit / (q + 1u) : rem + (unit - head) / q;
+}
 
 // position of 16 B chunk `c` of row `r` inside a 128 B-swizzled [rows x 128 B] tile
 __device__ __forceinline__ uint32_t sw128_off(uint32_t r, uint32_t c) {
@@ -158,19 +179,26 @@ __device__ __forceinline__ float sf_value(uint32_t byte) {
 __device__ void role_loader(const Ctx& cx) {
     const KParams& p = cx.p; Ctl& c = cx.c;
     uint32_t it = 0;
+    long long ld_wait = 0; const long long ld_t0 = clock64();
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, j = t & 0xFF;
         const int ntiles = type ? p.n2_tiles : p.n1_tiles, kunits = type ? p.k2_units : p.k1_units;
         const uint8_t* src = (type ? p.w2 : p.w1) + (static_cast<size_t>(e) * ntiles + j) * kunits * p.unit_bytes;
-        for (int u = 0; u < kunits; ++u, ++it) {
+        const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
+        for (int u = ub; u < ue; ++u, ++it) {
             const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
+            const long long lw0 = clock64();
             if (!cx.wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
+            ld_wait += clock64() - lw0;
+            if (it == 0) cx.trace(4);
             mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
             bulk_g2s(cx.smem + static_cast<size_t>(s) * p.unit_bytes, src + static_cast<size_t>(u) * p.unit_bytes,
                      p.unit_bytes, &c.full[s]);
         }
     }
+    cx.trace(5);
+    if (p.trace != nullptr) { p.trace[blockIdx.x * 32 + 16] = ld_wait; p.trace[blockIdx.x * 32 + 17] = clock64() - ld_t0; p.trace[blockIdx.x * 32 + 18] = it; }
 }
 
 // ============================================================================================= MMA issuer
@@ -182,25 +210,34 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     const uint32_t tm = c.tmem_base;
     const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 16
     uint32_t it = 0;
+    long long w_full = 0, w_task = 0, t_issue = 0; const long long mm_t0 = clock64();
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28;
-        const int kunits = type ? p.k2_units : p.k1_units;
+        const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         const uint32_t ab = ti & 1u, acc = ti & 1u, use = (ti >> 1) & 1u;
+        (void)type;
+        const long long tw0 = clock64();
         if (!__all_sync(0xffffffffu, cx.wait(&c.acts_full[ab], use, kErrWaitActsFull))) return;
         if (!__all_sync(0xffffffffu, cx.wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty))) return;
         tc_fence_after();
+        w_task += clock64() - tw0;
         const uint32_t act = smem_u32(cx.smem + p.sm_act + ab * p.act_bytes);
-        for (int u = 0; u < kunits; ++u, ++it) {
+        for (int u = ub; u < ue; ++u, ++it) {
             const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
+            const long long fw0 = clock64();
             if (!__all_sync(0xffffffffu, cx.wait(&c.full[s], ph, kErrWaitFull))) return;
             tc_fence_after();
-            if (lane == 0) {
+            const long long fw1 = clock64();
+            w_full += fw1 - fw0;
+            if (elect_one()) {
+                if (it == 0) cx.trace(6);
                 const uint32_t wsm = smem_u32(cx.smem + static_cast<size_t>(s) * p.unit_bytes);
                 const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u, sfb = tm + sfb_col + (it & 1u) * 16u;
                 const uint32_t asf = smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes) + static_cast<uint32_t>(u) * kPlanes * 256u;
                 #pragma unroll
                 for (uint32_t pl = 0; pl < kPlanes; ++pl) {
+                    if (p.dbg & 1) break;
                     // one scale word (4 scale bytes, K span 4 * vec) per row: lane = row % 32, column = row / 32.
                     // Token rows fill lanes 0..15 of a plane; lanes 16..31 receive the next plane's bytes and are never read.
                     utccp_32x128b_warpx4(sfa + pl * 4u, smem_desc(wsm + kUnitWBytes + pl * 512u, 128u, kLayoutNone));
@@ -209,11 +246,12 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
                 const uint32_t bsm = act + static_cast<uint32_t>(u) * (kTileTokens * 128u);
                 #pragma unroll
                 for (uint32_t ks = 0; ks < kUnitK / 64; ++ks) {
+                    if (p.dbg & 2) break;
                     const uint32_t pl = (ks * 64u) / (4u * kVec), sf_id = ((ks * 64u) % (4u * kVec)) / kVec;
                     const uint64_t adesc = smem_desc(wsm + ks * 32u, 1024u, kLayoutSw128);
                     const uint64_t bdesc = smem_desc(bsm + ks * 32u, 1024u, kLayoutSw128);
                     const uint32_t idesc = idesc_with_sf(kIdesc, sf_id, sf_id);
-                    const uint32_t accum = (u > 0 || ks > 0) ? 1u : 0u;
+                    const uint32_t accum = (u > ub || ks > 0) ? 1u : 0u;
                     if constexpr (kVec == 32)
                         umma_mxf4_block32(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
                     else
@@ -222,19 +260,25 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
                 tc_commit(&c.empty[s]);
             }
             __syncwarp();
+            t_issue += clock64() - fw1;
         }
-        if (lane == 0) {
+        if (elect_one()) {
             tc_commit(&c.tmem_full[acc]);
             tc_commit(&c.acts_empty[ab]);
+            cx.trace(7);
         }
         __syncwarp();
+    }
+    if (lane == 0 && p.trace != nullptr) {
+        p.trace[blockIdx.x * 32 + 19] = w_full; p.trace[blockIdx.x * 32 + 20] = w_task; p.trace[blockIdx.x * 32 + 21] = t_issue;
+        p.trace[blockIdx.x * 32 + 22] = clock64() - mm_t0;
     }
 }
 
 // ============================================================================================= activation stagers
 // Rows [16 mt, 16 mt + 16) of local expert e in canonical (source rank, token, slot) order -> c.rowref (flat receive
 // index). Executed by one full warp.
-__device__ __forceinline__ void find_rows(Ctl& c, uint32_t total, uint32_t e, uint32_t mt, uint32_t lane) {
+__device__ __forceinline__ void find_rows(Ctl& c, uint32_t* rowref, uint32_t total, uint32_t e, uint32_t mt, uint32_t lane) {
     const uint32_t lo = mt * kTileTokens, hi = lo + kTileTokens;
     uint32_t seen = 0;
     for (uint32_t base = 0; base < total && seen < hi; base += 32) {
@@ -242,71 +286,101 @@ __device__ __forceinline__ void find_rows(Ctl& c, uint32_t total, uint32_t e, ui
         const bool m = f < total && c.meta_e[f] == e;
         const uint32_t b = __ballot_sync(0xffffffffu, m);
         const uint32_t rank = seen + __popc(b & ((1u << lane) - 1u));
-        if (m && rank >= lo && rank < hi) c.rowref[rank - lo] = f;
+        if (m && rank >= lo && rank < hi) rowref[rank - lo] = f;
         seen += __popc(b);
     }
 }
 
-__device__ void role_stager(const Ctx& cx, uint32_t stid) {
+// Two stager warps; warp w stages the tasks with index parity w into staging buffer w, so that two consecutive tasks
+// (e.g. a split tile's share and the whole tile that follows) are fetched concurrently.
+__device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
     const KParams& p = cx.p; Ctl& c = cx.c;
-    const uint32_t lane = stid & 31u;
     const uint32_t total = c.rx_prefix[p.R];
     uint32_t* l1_done = reinterpret_cast<uint32_t*>(cx.buf + p.off_ctrl + kCtrlL1Done) + cx.par * kMaxLocalExperts;
-    for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
+    uint32_t* rowref = c.rowref[sw];
+    uint32_t* rowidx = c.rowidx[sw];
+    for (uint32_t ti = sw; ti < c.ntasks; ti += 2) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
-        const uint32_t ab = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u;
-        if (bar_red_or(kBarStager, kNumStagerThreads, !cx.wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty))) return;
-        if (stid < 32) {
-            find_rows(c, total, e, mt, lane);
-            if (lane == 0) {
-                const uint32_t left = c.exp_count[e] - mt * kTileTokens;
-                c.nvalid[ring] = left < kTileTokens ? left : kTileTokens;
-            }
-        }
-        bar_sync(kBarStager, kNumStagerThreads);
-        const uint32_t nv = c.nvalid[ring];
-        if (stid < nv) {
-            const uint32_t f = c.rowref[stid];
+        const uint32_t ab = sw, use = (ti >> 1) & 1u, ring = ti & 3u;
+        if (!__all_sync(0xffffffffu, cx.wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty))) return;
+        find_rows(c, rowref, total, e, mt, lane);
+        const uint32_t left = c.exp_count[e] - mt * kTileTokens;
+        const uint32_t nv = left < kTileTokens ? left : kTileTokens;
+        if (lane == 0) c.nvalid[ring] = nv;
+        __syncwarp();
+        if (lane < nv) {
+            const uint32_t f = rowref[lane];
             uint32_t r = 0;
             while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
             const uint32_t i = f - c.rx_prefix[r];
-            const uint4 m = ld_cg_v4(cx.rx_row(r, i) + p.rx_row_bytes - 16);
-            c.row_meta[ring][stid] = RowMeta{static_cast<int32_t>(r), static_cast<int32_t>(m.y), static_cast<int32_t>(m.z), __uint_as_float(m.w)};
-            c.rowidx[stid] = (r << 24) | i;
+            RowMeta m;
+            if (f < kMetaSmemRows) m = c.rx_meta[f];
+            else {
+                const uint4 q = ld_cg_v4(cx.rx_row(r, i) + p.rx_row_bytes - 16);
+                m = RowMeta{0, static_cast<int32_t>(q.y), static_cast<int32_t>(q.z), __uint_as_float(q.w)};
+            }
+            m.src = static_cast<int32_t>(r);
+            c.row_meta[ring][lane] = m;
+            rowidx[lane] = (r << 24) | i;
         }
-        if (type == 1u && stid == 0) {
-            const uint32_t need = static_cast<uint32_t>(p.n1_tiles) * ((c.exp_count[e] + kTileTokens - 1) / kTileTokens);
-            uint32_t spins = 0;
-            while (ld_acquire_gpu(l1_done + e) < need) {
-                if ((++spins & 0x3Fu) == 0u) {
-                    if (cx.aborted()) break;
-                    if (cx.expired()) { cx.fail(kErrWaitL1Done, e); break; }
+        bool ok = true;
+        if (type == 1u) {
+            if (lane == 0) {
+                const uint32_t need = static_cast<uint32_t>(p.n1_tiles) * ((c.exp_count[e] + kTileTokens - 1) / kTileTokens);
+                uint32_t spins = 0;
+                while (ld_acquire_gpu(l1_done + e) < need) {
+                    if ((++spins & 0x3Fu) == 0u) {
+                        if (cx.aborted()) { ok = false; break; }
+                        if (cx.expired()) { cx.fail(kErrWaitL1Done, e); ok = false; break; }
+                    }
+                }
+                if (p.trace != nullptr && p.trace[blockIdx.x * 32 + 24] == 0) cx.trace(24);
+            }
+        }
+        if (!__all_sync(0xffffffffu, ok)) return;
+        uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
+        uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
+        const uint32_t nchunk = (type ? p.I : p.H) / 32;                                   // 16 B chunks of one packed row
+        const uint32_t sfchunk = (type ? p.mid_sf_row_bytes : p.x_sf_row_bytes) / 16;      // 16 B chunks of one row's scale bytes
+        const uint32_t per_row = nchunk + sfchunk, items = nv * per_row;
+        const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
+        // all loads of a batch are in flight before the first store: one memory round trip per 4 x 32 items
+        for (uint32_t base = lane; base < items; base += 4 * 32) {
+            uint4 v[4];
+            #pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+                const uint32_t idx = base + u * 32;
+                if (idx < items) {
+                    const uint32_t n = idx / per_row, ci = idx % per_row;
+                    const uint8_t* src;
+                    if (type) src = ci < nchunk ? cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes + ci * 16u
+                                                : cx.buf + p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes + (ci - nchunk) * 16u;
+                    else src = cx.rx_row(rowidx[n] >> 24, rowidx[n] & 0xFFFFFFu) + ci * 16u;   // scale bytes follow the packed row
+                    v[u] = ld_cg_v4(src);
+                }
+            }
+            #pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+                const uint32_t idx = base + u * 32;
+                if (idx < items) {
+                    const uint32_t n = idx / per_row, ci = idx % per_row;
+                    if (ci < nchunk) {
+                        *reinterpret_cast<uint4*>(act + (ci >> 3) * (kTileTokens * 128u) + sw128_off(n, ci & 7u)) = v[u];
+                    } else {
+                        // four scale words: one 16 B slot per (scale word, token), word g of the row at slot g
+                        uint8_t* dst = asf + (ci - nchunk) * 4u * 256u + n * 16u;
+                        *reinterpret_cast<uint32_t*>(dst) = v[u].x;
+                        *reinterpret_cast<uint32_t*>(dst + 256u) = v[u].y;
+                        *reinterpret_cast<uint32_t*>(dst + 512u) = v[u].z;
+                        *reinterpret_cast<uint32_t*>(dst + 768u) = v[u].w;
+                    }
                 }
             }
         }
-        if (bar_red_or(kBarStager, kNumStagerThreads, cx.aborted())) return;
-        uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
-        uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
-        const uint32_t nchunk = (type ? p.I : p.H) / 32;                       // 16 B chunks of one packed row
-        const uint32_t sfwords = (type ? p.mid_sf_row_bytes : p.x_sf_row_bytes) / 4;   // scale words of one row
-        const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
-        for (uint32_t idx = stid; idx < nv * nchunk; idx += kNumStagerThreads) {
-            const uint32_t n = idx / nchunk, ci = idx % nchunk;
-            const uint8_t* src = type ? cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes
-                                      : cx.rx_row(c.rowidx[n] >> 24, c.rowidx[n] & 0xFFFFFFu);
-            const uint4 v = ld_cg_v4(src + ci * 16u);
-            *reinterpret_cast<uint4*>(act + (ci >> 3) * (kTileTokens * 128u) + sw128_off(n, ci & 7u)) = v;
-        }
-        for (uint32_t idx = stid; idx < nv * sfwords; idx += kNumStagerThreads) {
-            const uint32_t n = idx / sfwords, g = idx % sfwords;
-            const uint8_t* src = type ? cx.buf + p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes
-                                      : cx.rx_row(c.rowidx[n] >> 24, c.rowidx[n] & 0xFFFFFFu) + p.x_row_bytes;
-            *reinterpret_cast<uint32_t*>(asf + g * 256u + n * 16u) = ld_cg_u32(src + g * 4u);
-        }
         fence_proxy_async_smem();
-        bar_sync(kBarStager, kNumStagerThreads);
-        if (stid == 0) mbar_arrive(&c.acts_full[ab]);
+        __syncwarp();
+        if (lane == 0) { mbar_arrive(&c.acts_full[ab]); if (ti == 0) cx.trace(13); if (type == 1u) cx.trace(14); }
     }
 }
 
@@ -359,98 +433,141 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     const KParams& p = cx.p; Ctl& c = cx.c;
     const uint32_t ew = etid >> 5, lane = etid & 31u, row = etid;
     uint8_t* otile = cx.smem + p.sm_otile;
+    float* vt = reinterpret_cast<float*>(cx.smem + p.sm_vt) + row;      // this thread's accumulators: vt[n * 128], token n
     uint32_t* l1_done = reinterpret_cast<uint32_t*>(cx.buf + p.off_ctrl + kCtrlL1Done) + cx.par * kMaxLocalExperts;
     uint32_t it = 0;
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF, j = t & 0xFF;
         const uint32_t ab = ti & 1u, acc = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u;
-        bar_sync(kBarEpi, kNumEpiThreads);        // the previous task's output tile and metas are no longer in use
-        float v[kTileTokens];
-        uint32_t nv;
+        // ---- accumulators of the valid tokens -> shared memory (the loops below run over the valid tokens only)
+        bool ok;
+        uint32_t nv = 0;
         if constexpr (kUmma) {
-            if (bar_red_or(kBarEpi, kNumEpiThreads, !cx.wait(&c.tmem_full[acc], use, kErrWaitTmemFull))) return;
-            tc_fence_after();
-            if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
-            nv = c.nvalid[ring];
-            uint32_t raw[kTileTokens];
-            tmem_ld_32x32b_x16(c.tmem_base + ((ew * 32u) << 16) + acc * 16u, raw);
-            tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(&c.tmem_empty[acc]);
-            #pragma unroll
-            for (int n = 0; n < kTileTokens; ++n) v[n] = __uint_as_float(raw[n]);
-        } else {
-            if (bar_red_or(kBarEpi, kNumEpiThreads, !cx.wait(&c.acts_full[ab], use, kErrWaitActsFull))) return;
-            if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
-            nv = c.nvalid[ring];
-            #pragma unroll
-            for (int n = 0; n < kTileTokens; ++n) v[n] = 0.f;
-            const int kunits = type ? p.k2_units : p.k1_units;
-            const uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
-            const uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
-            for (int u = 0; u < kunits; ++u, ++it) {
-                const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
-                if (bar_red_or(kBarEpi, kNumEpiThreads, !cx.wait(&c.full[s], ph, kErrWaitFull))) return;
-                check_accumulate<kVec>(cx, cx.smem + static_cast<size_t>(s) * p.unit_bytes, act, asf, u, row, nv, v);
-                mbar_arrive(&c.empty[s]);
+            ok = __all_sync(0xffffffffu, cx.wait(&c.tmem_full[acc], use, kErrWaitTmemFull));
+            if (ok) {
+                tc_fence_after();
+                if (etid == 0) { if (ti == 0) cx.trace(8); cx.trace(type ? 26 : 25); }
+                if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
+                nv = c.nvalid[ring];
+                uint32_t raw[kTileTokens];
+                tmem_ld_32x32b_x16(c.tmem_base + ((ew * 32u) << 16) + acc * 16u, raw);
+                tmem_ld_wait();
+                tc_fence_before();
+                mbar_arrive(&c.tmem_empty[acc]);
+                #pragma unroll
+                for (int n = 0; n < kTileTokens; ++n) if (n < static_cast<int>(nv)) vt[n * kTileRows] = __uint_as_float(raw[n]);
             }
-            mbar_arrive(&c.acts_empty[ab]);
+        } else {
+            ok = __all_sync(0xffffffffu, cx.wait(&c.acts_full[ab], use, kErrWaitActsFull));
+            if (ok) {
+                if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
+                nv = c.nvalid[ring];
+                float v[kTileTokens];
+                #pragma unroll
+                for (int n = 0; n < kTileTokens; ++n) v[n] = 0.f;
+                const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
+                const uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
+                const uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
+                for (int u = ub; u < ue && ok; ++u, ++it) {
+                    const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
+                    ok = __all_sync(0xffffffffu, cx.wait(&c.full[s], ph, kErrWaitFull));
+                    if (ok) {
+                        check_accumulate<kVec>(cx, cx.smem + static_cast<size_t>(s) * p.unit_bytes, act, asf, u, row, nv, v);
+                        mbar_arrive(&c.empty[s]);
+                    }
+                }
+                if (ok) mbar_arrive(&c.acts_empty[ab]);
+                #pragma unroll
+                for (int n = 0; n < kTileTokens; ++n) if (n < static_cast<int>(nv)) vt[n * kTileRows] = v[n];
+            }
         }
-        bar_sync(kBarEpi, kNumEpiThreads);        // epi_meta visible
-        if (p.debug_acc != nullptr && blockIdx.x == 0 && ti < static_cast<uint32_t>(p.debug_tasks)) {
-            #pragma unroll
-            for (int n = 0; n < kTileTokens; ++n) p.debug_acc[(static_cast<size_t>(ti) * kTileTokens + n) * kTileRows + row] = v[n];
-        }
+        if (bar_red_or(kBarEpi, kNumEpiThreads, !ok)) return;        // also publishes epi_meta
+        if (p.debug_acc != nullptr && blockIdx.x == 0 && ti < static_cast<uint32_t>(p.debug_tasks))
+            for (uint32_t n = 0; n < nv; ++n) p.debug_acc[(static_cast<size_t>(ti) * kTileTokens + n) * kTileRows + row] = vt[n * kTileRows];
         const RowMeta* meta = c.epi_meta[acc];
         const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
+        const uint32_t np = (c.tasks2[ti] >> 16) & 0xFFu;
+        if (np > 1u) {
+            // this SM covered only part of the tile's K range: park the partial sums, count in, and let the last
+            // contributor add the parts in SM order (a fixed order: the result does not depend on who arrives last)
+            const uint32_t kunits = type ? p.k2_units : p.k1_units, tile = c.tasks3[ti], cfirst = c.tasks2[ti] >> 24;
+            const uint32_t q = c.sk_q[type], rem = c.sk_rem[type];
+            float* red = reinterpret_cast<float*>(cx.buf + p.off_red);
+            const uint32_t my_slot = (sk_lo(blockIdx.x, q, rem) / kunits == tile) ? 0u : 1u;
+            float* mine = red + ((static_cast<size_t>(blockIdx.x) * 2u + type) * 2u + my_slot) * (kTileTokens * kTileRows) + row;
+            for (uint32_t n = 0; n < nv; ++n) mine[n * kTileRows] = vt[n * kTileRows];
+            bar_sync(kBarEpi, kNumEpiThreads);
+            if (etid == 0) {
+                uint32_t* cnt = reinterpret_cast<uint32_t*>(cx.buf + p.off_cnt) + type * p.cnt_per_phase + tile;
+                const uint32_t old = atom_acq_rel_gpu_add(cnt, 1u);
+                if (old == np - 1u) *cnt = 0u;
+                c.red_old = old;
+            }
+            bar_sync(kBarEpi, kNumEpiThreads);
+            if (c.red_old != np - 1u) continue;
+            for (uint32_t n = 0; n < nv; ++n) {
+                float sum = 0.f;
+                for (uint32_t pc0 = 0; pc0 < np; pc0 += 4) {          // four parts' loads in flight together, added in SM order
+                    float part_v[4];
+                    #pragma unroll
+                    for (uint32_t d = 0; d < 4; ++d) {
+                        const uint32_t g = cfirst + pc0 + d;
+                        part_v[d] = 0.f;
+                        if (pc0 + d < np) {
+                            const uint32_t slot = (sk_lo(g, q, rem) / kunits == tile) ? 0u : 1u;
+                            const float* part = red + ((static_cast<size_t>(g) * 2u + type) * 2u + slot) * (kTileTokens * kTileRows);
+                            part_v[d] = __uint_as_float(ld_cg_u32(part + n * kTileRows + row));
+                        }
+                    }
+                    #pragma unroll
+                    for (uint32_t d = 0; d < 4; ++d) if (pc0 + d < np) sum += part_v[d];
+                }
+                vt[n * kTileRows] = sum;
+            }
+        }
 
         if (type == 0u) {
             // ---- L1: rows come in groups of 16 = 8 gate rows then the 8 matching up rows
             const bool is_up = (lane & 8u) != 0u;
-            float actv[kTileTokens];
-            #pragma unroll
-            for (int n = 0; n < kTileTokens; ++n) {
-                actv[n] = 0.f;
-                if (n < static_cast<int>(nv)) {
-                    const float mine = bf16_round(v[n] * p.l1_scale);
-                    const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
-                    float gate = is_up ? other : mine, up = is_up ? mine : other;
-                    if (p.has_clamp) { gate = fminf(gate, p.clamp); up = fminf(fmaxf(up, -p.clamp), p.clamp); }
-                    const float sig = p.fast_math ? __frcp_rn(1.0f + __expf(-gate)) : 1.0f / (1.0f + expf(-gate));
-                    actv[n] = gate * sig * up * meta[n].weight;
-                    if constexpr (kVec == 16) actv[n] = __fdiv_rn(actv[n], p.mid_gs);
-                    float a = fabsf(actv[n]);
-                    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
-                    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
-                    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
-                    a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
-                    if (lane == 0) c.amax_x[ew][n] = a;
-                }
+            for (uint32_t n = 0; n < nv; ++n) {
+                const float mine = bf16_round(vt[n * kTileRows] * p.l1_scale);
+                const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+                float gate = is_up ? other : mine, up = is_up ? mine : other;
+                if (p.has_clamp) { gate = fminf(gate, p.clamp); up = fminf(fmaxf(up, -p.clamp), p.clamp); }
+                const float sig = p.fast_math ? __frcp_rn(1.0f + __expf(-gate)) : 1.0f / (1.0f + expf(-gate));
+                float av = gate * sig * up * meta[n].weight;
+                if constexpr (kVec == 16) av = __fdiv_rn(av, p.mid_gs);
+                vt[n * kTileRows] = av;
+                float a = fabsf(av);
+                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+                if (lane == 0) c.amax_x[ew][n] = a;
             }
-            bar_sync(kBarEpi, kNumEpiThreads);
-            #pragma unroll
-            for (int n = 0; n < kTileTokens; ++n) {
-                if (n < static_cast<int>(nv)) {
-                    float amax = c.amax_x[ew][n];
-                    if constexpr (kVec == 32) amax = fmaxf(amax, c.amax_x[ew ^ 1u][n]);
-                    amax = fmaxf(amax, 1e-30f);
-                    uint32_t sf_byte; float scaled;
-                    if constexpr (kVec == 32) {
-                        sf_byte = ceil_pow2_exp(__fdiv_rn(amax, 6.0f));
-                        scaled = __fdiv_rn(actv[n], __uint_as_float(sf_byte << 23));
-                    } else {
-                        sf_byte = cvt_e4m3x2(__fdiv_rn(amax, 6.0f), 0.f) & 0xFFu;
-                        const float sf = e4m3_to_float(sf_byte);
-                        scaled = sf > 0.f ? __fdiv_rn(actv[n], sf) : (actv[n] == 0.f ? 0.f : copysignf(6.0f, actv[n]));
-                    }
-                    const float nb = __shfl_down_sync(0xffffffffu, scaled, 1);
-                    if (!is_up && (lane & 1u) == 0u)
-                        otile[n * 32 + ew * 8u + (lane >> 4) * 4u + ((lane & 7u) >> 1)] = static_cast<uint8_t>(cvt_e2m1x2(scaled, nb));
-                    if (lane == 0 && (kVec == 16 || (ew & 1u) == 0u)) {
-                        const uint32_t sfi = kVec == 32 ? 2u * j + (ew >> 1) : 4u * j + ew;
-                        cx.buf[p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes + sfi] = static_cast<uint8_t>(sf_byte);
-                    }
+            if constexpr (kVec == 32) bar_sync(kBarEpi, kNumEpiThreads);     // a 32-column scale block spans two warps
+            else __syncwarp();
+            for (uint32_t n = 0; n < nv; ++n) {
+                float amax = c.amax_x[ew][n];
+                if constexpr (kVec == 32) amax = fmaxf(amax, c.amax_x[ew ^ 1u][n]);
+                amax = fmaxf(amax, 1e-30f);
+                const float av = vt[n * kTileRows];
+                uint32_t sf_byte; float scaled;
+                if constexpr (kVec == 32) {
+                    sf_byte = ceil_pow2_exp(__fdiv_rn(amax, 6.0f));
+                    scaled = __fdiv_rn(av, __uint_as_float(sf_byte << 23));
+                } else {
+                    sf_byte = cvt_e4m3x2(__fdiv_rn(amax, 6.0f), 0.f) & 0xFFu;
+                    const float sf = e4m3_to_float(sf_byte);
+                    scaled = sf > 0.f ? __fdiv_rn(av, sf) : (av == 0.f ? 0.f : copysignf(6.0f, av));
+                }
+                const float nb = __shfl_down_sync(0xffffffffu, scaled, 1);
+                if (!is_up && (lane & 1u) == 0u)
+                    otile[n * 32 + ew * 8u + (lane >> 4) * 4u + ((lane & 7u) >> 1)] = static_cast<uint8_t>(cvt_e2m1x2(scaled, nb));
+                if (lane == 0 && (kVec == 16 || (ew & 1u) == 0u)) {
+                    const uint32_t sfi = kVec == 32 ? 2u * j + (ew >> 1) : 4u * j + ew;
+                    cx.buf[p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes + sfi] = static_cast<uint8_t>(sf_byte);
                 }
             }
             bar_sync(kBarEpi, kNumEpiThreads);
@@ -459,15 +576,12 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 const uint4 val = *reinterpret_cast<const uint4*>(otile + n * 32u + half * 16u);
                 st_global_v4(cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes + j * 32u + half * 16u, val);
             }
-            __threadfence();
-            bar_sync(kBarEpi, kNumEpiThreads);
-            if (etid == 0) red_release_gpu_add(l1_done + e, 1u);
+            bar_sync(kBarEpi, kNumEpiThreads);          // orders every thread's stores before the release below
+            if (etid == 0) { red_release_gpu_add(l1_done + e, 1u); cx.trace(23); }
         } else {
             // ---- L2: bf16 rows back to the token's source rank
             __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(otile);
-            #pragma unroll
-            for (int n = 0; n < kTileTokens; ++n)
-                if (n < static_cast<int>(nv)) ot[n * kTileRows + row] = __float2bfloat16_rn(v[n] * p.l2_scale);
+            for (uint32_t n = 0; n < nv; ++n) ot[n * kTileRows + row] = __float2bfloat16_rn(vt[n * kTileRows] * p.l2_scale);
             bar_sync(kBarEpi, kNumEpiThreads);
             for (uint32_t idx = etid; idx < nv * 16u; idx += kNumEpiThreads) {
                 const uint32_t n = idx >> 4, ch = idx & 15u;
@@ -477,6 +591,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 st_global_v4(dst, val);
             }
         }
+        if (etid == 0) cx.trace(9);
     }
 }
 
@@ -509,12 +624,13 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, c.epoch & 1u};
     const uint32_t epoch = c.epoch, par = cx.par;
     if (bid == 0 && tid == 0) { ctrl32[kCtrlStatus / 4 + 1] = epoch + 1u; cx.stamp(kStampEntry); }
+    if (tid == 0) cx.trace(0);
 
     // ---- dispatch: SM d pushes this rank's rows for rank d
-    if (bid < static_cast<uint32_t>(p.R) && tid >= 64) {
-        const uint32_t d = bid, dtid = tid - 64;
+    if (bid < static_cast<uint32_t>(p.R)) {
+        const uint32_t d = bid;
         uint32_t* dlist = reinterpret_cast<uint32_t*>(smem + p.sm_act);
-        if (warp == 2) {
+        if (warp == 0) {
             const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
             const uint32_t n = static_cast<uint32_t>(p.T) * p.topk;
             uint32_t cnt = 0;
@@ -528,35 +644,48 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
             }
             if (lane == 0) c.dcount = cnt;
         }
-        bar_sync(kBarDispatch, kNumDispatchThreads);
+        __syncthreads();
         const uint32_t cnt = c.dcount;
         const uint32_t nchunk = p.rx_row_bytes / 16, xq = p.x_row_bytes / 16, xs = p.x_sf_row_bytes / 16;
         uint8_t* dst_base = p.peer[d] + p.off_rx + static_cast<size_t>(par * p.R + p.rank) * p.cap * p.rx_row_bytes;
         const float* tw = reinterpret_cast<const float*>(buf + p.off_topk_w);
-        for (uint32_t idx = dtid; idx < cnt * nchunk; idx += kNumDispatchThreads) {
-            const uint32_t i = idx / nchunk, ci = idx % nchunk, ent = dlist[i];
-            const uint32_t tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
-            uint4 v;
-            if (ci < xq) v = *reinterpret_cast<const uint4*>(buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes + ci * 16u);
-            else if (ci < xq + xs) v = *reinterpret_cast<const uint4*>(buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes + (ci - xq) * 16u);
-            else v = make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot]));
-            st_global_v4(dst_base + static_cast<size_t>(i) * p.rx_row_bytes + ci * 16u, v);
+        const uint32_t items = cnt * nchunk;
+        for (uint32_t base = tid; base < items; base += 4 * kThreads) {
+            uint4 v[4];
+            #pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+                const uint32_t idx = base + u * kThreads;
+                if (idx < items) {
+                    const uint32_t i = idx / nchunk, ci = idx % nchunk, ent = dlist[i];
+                    const uint32_t tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
+                    if (ci < xq) v[u] = *reinterpret_cast<const uint4*>(buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes + ci * 16u);
+                    else if (ci < xq + xs) v[u] = *reinterpret_cast<const uint4*>(buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes + (ci - xq) * 16u);
+                    else v[u] = make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot]));
+                }
+            }
+            #pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+                const uint32_t idx = base + u * kThreads;
+                if (idx < items) st_global_v4(dst_base + static_cast<size_t>(idx / nchunk) * p.rx_row_bytes + (idx % nchunk) * 16u, v[u]);
+            }
         }
-        __threadfence_system();
-        bar_sync(kBarDispatch, kNumDispatchThreads);
-        if (dtid == 0) {
+        __syncthreads();
+        if (tid == 0) {
+            // release: the barrier orders every thread's row stores before this fence; the flag store follows it
             uint64_t* flag = reinterpret_cast<uint64_t*>(p.peer[d] + p.off_flags + kFlagDispatch) + par * kMaxRanks + p.rank;
-            st_release_sys64(flag, (static_cast<uint64_t>(epoch + 1u) << 32) | cnt);
+            fence_acq_rel_sys();
+            st_relaxed_sys64(flag, (static_cast<uint64_t>(epoch + 1u) << 32) | cnt);
         }
+        __syncthreads();
     }
-    __syncthreads();
     if (bid == 0 && tid == 0) cx.stamp(kStampDispatched);
+    if (tid == 0) cx.trace(1);
 
     // ---- the staging buffers start from zero: rows beyond a task's valid tokens only ever hold finite bytes
     for (uint32_t off = tid * 16u; off < 2u * (p.act_bytes + p.asf_bytes); off += kThreads * 16u)
         *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
 
-    // ---- receive: wait for every source rank's flag, then scan the rows' expert ids
+    // ---- receive: wait for every source rank's flag, then scan the received rows' records
     if (tid < static_cast<uint32_t>(p.R)) {
         const uint64_t* flag = reinterpret_cast<const uint64_t*>(buf + p.off_flags + kFlagDispatch) + par * kMaxRanks + tid;
         uint32_t spins = 0; uint64_t f;
@@ -569,69 +698,107 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         c.rx_count[tid] = static_cast<uint32_t>(f & 0xFFFFFFFFu);
     }
     __syncthreads();
-    if (tid == 0) {
-        uint32_t s = 0;
-        for (int r = 0; r < p.R; ++r) { c.rx_prefix[r] = s; s += c.rx_count[r]; }
-        c.rx_prefix[p.R] = s;
-        if (s > kMetaCap) cx.fail(kErrMetaCapacity, s >> 4);
-        if (bid == 0) cx.stamp(kStampFlagsSeen);
-    }
-    __syncthreads();
-    if (!cx.aborted()) {
-        const uint32_t total = c.rx_prefix[p.R];
-        for (uint32_t f = tid; f < total; f += kThreads) {
-            uint32_t r = 0;
-            while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
-            const uint32_t e = ld_cg_u32(cx.rx_row(r, f - c.rx_prefix[r]) + p.rx_row_bytes - 16) & 0xFFu;
-            c.meta_e[f] = static_cast<uint8_t>(e);
-            atomicAdd(&c.exp_count[e < kMaxLocalExperts ? e : 0], 1u);
+    uint32_t total = 0;
+    {
+        uint32_t pre[kMaxRanks + 1];
+        #pragma unroll
+        for (int r = 0; r < kMaxRanks; ++r) { pre[r] = total; if (r < p.R) total += c.rx_count[r]; }
+        pre[kMaxRanks] = total;
+        if (tid <= static_cast<uint32_t>(p.R)) c.rx_prefix[tid] = tid < static_cast<uint32_t>(p.R) ? pre[tid] : total;
+        if (tid == 0) {
+            if (total > kMetaCap) cx.fail(kErrMetaCapacity, total >> 4);
+            if (bid == 0) cx.stamp(kStampFlagsSeen);
+            cx.trace(2);
+        }
+        if (total <= kMetaCap) {
+            for (uint32_t f = tid; f < total; f += kThreads) {
+                uint32_t r = 0;
+                #pragma unroll
+                for (int q = 1; q < kMaxRanks; ++q) r += (q < p.R && f >= pre[q]) ? 1u : 0u;
+                const uint4 m = ld_cg_v4(cx.rx_row(r, f - pre[r]) + p.rx_row_bytes - 16);
+                const uint32_t e = m.x & 0xFFu;
+                c.meta_e[f] = static_cast<uint8_t>(e);
+                if (f < kMetaSmemRows) c.rx_meta[f] = RowMeta{0, static_cast<int32_t>(m.y), static_cast<int32_t>(m.z), __uint_as_float(m.w)};
+                atomicAdd(&c.exp_count[e < kMaxLocalExperts ? e : 0], 1u);
+            }
         }
     }
     __syncthreads();
 
-    // ---- schedule: L1 tiles of every active expert, then L2 tiles; SM g owns L1 task i when i % G == g. L2 tasks go
-    //      first (two rounds) to the SMs that own one L1 task fewer, then round-robin over all SMs.
+    // ---- schedule. 16-token tiles of the active experts, expert-major: M of them. Every SM derives its own task list
+    //      (L1 tasks, then L2 tasks) in closed form from the per-expert counts.
     if (warp == 0 && !cx.aborted()) {
-        if (lane == 0) {
-            uint32_t a1 = 0, a2 = 0, mb = 0;
-            for (int e = 0; e < p.e_local; ++e) {
-                const uint32_t mtiles = (c.exp_count[e] + kTileTokens - 1) / kTileTokens;
-                c.tb1[e] = a1; c.tb2[e] = a2; c.mid_base[e] = mb;
-                a1 += mtiles * p.n1_tiles; a2 += mtiles * p.n2_tiles; mb += mtiles * kTileTokens;
-            }
-            c.nt1 = a1; c.nt2 = a2;
+        const uint32_t el = p.e_local;
+        const uint32_t c0 = lane < el ? c.exp_count[lane] : 0u, c1 = lane + 32 < el ? c.exp_count[lane + 32] : 0u;
+        const uint32_t m0 = (c0 + kTileTokens - 1) / kTileTokens, m1 = (c1 + kTileTokens - 1) / kTileTokens;
+        uint32_t i0 = m0, i1 = m1;
+        #pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v0 = __shfl_up_sync(0xffffffffu, i0, o), v1 = __shfl_up_sync(0xffffffffu, i1, o);
+            if (static_cast<int>(lane) >= o) { i0 += v0; i1 += v1; }
+        }
+        const uint32_t tot0 = __shfl_sync(0xffffffffu, i0, 31), M = tot0 + __shfl_sync(0xffffffffu, i1, 31);
+        const uint32_t x0 = i0 - m0, x1 = tot0 + i1 - m1;
+        if (lane < el) c.mid_base[lane] = x0 * kTileTokens;
+        if (lane + 32 < el) c.mid_base[lane + 32] = x1 * kTileTokens;
+        if (M <= kMaxMTiles) {
+            for (uint32_t mt = 0; mt < m0; ++mt) c.mtl[x0 + mt] = (lane << 16) | mt;
+            for (uint32_t mt = 0; mt < m1; ++mt) c.mtl[x1 + mt] = ((lane + 32) << 16) | mt;
         }
         __syncwarp();
-        const uint32_t nt1 = c.nt1, r1 = nt1 % G, g2 = (r1 == 0u) ? G : G - r1;
+        // A phase has NT = M * n weight-tile tasks of k units each. The first NT % G tiles are the remainder: their units
+        // form one line of which every SM takes an equal contiguous share (split tiles, parts reduced by the last
+        // contributor); they run first. Then SM g runs the whole tiles NT % G + g, + G, ... Every SM streams the same
+        // number of units (+-1) and the epilogue that ends a phase is a whole-tile one.
         uint32_t nmine = 0;
-        for (uint32_t type = 0; type < 2; ++type) {
-            const uint32_t ntile = type ? p.n2_tiles : p.n1_tiles;
-            for (int e = 0; e < p.e_local; ++e) {
-                const uint32_t mtiles = (c.exp_count[e] + kTileTokens - 1) / kTileTokens;
-                for (uint32_t mt = 0; mt < mtiles; ++mt) {
-                    for (uint32_t j0 = 0; j0 < ntile; j0 += 32) {
-                        const uint32_t j = j0 + lane;
-                        const uint32_t gi = (type ? c.tb2[e] : c.tb1[e]) + mt * ntile + j;
-                        uint32_t owner;
-                        if (type == 0u) owner = gi % G;
-                        else if (r1 != 0u && gi < 2u * g2) owner = r1 + gi % g2;
-                        else owner = (gi - (r1 != 0u ? 2u * g2 : 0u)) % G;
-                        const bool m = j < ntile && owner == bid;
-                        const uint32_t b = __ballot_sync(0xffffffffu, m);
-                        const uint32_t pos = nmine + __popc(b & ((1u << lane) - 1u));
-                        if (m && pos < kMaxTasks) c.tasks[pos] = task_pack(type, e, mt, j);
-                        nmine += __popc(b);
+        if (M <= kMaxMTiles) {
+            for (uint32_t type = 0; type < 2; ++type) {
+                const uint32_t n = type ? p.n2_tiles : p.n1_tiles, k = type ? p.k2_units : p.k1_units;
+                const uint32_t NT = M * n, r = NT % G, U = r * k, q = U / G, rem = U % G;
+                if (lane == 0) { c.sk_q[type] = q; c.sk_rem[type] = rem; }
+                const uint32_t lo = sk_lo(bid, q, rem), hi = sk_lo(bid + 1u, q, rem);
+                if (hi > lo) {
+                    const uint32_t t_first = lo / k, t_last = (hi - 1u) / k;      // at most two tiles: the share is < k units
+                    const uint32_t t = t_first + lane;
+                    const bool m = t <= t_last;
+                    const uint32_t b = __ballot_sync(0xffffffffu, m);
+                    const uint32_t pos = nmine + __popc(b & ((1u << lane) - 1u));
+                    if (m && pos < kMaxTasks) {
+                        const uint32_t ub = (lo > t * k ? lo : t * k) - t * k, ue = (hi < (t + 1u) * k ? hi : (t + 1u) * k) - t * k;
+                        const uint32_t cfirst = sk_owner(t * k, q, rem), clast = sk_owner((t + 1u) * k - 1u, q, rem);
+                        const uint32_t ent = c.mtl[t / n];
+                        c.tasks[pos] = task_pack(type, ent >> 16, ent & 0xFFFFu, t % n);
+                        c.tasks2[pos] = ub | (ue << 8) | ((clast - cfirst + 1u) << 16) | (cfirst << 24);
+                        c.tasks3[pos] = t;
                     }
+                    nmine += __popc(b);
+                }
+                for (uint32_t i0 = 0;; i0 += 32) {
+                    const uint32_t t = r + bid + (i0 + lane) * G;
+                    const bool m = t < NT;
+                    const uint32_t b = __ballot_sync(0xffffffffu, m);
+                    if (b == 0u) break;
+                    const uint32_t pos = nmine + __popc(b & ((1u << lane) - 1u));
+                    if (m && pos < kMaxTasks) {
+                        const uint32_t ent = c.mtl[t / n];
+                        c.tasks[pos] = task_pack(type, ent >> 16, ent & 0xFFFFu, t % n);
+                        c.tasks2[pos] = (k << 8) | (1u << 16);
+                        c.tasks3[pos] = t;
+                    }
+                    nmine += __popc(b);
                 }
             }
         }
+        const uint32_t nt1 = M * p.n1_tiles, nt2 = M * p.n2_tiles;
         if (lane == 0) {
-            if (nmine > kMaxTasks) cx.fail(kErrTaskCapacity, nmine);
+            c.nt1 = nt1; c.nt2 = nt2;
+            if (M > kMaxMTiles || nmine > kMaxTasks) cx.fail(kErrTaskCapacity, nmine);
             else c.ntasks = nmine;
         }
     }
     __syncthreads();
     if (bid == 0 && tid == 0) cx.stamp(kStampScheduled);
+    if (tid == 0) { cx.trace(3); if (p.trace != nullptr) p.trace[bid * 32 + 15] = c.ntasks; }
     if (bid == 0 && tid < static_cast<uint32_t>(p.e_local) && p.stats != nullptr && !cx.aborted())
         p.stats[tid] += static_cast<int>(c.exp_count[tid]);
     // the other parity's L1 counters are idle during this launch: clear them for the next one
@@ -641,21 +808,32 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     if (!cx.aborted()) {
         if (warp == 0) { if (lane == 0) role_loader(cx); }
         else if (warp == 1) { if constexpr (kUmma) role_mma<kVec>(cx, lane); }
-        else if (warp < 4) role_stager(cx, tid - 64);
+        else if (warp < 4) role_stager(cx, warp - 2, lane);
         else role_epilogue<kVec, kUmma>(cx, tid - 128);
     }
     __syncthreads();
     if (bid == 0 && tid == 0) cx.stamp(kStampTasksDone);
+    if (tid == 0) cx.trace(10);
 
-    // ---- tell every rank that this rank's expert outputs have been written
+    // ---- combine, part 1: which routes of this thread's first (token, 16 B chunk) item are live (fetched before the wait)
+    const uint32_t chunks_per_row = p.H / 8, nitems = static_cast<uint32_t>(p.T) * chunks_per_row;
+    const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
+    const uint32_t first_item = bid + tid * G;
+    uint32_t first_mask = 0u;
+    if (first_item < nitems) {
+        const uint32_t tok = first_item / chunks_per_row;
+        for (int sl = 0; sl < p.topk; ++sl) first_mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
+    }
+
+    // ---- tell every rank that this rank's expert outputs have been written. The barrier above orders every thread's
+    //      stores before the counter's release; the last SM's fence carries all of them to system scope before the flags.
     if (tid == 0 && !cx.aborted()) {
-        __threadfence_system();
         const uint32_t old = atom_acq_rel_gpu_add(&ctrl32[kCtrlL2Done / 4], 1u);
         if (old == G - 1) {
             ctrl32[kCtrlL2Done / 4] = 0u;
-            __threadfence_system();
+            fence_acq_rel_sys();
             for (int r = 0; r < p.R; ++r)
-                st_release_sys(reinterpret_cast<uint32_t*>(p.peer[r] + p.off_flags + kFlagCombine) + par * kMaxRanks + p.rank, epoch + 1u);
+                st_relaxed_sys(reinterpret_cast<uint32_t*>(p.peer[r] + p.off_flags + kFlagCombine) + par * kMaxRanks + p.rank, epoch + 1u);
             cx.stamp(kStampL2Signalled);
         }
     }
@@ -672,20 +850,32 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     }
     __syncthreads();
     if (bid == 0 && tid == 0) cx.stamp(kStampCombineFlags);
+    if (tid == 0) cx.trace(11);
     if (!cx.aborted()) {
-        const uint32_t chunks_per_row = p.H / 8;
-        const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
-        for (uint32_t idx = bid * kThreads + tid; idx < static_cast<uint32_t>(p.T) * chunks_per_row; idx += G * kThreads) {
+        // item idx = (token, 16 B chunk); consecutive items go to different SMs so that a small batch uses the whole GPU
+        for (uint32_t idx = first_item; idx < nitems; idx += G * kThreads) {
             const uint32_t tok = idx / chunks_per_row, ch = idx % chunks_per_row;
+            uint32_t mask = first_mask;
+            if (idx != first_item) {
+                mask = 0u;
+                for (int sl = 0; sl < p.topk; ++sl) mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
+            }
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            for (int s = 0; s < p.topk; ++s) {
-                if (tk[tok * p.topk + s] < 0) continue;
-                const uint4 v = ld_cg_v4(buf + p.off_comb + ((static_cast<size_t>(tok) * p.topk + s) * p.H) * 2u + ch * 16u);
-                const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+            for (int s0 = 0; s0 < p.topk; s0 += 8) {
+                uint4 v[8];
                 #pragma unroll
-                for (int k = 0; k < 4; ++k) {
-                    acc[2 * k] += __uint_as_float(w[k] << 16);
-                    acc[2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
+                for (int u = 0; u < 8; ++u)
+                    if ((mask >> (s0 + u)) & 1u) v[u] = ld_cg_v4(buf + p.off_comb + ((static_cast<size_t>(tok) * p.topk + s0 + u) * p.H) * 2u + ch * 16u);
+                #pragma unroll
+                for (int u = 0; u < 8; ++u) {
+                    if ((mask >> (s0 + u)) & 1u) {
+                        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                        #pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            acc[2 * k] += __uint_as_float(w[k] << 16);
+                            acc[2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
+                        }
+                    }
                 }
             }
             uint4 o;
@@ -706,6 +896,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     if (warp == 1) { tc_fence_after(); tmem_dealloc(c.tmem_base, kTmemCols); }
     if (tid == 0) {
         if (bid == 0) cx.stamp(kStampExit);
+        cx.trace(12);
         atomicMax(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps) + kStampLastExit, globaltimer_ns());
     }
 }

@@ -146,7 +146,7 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
 
 
 def _launch(y, l1_weights, l2_weights, sym_buffer: SymmBuffer, stats, recipe, activation, activation_clamp, fast_math,
-            engine='umma', global_scales=(1.0, 1.0, 1.0, 1.0), timeout_ms=0.0, debug_accumulators=None):
+            engine='umma', global_scales=(1.0, 1.0, 1.0, 1.0), timeout_ms=0.0, debug_accumulators=None, debug_trace=None):
     lib = _lib.load()
     if activation != 'swiglu':
         raise RuntimeError('only the swiglu activation is supported')
@@ -174,7 +174,8 @@ def _launch(y, l1_weights, l2_weights, sym_buffer: SymmBuffer, stats, recipe, ac
         float(activation_clamp) if activation_clamp is not None else -1.0, int(bool(fast_math)),
         *[float(g) for g in global_scales], float(timeout_ms),
         debug_accumulators.data_ptr() if debug_accumulators is not None else None,
-        debug_accumulators.size(0) if debug_accumulators is not None else 0, 0)
+        debug_accumulators.size(0) if debug_accumulators is not None else 0, 0,
+        debug_trace.data_ptr() if debug_trace is not None else None)
     _lib.check(lib.mm_mega_moe_launch(ctypes.byref(b.cfg), ctypes.byref(args), torch.cuda.current_stream().cuda_stream),
                'mega_moe launch')
 
@@ -185,7 +186,7 @@ def fp4_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBu
                      activation_clamp: Optional[float] = None, fast_math: bool = True, *,
                      x_global_scale: float = 1.0, l1_global_scale: float = 1.0, l2_global_scale: float = 1.0,
                      mid_global_scale: float = 1.0, engine: str = 'umma', timeout_ms: float = 0.0,
-                     debug_accumulators: Optional[torch.Tensor] = None):
+                     debug_accumulators: Optional[torch.Tensor] = None, debug_trace: Optional[torch.Tensor] = None):
     """W4A4 MegaMoE, packed E2M1 activations and weights (`sm100_b200/mega___init__.py:244-274`).
 
     The caller has written `x`, `x_sf`, `topk_idx`, `topk_weights[:y.size(0)]` into the buffer views; the launch is
@@ -199,7 +200,7 @@ def fp4_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBu
     assert recipe[2] == sym_buffer.act_sf_vec_size
     _launch(y, l1_weights, l2_weights, sym_buffer, cumulative_local_expert_recv_stats, recipe, activation,
             activation_clamp, fast_math, engine, (x_global_scale, l1_global_scale, l2_global_scale, mid_global_scale),
-            timeout_ms, debug_accumulators)
+            timeout_ms, debug_accumulators, debug_trace)
 
 
 def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,

@@ -53,9 +53,12 @@ typedef struct mm_layout {
     int64_t off_mid;           /* [mid_rows][mid_row_bytes] requantised SwiGLU output (local) */
     int64_t off_mid_sf;        /* [mid_rows][mid_sf_row_bytes] */
     int64_t off_comb;          /* [T_max][topk][hidden] bf16 expert outputs written back by the peers */
+    int64_t off_red;           /* [256 SMs][2 phases][2][16][128] float partial sums of weight tiles split between SMs (local) */
+    int64_t off_cnt;           /* [2 phases][cnt_per_phase] uint32 contributors that have parked their part of a tile (local) */
     int64_t x_row_bytes, x_sf_row_bytes;
     int64_t rx_row_bytes, rx_cap_rows;
     int64_t mid_rows, mid_row_bytes, mid_sf_row_bytes;
+    int64_t cnt_per_phase;
     int32_t sf_vec;            /* elements per scale byte of the activation format */
     int32_t reserved;
 } mm_layout_t;
@@ -88,6 +91,7 @@ typedef struct mm_launch_args {
                                         of the first tasks of SM 0 (meaningful with num_sms = 1); NULL in production */
     int32_t debug_num_tasks;
     int32_t reserved;
+    void* debug_trace;               /* optional diagnostics: uint64 [num_sms][16] globaltimer stamps per SM; NULL in production */
 } mm_launch_args_t;
 
 /* Router frontend: bf16 router GEMM, top-k selection, token quantisation into the buffer views.

@@ -141,7 +141,7 @@ def test_bounded_wait_reports_timeout_and_buffer_recovers():
     peers = (ctypes.c_void_p * 2)(big.data_ptr(), big.data_ptr())
     y = torch.empty((0, hidden), dtype=torch.bfloat16, device=dev)
     args = _lib.MMLaunchArgs(big.data_ptr(), peers, l1[0].data_ptr(), l2[0].data_ptr(), None, 0, 0, None, -1.0, 1,
-                             1.0, 1.0, 1.0, 1.0, 30.0, None, 0, 0)
+                             1.0, 1.0, 1.0, 1.0, 30.0, None, 0, 0, None)
     assert lib.mm_mega_moe_launch(ctypes.byref(cfg2), ctypes.byref(args), torch.cuda.current_stream().cuda_stream) == 0
     words = (ctypes.c_uint32 * 16)()
     st = lib.mm_read_device_status(ctypes.byref(cfg2), big.data_ptr(), words, torch.cuda.current_stream().cuda_stream)

@@ -34,7 +34,7 @@ def test_layout_regions_are_ordered_and_sized():
     st, L = _layout()
     assert st == 0
     offs = [L.off_ctrl, L.off_flags, L.off_x, L.off_x_sf, L.off_topk_idx, L.off_topk_weights, L.off_rx, L.off_mid,
-            L.off_mid_sf, L.off_comb, L.total_bytes]
+            L.off_mid_sf, L.off_comb, L.off_red, L.off_cnt, L.total_bytes]
     assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs)
     assert L.x_row_bytes == 1536 and L.x_sf_row_bytes == 96 and L.rx_row_bytes == 1536 + 96 + 16
     assert L.rx_cap_rows == 128 * 8 and L.mid_row_bytes == 640 and L.mid_sf_row_bytes == 48

@@ -1,0 +1,85 @@
+"""Multi-rank parity worker (launched by torchrun, one process per GPU, NCCL + symmetric memory).
+
+Checks, per rank: per-expert receive counts exact, canonical slot order (through the intermediate rows), y within the
+parity tolerance of the CPU oracle that simulates all ranks in one process. Prints `MP_OK` on rank 0 when every rank passed.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+import hopper_megamoe_basedondeepgemm_b200 as mm          # noqa: E402
+from oracle import megamoe_oracle as O                     # noqa: E402
+from tests import util_moe as U                            # noqa: E402
+
+
+def main():
+    rank, world = int(os.environ['RANK']), int(os.environ['WORLD_SIZE'])
+    torch.cuda.set_device(int(os.environ.get('LOCAL_RANK', rank)))
+    dist.init_process_group('nccl', device_id=torch.device('cuda', torch.cuda.current_device()))
+    group = dist.group.WORLD
+    fmt = os.environ.get('MP_FORMAT', 'mxfp4')
+    engine = os.environ.get('MP_ENGINE', 'umma')
+    e_local, hidden, inter, topk = 8, 1024, 512, 4
+    num_experts = e_local * world
+    tokens = [(5 + 3 * r) % 7 for r in range(world)]          # ragged, some ranks may have 0 tokens
+    tokens[world - 1] = 0 if world > 2 else tokens[world - 1]
+    ok = True
+    buf = mm.get_symm_buffer_for_mega_moe(group, num_experts, 16, topk, hidden, inter, act_format=fmt)
+    weights = [O.make_expert_weights(e_local, hidden, inter, fmt, seed=50 + r, std=0.05)[0] for r in range(world)]
+    l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(weights[rank], fmt, 'cuda'))
+    for it in range(3):                                          # consecutive launches exercise both parities
+        inputs, sfbs = [], []
+        for r in range(world):
+            idx, tw = U.random_routing(tokens[r], num_experts, topk, 100 * it + r, masked_ratio=0.15)
+            _, inp, sfb = U.make_rank_inputs(tokens[r], hidden, fmt, 200 * it + r, idx, tw)
+            inputs.append(inp); sfbs.append(sfb)
+        ref = O.moe_layer_reference(inputs, weights, fmt, num_experts, clamp=10.0, keep_mid=True)
+        U.write_inputs(buf, inputs[rank], sfbs[rank])
+        y = torch.empty((tokens[rank], hidden), dtype=torch.bfloat16, device='cuda')
+        stats = torch.zeros(e_local, dtype=torch.int32, device='cuda')
+        dist.barrier()
+        mm.fp4_fp4_mega_moe(y, l1, l2, buf, cumulative_local_expert_recv_stats=stats, activation_clamp=10.0,
+                            engine=engine, timeout_ms=2000.0)
+        st, words = buf.device_status()
+        if st != 0:
+            print(f'rank {rank}: device status {st} {[hex(v) for v in words[:4]]}', flush=True)
+            ok = False
+            break
+        if not torch.equal(stats.cpu(), ref.counts[rank]):
+            print(f'rank {rank}: counts {stats.cpu().tolist()} != {ref.counts[rank].tolist()}', flush=True)
+            ok = False
+        if tokens[rank]:
+            err, cos = O.rel_rmse(y.cpu(), ref.y[rank]), O.cosine(y.cpu(), ref.y[rank])
+            if not (err <= 3e-3 and cos >= 0.9999):
+                print(f'rank {rank} it {it}: rel_rmse {err:.4e} cos {cos:.6f}', flush=True)
+                ok = False
+        # canonical slot order: intermediate rows of each local expert in (source rank, token, slot) order
+        vec = O.SF_VEC[fmt]
+        mid, mid_sf = buf.l2_acts.cpu(), buf.l2_acts_sf.cpu()
+        base = 0
+        for e, cnt in enumerate(ref.counts[rank].tolist()):
+            if cnt == 0:
+                continue
+            got = O.dequant_fp4_rows(mid[base:base + cnt], O.sf_bytes_to_float(mid_sf[base:base + cnt, :inter // vec], fmt), vec)
+            want = O.dequant_fp4_rows(ref.mid_q[rank][e], O.sf_bytes_to_float(ref.mid_sf[rank][e], fmt), vec)
+            if O.rel_rmse(got, want) > 0.05:
+                print(f'rank {rank} it {it}: expert {e} intermediate rows differ ({O.rel_rmse(got, want):.3f})', flush=True)
+                ok = False
+            base += (cnt + 15) // 16 * 16
+        torch.cuda.synchronize()
+        dist.barrier()
+    flag = torch.tensor([1 if ok else 0], device='cuda')
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    if rank == 0:
+        print('MP_OK' if int(flag) == 1 else 'MP_FAIL', flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == '__main__':
+    main()

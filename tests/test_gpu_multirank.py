@@ -1,0 +1,32 @@
+"""Expert-parallel runs over several GPUs of one node (skipped with fewer than two GPUs)."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _run(nproc, fmt, engine='umma'):
+    env = dict(os.environ, MP_FORMAT=fmt, MP_ENGINE=engine)
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={nproc}',
+           '--master-addr', '127.0.0.1', '--master-port', '29531', os.path.join(ROOT, 'tests', 'mp_worker.py')]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert 'MP_OK' in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
+
+
+@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4'])
+def test_two_ranks(fmt):
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    _run(2, fmt)
+
+
+def test_all_ranks_of_the_node():
+    n = torch.cuda.device_count()
+    if n < 4:
+        pytest.skip('needs at least four GPUs')
+    _run(8 if n >= 8 else 4, 'mxfp4')

@@ -30,38 +30,43 @@ def peaks():
 
 
 class ClockSampler:
-    QUERY = ('index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,'
-             'clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+    """Samples SM clock and throttle reasons through NVML from a thread while the timed region runs (read-only queries)."""
 
     def __init__(self, gpu_index):
-        self.gpu_index, self.proc = gpu_index, None
+        self.gpu_index, self.samples, self.reasons, self.max_mhz = gpu_index, [], set(), None
+        self._stop, self._thread = False, None
+
+    def _loop(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+            names = {'hw_slowdown': pynvml.nvmlClocksThrottleReasonHwSlowdown,
+                     'hw_thermal_slowdown': pynvml.nvmlClocksThrottleReasonHwThermalSlowdown,
+                     'sw_thermal_slowdown': pynvml.nvmlClocksThrottleReasonSwThermalSlowdown,
+                     'sw_power_cap': pynvml.nvmlClocksThrottleReasonSwPowerCap}
+            while not self._stop:
+                self.samples.append(float(pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)))
+                r = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for n, bit in names.items():
+                    if r & bit:
+                        self.reasons.add(n)
+                time.sleep(0.002)
+        except Exception as ex:                       # NVML missing: report it, never fail the benchmark
+            self.reasons.add(f'nvml unavailable: {type(ex).__name__}')
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(['nvidia-smi', f'--query-gpu={self.QUERY}', '--format=csv,noheader,nounits',
-                                          '-lms', '100', '-i', str(self.gpu_index)], stdout=subprocess.PIPE, text=True)
-        except OSError:
-            self.proc = None
+        import threading
+        self._thread = threading.Thread(target=self._loop, daemon=True)
+        self._thread.start()
 
     def stop(self):
-        if self.proc is None:
-            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
-        self.proc.terminate()
-        out, _ = self.proc.communicate(timeout=10)
-        sm, mx, reasons = [], [], set()
-        for line in out.strip().splitlines():
-            f = [v.strip() for v in line.split(',')]
-            if len(f) < 9:
-                continue
-            try:
-                sm.append(float(f[1])); mx.append(float(f[2]))
-            except ValueError:
-                continue
-            for name, v in zip(('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap'), f[5:9]):
-                if v.lower().startswith('active'):
-                    reasons.add(name)
-        return {'sm_mhz': statistics.median(sm) if sm else None, 'sm_max_mhz': max(mx) if mx else None,
-                'reasons': sorted(reasons), 'samples': len(sm)}
+        self._stop = True
+        if self._thread is not None:
+            self._thread.join(timeout=5)
+        return {'sm_mhz': statistics.median(self.samples) if self.samples else None, 'sm_max_mhz': self.max_mhz,
+                'reasons': sorted(self.reasons), 'samples': len(self.samples)}
 
 
 def cpu_reference_us(tokens, fmt, reps, threads=None):
@@ -109,7 +114,7 @@ def workload_config(args, n):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument('--gpus', type=int, default=1)
-    ap.add_argument('--steps', type=int, default=30)
+    ap.add_argument('--steps', type=int, default=200)
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--tokens-per-rank', type=int, default=1)
@@ -183,6 +188,7 @@ def main():
     torch.cuda.synchronize()
     if rank == 0:
         sampler.start()
+        time.sleep(0.05)
     t_wall0 = time.perf_counter()
     ks = timed(launch, args.steps, W_WARM)
     if world > 1:

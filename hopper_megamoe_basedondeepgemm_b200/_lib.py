@@ -47,9 +47,23 @@ class MMFrontendArgs(ctypes.Structure):
         ('x_global_scale', ctypes.c_float)]
 
 
+class MMStaticArgs(ctypes.Structure):
+    _fields_ = [
+        ('x', ctypes.c_void_p), ('x_sf', ctypes.c_void_p), ('topk_idx', ctypes.c_void_p), ('topk_weights', ctypes.c_void_p),
+        ('l1_weights', ctypes.c_void_p), ('l2_weights', ctypes.c_void_p), ('y', ctypes.c_void_p),
+        ('num_tokens', ctypes.c_int32), ('fast_math', ctypes.c_int32),
+        ('cumulative_local_expert_recv_stats', ctypes.c_void_p), ('activation_clamp', ctypes.c_float),
+        ('x_global_scale', ctypes.c_float), ('l1_global_scale', ctypes.c_float),
+        ('l2_global_scale', ctypes.c_float), ('mid_global_scale', ctypes.c_float),
+        ('timeout_ms', ctypes.c_float), ('device_status_out', ctypes.c_void_p)]
+
+
+STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
+
 EXPORTS = ('mm_get_layout', 'mm_get_weight_geometry', 'mm_get_token_alignment', 'mm_mega_moe_launch',
            'mm_frontend_launch', 'mm_frontend_workspace_bytes', 'mm_mega_moe_from_hidden_launch', 'mm_reset',
-           'mm_read_device_status', 'mm_read_phase_stamps', 'mm_status_string', 'mm_last_cuda_error')
+           'mm_read_device_status', 'mm_read_phase_stamps', 'mm_status_string', 'mm_last_cuda_error',
+           'mm_mega_moe_launch_static_scratch')
 
 _lib = None
 
@@ -72,6 +86,7 @@ def load() -> ctypes.CDLL:
     lib.mm_frontend_workspace_bytes.argtypes = [P(MMConfig)]
     lib.mm_frontend_workspace_bytes.restype = ctypes.c_int64
     lib.mm_mega_moe_from_hidden_launch.argtypes = [P(MMConfig), P(MMLaunchArgs), P(MMFrontendArgs), ctypes.c_void_p]
+    lib.mm_mega_moe_launch_static_scratch.argtypes = [P(MMConfig), P(MMStaticArgs), ctypes.c_void_p]
     lib.mm_reset.argtypes = [P(MMConfig), ctypes.c_void_p, ctypes.c_void_p]
     lib.mm_read_device_status.argtypes = [P(MMConfig), ctypes.c_void_p, P(ctypes.c_uint32), ctypes.c_void_p]
     lib.mm_read_phase_stamps.argtypes = [P(MMConfig), ctypes.c_void_p, P(ctypes.c_uint64), ctypes.c_void_p]

@@ -284,4 +284,70 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     return mm_mega_moe_launch(cfg, args, stream);
 }
 
+// ----------------------------------------------------------------------------- launch without any allocation
+// Working memory of mm_mega_moe_launch_static_scratch: one fixed array per GPU that loads this library, held until
+// the process exits. In host code the symbol below is only a handle; the device address comes from
+// cudaGetSymbolAddress (looked up once per device, with that device current) and that address is what the kernel gets.
+static __device__ __align__(256) unsigned char g_static_scratch[MM_STATIC_SCRATCH_BYTES];
+
+namespace {
+constexpr int kMaxDevices = 64;
+unsigned char* g_static_scratch_addr[kMaxDevices] = {};
+}  // namespace
+
+int mm_mega_moe_launch_static_scratch(const mm_config_t* cfg, const mm_static_args_t* a, void* stream) {
+    if (cfg == nullptr || a == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (cfg->num_ranks != 1 || cfg->rank != 0) {
+        snprintf(g_cuda_error, sizeof(g_cuda_error), "static scratch serves one rank only: peers cannot map it");
+        return MM_ERR_UNSUPPORTED;
+    }
+    mm_layout_t L;
+    int st = mm_get_layout(cfg, &L);
+    if (st != MM_OK) return st;
+    if (L.total_bytes > static_cast<int64_t>(MM_STATIC_SCRATCH_BYTES)) {
+        snprintf(g_cuda_error, sizeof(g_cuda_error), "configuration needs %lld bytes of working memory, the static scratch holds %lld",
+                 static_cast<long long>(L.total_bytes), static_cast<long long>(MM_STATIC_SCRATCH_BYTES));
+        return MM_ERR_UNSUPPORTED;
+    }
+    if (a->num_tokens < 0 || a->num_tokens > cfg->num_max_tokens_per_rank) return MM_ERR_INVALID_ARGUMENT;
+    if (a->num_tokens > 0 && (a->x == nullptr || a->x_sf == nullptr || a->topk_idx == nullptr || a->topk_weights == nullptr || a->y == nullptr))
+        return MM_ERR_INVALID_ARGUMENT;
+    int dev = 0;
+    MM_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices) return MM_ERR_UNSUPPORTED;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        // first call on this device: resolve the array's device address (do this before any stream capture)
+        void* ptr = nullptr;
+        MM_CUDA(cudaGetSymbolAddress(&ptr, g_static_scratch));
+        g_static_scratch_addr[dev] = static_cast<unsigned char*>(ptr);
+    }
+    unsigned char* scratch = g_static_scratch_addr[dev];
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the array keeps the previous call's contents: the control block, the arrival flags and the split-tile counters
+    // must start from zero (the launch counters restart with them, so every call runs as the buffer's first launch)
+    MM_CUDA(cudaMemsetAsync(scratch + L.off_ctrl, 0, L.off_x - L.off_ctrl, s));
+    MM_CUDA(cudaMemsetAsync(scratch + L.off_cnt, 0, L.total_bytes - L.off_cnt, s));
+    const size_t t = static_cast<size_t>(a->num_tokens);
+    if (t > 0) {
+        MM_CUDA(cudaMemcpyAsync(scratch + L.off_x, a->x, t * L.x_row_bytes, cudaMemcpyDeviceToDevice, s));
+        MM_CUDA(cudaMemcpyAsync(scratch + L.off_x_sf, a->x_sf, t * L.x_sf_row_bytes, cudaMemcpyDeviceToDevice, s));
+        MM_CUDA(cudaMemcpyAsync(scratch + L.off_topk_idx, a->topk_idx, t * cfg->num_topk * 8, cudaMemcpyDeviceToDevice, s));
+        MM_CUDA(cudaMemcpyAsync(scratch + L.off_topk_weights, a->topk_weights, t * cfg->num_topk * 4, cudaMemcpyDeviceToDevice, s));
+    }
+    void* peers[1] = {scratch};
+    mm_launch_args_t la;
+    memset(&la, 0, sizeof(la));
+    la.buffer = scratch; la.peer_buffers = peers;
+    la.l1_weights = a->l1_weights; la.l2_weights = a->l2_weights; la.y = a->y; la.num_tokens = a->num_tokens;
+    la.engine = MM_ENGINE_UMMA; la.cumulative_local_expert_recv_stats = a->cumulative_local_expert_recv_stats;
+    la.activation_clamp = a->activation_clamp; la.fast_math = a->fast_math;
+    la.x_global_scale = a->x_global_scale; la.l1_global_scale = a->l1_global_scale;
+    la.l2_global_scale = a->l2_global_scale; la.mid_global_scale = a->mid_global_scale; la.timeout_ms = a->timeout_ms;
+    st = mm_mega_moe_launch(cfg, &la, stream);
+    if (st != MM_OK) return st;
+    if (a->device_status_out != nullptr)
+        MM_CUDA(cudaMemcpyAsync(a->device_status_out, scratch + L.off_ctrl + mm::kCtrlStatus, 64, cudaMemcpyDeviceToDevice, s));
+    return MM_OK;
+}
+
 }  // extern "C"

@@ -130,6 +130,38 @@ int mm_read_device_status(const mm_config_t* cfg, const void* buffer, uint32_t o
 /* Synchronises `stream`, then copies the 32 phase stamps (globaltimer ns) of the last launch.
  * Replaces the `DG_SM100_PHASE_STAMPS_PTR` facility (sm100_b200/sm100_fp4_fp4_mega_moe.cuh:97-128). */
 int mm_read_phase_stamps(const mm_config_t* cfg, const void* buffer, uint64_t out_stamps[32], void* stream);
+/* Bytes of the library's built-in working memory (one array per GPU, resident from library load to process exit). */
+#define MM_STATIC_SCRATCH_BYTES (16ll * 1024 * 1024)
+
+typedef struct mm_static_args {
+    const void* x;                   /* packed tokens [num_tokens][hidden / 2] (device) */
+    const void* x_sf;                /* scale bytes [num_tokens][hidden / vec] (device) */
+    const int64_t* topk_idx;         /* [num_tokens][topk], -1 = masked slot (device) */
+    const float* topk_weights;       /* [num_tokens][topk] (device) */
+    const void* l1_weights;          /* pre-tiled streams, as in mm_launch_args */
+    const void* l2_weights;
+    void* y;                         /* bf16 [num_tokens][hidden] (device) */
+    int32_t num_tokens;
+    int32_t fast_math;
+    int32_t* cumulative_local_expert_recv_stats;   /* optional */
+    float activation_clamp;
+    float x_global_scale, l1_global_scale, l2_global_scale, mid_global_scale;
+    float timeout_ms;
+    uint32_t* device_status_out;     /* optional: 16 words (device), filled on the stream after the kernel */
+} mm_static_args_t;
+
+/* No counterpart in the reference. A single-rank launch of the layer for hosts that must not allocate device
+ * memory at call time: serving processes that carve up the GPU once at start-up and forbid cudaMalloc afterwards
+ * (it synchronises the device and can fail late), plugins running inside another framework's memory plan, real-time
+ * loops. The caller passes only inputs, weights and the output; the layer's working memory (receive pool,
+ * intermediate rows, combine rows, counters) is the library's own fixed array of MM_STATIC_SCRATCH_BYTES per GPU.
+ * The call issues memsets, device-to-device copies of the inputs and the kernel on `stream`, and calls no cudaMalloc,
+ * cudaFree or other allocating routine. Limits: num_ranks must be 1; a configuration whose mm_layout.total_bytes
+ * exceeds MM_STATIC_SCRATCH_BYTES is refused with MM_ERR_UNSUPPORTED (mm_last_cuda_error() says by how much).
+ * The first call on each device looks up the array's device address; make that call outside any stream capture.
+ * All calls on a GPU share the one array and it keeps the previous call's bytes (the call clears the parts that must
+ * start from zero), so two calls that overlap on the GPU, e.g. on different streams, race: serialise them. */
+int mm_mega_moe_launch_static_scratch(const mm_config_t* cfg, const mm_static_args_t* args, void* stream);
 const char* mm_status_string(int status);
 const char* mm_last_cuda_error(void);
 

@@ -428,3 +428,55 @@ def rel_rmse(a: torch.Tensor, b: torch.Tensor) -> float:
 def cosine(a: torch.Tensor, b: torch.Tensor) -> float:
     a, b = a.float().flatten(), b.float().flatten()
     return float((a @ b) / (a.norm() * b.norm()).clamp_min(1e-30))
+
+
+# ----------------------------------------------------------------------------- router, device reduction order
+def router_logits_device_order(x: torch.Tensor, router_w: torch.Tensor) -> torch.Tensor:
+    """bf16 router logits with the summation order of this build's frontend kernel, bit for bit.
+
+    The reference's GEMV also fixes an order (fp32 FMA chain per lane, butterfly, one bf16 rounding,
+    `sm100_b200/fe_sm100/fable_frontend_sm100.cu:610-740`); its value-level contract is the torch rule of
+    `router_reference`. Order used here: lane l of 32 owns the 8-element chunks l, l + 32, ... of K and runs one fused
+    multiply-add chain over them; the 32 partial sums are combined by a butterfly (xor 16, 8, 4, 2, 1); one rounding
+    to bf16; -0.0 becomes +0.0. The fused multiply-add is evaluated in float64 (the product of two bf16 values and
+    the sum with an fp32 accumulator are exact there) and rounded once to fp32.
+    """
+    import numpy as np
+    xf = x.float().numpy().astype(np.float64)
+    wf = router_w.float().numpy().astype(np.float64)
+    t, h = xf.shape
+    e = wf.shape[0]
+    nchunk = h // 8
+    acc = np.zeros((t, e, 32), dtype=np.float32)
+    for c0 in range(0, nchunk, 32):
+        lanes = min(32, nchunk - c0)
+        for k in range(8):
+            cols = (c0 + np.arange(lanes)) * 8 + k
+            prod = xf[:, None, cols] * wf[None, :, cols]
+            acc[:, :, :lanes] = (prod + acc[:, :, :lanes].astype(np.float64)).astype(np.float32)
+    idx = np.arange(32)
+    for o in (16, 8, 4, 2, 1):
+        acc = (acc + acc[:, :, idx ^ o]).astype(np.float32)
+    logits = torch.from_numpy(acc[:, :, 0].copy()).to(torch.bfloat16)
+    return (logits.float() + 0.0).to(torch.bfloat16)
+
+
+def route_from_logits(logits: torch.Tensor, x: torch.Tensor, topk: int = 8, score: str = 'softmax',
+                      bias: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Top-k selection and weights from given bf16 logits (the rules of `router_reference`)."""
+    lf = logits.float() + 0.0
+    if score == 'softmax':
+        order = torch.sort(lf, dim=-1, descending=True, stable=True).indices[:, :topk]
+        w = torch.softmax(torch.gather(lf, 1, order), dim=-1)
+    else:
+        sig = torch.sigmoid(lf)
+        sc = sig + (bias.float()[None, :] if bias is not None else 0.0)
+        order = torch.sort(sc, dim=-1, descending=True, stable=True).indices[:, :topk]
+        sel = torch.gather(sig, 1, order)
+        w = sel / sel.sum(dim=-1, keepdim=True)
+    idx = order.to(torch.int64)
+    zero = (x.float() == 0).all(dim=-1)
+    idx[zero] = -1
+    w = w.clone().float()
+    w[zero] = 0
+    return idx, w

@@ -1,0 +1,107 @@
+"""Router frontend on the GPU against the oracle: top-8 indices and quantised tokens bit-exact, weights to 1e-6."""
+import pytest
+import torch
+
+import hopper_megamoe_basedondeepgemm_b200 as mm
+from oracle import megamoe_oracle as O
+from tests import util_moe as U
+
+pytestmark = pytest.mark.gpu
+
+
+def _canon(packed):
+    """-0 and +0 are the same E2M1 value: clear the sign of zero nibbles before comparing bytes."""
+    u = packed.view(torch.uint8).clone()
+    lo, hi = u & 0xF, u >> 4
+    lo[lo == 8] = 0
+    hi[hi == 8] = 0
+    return lo | (hi << 4)
+
+
+def _run_frontend(fmt, tokens, num_experts, hidden, score_mode=0, bias=None, seed=0, x_gs=1.0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn((tokens, hidden), generator=g).to(torch.bfloat16)
+    if tokens > 2:
+        x[1] = 0                                                      # an all-zero token row
+    wr = (torch.randn((num_experts, hidden), generator=g) / hidden ** 0.5).to(torch.bfloat16)
+    buf = mm.get_symm_buffer_for_mega_moe(None, num_experts, max(tokens, 16), 8, hidden, 1280, act_format=fmt)
+    return x, wr, buf
+
+
+def test_frontend_384_experts_through_the_c_abi():
+    """The 8-rank routing width (384 experts) on one GPU: the frontend only needs this rank's buffer."""
+    import ctypes
+    from hopper_megamoe_basedondeepgemm_b200 import _lib
+    lib = _lib.load()
+    tokens, num_experts, hidden = 4, 384, 3072
+    g = torch.Generator().manual_seed(21)
+    x = torch.randn((tokens, hidden), generator=g).to(torch.bfloat16)
+    wr = (torch.randn((num_experts, hidden), generator=g) / hidden ** 0.5).to(torch.bfloat16)
+    cfg = _lib.MMConfig(8, 0, num_experts, 16, 8, hidden, 1280, _lib.FMT['mxfp4'], 0)
+    L = _lib.MMLayout()
+    assert lib.mm_get_layout(ctypes.byref(cfg), ctypes.byref(L)) == 0
+    buf = torch.zeros(int(L.total_bytes), dtype=torch.uint8, device='cuda')
+    ws = torch.zeros(int(lib.mm_frontend_workspace_bytes(ctypes.byref(cfg))), dtype=torch.uint8, device='cuda')
+    xd, wd = x.cuda(), wr.cuda()
+    args = _lib.MMFrontendArgs(xd.data_ptr(), wd.data_ptr(), None, tokens, 0, ws.data_ptr(), 1.0)
+    assert lib.mm_frontend_launch(ctypes.byref(cfg), buf.data_ptr(), ctypes.byref(args),
+                                  torch.cuda.current_stream().cuda_stream) == 0
+    torch.cuda.synchronize()
+    logits = O.router_logits_device_order(x, wr)
+    idx, w = O.route_from_logits(logits, x, 8)
+    got_idx = buf[L.off_topk_idx:L.off_topk_idx + tokens * 64].view(torch.int64).view(tokens, 8).cpu()
+    got_w = buf[L.off_topk_weights:L.off_topk_weights + tokens * 32].view(torch.float32).view(tokens, 8).cpu()
+    assert torch.equal(got_idx, idx)
+    assert torch.allclose(got_w, w, rtol=2e-6, atol=1e-7)
+
+
+@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4'])
+@pytest.mark.parametrize('score_mode', [0, 1])
+def test_frontend_matches_oracle(fmt, score_mode):
+    tokens, num_experts, hidden = 9, 48, 3072
+    x, wr, buf = _run_frontend(fmt, tokens, num_experts, hidden, seed=3 + score_mode)
+    bias = None
+    if score_mode == 1:
+        ranks = torch.arange(1, num_experts + 1, dtype=torch.float32)
+        bias = (0.2 / ranks ** 1.2)[torch.randperm(num_experts, generator=torch.Generator().manual_seed(5))]
+    ws = torch.zeros(mm.fe_workspace_bytes(buf), dtype=torch.uint8, device='cuda')
+    x_gs = 1.0 / 64.0 if fmt == 'nvfp4' else 1.0
+    mm.fe_forward(x.cuda(), wr.cuda(), buf, ws, score_mode=score_mode,
+                  expert_bias=bias.cuda() if bias is not None else None, x_global_scale=x_gs)
+    torch.cuda.synchronize()
+    logits_gpu = ws[256:256 + tokens * num_experts * 4].view(torch.float32).view(tokens, num_experts).cpu()
+    logits = O.router_logits_device_order(x, wr)
+    assert torch.equal(logits_gpu, logits.float())                    # bit-exact logits
+    idx, w = O.route_from_logits(logits, x, 8, 'softmax' if score_mode == 0 else 'sigmoid_bias', bias)
+    assert torch.equal(buf.topk_idx[:tokens].cpu(), idx)              # bit-exact top-8, tie rule included
+    assert torch.allclose(buf.topk_weights[:tokens].cpu(), w, rtol=2e-6, atol=1e-7)
+    assert buf.topk_idx[1].tolist() == [-1] * 8 and float(buf.topk_weights[1].abs().sum()) == 0.0
+    # value-level agreement with the reference's torch rule (fp32 matmul -> bf16): same experts for (almost) every token
+    idx_ref, _, _ = O.router_reference(x, wr, 8, 'softmax' if score_mode == 0 else 'sigmoid_bias', bias)
+    same = sum(set(a.tolist()) == set(b.tolist()) for a, b in zip(idx, idx_ref))
+    assert same >= tokens - 1
+    # quantised tokens
+    q, sf, sfb = O.quantise_tokens(x, fmt, rounding='rne', sf_rule='mul', global_scale=x_gs)
+    assert torch.equal(_canon(buf.x[:tokens].cpu()), _canon(q))
+    got_sf = buf.x_sf[:tokens].cpu().contiguous().view(torch.uint8).view(tokens, -1)
+    assert torch.equal(got_sf, sfb)
+
+
+def test_frontend_then_layer_matches_oracle():
+    fmt, tokens, e_local, hidden, inter = 'mxfp4', 6, 48, 3072, 1280
+    g = torch.Generator().manual_seed(11)
+    x = torch.randn((tokens, hidden), generator=g).to(torch.bfloat16)
+    wr = (torch.randn((e_local, hidden), generator=g) / hidden ** 0.5).to(torch.bfloat16)
+    w, _, _ = O.make_expert_weights(e_local, hidden, inter, fmt, seed=12, std=0.02)
+    buf = mm.get_symm_buffer_for_mega_moe(None, e_local, 16, 8, hidden, inter, act_format=fmt)
+    l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(w, fmt, 'cuda'))
+    ws = torch.zeros(mm.fe_workspace_bytes(buf), dtype=torch.uint8, device='cuda')
+    mm.fe_forward(x.cuda(), wr.cuda(), buf, ws)
+    y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device='cuda')
+    mm.fp4_fp4_mega_moe(y, l1, l2, buf, activation_clamp=10.0, timeout_ms=500.0)
+    assert buf.device_status()[0] == 0
+    logits = O.router_logits_device_order(x, wr)
+    idx, tw = O.route_from_logits(logits, x, 8)
+    q, sf, _ = O.quantise_tokens(x, fmt, rounding='rne', sf_rule='mul')
+    ref = O.moe_layer_reference([O.RankInput(q, sf, idx, tw)], [w], fmt, e_local, clamp=10.0)
+    assert O.rel_rmse(y.cpu(), ref.y[0]) <= 3e-3 and O.cosine(y.cpu(), ref.y[0]) >= 0.9999

@@ -277,11 +277,39 @@ int mm_frontend_launch(const mm_config_t* cfg, void* buffer, const mm_frontend_a
     return MM_OK;
 }
 
-int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_t* args, const mm_frontend_args_t* fe, void* stream) {
-    if (args == nullptr) return MM_ERR_INVALID_ARGUMENT;
-    int st = mm_frontend_launch(cfg, args->buffer, fe, stream);
+int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_t* a, const mm_frontend_args_t* fe, void* stream) {
+    mm::KParams p;
+    int grid = 0;
+    size_t smem_bytes = 0;
+    int st = fill_params(cfg, a, &p, &grid, &smem_bytes);
     if (st != MM_OK) return st;
-    return mm_mega_moe_launch(cfg, args, stream);
+    if (fe == nullptr || fe->hidden_states == nullptr || fe->router_weight == nullptr || fe->workspace == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (fe->num_tokens != a->num_tokens) return MM_ERR_INVALID_ARGUMENT;
+    if (cfg->num_topk != 8 || cfg->num_experts > 1024) return MM_ERR_UNSUPPORTED;
+    if (fe->score_mode == 1 && fe->expert_bias == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (static_cast<size_t>(cfg->num_experts) * 4 * (mm::kThreads / 32) > 2 * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
+    mm_layout_t L;
+    mm_get_layout(cfg, &L);
+    uint8_t* b = static_cast<uint8_t*>(a->buffer);
+    mm::FeParams& q = p.fe;
+    q.hidden = static_cast<const __nv_bfloat16*>(fe->hidden_states);
+    q.router_w = static_cast<const __nv_bfloat16*>(fe->router_weight);
+    q.bias = fe->expert_bias;
+    q.logits = reinterpret_cast<float*>(static_cast<uint8_t*>(fe->workspace) + 256);
+    q.arrive = nullptr;
+    q.T = fe->num_tokens; q.H = cfg->hidden; q.E = cfg->num_experts; q.topk = cfg->num_topk;
+    q.score_mode = fe->score_mode; q.fmt = cfg->act_format;
+    q.x_gs = fe->x_global_scale > 0.f ? fe->x_global_scale : 1.f;
+    q.x = b + L.off_x; q.x_sf = b + L.off_x_sf;
+    q.topk_idx = reinterpret_cast<long long*>(b + L.off_topk_idx);
+    q.topk_w = reinterpret_cast<float*>(b + L.off_topk_weights);
+    q.x_row_bytes = static_cast<int>(L.x_row_bytes); q.x_sf_row_bytes = static_cast<int>(L.x_sf_row_bytes);
+    p.fe_enabled = fe->num_tokens > 0 ? 1 : 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool umma = a->engine == MM_ENGINE_UMMA;
+    if (cfg->act_format == MM_FMT_MXFP4)
+        return umma ? launch_variant<32, true>(p, grid, smem_bytes, s) : launch_variant<32, false>(p, grid, smem_bytes, s);
+    return umma ? launch_variant<16, true>(p, grid, smem_bytes, s) : launch_variant<16, false>(p, grid, smem_bytes, s);
 }
 
 // ----------------------------------------------------------------------------- launch without any allocation

@@ -26,10 +26,8 @@ __device__ __forceinline__ void unpack_bf16x8(const uint4& v, float (&f)[8]) {
     for (int i = 0; i < 4; ++i) { f[2 * i] = __uint_as_float(w[i] << 16); f[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u); }
 }
 
-// one warp per (expert, block of up to 4 tokens)
-__global__ void __launch_bounds__(256) frontend_logits_kernel(const FeParams q) {
-    const uint32_t lane = threadIdx.x & 31u;
-    const uint32_t warp = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), nwarps = gridDim.x * (blockDim.x >> 5);
+// one warp per (expert, block of up to 4 tokens); `warp` of `nwarps` warps cooperate
+__device__ __forceinline__ void fe_logits_items(const FeParams& q, uint32_t warp, uint32_t nwarps, uint32_t lane) {
     const uint32_t tblocks = (q.T + 3) / 4, nchunk = q.H / 8;
     for (uint32_t item = warp; item < static_cast<uint32_t>(q.E) * tblocks; item += nwarps) {
         const uint32_t e = item % q.E, t0 = (item / q.E) * 4;
@@ -58,6 +56,10 @@ __global__ void __launch_bounds__(256) frontend_logits_kernel(const FeParams q) 
     }
 }
 
+__global__ void __launch_bounds__(256) frontend_logits_kernel(const FeParams q) {
+    fe_logits_items(q, blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), gridDim.x * (blockDim.x >> 5), threadIdx.x & 31u);
+}
+
 __device__ __forceinline__ uint32_t orderable_f32(float v) {
     const uint32_t b = __float_as_uint(v);
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
@@ -71,41 +73,26 @@ __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v)
     return v;
 }
 
-// one warp per token: top-8 + weights, then the token's quantisation
-__global__ void __launch_bounds__(128) frontend_select_quant_kernel(const FeParams q) {
-    extern __shared__ float fe_scores[];                 // [4 warps][E]
-    const uint32_t lane = threadIdx.x & 31u, w = threadIdx.x >> 5;
-    const uint32_t t = blockIdx.x * 4 + w;
-    if (t >= static_cast<uint32_t>(q.T)) return;
-    float* sc = fe_scores + w * q.E;
-    const float* lg = q.logits + static_cast<size_t>(t) * q.E;
-    for (int e = lane; e < q.E; e += 32) {
-        const float v = lg[e];
-        sc[e] = q.score_mode == 1 ? (1.0f / (1.0f + expf(-v))) + q.bias[e] : v;
-    }
-    __syncwarp();
-
-    // ---- quantise the token (and learn whether the row is all zero)
-    const int vec = q.fmt == 1 ? 16 : 32, lanes_per_group = vec / 8;
-    const __nv_bfloat16* xrow = q.hidden + static_cast<size_t>(t) * q.H;
-    uint8_t* qrow = q.x + static_cast<size_t>(t) * q.x_row_bytes;
-    uint8_t* sfrow = q.x_sf + static_cast<size_t>(t) * q.x_sf_row_bytes;
+// One warp quantises token row `xrow` (bf16 [H]) to packed E2M1 + scale bytes; returns whether any element is non-zero.
+__device__ __forceinline__ bool fe_quant_token(const __nv_bfloat16* xrow, int H, int fmt, float x_gs,
+                                               uint8_t* qrow, uint8_t* sfrow, uint32_t lane) {
+    const int vec = fmt == 1 ? 16 : 32, lanes_per_group = vec / 8;
     bool nonzero = false;
-    for (int k0 = lane * 8; k0 < q.H; k0 += 256) {
+    for (int k0 = lane * 8; k0 < H; k0 += 256) {
         float x[8];
         unpack_bf16x8(*reinterpret_cast<const uint4*>(xrow + k0), x);
         float local = 0.f;
         #pragma unroll
         for (int j = 0; j < 8; ++j) {
             nonzero |= x[j] != 0.f;
-            if (q.fmt == 1) x[j] = __fdiv_rn(x[j], q.x_gs);
+            if (fmt == 1) x[j] = __fdiv_rn(x[j], x_gs);
             local = fmaxf(local, fabsf(x[j]));
         }
         local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, 1));
         if (lanes_per_group == 4) local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, 2));
         const float v = fmaxf(local, 1.0e-30f) * (1.0f / 6.0f);
         uint32_t sf_byte; float sf;
-        if (q.fmt == 1) {
+        if (fmt == 1) {
             sf_byte = cvt_e4m3x2(v, 0.f) & 0xFFu;
             if (sf_byte == 0u) sf_byte = 1u;
             sf = e4m3_to_float(sf_byte);
@@ -120,9 +107,29 @@ __global__ void __launch_bounds__(128) frontend_select_quant_kernel(const FePara
         for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(x[2 * j] * inv, x[2 * j + 1] * inv) << (8 * j);
         *reinterpret_cast<uint32_t*>(qrow + k0 / 2) = packed;
     }
-    nonzero = __any_sync(0xffffffffu, nonzero);
+    return __any_sync(0xffffffffu, nonzero);
+}
 
-    // ---- top-8: eight rounds of a warp-wide maximum over 64-bit keys (score, then smaller expert id)
+// One warp: is any element of the bf16 row non-zero?
+__device__ __forceinline__ bool fe_row_nonzero(const __nv_bfloat16* xrow, int H, uint32_t lane) {
+    bool nz = false;
+    for (int k0 = lane * 8; k0 < H; k0 += 256) {
+        const uint4 v = *reinterpret_cast<const uint4*>(xrow + k0);
+        nz |= ((v.x | v.y | v.z | v.w) & 0x7FFF7FFFu) != 0u;
+    }
+    return __any_sync(0xffffffffu, nz);
+}
+
+// One warp selects the top-8 experts of token t from its logits (read with L2-level loads: other SMs wrote them) and
+// writes topk_idx / topk_weights. `sc` is a per-warp scratch of E floats in shared memory.
+__device__ __forceinline__ void fe_select_token(const FeParams& q, uint32_t t, float* sc, bool nonzero, uint32_t lane) {
+    const float* lg = q.logits + static_cast<size_t>(t) * q.E;
+    for (int e = lane; e < q.E; e += 32) {
+        const float v = __uint_as_float(ld_cg_u32(lg + e));
+        sc[e] = q.score_mode == 1 ? (1.0f / (1.0f + expf(-v))) + q.bias[e] : v;
+    }
+    __syncwarp();
+    // eight rounds of a warp-wide maximum over 64-bit keys (score, then smaller expert id)
     unsigned long long chosen = 0ull;
     for (int k = 0; k < 8; ++k) {
         unsigned long long best = 0ull;
@@ -139,7 +146,7 @@ __global__ void __launch_bounds__(128) frontend_select_quant_kernel(const FePara
         __syncwarp();
     }
     const int e_sel = static_cast<int>(chosen);
-    const float v_sel = lane < 8 ? lg[e_sel] : -INFINITY;
+    const float v_sel = lane < 8 ? __uint_as_float(ld_cg_u32(lg + e_sel)) : -INFINITY;
     float wgt;
     if (q.score_mode == 1) {
         const float s = lane < 8 ? 1.0f / (1.0f + expf(-v_sel)) : 0.f;
@@ -161,6 +168,17 @@ __global__ void __launch_bounds__(128) frontend_select_quant_kernel(const FePara
         q.topk_idx[static_cast<size_t>(t) * 8 + lane] = nonzero ? e_sel : -1;
         q.topk_w[static_cast<size_t>(t) * 8 + lane] = nonzero ? wgt : 0.f;
     }
+}
+
+// one warp per token: the token's quantisation, then top-8 + weights
+__global__ void __launch_bounds__(128) frontend_select_quant_kernel(const FeParams q) {
+    extern __shared__ float fe_scores[];                 // [4 warps][E]
+    const uint32_t lane = threadIdx.x & 31u, w = threadIdx.x >> 5;
+    const uint32_t t = blockIdx.x * 4 + w;
+    if (t >= static_cast<uint32_t>(q.T)) return;
+    const bool nonzero = fe_quant_token(q.hidden + static_cast<size_t>(t) * q.H, q.H, q.fmt, q.x_gs,
+                                        q.x + static_cast<size_t>(t) * q.x_row_bytes, q.x_sf + static_cast<size_t>(t) * q.x_sf_row_bytes, lane);
+    fe_select_token(q, t, fe_scores + w * q.E, nonzero, lane);
 }
 
 }  // namespace mm

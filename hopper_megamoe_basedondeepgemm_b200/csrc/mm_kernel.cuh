@@ -21,6 +21,7 @@
 #include <cuda_fp16.h>
 #include <cstdint>
 #include "mm_ptx.cuh"
+#include "mm_frontend.cuh"
 
 namespace mm {
 
@@ -89,6 +90,7 @@ struct KParams {
     float* debug_acc; int debug_tasks;   // optional diagnostics: raw accumulators of SM 0's first tasks [task][token][row]
     unsigned long long* trace;           // optional diagnostics: 16 globaltimer stamps per SM
     int dbg;
+    FeParams fe; int fe_enabled;         // router frontend run at the head of the same launch (optional)
 };
 
 struct Ctl {
@@ -143,7 +145,7 @@ struct Ctx {
         return true;
     }
     __device__ __forceinline__ void trace(int slot) const {
-        if (p.trace != nullptr) p.trace[blockIdx.x * 32 + slot] = globaltimer_ns();
+        if (p.trace != nullptr) p.trace[blockIdx.x * 96 + slot] = globaltimer_ns();
     }
     __device__ __forceinline__ void stamp(int slot) const {
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[slot] = globaltimer_ns();
@@ -198,7 +200,7 @@ __device__ void role_loader(const Ctx& cx) {
         }
     }
     cx.trace(5);
-    if (p.trace != nullptr) { p.trace[blockIdx.x * 32 + 16] = ld_wait; p.trace[blockIdx.x * 32 + 17] = clock64() - ld_t0; p.trace[blockIdx.x * 32 + 18] = it; }
+    if (p.trace != nullptr) { p.trace[blockIdx.x * 96 + 16] = ld_wait; p.trace[blockIdx.x * 96 + 17] = clock64() - ld_t0; p.trace[blockIdx.x * 96 + 18] = it; }
 }
 
 // ============================================================================================= MMA issuer
@@ -232,6 +234,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
             w_full += fw1 - fw0;
             if (elect_one()) {
                 if (it == 0) cx.trace(6);
+                if (p.trace != nullptr && it < 30) p.trace[blockIdx.x * 96 + 32 + 2 * it] = globaltimer_ns();
                 const uint32_t wsm = smem_u32(cx.smem + static_cast<size_t>(s) * p.unit_bytes);
                 const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u, sfb = tm + sfb_col + (it & 1u) * 16u;
                 const uint32_t asf = smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes) + static_cast<uint32_t>(u) * kPlanes * 256u;
@@ -258,6 +261,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
                         umma_nvf4_block16(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
                 }
                 tc_commit(&c.empty[s]);
+                if (p.trace != nullptr && it < 30) p.trace[blockIdx.x * 96 + 33 + 2 * it] = globaltimer_ns();
             }
             __syncwarp();
             t_issue += clock64() - fw1;
@@ -270,8 +274,8 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         __syncwarp();
     }
     if (lane == 0 && p.trace != nullptr) {
-        p.trace[blockIdx.x * 32 + 19] = w_full; p.trace[blockIdx.x * 32 + 20] = w_task; p.trace[blockIdx.x * 32 + 21] = t_issue;
-        p.trace[blockIdx.x * 32 + 22] = clock64() - mm_t0;
+        p.trace[blockIdx.x * 96 + 19] = w_full; p.trace[blockIdx.x * 96 + 20] = w_task; p.trace[blockIdx.x * 96 + 21] = t_issue;
+        p.trace[blockIdx.x * 96 + 22] = clock64() - mm_t0;
     }
 }
 
@@ -335,7 +339,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                         if (cx.expired()) { cx.fail(kErrWaitL1Done, e); ok = false; break; }
                     }
                 }
-                if (p.trace != nullptr && p.trace[blockIdx.x * 32 + 24] == 0) cx.trace(24);
+                if (p.trace != nullptr && p.trace[blockIdx.x * 96 + 24] == 0) cx.trace(24);
             }
         }
         if (!__all_sync(0xffffffffu, ok)) return;
@@ -626,6 +630,33 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     if (bid == 0 && tid == 0) { ctrl32[kCtrlStatus / 4 + 1] = epoch + 1u; cx.stamp(kStampEntry); }
     if (tid == 0) cx.trace(0);
 
+    // ---- router frontend (optional): all SMs compute logits; the dispatching SMs select the top-8 of every token
+    if (p.fe_enabled) {
+        fe_logits_items(p.fe, bid * (kThreads / 32) + warp, G * (kThreads / 32), lane);
+        __syncthreads();
+        uint32_t* fe_arrive = ctrl32 + kCtrlFeArrive / 4;
+        if (tid == 0) red_release_gpu_add(fe_arrive, 1u);
+        if (bid < static_cast<uint32_t>(p.R)) {
+            if (tid == 0) {
+                uint32_t spins = 0;
+                while (ld_acquire_gpu(fe_arrive) < G * (epoch + 1u)) {
+                    if ((++spins & 0x3Fu) == 0u) {
+                        if (cx.aborted()) break;
+                        if (cx.expired()) { cx.fail(kErrWaitFrontend); break; }
+                    }
+                }
+            }
+            __syncthreads();
+            float* sc = reinterpret_cast<float*>(smem + p.sm_act) + warp * p.fe.E;
+            for (uint32_t t = warp; t < static_cast<uint32_t>(p.T); t += kThreads / 32) {
+                const bool nz = fe_row_nonzero(p.fe.hidden + static_cast<size_t>(t) * p.H, p.H, lane);
+                fe_select_token(p.fe, t, sc, nz, lane);
+            }
+            __syncthreads();
+        }
+        if (bid == 0 && tid == 0) cx.stamp(kStampFrontend);
+    }
+
     // ---- dispatch: SM d pushes this rank's rows for rank d
     if (bid < static_cast<uint32_t>(p.R)) {
         const uint32_t d = bid;
@@ -646,6 +677,16 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         }
         __syncthreads();
         const uint32_t cnt = c.dcount;
+        if (p.fe_enabled) {
+            // quantise the tokens this SM is about to send into the x / x_sf views (the same bytes whichever SM writes them)
+            for (uint32_t i = warp; i < cnt; i += kThreads / 32) {
+                const uint32_t tok = dlist[i] >> 16;
+                fe_quant_token(p.fe.hidden + static_cast<size_t>(tok) * p.H, p.H, kVec == 32 ? 0 : 1, p.fe.x_gs,
+                               buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes,
+                               buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes, lane);
+            }
+            __syncthreads();
+        }
         const uint32_t nchunk = p.rx_row_bytes / 16, xq = p.x_row_bytes / 16, xs = p.x_sf_row_bytes / 16;
         uint8_t* dst_base = p.peer[d] + p.off_rx + static_cast<size_t>(par * p.R + p.rank) * p.cap * p.rx_row_bytes;
         const float* tw = reinterpret_cast<const float*>(buf + p.off_topk_w);
@@ -798,7 +839,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     }
     __syncthreads();
     if (bid == 0 && tid == 0) cx.stamp(kStampScheduled);
-    if (tid == 0) { cx.trace(3); if (p.trace != nullptr) p.trace[bid * 32 + 15] = c.ntasks; }
+    if (tid == 0) { cx.trace(3); if (p.trace != nullptr) p.trace[bid * 96 + 15] = c.ntasks; }
     if (bid == 0 && tid < static_cast<uint32_t>(p.e_local) && p.stats != nullptr && !cx.aborted())
         p.stats[tid] += static_cast<int>(c.exp_count[tid]);
     // the other parity's L1 counters are idle during this launch: clear them for the next one

@@ -211,6 +211,40 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBu
     raise RuntimeError('fp8_fp4_mega_moe: the FP8-activation variant is not built yet')
 
 
+def mega_moe_from_hidden(y: torch.Tensor, hidden: torch.Tensor, router_weight: torch.Tensor, l1_weights, l2_weights,
+                         sym_buffer: SymmBuffer, workspace: torch.Tensor,
+                         cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
+                         activation_clamp: Optional[float] = None, fast_math: bool = True, score_mode: int = 0,
+                         expert_bias: Optional[torch.Tensor] = None, x_global_scale: float = 1.0,
+                         l1_global_scale: float = 1.0, l2_global_scale: float = 1.0, mid_global_scale: float = 1.0,
+                         engine: str = 'umma', timeout_ms: float = 0.0):
+    """The whole layer from bf16 hidden states in ONE persistent kernel: router GEMM, top-8, routing weights and token
+    quantisation run at the head of the launch, then dispatch, both grouped GEMMs and the combine. The reference runs
+    its frontend as a separate kernel in the same CUDA graph (`sm100_b200/fe_sm100/test_e2e_b200.py:204-231`). The
+    routing and the quantised tokens still land in `sym_buffer.topk_idx / topk_weights / x / x_sf`."""
+    lib = _lib.load()
+    b = sym_buffer
+    if hidden.dtype != torch.bfloat16 or router_weight.dtype != torch.bfloat16 or not hidden.is_contiguous():
+        raise RuntimeError('hidden states and router weight must be contiguous bf16')
+    if hidden.size(0) != y.size(0) or hidden.size(1) != b.hidden or tuple(router_weight.shape) != (b.num_experts, b.hidden):
+        raise RuntimeError('router shapes do not match the buffer')
+    if workspace.numel() * workspace.element_size() < fe_workspace_bytes(b):
+        raise RuntimeError('frontend workspace too small')
+    (w1, _), (w2, _) = l1_weights, l2_weights
+    stats = cumulative_local_expert_recv_stats
+    args = _lib.MMLaunchArgs(
+        b.buffer.data_ptr(), b._peer_array, w1.data_ptr(), w2.data_ptr(), y.data_ptr() if y.numel() else None,
+        y.size(0), _lib.ENGINE[engine], stats.data_ptr() if stats is not None else None,
+        float(activation_clamp) if activation_clamp is not None else -1.0, int(bool(fast_math)),
+        float(x_global_scale), float(l1_global_scale), float(l2_global_scale), float(mid_global_scale),
+        float(timeout_ms), None, 0, 0, None)
+    fe = _lib.MMFrontendArgs(hidden.data_ptr(), router_weight.data_ptr(),
+                             expert_bias.data_ptr() if expert_bias is not None else None,
+                             hidden.size(0), score_mode, workspace.data_ptr(), float(x_global_scale))
+    _lib.check(lib.mm_mega_moe_from_hidden_launch(ctypes.byref(b.cfg), ctypes.byref(args), ctypes.byref(fe),
+                                                  torch.cuda.current_stream().cuda_stream), 'mega_moe_from_hidden')
+
+
 def fe_workspace_bytes(sym_buffer: SymmBuffer) -> int:
     return int(_lib.load().mm_frontend_workspace_bytes(ctypes.byref(sym_buffer.cfg)))
 

@@ -105,3 +105,34 @@ def test_frontend_then_layer_matches_oracle():
     q, sf, _ = O.quantise_tokens(x, fmt, rounding='rne', sf_rule='mul')
     ref = O.moe_layer_reference([O.RankInput(q, sf, idx, tw)], [w], fmt, e_local, clamp=10.0)
     assert O.rel_rmse(y.cpu(), ref.y[0]) <= 3e-3 and O.cosine(y.cpu(), ref.y[0]) >= 0.9999
+
+
+@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4'])
+def test_layer_from_hidden_states_in_one_kernel(fmt):
+    """Router, top-8, quantisation, dispatch, both GEMMs and the combine in a single launch."""
+    tokens, e_local, hidden, inter = 7, 48, 3072, 1280
+    g = torch.Generator().manual_seed(31)
+    x = torch.randn((tokens, hidden), generator=g).to(torch.bfloat16)
+    x[2] = 0
+    wr = (torch.randn((e_local, hidden), generator=g) / hidden ** 0.5).to(torch.bfloat16)
+    w, gs1, gs2 = O.make_expert_weights(e_local, hidden, inter, fmt, seed=32, std=0.02)
+    x_gs, mid_gs = (1.0 / 64.0, 1.0 / 512.0) if fmt == 'nvfp4' else (1.0, 1.0)
+    buf = mm.get_symm_buffer_for_mega_moe(None, e_local, 16, 8, hidden, inter, act_format=fmt)
+    l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(w, fmt, 'cuda'))
+    ws = torch.zeros(mm.fe_workspace_bytes(buf), dtype=torch.uint8, device='cuda')
+    y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device='cuda')
+    for _ in range(2):                                           # second launch: other parity, arrival counter carries on
+        mm.mega_moe_from_hidden(y, x.cuda(), wr.cuda(), l1, l2, buf, ws, activation_clamp=10.0, x_global_scale=x_gs,
+                                l1_global_scale=gs1, l2_global_scale=gs2, mid_global_scale=mid_gs, timeout_ms=500.0)
+        st, words = buf.device_status()
+        assert st == 0, [hex(v) for v in words[:4]]
+    logits = O.router_logits_device_order(x, wr)
+    idx, tw = O.route_from_logits(logits, x, 8)
+    assert torch.equal(buf.topk_idx[:tokens].cpu(), idx)
+    q, sf, sfb = O.quantise_tokens(x, fmt, rounding='rne', sf_rule='mul', global_scale=x_gs)
+    routed = (idx >= 0).any(dim=1)
+    assert torch.equal(_canon(buf.x[:tokens].cpu())[routed], _canon(q)[routed])
+    ref = O.moe_layer_reference([O.RankInput(q, sf, idx, tw)], [w], fmt, e_local, clamp=10.0, x_global_scale=x_gs,
+                                w1_global_scale=gs1, w2_global_scale=gs2, mid_global_scale=mid_gs)
+    assert O.rel_rmse(y.cpu(), ref.y[0]) <= 3e-3 and O.cosine(y.cpu(), ref.y[0]) >= 0.9999
+    assert float(y[2].float().abs().sum()) == 0.0                # the all-zero token routes nowhere

@@ -108,7 +108,7 @@ def workload_config(args, n):
     return {'workload': f'EP{n} W4A4 {args.format.upper()} MegaMoE layer, E={E_LOCAL * n} ({E_LOCAL}/rank), H={HIDDEN}, '
                         f'I={INTER}, top-{TOPK}, forced-balanced routing, {args.tokens_per_rank} token(s) per rank '
                         f'(global M={args.tokens_per_rank * n}), weights ~N(0,0.02)',
-            'l2': 'flushed by a 256 MiB write before every timed step', 'parallelism': f'ep{n}'}
+            'l2': 'flushed by a 256 MiB write before every timed step; then the inputs are copied into the buffer views', 'parallelism': f'ep{n}'}
 
 
 def main():
@@ -165,15 +165,17 @@ def main():
         mm.fp4_fp4_mega_moe(y, l1, l2, buf, activation_clamp=10.0, fast_math=True, x_global_scale=x_gs,
                             l1_global_scale=gs1, l2_global_scale=gs2, mid_global_scale=mid_gs)
 
-    def timed(step_fn, steps, warm):
+    def timed(step_fn, steps, warm, e2e=False):
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
         for _ in range(20):                        # let the host run ahead of the GPU: events then bracket the kernel,
             flush.zero_()                          # not the host's launch latency
         for i in range(warm + steps):
             flush.zero_()
-            if world > 1:
-                dist.all_reduce(align)             # aligns the ranks on the stream, as the reference's streamed replay does
+            if not e2e:
+                write_inputs_from_device()         # flush -> input copy -> rank alignment -> kernel, as the reference's
+            if world > 1:                          # streamed replay does (sm100_b200/test_mega_moe.py:351-357)
+                dist.all_reduce(align)
             if i >= warm:
                 starts[i - warm].record()
             step_fn()
@@ -201,12 +203,15 @@ def main():
     spans = []
     for _ in range(10):
         flush.zero_()
+        write_inputs_from_device()
         if world > 1:
             dist.all_reduce(align)
         launch()
         stamps = buf.phase_stamps()
         spans.append((stamps[8] - stamps[0]) / 1e3)
     span_us = statistics.median(spans)
+    phase_names = ['entry', 'dispatched', 'dispatch_flags_seen', 'scheduled', 'tasks_done', 'l2_signalled', 'combine_flags_seen', 'exit', 'last_sm_exit']
+    phases = {n: round((stamps[i] - stamps[0]) / 1e3, 2) for i, n in enumerate(phase_names) if stamps[i]}
     st, words = buf.device_status()
     if st != 0:
         raise RuntimeError(f'device status {st}: {[hex(v) for v in words[:4]]}')
@@ -217,7 +222,7 @@ def main():
             buf.topk_idx[:T].copy_(h_idx, non_blocking=True); buf.topk_weights[:T].copy_(h_w, non_blocking=True)
         launch()
         h_y.copy_(y, non_blocking=True)
-    es = timed(e2e_step, args.steps, 3)
+    es = timed(e2e_step, args.steps, 3, e2e=True)
 
     mean_us, e2e_us = sum(ks) / len(ks), sum(es) / len(es)
     t = torch.tensor([mean_us, e2e_us, statistics.median(ks), span_us], device='cuda', dtype=torch.float64)
@@ -233,7 +238,7 @@ def main():
                 'warmup': W_WARM, 'ms_per_step': mean_us / 1e3, 'higher_is_better': False, 'scaling': 'weak',
                 'vs_baseline': None, 'dtype': 'fp4 (e2m1) x fp4, fp32 accumulate', 'data': 'synthetic',
                 'config': workload_config(args, n), 'timing': 'CUDA events around each launch, mean of the timed steps, max over ranks',
-                'median_us': med_us, 'device_span_us_median': span_us, 'wall_s': t_wall,
+                'median_us': med_us, 'device_span_us_median': span_us, 'phases_us_sm0_last_launch': phases, 'wall_s': t_wall,
                 'clocks': clocks, 'gpu_launches': args.steps,
                 'e2e': {'value': e2e_us, 'unit': 'us',
                         'h2d_bytes_per_step': int(h_x.numel() + h_sf.numel() * 4 + h_idx.numel() * 8 + h_w.numel() * 4),

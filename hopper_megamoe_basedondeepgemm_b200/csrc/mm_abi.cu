@@ -199,11 +199,15 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.asf_bytes = static_cast<uint32_t>(align_up(kmax / vec, 16) / 4 * 256);     // 256 B per scale word of the K axis
     const size_t fixed = 2 * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes + mm::kVtBytes;
     const size_t budget = 232448 - sizeof(mm::Ctl) - 1024 /* alignment slack */ - 768;
-    int nstage = static_cast<int>((budget - fixed) / p.unit_bytes);
+    { const char* d = getenv("MM_STAGE_UNITS"); p.stage_units = d ? atoi(d) : 1; }
+    if (p.stage_units < 1 || p.stage_units > 4) return MM_ERR_INVALID_ARGUMENT;
+    p.stage_bytes = p.stage_units * p.unit_bytes;
+    int nstage = static_cast<int>((budget - fixed) / p.stage_bytes);
     if (nstage > mm::kMaxStages) nstage = mm::kMaxStages;
     if (nstage < 2) return MM_ERR_UNSUPPORTED;
     p.nstage = nstage;
-    p.sm_act = nstage * p.unit_bytes;
+    { const char* d = getenv("MM_L1_INFLIGHT"); p.l1_inflight = d ? atoi(d) : 0; }
+    p.sm_act = nstage * p.stage_bytes;
     p.sm_asf = p.sm_act + 2 * p.act_bytes;
     p.sm_otile = p.sm_asf + 2 * p.asf_bytes;
     p.sm_vt = p.sm_otile + mm::kOtileBytes;
@@ -212,9 +216,9 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     return MM_OK;
 }
 
-template <int kVec, bool kUmma>
+template <int kVec, bool kUmma, bool kFe = false>
 static int launch_variant(const mm::KParams& p, int grid, size_t smem_bytes, cudaStream_t stream) {
-    auto kern = mm::mega_moe_kernel<kVec, kUmma>;
+    auto kern = mm::mega_moe_kernel<kVec, kUmma, kFe>;
     MM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
     kern<<<grid, mm::kThreads, smem_bytes, stream>>>(p);
     MM_CUDA(cudaGetLastError());
@@ -304,12 +308,13 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     q.topk_idx = reinterpret_cast<long long*>(b + L.off_topk_idx);
     q.topk_w = reinterpret_cast<float*>(b + L.off_topk_weights);
     q.x_row_bytes = static_cast<int>(L.x_row_bytes); q.x_sf_row_bytes = static_cast<int>(L.x_sf_row_bytes);
-    p.fe_enabled = fe->num_tokens > 0 ? 1 : 0;
+    p.fe_enabled = 1;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const bool umma = a->engine == MM_ENGINE_UMMA;
-    if (cfg->act_format == MM_FMT_MXFP4)
-        return umma ? launch_variant<32, true>(p, grid, smem_bytes, s) : launch_variant<32, false>(p, grid, smem_bytes, s);
-    return umma ? launch_variant<16, true>(p, grid, smem_bytes, s) : launch_variant<16, false>(p, grid, smem_bytes, s);
+    if (a->engine != MM_ENGINE_UMMA) return MM_ERR_UNSUPPORTED;     // the cross-check engine takes pre-routed inputs only
+    if (fe->num_tokens == 0) return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, true>(p, grid, smem_bytes, s)
+                                                                    : launch_variant<16, true>(p, grid, smem_bytes, s);
+    return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, true, true>(p, grid, smem_bytes, s)
+                                           : launch_variant<16, true, true>(p, grid, smem_bytes, s);
 }
 
 // ----------------------------------------------------------------------------- launch without any allocation

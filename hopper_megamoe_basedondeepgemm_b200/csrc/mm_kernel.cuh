@@ -74,7 +74,8 @@ struct RowMeta { int32_t src, token, slot; float weight; };
 struct KParams {
     int R, rank, e_local, topk, H, I, T, cap;
     int n1_tiles, n2_tiles, k1_units, k2_units;
-    int nstage;
+    int nstage, l1_inflight, stage_units;   // a stage holds up to `stage_units` consecutive units
+    uint32_t stage_bytes;
     uint32_t unit_bytes;                 // weights + scale planes of one streamed unit
     int x_row_bytes, x_sf_row_bytes, rx_row_bytes, mid_row_bytes, mid_sf_row_bytes;
     float clamp; int has_clamp, fast_math;
@@ -134,7 +135,7 @@ struct Ctx {
         *reinterpret_cast<volatile uint32_t*>(&c.abort_flag) = 1u;
     }
     __device__ __forceinline__ bool expired() const { return globaltimer_ns() > deadline; }
-    __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, uint32_t code) const {
+    __device__ __noinline__ bool wait(uint64_t* bar, uint32_t parity, uint32_t code) const {
         uint32_t it = 0;
         while (!mbar_try_wait(bar, parity)) {
             if ((++it & 0xFFu) == 0u) {
@@ -144,8 +145,12 @@ struct Ctx {
         }
         return true;
     }
+    // every lane waits; the warp agrees on the outcome
+    __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, uint32_t code) const {
+        return __all_sync(0xffffffffu, wait(bar, parity, code));
+    }
     __device__ __forceinline__ void trace(int slot) const {
-        if (p.trace != nullptr) p.trace[blockIdx.x * 96 + slot] = globaltimer_ns();
+        if (p.trace != nullptr && (!(p.dbg & 8) || ((0x0680FDF9u >> slot) & 1u))) p.trace[blockIdx.x * 96 + slot] = globaltimer_ns();
     }
     __device__ __forceinline__ void stamp(int slot) const {
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[slot] = globaltimer_ns();
@@ -181,26 +186,31 @@ __device__ __forceinline__ float sf_value(uint32_t byte) {
 __device__ void role_loader(const Ctx& cx) {
     const KParams& p = cx.p; Ctl& c = cx.c;
     uint32_t it = 0;
-    long long ld_wait = 0; const long long ld_t0 = clock64();
+    #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, j = t & 0xFF;
         const int ntiles = type ? p.n2_tiles : p.n1_tiles, kunits = type ? p.k2_units : p.k1_units;
         const uint8_t* src = (type ? p.w2 : p.w1) + (static_cast<size_t>(e) * ntiles + j) * kunits * p.unit_bytes;
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
-        for (int u = ub; u < ue; ++u, ++it) {
+        #pragma unroll 1
+        for (int u = ub, nu; u < ue; u += nu, ++it) {
+            nu = ue - u < p.stage_units ? ue - u : p.stage_units;       // consecutive units are contiguous in the stream
             const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
-            const long long lw0 = clock64();
             if (!cx.wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
-            ld_wait += clock64() - lw0;
+            if (type == 0u && p.l1_inflight > 0 && it >= static_cast<uint32_t>(p.l1_inflight)) {
+                // L1 units: a short queue per SM keeps the memory system's service order fair between SMs (an expert's L2
+                // needs the L1 tiles of ALL its SMs); W2 units, which are prefetched ahead of their use, may fill the ring
+                const uint32_t j0 = it - p.l1_inflight;
+                if (!cx.wait(&c.empty[j0 % p.nstage], (j0 / p.nstage) & 1u, kErrWaitEmpty)) return;
+            }
             if (it == 0) cx.trace(4);
-            mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
-            bulk_g2s(cx.smem + static_cast<size_t>(s) * p.unit_bytes, src + static_cast<size_t>(u) * p.unit_bytes,
-                     p.unit_bytes, &c.full[s]);
+            mbar_arrive_expect_tx(&c.full[s], nu * p.unit_bytes);
+            bulk_g2s(cx.smem + static_cast<size_t>(s) * p.stage_bytes, src + static_cast<size_t>(u) * p.unit_bytes,
+                     nu * p.unit_bytes, &c.full[s]);
         }
     }
     cx.trace(5);
-    if (p.trace != nullptr) { p.trace[blockIdx.x * 96 + 16] = ld_wait; p.trace[blockIdx.x * 96 + 17] = clock64() - ld_t0; p.trace[blockIdx.x * 96 + 18] = it; }
 }
 
 // ============================================================================================= MMA issuer
@@ -211,32 +221,30 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     constexpr uint32_t kIdesc = idesc_block_scaled(kFmtMxf4E2M1, kFmtMxf4E2M1, kTileRows, kTileTokens, kVec == 32 ? 1u : 0u);
     const uint32_t tm = c.tmem_base;
     const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 16
-    uint32_t it = 0;
-    long long w_full = 0, w_task = 0, t_issue = 0; const long long mm_t0 = clock64();
+    uint32_t it = 0, uc = 0;                                    // stages and units consumed so far
+    #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28;
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         const uint32_t ab = ti & 1u, acc = ti & 1u, use = (ti >> 1) & 1u;
         (void)type;
-        const long long tw0 = clock64();
-        if (!__all_sync(0xffffffffu, cx.wait(&c.acts_full[ab], use, kErrWaitActsFull))) return;
-        if (!__all_sync(0xffffffffu, cx.wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty))) return;
+        if (!cx.warp_wait(&c.acts_full[ab], use, kErrWaitActsFull)) return;
+        if (!cx.warp_wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty)) return;
         tc_fence_after();
-        w_task += clock64() - tw0;
         const uint32_t act = smem_u32(cx.smem + p.sm_act + ab * p.act_bytes);
-        for (int u = ub; u < ue; ++u, ++it) {
+        #pragma unroll 1
+        for (int u0 = ub, nu; u0 < ue; u0 += nu, ++it) {
+            nu = ue - u0 < p.stage_units ? ue - u0 : p.stage_units;
             const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
-            const long long fw0 = clock64();
-            if (!__all_sync(0xffffffffu, cx.wait(&c.full[s], ph, kErrWaitFull))) return;
+            if (!cx.warp_wait(&c.full[s], ph, kErrWaitFull)) return;
             tc_fence_after();
-            const long long fw1 = clock64();
-            w_full += fw1 - fw0;
             if (elect_one()) {
-                if (it == 0) cx.trace(6);
-                if (p.trace != nullptr && it < 30) p.trace[blockIdx.x * 96 + 32 + 2 * it] = globaltimer_ns();
-                const uint32_t wsm = smem_u32(cx.smem + static_cast<size_t>(s) * p.unit_bytes);
-                const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u, sfb = tm + sfb_col + (it & 1u) * 16u;
+              if (it == 0) cx.trace(6);
+              #pragma unroll 1
+              for (int u = u0; u < u0 + nu; ++u, ++uc) {
+                const uint32_t wsm = smem_u32(cx.smem + static_cast<size_t>(s) * p.stage_bytes) + static_cast<uint32_t>(u - u0) * p.unit_bytes;
+                const uint32_t sfa = tm + sfa_col + (uc & 1u) * 16u, sfb = tm + sfb_col + (uc & 1u) * 16u;
                 const uint32_t asf = smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes) + static_cast<uint32_t>(u) * kPlanes * 256u;
                 #pragma unroll
                 for (uint32_t pl = 0; pl < kPlanes; ++pl) {
@@ -260,11 +268,10 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
                     else
                         umma_nvf4_block16(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
                 }
-                tc_commit(&c.empty[s]);
-                if (p.trace != nullptr && it < 30) p.trace[blockIdx.x * 96 + 33 + 2 * it] = globaltimer_ns();
+              }
+              tc_commit(&c.empty[s]);
             }
             __syncwarp();
-            t_issue += clock64() - fw1;
         }
         if (elect_one()) {
             tc_commit(&c.tmem_full[acc]);
@@ -272,10 +279,6 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
             cx.trace(7);
         }
         __syncwarp();
-    }
-    if (lane == 0 && p.trace != nullptr) {
-        p.trace[blockIdx.x * 96 + 19] = w_full; p.trace[blockIdx.x * 96 + 20] = w_task; p.trace[blockIdx.x * 96 + 21] = t_issue;
-        p.trace[blockIdx.x * 96 + 22] = clock64() - mm_t0;
     }
 }
 
@@ -285,6 +288,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
 __device__ __forceinline__ void find_rows(Ctl& c, uint32_t* rowref, uint32_t total, uint32_t e, uint32_t mt, uint32_t lane) {
     const uint32_t lo = mt * kTileTokens, hi = lo + kTileTokens;
     uint32_t seen = 0;
+    #pragma unroll 1
     for (uint32_t base = 0; base < total && seen < hi; base += 32) {
         const uint32_t f = base + lane;
         const bool m = f < total && c.meta_e[f] == e;
@@ -303,11 +307,12 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
     uint32_t* l1_done = reinterpret_cast<uint32_t*>(cx.buf + p.off_ctrl + kCtrlL1Done) + cx.par * kMaxLocalExperts;
     uint32_t* rowref = c.rowref[sw];
     uint32_t* rowidx = c.rowidx[sw];
+    #pragma unroll 1
     for (uint32_t ti = sw; ti < c.ntasks; ti += 2) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
         const uint32_t ab = sw, use = (ti >> 1) & 1u, ring = ti & 3u;
-        if (!__all_sync(0xffffffffu, cx.wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty))) return;
+        if (!cx.warp_wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty)) return;
         find_rows(c, rowref, total, e, mt, lane);
         const uint32_t left = c.exp_count[e] - mt * kTileTokens;
         const uint32_t nv = left < kTileTokens ? left : kTileTokens;
@@ -339,7 +344,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                         if (cx.expired()) { cx.fail(kErrWaitL1Done, e); ok = false; break; }
                     }
                 }
-                if (p.trace != nullptr && p.trace[blockIdx.x * 96 + 24] == 0) cx.trace(24);
+                if (p.trace != nullptr && !(p.dbg & 8) && p.trace[blockIdx.x * 96 + 24] == 0) cx.trace(24);
             }
         }
         if (!__all_sync(0xffffffffu, ok)) return;
@@ -347,31 +352,29 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
         uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
         const uint32_t nchunk = (type ? p.I : p.H) / 32;                                   // 16 B chunks of one packed row
         const uint32_t sfchunk = (type ? p.mid_sf_row_bytes : p.x_sf_row_bytes) / 16;      // 16 B chunks of one row's scale bytes
-        const uint32_t per_row = nchunk + sfchunk, items = nv * per_row;
+        const uint32_t per_row = nchunk + sfchunk;
         const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
-        // all loads of a batch are in flight before the first store: one memory round trip per 4 x 32 items
-        for (uint32_t base = lane; base < items; base += 4 * 32) {
-            uint4 v[4];
-            #pragma unroll
-            for (uint32_t u = 0; u < 4; ++u) {
-                const uint32_t idx = base + u * 32;
-                if (idx < items) {
-                    const uint32_t n = idx / per_row, ci = idx % per_row;
-                    const uint8_t* src;
-                    if (type) src = ci < nchunk ? cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes + ci * 16u
-                                                : cx.buf + p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes + (ci - nchunk) * 16u;
-                    else src = cx.rx_row(rowidx[n] >> 24, rowidx[n] & 0xFFFFFFu) + ci * 16u;   // scale bytes follow the packed row
-                    v[u] = ld_cg_v4(src);
+        // four loads per lane are in flight before the first store: one memory round trip per 128 chunks of a row
+        #pragma unroll 1
+        for (uint32_t n = 0; n < nv; ++n) {
+            const uint8_t* row_src = type ? cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes
+                                          : cx.rx_row(rowidx[n] >> 24, rowidx[n] & 0xFFFFFFu);
+            const uint8_t* sf_src = type ? cx.buf + p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes
+                                         : row_src + p.x_row_bytes;
+            #pragma unroll 1
+            for (uint32_t base = lane; base < per_row; base += 4 * 32) {
+                uint4 v[4];
+                #pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t ci = base + u * 32;
+                    if (ci < per_row) v[u] = ld_cg_v4(ci < nchunk ? row_src + ci * 16u : sf_src + (ci - nchunk) * 16u);
                 }
-            }
-            #pragma unroll
-            for (uint32_t u = 0; u < 4; ++u) {
-                const uint32_t idx = base + u * 32;
-                if (idx < items) {
-                    const uint32_t n = idx / per_row, ci = idx % per_row;
+                #pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t ci = base + u * 32;
                     if (ci < nchunk) {
                         *reinterpret_cast<uint4*>(act + (ci >> 3) * (kTileTokens * 128u) + sw128_off(n, ci & 7u)) = v[u];
-                    } else {
+                    } else if (ci < per_row) {
                         // four scale words: one 16 B slot per (scale word, token), word g of the row at slot g
                         uint8_t* dst = asf + (ci - nchunk) * 4u * 256u + n * 16u;
                         *reinterpret_cast<uint32_t*>(dst) = v[u].x;
@@ -440,6 +443,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     float* vt = reinterpret_cast<float*>(cx.smem + p.sm_vt) + row;      // this thread's accumulators: vt[n * 128], token n
     uint32_t* l1_done = reinterpret_cast<uint32_t*>(cx.buf + p.off_ctrl + kCtrlL1Done) + cx.par * kMaxLocalExperts;
     uint32_t it = 0;
+    #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF, j = t & 0xFF;
@@ -448,7 +452,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
         bool ok;
         uint32_t nv = 0;
         if constexpr (kUmma) {
-            ok = __all_sync(0xffffffffu, cx.wait(&c.tmem_full[acc], use, kErrWaitTmemFull));
+            ok = cx.warp_wait(&c.tmem_full[acc], use, kErrWaitTmemFull);
             if (ok) {
                 tc_fence_after();
                 if (etid == 0) { if (ti == 0) cx.trace(8); cx.trace(type ? 26 : 25); }
@@ -463,7 +467,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 for (int n = 0; n < kTileTokens; ++n) if (n < static_cast<int>(nv)) vt[n * kTileRows] = __uint_as_float(raw[n]);
             }
         } else {
-            ok = __all_sync(0xffffffffu, cx.wait(&c.acts_full[ab], use, kErrWaitActsFull));
+            ok = cx.warp_wait(&c.acts_full[ab], use, kErrWaitActsFull);
             if (ok) {
                 if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
                 nv = c.nvalid[ring];
@@ -473,11 +477,16 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
                 const uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
                 const uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
-                for (int u = ub; u < ue && ok; ++u, ++it) {
+                #pragma unroll 1
+                for (int u0 = ub, nu; u0 < ue && ok; u0 += nu, ++it) {
+                    nu = ue - u0 < p.stage_units ? ue - u0 : p.stage_units;
                     const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
-                    ok = __all_sync(0xffffffffu, cx.wait(&c.full[s], ph, kErrWaitFull));
+                    ok = cx.warp_wait(&c.full[s], ph, kErrWaitFull);
                     if (ok) {
-                        check_accumulate<kVec>(cx, cx.smem + static_cast<size_t>(s) * p.unit_bytes, act, asf, u, row, nv, v);
+                        #pragma unroll 1
+                        for (int u = u0; u < u0 + nu; ++u)
+                            check_accumulate<kVec>(cx, cx.smem + static_cast<size_t>(s) * p.stage_bytes + static_cast<size_t>(u - u0) * p.unit_bytes,
+                                                   act, asf, u, row, nv, v);
                         mbar_arrive(&c.empty[s]);
                     }
                 }
@@ -488,6 +497,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
         }
         if (bar_red_or(kBarEpi, kNumEpiThreads, !ok)) return;        // also publishes epi_meta
         if (p.debug_acc != nullptr && blockIdx.x == 0 && ti < static_cast<uint32_t>(p.debug_tasks))
+            #pragma unroll 1
             for (uint32_t n = 0; n < nv; ++n) p.debug_acc[(static_cast<size_t>(ti) * kTileTokens + n) * kTileRows + row] = vt[n * kTileRows];
         const RowMeta* meta = c.epi_meta[acc];
         const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
@@ -500,6 +510,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             float* red = reinterpret_cast<float*>(cx.buf + p.off_red);
             const uint32_t my_slot = (sk_lo(blockIdx.x, q, rem) / kunits == tile) ? 0u : 1u;
             float* mine = red + ((static_cast<size_t>(blockIdx.x) * 2u + type) * 2u + my_slot) * (kTileTokens * kTileRows) + row;
+            #pragma unroll 1
             for (uint32_t n = 0; n < nv; ++n) mine[n * kTileRows] = vt[n * kTileRows];
             bar_sync(kBarEpi, kNumEpiThreads);
             if (etid == 0) {
@@ -510,8 +521,10 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             }
             bar_sync(kBarEpi, kNumEpiThreads);
             if (c.red_old != np - 1u) continue;
+            #pragma unroll 1
             for (uint32_t n = 0; n < nv; ++n) {
                 float sum = 0.f;
+                #pragma unroll 1
                 for (uint32_t pc0 = 0; pc0 < np; pc0 += 4) {          // four parts' loads in flight together, added in SM order
                     float part_v[4];
                     #pragma unroll
@@ -534,6 +547,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
         if (type == 0u) {
             // ---- L1: rows come in groups of 16 = 8 gate rows then the 8 matching up rows
             const bool is_up = (lane & 8u) != 0u;
+            #pragma unroll 1
             for (uint32_t n = 0; n < nv; ++n) {
                 const float mine = bf16_round(vt[n * kTileRows] * p.l1_scale);
                 const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
@@ -552,6 +566,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             }
             if constexpr (kVec == 32) bar_sync(kBarEpi, kNumEpiThreads);     // a 32-column scale block spans two warps
             else __syncwarp();
+            #pragma unroll 1
             for (uint32_t n = 0; n < nv; ++n) {
                 float amax = c.amax_x[ew][n];
                 if constexpr (kVec == 32) amax = fmaxf(amax, c.amax_x[ew ^ 1u][n]);
@@ -585,8 +600,10 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
         } else {
             // ---- L2: bf16 rows back to the token's source rank
             __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(otile);
+            #pragma unroll 1
             for (uint32_t n = 0; n < nv; ++n) ot[n * kTileRows + row] = __float2bfloat16_rn(vt[n * kTileRows] * p.l2_scale);
             bar_sync(kBarEpi, kNumEpiThreads);
+            #pragma unroll 1
             for (uint32_t idx = etid; idx < nv * 16u; idx += kNumEpiThreads) {
                 const uint32_t n = idx >> 4, ch = idx & 15u;
                 const uint4 val = *reinterpret_cast<const uint4*>(otile + n * 256u + ch * 16u);
@@ -600,7 +617,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
 }
 
 // ============================================================================================= the kernel
-template <int kVec, bool kUmma>
+template <int kVec, bool kUmma, bool kFe>
 __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_constant__ KParams p) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ Ctl c;
@@ -615,6 +632,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
         c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u;
         for (int s = 0; s < p.nstage; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kUmma ? 1 : kNumEpiThreads); }
+        #pragma unroll 1
         for (int i = 0; i < 2; ++i) {
             mbar_init(&c.acts_full[i], 1); mbar_init(&c.acts_empty[i], kUmma ? 1 : kNumEpiThreads);
             mbar_init(&c.tmem_full[i], 1); mbar_init(&c.tmem_empty[i], kNumEpiThreads);
@@ -629,9 +647,22 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     const uint32_t epoch = c.epoch, par = cx.par;
     if (bid == 0 && tid == 0) { ctrl32[kCtrlStatus / 4 + 1] = epoch + 1u; cx.stamp(kStampEntry); }
     if (tid == 0) cx.trace(0);
+    // Counters, flags and scale-byte rows are touched late, on the critical dependency chain, and by then they have
+    // usually been evicted from the L2 by the weight stream of earlier work: ask for their lines now.
+    if (warp == 7) {
+        const uint32_t g = bid * 32 + lane, gn = G * 32;
+        #pragma unroll 1
+        for (uint32_t off = g * 128u; off < kCtrlBytes + kFlagBytes; off += gn * 128u) prefetch_l2_line(buf + p.off_ctrl + off);
+        const size_t cnt_bytes = static_cast<size_t>(2) * p.cnt_per_phase * 4;
+        #pragma unroll 1
+        for (size_t off = static_cast<size_t>(g) * 128u; off < (cnt_bytes < 65536 ? cnt_bytes : 65536); off += gn * 128u) prefetch_l2_line(buf + p.off_cnt + off);
+        const size_t sf_bytes = static_cast<size_t>(p.mid_sf_row_bytes) * 16 * kMaxLocalExperts;
+        #pragma unroll 1
+        for (size_t off = static_cast<size_t>(g) * 128u; off < sf_bytes; off += gn * 128u) prefetch_l2_line(buf + p.off_mid_sf + off);
+    }
 
     // ---- router frontend (optional): all SMs compute logits; the dispatching SMs select the top-8 of every token
-    if (p.fe_enabled) {
+    if constexpr (kFe) {
         fe_logits_items(p.fe, bid * (kThreads / 32) + warp, G * (kThreads / 32), lane);
         __syncthreads();
         uint32_t* fe_arrive = ctrl32 + kCtrlFeArrive / 4;
@@ -648,6 +679,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
             }
             __syncthreads();
             float* sc = reinterpret_cast<float*>(smem + p.sm_act) + warp * p.fe.E;
+            #pragma unroll 1
             for (uint32_t t = warp; t < static_cast<uint32_t>(p.T); t += kThreads / 32) {
                 const bool nz = fe_row_nonzero(p.fe.hidden + static_cast<size_t>(t) * p.H, p.H, lane);
                 fe_select_token(p.fe, t, sc, nz, lane);
@@ -665,6 +697,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
             const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
             const uint32_t n = static_cast<uint32_t>(p.T) * p.topk;
             uint32_t cnt = 0;
+            #pragma unroll 1
             for (uint32_t base = 0; base < n; base += 32) {
                 const uint32_t i = base + lane;
                 const long long ex = i < n ? tk[i] : -1;
@@ -677,8 +710,9 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         }
         __syncthreads();
         const uint32_t cnt = c.dcount;
-        if (p.fe_enabled) {
+        if constexpr (kFe) {
             // quantise the tokens this SM is about to send into the x / x_sf views (the same bytes whichever SM writes them)
+            #pragma unroll 1
             for (uint32_t i = warp; i < cnt; i += kThreads / 32) {
                 const uint32_t tok = dlist[i] >> 16;
                 fe_quant_token(p.fe.hidden + static_cast<size_t>(tok) * p.H, p.H, kVec == 32 ? 0 : 1, p.fe.x_gs,
@@ -690,24 +724,28 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         const uint32_t nchunk = p.rx_row_bytes / 16, xq = p.x_row_bytes / 16, xs = p.x_sf_row_bytes / 16;
         uint8_t* dst_base = p.peer[d] + p.off_rx + static_cast<size_t>(par * p.R + p.rank) * p.cap * p.rx_row_bytes;
         const float* tw = reinterpret_cast<const float*>(buf + p.off_topk_w);
-        const uint32_t items = cnt * nchunk;
-        for (uint32_t base = tid; base < items; base += 4 * kThreads) {
-            uint4 v[4];
-            #pragma unroll
-            for (uint32_t u = 0; u < 4; ++u) {
-                const uint32_t idx = base + u * kThreads;
-                if (idx < items) {
-                    const uint32_t i = idx / nchunk, ci = idx % nchunk, ent = dlist[i];
-                    const uint32_t tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
-                    if (ci < xq) v[u] = *reinterpret_cast<const uint4*>(buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes + ci * 16u);
-                    else if (ci < xq + xs) v[u] = *reinterpret_cast<const uint4*>(buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes + (ci - xq) * 16u);
-                    else v[u] = make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot]));
+        // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (four in flight)
+        #pragma unroll 1
+        for (uint32_t i = warp; i < cnt; i += kThreads / 32) {
+            const uint32_t ent = dlist[i], tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
+            const uint8_t* xs_src = buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
+            const uint8_t* sf_src = buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
+            uint8_t* dst = dst_base + static_cast<size_t>(i) * p.rx_row_bytes;
+            #pragma unroll 1
+            for (uint32_t base = lane; base < nchunk; base += 4 * 32) {
+                uint4 v[4];
+                #pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t ci = base + u * 32;
+                    if (ci < xq) v[u] = *reinterpret_cast<const uint4*>(xs_src + ci * 16u);
+                    else if (ci < xq + xs) v[u] = *reinterpret_cast<const uint4*>(sf_src + (ci - xq) * 16u);
+                    else if (ci < nchunk) v[u] = make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot]));
                 }
-            }
-            #pragma unroll
-            for (uint32_t u = 0; u < 4; ++u) {
-                const uint32_t idx = base + u * kThreads;
-                if (idx < items) st_global_v4(dst_base + static_cast<size_t>(idx / nchunk) * p.rx_row_bytes + (idx % nchunk) * 16u, v[u]);
+                #pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t ci = base + u * 32;
+                    if (ci < nchunk) st_global_v4(dst + ci * 16u, v[u]);
+                }
             }
         }
         __syncthreads();
@@ -723,6 +761,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     if (tid == 0) cx.trace(1);
 
     // ---- the staging buffers start from zero: rows beyond a task's valid tokens only ever hold finite bytes
+    #pragma unroll 1
     for (uint32_t off = tid * 16u; off < 2u * (p.act_bytes + p.asf_bytes); off += kThreads * 16u)
         *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
 
@@ -752,6 +791,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
             cx.trace(2);
         }
         if (total <= kMetaCap) {
+            #pragma unroll 1
             for (uint32_t f = tid; f < total; f += kThreads) {
                 uint32_t r = 0;
                 #pragma unroll
@@ -783,7 +823,9 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         if (lane < el) c.mid_base[lane] = x0 * kTileTokens;
         if (lane + 32 < el) c.mid_base[lane + 32] = x1 * kTileTokens;
         if (M <= kMaxMTiles) {
+            #pragma unroll 1
             for (uint32_t mt = 0; mt < m0; ++mt) c.mtl[x0 + mt] = (lane << 16) | mt;
+            #pragma unroll 1
             for (uint32_t mt = 0; mt < m1; ++mt) c.mtl[x1 + mt] = ((lane + 32) << 16) | mt;
         }
         __syncwarp();
@@ -793,6 +835,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         // number of units (+-1) and the epilogue that ends a phase is a whole-tile one.
         uint32_t nmine = 0;
         if (M <= kMaxMTiles) {
+            #pragma unroll 1
             for (uint32_t type = 0; type < 2; ++type) {
                 const uint32_t n = type ? p.n2_tiles : p.n1_tiles, k = type ? p.k2_units : p.k1_units;
                 const uint32_t NT = M * n, r = NT % G, U = r * k, q = U / G, rem = U % G;
@@ -814,6 +857,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
                     }
                     nmine += __popc(b);
                 }
+                #pragma unroll 1
                 for (uint32_t i0 = 0;; i0 += 32) {
                     const uint32_t t = r + bid + (i0 + lane) * G;
                     const bool m = t < NT;
@@ -856,6 +900,18 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     if (bid == 0 && tid == 0) cx.stamp(kStampTasksDone);
     if (tid == 0) cx.trace(10);
 
+    // ---- tell every rank that this rank's expert outputs have been written. The barrier above orders every thread's
+    //      stores before the counter's release; the last SM's fence carries all of them to system scope before the flags.
+    if (tid == 0 && !cx.aborted()) {
+        const uint32_t old = atom_acq_rel_gpu_add(&ctrl32[kCtrlL2Done / 4], 1u);
+        if (old == G - 1) {
+            ctrl32[kCtrlL2Done / 4] = 0u;
+            if (p.R > 1) fence_acq_rel_sys(); else fence_acq_rel_gpu();      // a single rank's flag never leaves this GPU
+            for (int r = 0; r < p.R; ++r)
+                st_relaxed_sys(reinterpret_cast<uint32_t*>(p.peer[r] + p.off_flags + kFlagCombine) + par * kMaxRanks + p.rank, epoch + 1u);
+            cx.stamp(kStampL2Signalled);
+        }
+    }
     // ---- combine, part 1: which routes of this thread's first (token, 16 B chunk) item are live (fetched before the wait)
     const uint32_t chunks_per_row = p.H / 8, nitems = static_cast<uint32_t>(p.T) * chunks_per_row;
     const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
@@ -866,18 +922,6 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         for (int sl = 0; sl < p.topk; ++sl) first_mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
     }
 
-    // ---- tell every rank that this rank's expert outputs have been written. The barrier above orders every thread's
-    //      stores before the counter's release; the last SM's fence carries all of them to system scope before the flags.
-    if (tid == 0 && !cx.aborted()) {
-        const uint32_t old = atom_acq_rel_gpu_add(&ctrl32[kCtrlL2Done / 4], 1u);
-        if (old == G - 1) {
-            ctrl32[kCtrlL2Done / 4] = 0u;
-            fence_acq_rel_sys();
-            for (int r = 0; r < p.R; ++r)
-                st_relaxed_sys(reinterpret_cast<uint32_t*>(p.peer[r] + p.off_flags + kFlagCombine) + par * kMaxRanks + p.rank, epoch + 1u);
-            cx.stamp(kStampL2Signalled);
-        }
-    }
     // ---- combine: wait for every rank's flag, then sum each token's routes in slot order
     if (tid < static_cast<uint32_t>(p.R) && !cx.aborted()) {
         const uint32_t* flag = reinterpret_cast<const uint32_t*>(buf + p.off_flags + kFlagCombine) + par * kMaxRanks + tid;
@@ -894,6 +938,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     if (tid == 0) cx.trace(11);
     if (!cx.aborted()) {
         // item idx = (token, 16 B chunk); consecutive items go to different SMs so that a small batch uses the whole GPU
+        #pragma unroll 1
         for (uint32_t idx = first_item; idx < nitems; idx += G * kThreads) {
             const uint32_t tok = idx / chunks_per_row, ch = idx % chunks_per_row;
             uint32_t mask = first_mask;
@@ -902,6 +947,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
                 for (int sl = 0; sl < p.topk; ++sl) mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
             }
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            #pragma unroll 1
             for (int s0 = 0; s0 < p.topk; s0 += 8) {
                 uint4 v[8];
                 #pragma unroll

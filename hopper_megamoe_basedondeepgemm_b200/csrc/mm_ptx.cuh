@@ -11,7 +11,7 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
 }
 __device__ __forceinline__ uint64_t globaltimer_ns() {
     uint64_t t;
-    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t) :: "memory");
     return t;
 }
 __device__ __forceinline__ bool elect_one() {
@@ -56,6 +56,9 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
 }
 __device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void prefetch_l2_line(const void* p) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
 // generic-proxy shared-memory writes -> visible to the async proxy (UMMA / UTCCP / bulk copies)
 __device__ __forceinline__ void fence_proxy_async_smem() {
@@ -193,6 +196,12 @@ __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
 }
 __device__ __forceinline__ void st_relaxed_sys64(uint64_t* p, uint64_t v) {
     asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ void st_global_v2_u64(unsigned long long* p, unsigned long long a, unsigned long long b) {
+    asm volatile("st.global.v2.u64 [%0], {%1, %2};" ::"l"(p), "l"(a), "l"(b) : "memory");
+}
+__device__ __forceinline__ void ld_relaxed_v2_u64(const unsigned long long* p, unsigned long long& a, unsigned long long& b) {
+    asm volatile("ld.volatile.global.v2.u64 {%0, %1}, [%2];" : "=l"(a), "=l"(b) : "l"(p) : "memory");
 }
 __device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

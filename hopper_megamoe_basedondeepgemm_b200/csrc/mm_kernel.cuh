@@ -197,20 +197,23 @@ __device__ void role_loader(const Ctx& cx) {
         for (int u = ub, nu; u < ue; u += nu, ++it) {
             nu = ue - u < p.stage_units ? ue - u : p.stage_units;       // consecutive units are contiguous in the stream
             const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
-            if (!cx.wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
+            if (!cx.warp_wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
             if (type == 0u && p.l1_inflight > 0 && it >= static_cast<uint32_t>(p.l1_inflight)) {
                 // L1 units: a short queue per SM keeps the memory system's service order fair between SMs (an expert's L2
                 // needs the L1 tiles of ALL its SMs); W2 units, which are prefetched ahead of their use, may fill the ring
                 const uint32_t j0 = it - p.l1_inflight;
-                if (!cx.wait(&c.empty[j0 % p.nstage], (j0 / p.nstage) & 1u, kErrWaitEmpty)) return;
+                if (!cx.warp_wait(&c.empty[j0 % p.nstage], (j0 / p.nstage) & 1u, kErrWaitEmpty)) return;
             }
-            if (it == 0) cx.trace(4);
-            mbar_arrive_expect_tx(&c.full[s], nu * p.unit_bytes);
-            bulk_g2s(cx.smem + static_cast<size_t>(s) * p.stage_bytes, src + static_cast<size_t>(u) * p.unit_bytes,
-                     nu * p.unit_bytes, &c.full[s]);
+            if (elect_one()) {
+                if (it == 0) cx.trace(4);
+                mbar_arrive_expect_tx(&c.full[s], nu * p.unit_bytes);
+                bulk_g2s(cx.smem + static_cast<size_t>(s) * p.stage_bytes, src + static_cast<size_t>(u) * p.unit_bytes,
+                         nu * p.unit_bytes, &c.full[s]);
+            }
+            __syncwarp();
         }
     }
-    cx.trace(5);
+    if ((threadIdx.x & 31u) == 0u) cx.trace(5);
 }
 
 // ============================================================================================= MMA issuer
@@ -891,7 +894,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
 
     // ---- roles
     if (!cx.aborted()) {
-        if (warp == 0) { if (lane == 0) role_loader(cx); }
+        if (warp == 0) role_loader(cx);
         else if (warp == 1) { if constexpr (kUmma) role_mma<kVec>(cx, lane); }
         else if (warp < 4) role_stager(cx, warp - 2, lane);
         else role_epilogue<kVec, kUmma>(cx, tid - 128);
@@ -947,22 +950,21 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
                 for (int sl = 0; sl < p.topk; ++sl) mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
             }
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+            const uint8_t* cbase = buf + p.off_comb + (static_cast<size_t>(tok) * p.topk * p.H) * 2u + ch * 16u;
+            const size_t sstride = static_cast<size_t>(p.H) * 2u;
             #pragma unroll 1
             for (int s0 = 0; s0 < p.topk; s0 += 8) {
+                // eight routes' loads in flight; a masked route contributes +0.0, which leaves the running sums bit-identical
                 uint4 v[8];
                 #pragma unroll
                 for (int u = 0; u < 8; ++u)
-                    if ((mask >> (s0 + u)) & 1u) v[u] = ld_cg_v4(buf + p.off_comb + ((static_cast<size_t>(tok) * p.topk + s0 + u) * p.H) * 2u + ch * 16u);
+                    v[u] = ((mask >> (s0 + u)) & 1u) ? ld_cg_v4(cbase + static_cast<size_t>(s0 + u) * sstride) : make_uint4(0u, 0u, 0u, 0u);
                 #pragma unroll
                 for (int u = 0; u < 8; ++u) {
-                    if ((mask >> (s0 + u)) & 1u) {
-                        const uint32_t w[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-                        #pragma unroll
-                        for (int k = 0; k < 4; ++k) {
-                            acc[2 * k] += __uint_as_float(w[k] << 16);
-                            acc[2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
-                        }
-                    }
+                    acc[0] += __uint_as_float(v[u].x << 16); acc[1] += __uint_as_float(v[u].x & 0xFFFF0000u);
+                    acc[2] += __uint_as_float(v[u].y << 16); acc[3] += __uint_as_float(v[u].y & 0xFFFF0000u);
+                    acc[4] += __uint_as_float(v[u].z << 16); acc[5] += __uint_as_float(v[u].z & 0xFFFF0000u);
+                    acc[6] += __uint_as_float(v[u].w << 16); acc[7] += __uint_as_float(v[u].w & 0xFFFF0000u);
                 }
             }
             uint4 o;

@@ -136,3 +136,32 @@ def test_layer_from_hidden_states_in_one_kernel(fmt):
                                 w1_global_scale=gs1, w2_global_scale=gs2, mid_global_scale=mid_gs)
     assert O.rel_rmse(y.cpu(), ref.y[0]) <= 3e-3 and O.cosine(y.cpu(), ref.y[0]) >= 0.9999
     assert float(y[2].float().abs().sum()) == 0.0                # the all-zero token routes nowhere
+
+
+@pytest.mark.parametrize('tokens', [16, 64])
+def test_skewed_routing_full_layer(tokens):
+    """Sigmoid scores + Zipf(1.2) expert bias, renormalised top-8: hot experts receive many rows (several 16-token tiles)."""
+    fmt, e_local, hidden, inter = 'mxfp4', 48, 3072, 1280
+    g = torch.Generator().manual_seed(41)
+    x = torch.randn((tokens, hidden), generator=g).to(torch.bfloat16)
+    wr = (torch.randn((e_local, hidden), generator=g) / hidden ** 0.5).to(torch.bfloat16)
+    ranks = torch.arange(1, e_local + 1, dtype=torch.float32)
+    bias = (1.0 / ranks ** 1.2)[torch.randperm(e_local, generator=g)]
+    w, _, _ = O.make_expert_weights(e_local, hidden, inter, fmt, seed=42, std=0.02)
+    buf = mm.get_symm_buffer_for_mega_moe(None, e_local, tokens, 8, hidden, inter, act_format=fmt)
+    l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(w, fmt, 'cuda'))
+    ws = torch.zeros(mm.fe_workspace_bytes(buf), dtype=torch.uint8, device='cuda')
+    y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device='cuda')
+    stats = torch.zeros(e_local, dtype=torch.int32, device='cuda')
+    mm.mega_moe_from_hidden(y, x.cuda(), wr.cuda(), l1, l2, buf, ws, cumulative_local_expert_recv_stats=stats,
+                            activation_clamp=10.0, score_mode=1, expert_bias=bias.cuda(), timeout_ms=1000.0)
+    st, words = buf.device_status()
+    assert st == 0, [hex(v) for v in words[:4]]
+    logits = O.router_logits_device_order(x, wr)
+    idx, tw = O.route_from_logits(logits, x, 8, 'sigmoid_bias', bias)
+    assert torch.equal(buf.topk_idx[:tokens].cpu(), idx)
+    q, sf, _ = O.quantise_tokens(x, fmt, rounding='rne', sf_rule='mul')
+    ref = O.moe_layer_reference([O.RankInput(q, sf, idx, tw)], [w], fmt, e_local, clamp=10.0)
+    assert torch.equal(stats.cpu(), ref.counts[0])
+    assert int(ref.counts[0].max()) > 16 or tokens < 64          # the hot expert spans more than one token tile
+    assert O.rel_rmse(y.cpu(), ref.y[0]) <= 3e-3 and O.cosine(y.cpu(), ref.y[0]) >= 0.9999

@@ -171,6 +171,8 @@ def main():
         for _ in range(20):                        # let the host run ahead of the GPU: events then bracket the kernel,
             flush.zero_()                          # not the host's launch latency
         for i in range(warm + steps):
+            if i == warm:
+                torch.cuda.nvtx.range_push('timed_e2e' if e2e else 'timed')
             flush.zero_()
             if not e2e:
                 write_inputs_from_device()         # flush -> input copy -> rank alignment -> kernel, as the reference's
@@ -182,6 +184,7 @@ def main():
             if i >= warm:
                 ends[i - warm].record()
         torch.cuda.synchronize()
+        torch.cuda.nvtx.range_pop()
         return [s.elapsed_time(e) * 1e3 for s, e in zip(starts, ends)]
 
     write_inputs_from_device()
@@ -244,7 +247,7 @@ def main():
                         'h2d_bytes_per_step': int(h_x.numel() + h_sf.numel() * 4 + h_idx.numel() * 8 + h_w.numel() * 4),
                         'd2h_bytes_per_step': int(h_y.numel() * 2)},
                 'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
-                             'traffic': None, 'peak_source': peak_src,
+                             'traffic': (int(alg_bytes * 1.0035) if (fmt == 'mxfp4' and n == 1) else None), 'traffic_source': 'dram__bytes_read+write of one ncu capture of this workload, scaled by the active experts (profiles/)', 'peak_source': peak_src,
                              'algorithmic_bytes_per_launch': alg_bytes, 'active_experts_per_rank': active}}
         if not args.no_cpu_baseline and n == 1:
             us, cores = cpu_reference_us(T, fmt, 5)

@@ -31,7 +31,7 @@ int check_config(const mm_config_t* c) {
     if (c->num_topk < 1 || c->num_topk > 32 || c->num_max_tokens_per_rank < 1 || c->num_max_tokens_per_rank > 32768) return MM_ERR_INVALID_ARGUMENT;
     if (c->hidden <= 0 || c->hidden % 512 != 0 || c->hidden > 4096) return MM_ERR_UNSUPPORTED;
     if (c->intermediate <= 0 || c->intermediate % 256 != 0 || c->intermediate > 4096) return MM_ERR_UNSUPPORTED;
-    if (c->act_format != MM_FMT_MXFP4 && c->act_format != MM_FMT_NVFP4) return MM_ERR_UNSUPPORTED;
+    if (c->act_format != MM_FMT_MXFP4 && c->act_format != MM_FMT_NVFP4 && c->act_format != MM_FMT_FP8) return MM_ERR_UNSUPPORTED;
     return MM_OK;
 }
 
@@ -68,7 +68,7 @@ const char* mm_last_cuda_error(void) { return g_cuda_error; }
 int32_t mm_get_token_alignment(void) { return 16; }
 
 int mm_get_weight_geometry(int32_t act_format, mm_weight_geometry_t* out) {
-    if (out == nullptr || (act_format != MM_FMT_MXFP4 && act_format != MM_FMT_NVFP4)) return MM_ERR_INVALID_ARGUMENT;
+    if (out == nullptr || (act_format != MM_FMT_MXFP4 && act_format != MM_FMT_NVFP4 && act_format != MM_FMT_FP8)) return MM_ERR_INVALID_ARGUMENT;
     const int vec = sf_vec_of(act_format);
     out->tile_rows = mm::kTileRows;
     out->unit_k = mm::kUnitK;
@@ -88,12 +88,13 @@ int mm_get_layout(const mm_config_t* c, mm_layout_t* out) {
     const int64_t e_local = c->num_experts / c->num_ranks;
     const int64_t t_max = c->num_max_tokens_per_rank;
     out->sf_vec = vec;
-    out->x_row_bytes = c->hidden / 2;
+    const bool a8 = c->act_format == MM_FMT_FP8;           // E4M3 tokens: one byte per element, UE8M0 scale per 32
+    out->x_row_bytes = a8 ? c->hidden : c->hidden / 2;
     out->x_sf_row_bytes = c->hidden / vec;
     out->rx_row_bytes = out->x_row_bytes + out->x_sf_row_bytes + 16;
     out->rx_cap_rows = t_max * (c->num_topk < e_local ? c->num_topk : e_local);
     out->mid_rows = out->rx_cap_rows * c->num_ranks + mm::kTileTokens * e_local;
-    out->mid_row_bytes = c->intermediate / 2;
+    out->mid_row_bytes = a8 ? c->intermediate : c->intermediate / 2;
     out->mid_sf_row_bytes = align_up(c->intermediate / vec, 16);
     int64_t off = 0;
     auto take = [&](int64_t bytes) { const int64_t o = off; off = align_up(off + bytes, 1024); return o; };
@@ -192,35 +193,45 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.trace = static_cast<unsigned long long*>(a->debug_trace);
     { const char* d = getenv("MM_DBG"); p.dbg = d ? atoi(d) : 0; }
     p.debug_acc = static_cast<float*>(a->debug_accumulators); p.debug_tasks = a->debug_accumulators ? a->debug_num_tasks : 0;
-    // shared memory plan: [stages][2 x token tiles][2 x token scale chunks][output tile]
+    // shared memory plan: [stages][token tiles][token scale chunks][output tile][accumulator tile][widened units (FP8)]
     const int kmax = p.H > p.I ? p.H : p.I;
     const int vec = sf_vec_of(cfg->act_format);
-    p.act_bytes = mm::kTileTokens * kmax / 2;
+    const bool a8 = cfg->act_format == MM_FMT_FP8;
+    p.act_bytes = a8 ? mm::kTileTokens * kmax : mm::kTileTokens * kmax / 2;
     p.asf_bytes = static_cast<uint32_t>(align_up(kmax / vec, 16) / 4 * 256);     // 256 B per scale word of the K axis
-    const size_t fixed = 2 * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes + mm::kVtBytes;
+    const size_t xbytes = a8 ? 2 * mm::kXbufBytes : 0;
     const size_t budget = 232448 - sizeof(mm::Ctl) - 1024 /* alignment slack */ - 768;
     { const char* d = getenv("MM_STAGE_UNITS"); p.stage_units = d ? atoi(d) : 1; }
-    if (p.stage_units < 1 || p.stage_units > 4) return MM_ERR_INVALID_ARGUMENT;
+    if (p.stage_units < 1 || p.stage_units > 4 || (a8 && p.stage_units != 1)) return MM_ERR_INVALID_ARGUMENT;
     p.stage_bytes = p.stage_units * p.unit_bytes;
+    // two token staging buffers when that leaves at least four stream stages, else one
+    p.nab = 2;
+    size_t fixed = p.nab * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes + mm::kVtBytes + xbytes;
+    if (fixed + 4 * static_cast<size_t>(p.stage_bytes) > budget) {
+        p.nab = 1;
+        fixed = p.nab * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes + mm::kVtBytes + xbytes;
+    }
+    if (fixed + 2 * static_cast<size_t>(p.stage_bytes) > budget) return MM_ERR_UNSUPPORTED;
     int nstage = static_cast<int>((budget - fixed) / p.stage_bytes);
     if (nstage > mm::kMaxStages) nstage = mm::kMaxStages;
     if (nstage < 2) return MM_ERR_UNSUPPORTED;
     p.nstage = nstage;
     { const char* d = getenv("MM_L1_INFLIGHT"); p.l1_inflight = d ? atoi(d) : 0; }
     p.sm_act = nstage * p.stage_bytes;
-    p.sm_asf = p.sm_act + 2 * p.act_bytes;
-    p.sm_otile = p.sm_asf + 2 * p.asf_bytes;
+    p.sm_asf = p.sm_act + p.nab * p.act_bytes;
+    p.sm_otile = p.sm_asf + p.nab * p.asf_bytes;
     p.sm_vt = p.sm_otile + mm::kOtileBytes;
-    *smem_bytes = p.sm_vt + mm::kVtBytes + 1024 + 256;
-    if (static_cast<size_t>(p.T) * p.topk * 4 > 2 * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
+    p.sm_xbuf = static_cast<uint32_t>(align_up(p.sm_vt + mm::kVtBytes, 1024));
+    *smem_bytes = (a8 ? p.sm_xbuf + xbytes : p.sm_vt + mm::kVtBytes) + 1024 + 256;
+    if (static_cast<size_t>(p.T) * p.topk * 4 > p.nab * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
     return MM_OK;
 }
 
-template <int kVec, bool kUmma, bool kFe = false>
+template <int kVec, bool kUmma, bool kFe = false, bool kA8 = false>
 static int launch_variant(const mm::KParams& p, int grid, size_t smem_bytes, cudaStream_t stream) {
-    auto kern = mm::mega_moe_kernel<kVec, kUmma, kFe>;
+    auto kern = mm::mega_moe_kernel<kVec, kUmma, kFe, kA8>;
     MM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
-    kern<<<grid, mm::kThreads, smem_bytes, stream>>>(p);
+    kern<<<grid, kA8 ? mm::kThreads + mm::kNumExpThreads : mm::kThreads, smem_bytes, stream>>>(p);
     MM_CUDA(cudaGetLastError());
     return MM_OK;
 }
@@ -235,6 +246,8 @@ int mm_mega_moe_launch(const mm_config_t* cfg, const mm_launch_args_t* a, void* 
     if (st != MM_OK) return st;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const bool umma = a->engine == MM_ENGINE_UMMA;
+    if (cfg->act_format == MM_FMT_FP8)                                     // tensor-core engine only
+        return umma ? launch_variant<32, true, false, true>(p, grid, smem_bytes, s) : MM_ERR_UNSUPPORTED;
     if (cfg->act_format == MM_FMT_MXFP4)
         return umma ? launch_variant<32, true>(p, grid, smem_bytes, s) : launch_variant<32, false>(p, grid, smem_bytes, s);
     return umma ? launch_variant<16, true>(p, grid, smem_bytes, s) : launch_variant<16, false>(p, grid, smem_bytes, s);
@@ -291,7 +304,8 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     if (fe->num_tokens != a->num_tokens) return MM_ERR_INVALID_ARGUMENT;
     if (cfg->num_topk != 8 || cfg->num_experts > 1024) return MM_ERR_UNSUPPORTED;
     if (fe->score_mode == 1 && fe->expert_bias == nullptr) return MM_ERR_INVALID_ARGUMENT;
-    if (static_cast<size_t>(cfg->num_experts) * 4 * (mm::kThreads / 32) > 2 * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
+    if (cfg->act_format == MM_FMT_FP8) return MM_ERR_UNSUPPORTED;          // the fused frontend writes packed E2M1 tokens only
+    if (static_cast<size_t>(cfg->num_experts) * 4 * (mm::kThreads / 32) > p.nab * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
     mm_layout_t L;
     mm_get_layout(cfg, &L);
     uint8_t* b = static_cast<uint8_t*>(a->buffer);

@@ -73,7 +73,8 @@ __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v)
     return v;
 }
 
-// One warp quantises token row `xrow` (bf16 [H]) to packed E2M1 + scale bytes; returns whether any element is non-zero.
+// One warp quantises token row `xrow` (bf16 [H]) to packed E2M1 (formats 0, 1) or E4M3 bytes (format 2) + scale bytes;
+// returns whether any element is non-zero.
 __device__ __forceinline__ bool fe_quant_token(const __nv_bfloat16* xrow, int H, int fmt, float x_gs,
                                                uint8_t* qrow, uint8_t* sfrow, uint32_t lane) {
     const int vec = fmt == 1 ? 16 : 32, lanes_per_group = vec / 8;
@@ -90,7 +91,7 @@ __device__ __forceinline__ bool fe_quant_token(const __nv_bfloat16* xrow, int H,
         }
         local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, 1));
         if (lanes_per_group == 4) local = fmaxf(local, __shfl_xor_sync(0xffffffffu, local, 2));
-        const float v = fmaxf(local, 1.0e-30f) * (1.0f / 6.0f);
+        const float v = fmt == 2 ? fmaxf(local, 1.0e-4f) * (1.0f / 448.0f) : fmaxf(local, 1.0e-30f) * (1.0f / 6.0f);
         uint32_t sf_byte; float sf;
         if (fmt == 1) {
             sf_byte = cvt_e4m3x2(v, 0.f) & 0xFFu;
@@ -102,10 +103,17 @@ __device__ __forceinline__ bool fe_quant_token(const __nv_bfloat16* xrow, int H,
         }
         if ((lane % lanes_per_group) == 0) sfrow[k0 / vec] = static_cast<uint8_t>(sf_byte);
         const float inv = 1.0f / sf;
-        uint32_t packed = 0u;
-        #pragma unroll
-        for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(x[2 * j] * inv, x[2 * j + 1] * inv) << (8 * j);
-        *reinterpret_cast<uint32_t*>(qrow + k0 / 2) = packed;
+        if (fmt == 2) {
+            uint2 bytes;
+            bytes.x = cvt_e4m3x2(x[0] * inv, x[1] * inv) | (cvt_e4m3x2(x[2] * inv, x[3] * inv) << 16);
+            bytes.y = cvt_e4m3x2(x[4] * inv, x[5] * inv) | (cvt_e4m3x2(x[6] * inv, x[7] * inv) << 16);
+            *reinterpret_cast<uint2*>(qrow + k0) = bytes;
+        } else {
+            uint32_t packed = 0u;
+            #pragma unroll
+            for (int j = 0; j < 4; ++j) packed |= cvt_e2m1x2(x[2 * j] * inv, x[2 * j + 1] * inv) << (8 * j);
+            *reinterpret_cast<uint32_t*>(qrow + k0 / 2) = packed;
+        }
     }
     return __any_sync(0xffffffffu, nonzero);
 }

@@ -38,7 +38,9 @@ constexpr int kTileTokens = 16;         // UMMA N: token rows per task
 constexpr int kUnitK = 256;             // K elements per streamed unit (one 128 B swizzle atom of packed E2M1)
 constexpr int kUnitWBytes = kTileRows * 128;
 constexpr int kNumEpiThreads = 128, kNumStagerThreads = 64, kNumDispatchThreads = 192;
-constexpr uint32_t kBarEpi = 1, kBarStager = 2, kBarDispatch = 3;
+constexpr uint32_t kBarEpi = 1, kBarStager = 2, kBarDispatch = 3, kBarExp = 4;
+constexpr int kNumExpThreads = 128;      // FP8-activation variant: warps 8..11 widen the packed E2M1 weights to 8-bit containers
+constexpr uint32_t kXbufBytes = 2 * kUnitWBytes + 1024;   // one widened unit + its two scale planes
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kOtileBytes = 4096;
 constexpr uint32_t kVtBytes = kTileTokens * kTileRows * 4;   // fp32 accumulators of one task, token-major
@@ -87,6 +89,7 @@ struct KParams {
     int cnt_per_phase;
     uint32_t sm_act, sm_asf, sm_otile, sm_vt;   // dynamic shared memory offsets (stages start at 0)
     uint32_t act_bytes, asf_bytes;
+    uint32_t sm_xbuf; int nab;           // widened-unit buffers (FP8 variant); number of token staging buffers (1 or 2)
     unsigned long long timeout_ns;
     float* debug_acc; int debug_tasks;   // optional diagnostics: raw accumulators of SM 0's first tasks [task][token][row]
     unsigned long long* trace;           // optional diagnostics: 16 globaltimer stamps per SM
@@ -97,6 +100,7 @@ struct KParams {
 struct Ctl {
     uint64_t full[kMaxStages], empty[kMaxStages];
     uint64_t acts_full[2], acts_empty[2], tmem_full[2], tmem_empty[2];
+    uint64_t xfull[2], xempty[2];        // FP8-activation variant: widened weight units
     uint32_t tmem_base, epoch, abort_flag, ntasks;
     uint32_t rx_count[kMaxRanks], rx_prefix[kMaxRanks + 1];
     uint32_t exp_count[kMaxLocalExperts], mid_base[kMaxLocalExperts];
@@ -217,22 +221,22 @@ __device__ void role_loader(const Ctx& cx) {
 }
 
 // ============================================================================================= MMA issuer
-template <int kVec>
+template <int kVec, bool kA8>
 __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     const KParams& p = cx.p; Ctl& c = cx.c;
     constexpr uint32_t kPlanes = kUnitK / (4 * kVec);           // scale words per row per unit
-    constexpr uint32_t kIdesc = idesc_block_scaled(kFmtMxf4E2M1, kFmtMxf4E2M1, kTileRows, kTileTokens, kVec == 32 ? 1u : 0u);
+    constexpr uint32_t kIdesc = kA8 ? idesc_block_scaled(kFmtF8E2M1, kFmtF8E4M3, kTileRows, kTileTokens, 1u)
+                                    : idesc_block_scaled(kFmtMxf4E2M1, kFmtMxf4E2M1, kTileRows, kTileTokens, kVec == 32 ? 1u : 0u);
+    constexpr uint32_t kStepK = kA8 ? 32u : 64u;                // K elements per MMA instruction
+    constexpr uint32_t kStepsPerAtom = kA8 ? 4u : 4u;           // 128 B of operand bytes per swizzle atom either way
     const uint32_t tm = c.tmem_base;
     const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 16
     uint32_t it = 0, uc = 0;                                    // stages and units consumed so far
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
-        const uint32_t t = c.tasks[ti];
-        const uint32_t type = t >> 28;
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
-        const uint32_t ab = ti & 1u, acc = ti & 1u, use = (ti >> 1) & 1u;
-        (void)type;
-        if (!cx.warp_wait(&c.acts_full[ab], use, kErrWaitActsFull)) return;
+        const uint32_t ab = ti % p.nab, acc = ti & 1u, use_a = (ti / p.nab) & 1u, use = (ti >> 1) & 1u;
+        if (!cx.warp_wait(&c.acts_full[ab], use_a, kErrWaitActsFull)) return;
         if (!cx.warp_wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty)) return;
         tc_fence_after();
         const uint32_t act = smem_u32(cx.smem + p.sm_act + ab * p.act_bytes);
@@ -240,39 +244,44 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         for (int u0 = ub, nu; u0 < ue; u0 += nu, ++it) {
             nu = ue - u0 < p.stage_units ? ue - u0 : p.stage_units;
             const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
-            if (!cx.warp_wait(&c.full[s], ph, kErrWaitFull)) return;
+            uint64_t* ready = kA8 ? &c.xfull[it & 1u] : &c.full[s];
+            if (!cx.warp_wait(ready, kA8 ? (it >> 1) & 1u : ph, kErrWaitFull)) return;
             tc_fence_after();
             if (elect_one()) {
               if (it == 0) cx.trace(6);
               #pragma unroll 1
               for (int u = u0; u < u0 + nu; ++u, ++uc) {
-                const uint32_t wsm = smem_u32(cx.smem + static_cast<size_t>(s) * p.stage_bytes) + static_cast<uint32_t>(u - u0) * p.unit_bytes;
+                const uint32_t wsm = kA8 ? smem_u32(cx.smem + p.sm_xbuf + (it & 1u) * kXbufBytes)
+                                         : smem_u32(cx.smem + static_cast<size_t>(s) * p.stage_bytes) + static_cast<uint32_t>(u - u0) * p.unit_bytes;
+                const uint32_t wsf = wsm + (kA8 ? 2u * kUnitWBytes : static_cast<uint32_t>(kUnitWBytes));
                 const uint32_t sfa = tm + sfa_col + (uc & 1u) * 16u, sfb = tm + sfb_col + (uc & 1u) * 16u;
                 const uint32_t asf = smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes) + static_cast<uint32_t>(u) * kPlanes * 256u;
                 #pragma unroll
                 for (uint32_t pl = 0; pl < kPlanes; ++pl) {
-                    if (p.dbg & 1) break;
                     // one scale word (4 scale bytes, K span 4 * vec) per row: lane = row % 32, column = row / 32.
                     // Token rows fill lanes 0..15 of a plane; lanes 16..31 receive the next plane's bytes and are never read.
-                    utccp_32x128b_warpx4(sfa + pl * 4u, smem_desc(wsm + kUnitWBytes + pl * 512u, 128u, kLayoutNone));
+                    utccp_32x128b_warpx4(sfa + pl * 4u, smem_desc(wsf + pl * 512u, 128u, kLayoutNone));
                     utccp_32x128b_warpx4(sfb + pl * 4u, smem_desc(asf + pl * 256u, 128u, kLayoutNone));
                 }
-                const uint32_t bsm = act + static_cast<uint32_t>(u) * (kTileTokens * 128u);
+                // token tile: [K atoms][16 rows x 128 B]; an atom holds 256 packed E2M1 or 128 E4M3 elements
+                const uint32_t bsm = act + static_cast<uint32_t>(u) * (kA8 ? 2u : 1u) * (kTileTokens * 128u);
                 #pragma unroll
-                for (uint32_t ks = 0; ks < kUnitK / 64; ++ks) {
-                    if (p.dbg & 2) break;
-                    const uint32_t pl = (ks * 64u) / (4u * kVec), sf_id = ((ks * 64u) % (4u * kVec)) / kVec;
-                    const uint64_t adesc = smem_desc(wsm + ks * 32u, 1024u, kLayoutSw128);
-                    const uint64_t bdesc = smem_desc(bsm + ks * 32u, 1024u, kLayoutSw128);
+                for (uint32_t ks = 0; ks < kUnitK / kStepK; ++ks) {
+                    const uint32_t pl = (ks * kStepK) / (4u * kVec), sf_id = ((ks * kStepK) % (4u * kVec)) / kVec;
+                    const uint32_t atom = ks / kStepsPerAtom, in_atom = (ks % kStepsPerAtom) * 32u;
+                    const uint64_t adesc = smem_desc(wsm + (kA8 ? atom * kUnitWBytes : 0u) + in_atom, 1024u, kLayoutSw128);
+                    const uint64_t bdesc = smem_desc(bsm + (kA8 ? atom * (kTileTokens * 128u) : 0u) + in_atom, 1024u, kLayoutSw128);
                     const uint32_t idesc = idesc_with_sf(kIdesc, sf_id, sf_id);
                     const uint32_t accum = (u > ub || ks > 0) ? 1u : 0u;
-                    if constexpr (kVec == 32)
+                    if constexpr (kA8)
+                        umma_mxf8f6f4(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
+                    else if constexpr (kVec == 32)
                         umma_mxf4_block32(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
                     else
                         umma_nvf4_block16(tm + acc_col + acc * 16u, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
                 }
               }
-              tc_commit(&c.empty[s]);
+              tc_commit(kA8 ? &c.xempty[it & 1u] : &c.empty[s]);
             }
             __syncwarp();
         }
@@ -282,6 +291,40 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
             cx.trace(7);
         }
         __syncwarp();
+    }
+}
+
+// ============================================================================================= weight widener (FP8 variant)
+// kind::mxf8f6f4 reads 4-bit operands from 8-bit-wide shared-memory slots: every 16 E2M1 values (8 bytes) sit in a
+// 16-byte slot. HBM keeps the weights packed; four extra warps widen each streamed unit from its packed image
+// (128 rows x 128 B, one swizzle atom) into two atoms of 128 rows x 128 B and hand it to the MMA issuer.
+__device__ void role_expander(const Ctx& cx, uint32_t xtid) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    uint32_t it = 0;
+    #pragma unroll 1
+    for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
+        const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
+        #pragma unroll 1
+        for (int u = ub; u < ue; ++u, ++it) {
+            const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u, x = it & 1u;
+            if (bar_red_or(kBarExp, kNumExpThreads, !cx.warp_wait(&c.full[s], ph, kErrWaitFull))) return;
+            if (bar_red_or(kBarExp, kNumExpThreads, !cx.warp_wait(&c.xempty[x], ((it >> 1) & 1u) ^ 1u, kErrWaitEmpty))) return;
+            const uint8_t* wsm = cx.smem + static_cast<size_t>(s) * p.stage_bytes;
+            uint8_t* xb = cx.smem + p.sm_xbuf + x * kXbufBytes;
+            #pragma unroll
+            for (uint32_t k = 0; k < 8; ++k) {
+                const uint32_t idx = k * kNumExpThreads + xtid, r = idx >> 3, ch = idx & 7u;
+                const uint4 v = *reinterpret_cast<const uint4*>(wsm + r * 128u + ((ch ^ (r & 7u)) << 4));
+                uint8_t* drow = xb + (ch >> 2) * kUnitWBytes + r * 128u;
+                const uint32_t j0 = (2u * ch) & 7u;
+                *reinterpret_cast<uint4*>(drow + ((j0 ^ (r & 7u)) << 4)) = make_uint4(v.x, v.y, 0u, 0u);
+                *reinterpret_cast<uint4*>(drow + (((j0 + 1u) ^ (r & 7u)) << 4)) = make_uint4(v.z, v.w, 0u, 0u);
+            }
+            if (xtid < 64) *reinterpret_cast<uint4*>(xb + 2 * kUnitWBytes + xtid * 16u) = *reinterpret_cast<const uint4*>(wsm + kUnitWBytes + xtid * 16u);
+            fence_proxy_async_smem();
+            bar_sync(kBarExp, kNumExpThreads);
+            if (xtid == 0) { mbar_arrive(&c.xfull[x]); mbar_arrive(&c.empty[s]); }
+        }
     }
 }
 
@@ -310,11 +353,12 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
     uint32_t* l1_done = reinterpret_cast<uint32_t*>(cx.buf + p.off_ctrl + kCtrlL1Done) + cx.par * kMaxLocalExperts;
     uint32_t* rowref = c.rowref[sw];
     uint32_t* rowidx = c.rowidx[sw];
+    if (sw >= static_cast<uint32_t>(p.nab)) return;
     #pragma unroll 1
-    for (uint32_t ti = sw; ti < c.ntasks; ti += 2) {
+    for (uint32_t ti = sw; ti < c.ntasks; ti += p.nab) {      // with one staging buffer, stager 0 takes every task
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
-        const uint32_t ab = sw, use = (ti >> 1) & 1u, ring = ti & 3u;
+        const uint32_t ab = ti % p.nab, use = (ti / p.nab) & 1u, ring = ti & 3u;
         if (!cx.warp_wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty)) return;
         find_rows(c, rowref, total, e, mt, lane);
         const uint32_t left = c.exp_count[e] - mt * kTileTokens;
@@ -353,7 +397,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
         if (!__all_sync(0xffffffffu, ok)) return;
         uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
         uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
-        const uint32_t nchunk = (type ? p.I : p.H) / 32;                                   // 16 B chunks of one packed row
+        const uint32_t nchunk = (type ? p.mid_row_bytes : p.x_row_bytes) / 16;             // 16 B chunks of one token row
         const uint32_t sfchunk = (type ? p.mid_sf_row_bytes : p.x_sf_row_bytes) / 16;      // 16 B chunks of one row's scale bytes
         const uint32_t per_row = nchunk + sfchunk;
         const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
@@ -438,7 +482,7 @@ __device__ __forceinline__ void check_accumulate(const Ctx& cx, const uint8_t* w
     }
 }
 
-template <int kVec, bool kUmma>
+template <int kVec, bool kUmma, bool kA8>
 __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     const KParams& p = cx.p; Ctl& c = cx.c;
     const uint32_t ew = etid >> 5, lane = etid & 31u, row = etid;
@@ -450,7 +494,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF, j = t & 0xFF;
-        const uint32_t ab = ti & 1u, acc = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u;
+        const uint32_t ab = ti % p.nab, acc = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u;
         // ---- accumulators of the valid tokens -> shared memory (the loops below run over the valid tokens only)
         bool ok;
         uint32_t nv = 0;
@@ -576,7 +620,10 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 amax = fmaxf(amax, 1e-30f);
                 const float av = vt[n * kTileRows];
                 uint32_t sf_byte; float scaled;
-                if constexpr (kVec == 32) {
+                if constexpr (kA8) {
+                    sf_byte = ceil_pow2_exp(__fdiv_rn(amax, 448.0f));
+                    scaled = __fdiv_rn(av, __uint_as_float(sf_byte << 23));
+                } else if constexpr (kVec == 32) {
                     sf_byte = ceil_pow2_exp(__fdiv_rn(amax, 6.0f));
                     scaled = __fdiv_rn(av, __uint_as_float(sf_byte << 23));
                 } else {
@@ -585,18 +632,25 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                     scaled = sf > 0.f ? __fdiv_rn(av, sf) : (av == 0.f ? 0.f : copysignf(6.0f, av));
                 }
                 const float nb = __shfl_down_sync(0xffffffffu, scaled, 1);
-                if (!is_up && (lane & 1u) == 0u)
-                    otile[n * 32 + ew * 8u + (lane >> 4) * 4u + ((lane & 7u) >> 1)] = static_cast<uint8_t>(cvt_e2m1x2(scaled, nb));
+                if (!is_up && (lane & 1u) == 0u) {
+                    if constexpr (kA8)
+                        *reinterpret_cast<uint16_t*>(otile + n * 64u + ew * 16u + (lane >> 4) * 8u + (lane & 7u)) = static_cast<uint16_t>(cvt_e4m3x2(scaled, nb));
+                    else
+                        otile[n * 32 + ew * 8u + (lane >> 4) * 4u + ((lane & 7u) >> 1)] = static_cast<uint8_t>(cvt_e2m1x2(scaled, nb));
+                }
                 if (lane == 0 && (kVec == 16 || (ew & 1u) == 0u)) {
                     const uint32_t sfi = kVec == 32 ? 2u * j + (ew >> 1) : 4u * j + ew;
                     cx.buf[p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes + sfi] = static_cast<uint8_t>(sf_byte);
                 }
             }
             bar_sync(kBarEpi, kNumEpiThreads);
-            if (etid < nv * 2u) {
-                const uint32_t n = etid >> 1, half = etid & 1u;
-                const uint4 val = *reinterpret_cast<const uint4*>(otile + n * 32u + half * 16u);
-                st_global_v4(cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes + j * 32u + half * 16u, val);
+            {
+                constexpr uint32_t kChunks = kA8 ? 4u : 2u;                    // 16 B chunks of one token's 64 output columns
+                if (etid < nv * kChunks) {
+                    const uint32_t n = etid / kChunks, q16 = etid % kChunks;
+                    const uint4 val = *reinterpret_cast<const uint4*>(otile + (n * kChunks + q16) * 16u);
+                    st_global_v4(cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes + (j * kChunks + q16) * 16u, val);
+                }
             }
             bar_sync(kBarEpi, kNumEpiThreads);          // orders every thread's stores before the release below
             if (etid == 0) { red_release_gpu_add(l1_done + e, 1u); cx.trace(23); }
@@ -620,8 +674,9 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
 }
 
 // ============================================================================================= the kernel
-template <int kVec, bool kUmma, bool kFe>
-__global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_constant__ KParams p) {
+template <int kVec, bool kUmma, bool kFe, bool kA8>
+__global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1) mega_moe_kernel(const __grid_constant__ KParams p) {
+    constexpr uint32_t kNT = kA8 ? kThreads + kNumExpThreads : kThreads;       // threads of this instantiation
     extern __shared__ uint8_t smem_raw[];
     __shared__ Ctl c;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023u));
@@ -639,6 +694,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         for (int i = 0; i < 2; ++i) {
             mbar_init(&c.acts_full[i], 1); mbar_init(&c.acts_empty[i], kUmma ? 1 : kNumEpiThreads);
             mbar_init(&c.tmem_full[i], 1); mbar_init(&c.tmem_empty[i], kNumEpiThreads);
+            mbar_init(&c.xfull[i], 1); mbar_init(&c.xempty[i], 1);
         }
         mbar_fence_init();
     }
@@ -666,7 +722,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
 
     // ---- router frontend (optional): all SMs compute logits; the dispatching SMs select the top-8 of every token
     if constexpr (kFe) {
-        fe_logits_items(p.fe, bid * (kThreads / 32) + warp, G * (kThreads / 32), lane);
+        fe_logits_items(p.fe, bid * (kNT / 32) + warp, G * (kNT / 32), lane);
         __syncthreads();
         uint32_t* fe_arrive = ctrl32 + kCtrlFeArrive / 4;
         if (tid == 0) red_release_gpu_add(fe_arrive, 1u);
@@ -683,7 +739,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
             __syncthreads();
             float* sc = reinterpret_cast<float*>(smem + p.sm_act) + warp * p.fe.E;
             #pragma unroll 1
-            for (uint32_t t = warp; t < static_cast<uint32_t>(p.T); t += kThreads / 32) {
+            for (uint32_t t = warp; t < static_cast<uint32_t>(p.T); t += kNT / 32) {
                 const bool nz = fe_row_nonzero(p.fe.hidden + static_cast<size_t>(t) * p.H, p.H, lane);
                 fe_select_token(p.fe, t, sc, nz, lane);
             }
@@ -716,7 +772,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         if constexpr (kFe) {
             // quantise the tokens this SM is about to send into the x / x_sf views (the same bytes whichever SM writes them)
             #pragma unroll 1
-            for (uint32_t i = warp; i < cnt; i += kThreads / 32) {
+            for (uint32_t i = warp; i < cnt; i += kNT / 32) {
                 const uint32_t tok = dlist[i] >> 16;
                 fe_quant_token(p.fe.hidden + static_cast<size_t>(tok) * p.H, p.H, kVec == 32 ? 0 : 1, p.fe.x_gs,
                                buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes,
@@ -729,7 +785,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         const float* tw = reinterpret_cast<const float*>(buf + p.off_topk_w);
         // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (four in flight)
         #pragma unroll 1
-        for (uint32_t i = warp; i < cnt; i += kThreads / 32) {
+        for (uint32_t i = warp; i < cnt; i += kNT / 32) {
             const uint32_t ent = dlist[i], tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
             const uint8_t* xs_src = buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
             const uint8_t* sf_src = buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
@@ -765,7 +821,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
 
     // ---- the staging buffers start from zero: rows beyond a task's valid tokens only ever hold finite bytes
     #pragma unroll 1
-    for (uint32_t off = tid * 16u; off < 2u * (p.act_bytes + p.asf_bytes); off += kThreads * 16u)
+    for (uint32_t off = tid * 16u; off < p.nab * (p.act_bytes + p.asf_bytes); off += kNT * 16u)
         *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
 
     // ---- receive: wait for every source rank's flag, then scan the received rows' records
@@ -795,7 +851,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
         }
         if (total <= kMetaCap) {
             #pragma unroll 1
-            for (uint32_t f = tid; f < total; f += kThreads) {
+            for (uint32_t f = tid; f < total; f += kNT) {
                 uint32_t r = 0;
                 #pragma unroll
                 for (int q = 1; q < kMaxRanks; ++q) r += (q < p.R && f >= pre[q]) ? 1u : 0u;
@@ -895,9 +951,10 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     // ---- roles
     if (!cx.aborted()) {
         if (warp == 0) role_loader(cx);
-        else if (warp == 1) { if constexpr (kUmma) role_mma<kVec>(cx, lane); }
+        else if (warp == 1) { if constexpr (kUmma) role_mma<kVec, kA8>(cx, lane); }
         else if (warp < 4) role_stager(cx, warp - 2, lane);
-        else role_epilogue<kVec, kUmma>(cx, tid - 128);
+        else if (warp < 8) role_epilogue<kVec, kUmma, kA8>(cx, tid - 128);
+        else { if constexpr (kA8) role_expander(cx, tid - kThreads); }
     }
     __syncthreads();
     if (bid == 0 && tid == 0) cx.stamp(kStampTasksDone);
@@ -942,7 +999,7 @@ __global__ void __launch_bounds__(kThreads, 1) mega_moe_kernel(const __grid_cons
     if (!cx.aborted()) {
         // item idx = (token, 16 B chunk); consecutive items go to different SMs so that a small batch uses the whole GPU
         #pragma unroll 1
-        for (uint32_t idx = first_item; idx < nitems; idx += G * kThreads) {
+        for (uint32_t idx = first_item; idx < nitems; idx += G * kNT) {
             const uint32_t tok = idx / chunks_per_row, ch = idx % chunks_per_row;
             uint32_t mask = first_mask;
             if (idx != first_item) {

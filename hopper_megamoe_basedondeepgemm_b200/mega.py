@@ -68,7 +68,9 @@ class SymmBuffer:
 
         def view(off, nbytes_, dtype, shape):
             return self.buffer[off:off + nbytes_].view(dtype).view(*shape)
-        self.x = view(L.off_x, t * L.x_row_bytes, torch.int8, (t, int(L.x_row_bytes)))
+        # packed E2M1 pairs as int8 [t, hidden / 2], or E4M3 [t, hidden] for the FP8-activation variant
+        self.x = view(L.off_x, t * L.x_row_bytes, torch.float8_e4m3fn if act_format == 'fp8' else torch.int8,
+                      (t, int(L.x_row_bytes)))
         self.x_sf = view(L.off_x_sf, t * L.x_sf_row_bytes, torch.int32, (t, hidden // (4 * vec)))
         self.topk_idx = view(L.off_topk_idx, t * num_topk * 8, torch.int64, (t, num_topk))
         self.topk_weights = view(L.off_topk_weights, t * num_topk * 4, torch.float32, (t, num_topk))
@@ -151,7 +153,7 @@ def _launch(y, l1_weights, l2_weights, sym_buffer: SymmBuffer, stats, recipe, ac
     if activation != 'swiglu':
         raise RuntimeError('only the swiglu activation is supported')
     b = sym_buffer
-    vec = b.act_sf_vec_size
+    vec = b.act_sf_vec_size or 32        # FP8 tokens carry one UE8M0 scale per 32 elements, like the MXFP4 weights
     if tuple(recipe) != (1, 1, vec):
         raise RuntimeError(f'recipe {recipe} does not match the buffer format {b.act_format}')
     if y.dtype != torch.bfloat16 or y.dim() != 2 or y.size(1) != b.hidden or not y.is_contiguous():
@@ -206,9 +208,19 @@ def fp4_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBu
 def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
                      cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
                      recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = 'swiglu',
-                     activation_clamp: Optional[float] = None, fast_math: bool = True):
-    """W-MXFP4 x A-FP8 MegaMoE (`sm100_b200/mega___init__.py:221-241`)."""
-    raise RuntimeError('fp8_fp4_mega_moe: the FP8-activation variant is not built yet')
+                     activation_clamp: Optional[float] = None, fast_math: bool = True, *,
+                     engine: str = 'umma', timeout_ms: float = 0.0,
+                     debug_accumulators: Optional[torch.Tensor] = None, debug_trace: Optional[torch.Tensor] = None):
+    """W-MXFP4 x A-FP8 MegaMoE (`sm100_b200/mega___init__.py:221-241`).
+
+    Tokens are E4M3 with one UE8M0 scale per 32 elements, the intermediate is requantised the same way, weights are
+    the MXFP4 streams of `transform_weights_for_mega_moe`. The tensor cores read 4-bit operands of an 8-bit x 4-bit
+    product from byte-wide slots, so the kernel widens each streamed weight unit in shared memory; HBM traffic is
+    that of the W4A4 variant.
+    """
+    assert sym_buffer.act_format == 'fp8', 'buffer must be created with act_format fp8'
+    _launch(y, l1_weights, l2_weights, sym_buffer, cumulative_local_expert_recv_stats, recipe, activation,
+            activation_clamp, fast_math, engine, (1.0, 1.0, 1.0, 1.0), timeout_ms, debug_accumulators, debug_trace)
 
 
 def mega_moe_from_hidden(y: torch.Tensor, hidden: torch.Tensor, router_weight: torch.Tensor, l1_weights, l2_weights,

@@ -35,9 +35,13 @@ def run_layer(fmt, e_local, hidden, inter, topk, tokens, routing, engine, seed=0
     U.write_inputs(buf, inp, sfb)
     y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
     stats = torch.full((e_local,), 7, dtype=torch.int32, device=dev)
-    mm.fp4_fp4_mega_moe(y, l1, l2, buf, cumulative_local_expert_recv_stats=stats, activation_clamp=clamp,
-                        fast_math=True, engine=engine, x_global_scale=x_gs, l1_global_scale=gs1,
-                        l2_global_scale=gs2, mid_global_scale=mid_gs, timeout_ms=500.0)
+    if fmt == 'fp8':
+        mm.fp8_fp4_mega_moe(y, l1, l2, buf, cumulative_local_expert_recv_stats=stats, activation_clamp=clamp,
+                            fast_math=True, engine=engine, timeout_ms=500.0)
+    else:
+        mm.fp4_fp4_mega_moe(y, l1, l2, buf, cumulative_local_expert_recv_stats=stats, activation_clamp=clamp,
+                            fast_math=True, engine=engine, x_global_scale=x_gs, l1_global_scale=gs1,
+                            l2_global_scale=gs2, mid_global_scale=mid_gs, timeout_ms=500.0)
     st, words = buf.device_status()
     assert st == 0, f'device status {st}: {[hex(v) for v in words[:4]]}'
     return y.cpu(), stats.cpu(), ref, buf, inp
@@ -59,8 +63,9 @@ def check_against_oracle(y, stats, ref, buf, fmt, inter):
             continue
         got_q = mid[base:base + cnt]
         got_sf = mid_sf[base:base + cnt, :inter // vec]
-        want = O.dequant_fp4_rows(ref.mid_q[0][e], O.sf_bytes_to_float(ref.mid_sf[0][e], fmt), vec)
-        got = O.dequant_fp4_rows(got_q, O.sf_bytes_to_float(got_sf, fmt), vec)
+        deq = O.dequant_fp8_rows if fmt == 'fp8' else (lambda q, sf: O.dequant_fp4_rows(q, sf, vec))
+        want = deq(ref.mid_q[0][e], O.sf_bytes_to_float(ref.mid_sf[0][e], fmt))
+        got = deq(got_q, O.sf_bytes_to_float(got_sf, fmt))
         # rows in the right order: each row is far closer to its own reference row than to any other
         assert O.rel_rmse(got, want) < 0.05, (e, O.rel_rmse(got, want))
         mismatched += int((got != want).sum())
@@ -74,6 +79,23 @@ def check_against_oracle(y, stats, ref, buf, fmt, inter):
 def test_small_layer(engine, fmt):
     y, stats, ref, buf, _ = run_layer(fmt, e_local=4, hidden=512, inter=256, topk=2, tokens=5, routing='random', engine=engine)
     check_against_oracle(y, stats, ref, buf, fmt, 256)
+
+
+def test_small_layer_fp8_activations():
+    y, stats, ref, buf, _ = run_layer('fp8', e_local=4, hidden=512, inter=256, topk=2, tokens=5, routing='random', engine='umma')
+    check_against_oracle(y, stats, ref, buf, 'fp8', 256)
+
+
+def test_many_rows_fp8_activations():
+    y, stats, ref, buf, _ = run_layer('fp8', e_local=4, hidden=1024, inter=512, topk=3, tokens=40, routing='random',
+                                      engine='umma', masked_ratio=0.2)
+    check_against_oracle(y, stats, ref, buf, 'fp8', 512)
+
+
+def test_full_shape_fp8_activations():
+    y, stats, ref, buf, _ = run_layer('fp8', e_local=48, hidden=3072, inter=1280, topk=8, tokens=8, routing='balanced',
+                                      engine='umma', std=0.02)
+    check_against_oracle(y, stats, ref, buf, 'fp8', 1280)
 
 
 @pytest.mark.parametrize('engine', ['check', 'umma'])

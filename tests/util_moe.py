@@ -44,7 +44,7 @@ def write_inputs(buf, inp: O.RankInput, sfb: torch.Tensor):
     t = inp.x_q.shape[0]
     if t == 0:
         return
-    buf.x[:t].copy_(inp.x_q.view(torch.int8))
+    buf.x[:t].copy_(inp.x_q.view(buf.x.dtype))
     buf.x_sf[:t].copy_(sfb.contiguous().view(torch.int32))
     buf.topk_idx[:t].copy_(inp.topk_idx)
     buf.topk_weights[:t].copy_(inp.topk_weights)

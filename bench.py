@@ -18,6 +18,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 HIDDEN, INTER, TOPK, E_LOCAL = 3072, 1280, 8, 48
+DTYPE_NAME = {'mxfp4': 'fp4 (e2m1) x fp4, fp32 accumulate', 'nvfp4': 'fp4 (e2m1) x fp4, fp32 accumulate',
+              'fp8': 'fp8 (e4m3) x fp4 (e2m1), fp32 accumulate'}
 PUBLISHED_US = {}          # BASELINE.json `published` is empty: no number measured for this exact metric
 
 
@@ -97,7 +99,7 @@ def run_reference(args):
               f'over 48 experts, H=3072, I=1280, {args.format}; weights dequantised inside the timed call')
     line = {'impl': 'reference', 'metric': 'moe_layer_kernel_us', 'value': us, 'unit': 'us', 'n_gpus': args.gpus,
             'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': us / 1e3, 'higher_is_better': False,
-            'scaling': 'weak', 'vs_baseline': None, 'dtype': 'fp4 (e2m1) x fp4, fp32 accumulate', 'data': 'synthetic',
+            'scaling': 'weak', 'vs_baseline': None, 'dtype': DTYPE_NAME[args.format], 'data': 'synthetic',
             'config': workload_config(args, args.gpus),
             'cpu_baseline': {'value': us, 'unit': 'us', 'cores': cores, 'kind': 'port', 'sample': sample},
             'e2e': {'value': us, 'unit': 'us', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0}}
@@ -105,7 +107,7 @@ def run_reference(args):
 
 
 def workload_config(args, n):
-    return {'workload': f'EP{n} W4A4 {args.format.upper()} MegaMoE layer, E={E_LOCAL * n} ({E_LOCAL}/rank), H={HIDDEN}, '
+    return {'workload': f'EP{n} {"W4A8 (MXFP4 x FP8)" if args.format == "fp8" else "W4A4 " + args.format.upper()} MegaMoE layer, E={E_LOCAL * n} ({E_LOCAL}/rank), H={HIDDEN}, '
                         f'I={INTER}, top-{TOPK}, forced-balanced routing, {args.tokens_per_rank} token(s) per rank '
                         f'(global M={args.tokens_per_rank * n}), weights ~N(0,0.02)',
             'l2': 'flushed by a 256 MiB write before every timed step; then the inputs are copied into the buffer views', 'parallelism': f'ep{n}'}
@@ -118,7 +120,7 @@ def main():
     ap.add_argument('--warmup', type=int, default=5)
     ap.add_argument('--impl', default='ours', choices=['ours', 'reference'])
     ap.add_argument('--tokens-per-rank', type=int, default=1)
-    ap.add_argument('--format', default='mxfp4', choices=['mxfp4', 'nvfp4'])
+    ap.add_argument('--format', default='mxfp4', choices=['mxfp4', 'nvfp4', 'fp8'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--num-sms', type=int, default=0)
     args = ap.parse_args()
@@ -162,8 +164,11 @@ def main():
             buf.x[:T].copy_(xq); buf.x_sf[:T].copy_(xsf); buf.topk_idx[:T].copy_(idx); buf.topk_weights[:T].copy_(tw)
 
     def launch():
-        mm.fp4_fp4_mega_moe(y, l1, l2, buf, activation_clamp=10.0, fast_math=True, x_global_scale=x_gs,
-                            l1_global_scale=gs1, l2_global_scale=gs2, mid_global_scale=mid_gs)
+        if fmt == 'fp8':
+            mm.fp8_fp4_mega_moe(y, l1, l2, buf, activation_clamp=10.0, fast_math=True)
+        else:
+            mm.fp4_fp4_mega_moe(y, l1, l2, buf, activation_clamp=10.0, fast_math=True, x_global_scale=x_gs,
+                                l1_global_scale=gs1, l2_global_scale=gs2, mid_global_scale=mid_gs)
 
     def timed(step_fn, steps, warm, e2e=False):
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
@@ -239,12 +244,12 @@ def main():
         achieved = alg_bytes / (mean_us * 1e-6) / 1e9
         line = {'metric': 'moe_layer_kernel_us', 'value': mean_us, 'unit': 'us', 'n_gpus': n, 'steps': args.steps,
                 'warmup': W_WARM, 'ms_per_step': mean_us / 1e3, 'higher_is_better': False, 'scaling': 'weak',
-                'vs_baseline': None, 'dtype': 'fp4 (e2m1) x fp4, fp32 accumulate', 'data': 'synthetic',
+                'vs_baseline': None, 'dtype': DTYPE_NAME[fmt], 'data': 'synthetic',
                 'config': workload_config(args, n), 'timing': 'CUDA events around each launch, mean of the timed steps, max over ranks',
                 'median_us': med_us, 'device_span_us_median': span_us, 'phases_us_sm0_last_launch': phases, 'wall_s': t_wall,
                 'clocks': clocks, 'gpu_launches': args.steps,
                 'e2e': {'value': e2e_us, 'unit': 'us',
-                        'h2d_bytes_per_step': int(h_x.numel() + h_sf.numel() * 4 + h_idx.numel() * 8 + h_w.numel() * 4),
+                        'h2d_bytes_per_step': int(h_x.numel() * h_x.element_size() + h_sf.numel() * 4 + h_idx.numel() * 8 + h_w.numel() * 4),
                         'd2h_bytes_per_step': int(h_y.numel() * 2)},
                 'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
                              'traffic': (int(alg_bytes * 1.0035) if (fmt == 'mxfp4' and n == 1) else None), 'traffic_source': 'dram__bytes_read+write of one ncu capture of this workload, scaled by the active experts (profiles/)', 'peak_source': peak_src,

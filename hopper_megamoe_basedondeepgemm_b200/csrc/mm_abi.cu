@@ -304,8 +304,8 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     if (fe->num_tokens != a->num_tokens) return MM_ERR_INVALID_ARGUMENT;
     if (cfg->num_topk != 8 || cfg->num_experts > 1024) return MM_ERR_UNSUPPORTED;
     if (fe->score_mode == 1 && fe->expert_bias == nullptr) return MM_ERR_INVALID_ARGUMENT;
-    if (cfg->act_format == MM_FMT_FP8) return MM_ERR_UNSUPPORTED;          // the fused frontend writes packed E2M1 tokens only
-    if (static_cast<size_t>(cfg->num_experts) * 4 * (mm::kThreads / 32) > p.nab * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
+    const bool a8 = cfg->act_format == MM_FMT_FP8;
+    if (static_cast<size_t>(cfg->num_experts) * 4 * ((mm::kThreads + (a8 ? mm::kNumExpThreads : 0)) / 32) > p.nab * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
     mm_layout_t L;
     mm_get_layout(cfg, &L);
     uint8_t* b = static_cast<uint8_t*>(a->buffer);
@@ -325,6 +325,8 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     p.fe_enabled = 1;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (a->engine != MM_ENGINE_UMMA) return MM_ERR_UNSUPPORTED;     // the cross-check engine takes pre-routed inputs only
+    if (a8) return fe->num_tokens == 0 ? launch_variant<32, true, false, true>(p, grid, smem_bytes, s)
+                                       : launch_variant<32, true, true, true>(p, grid, smem_bytes, s);
     if (fe->num_tokens == 0) return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, true>(p, grid, smem_bytes, s)
                                                                     : launch_variant<16, true>(p, grid, smem_bytes, s);
     return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, true, true>(p, grid, smem_bytes, s)

@@ -774,7 +774,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             #pragma unroll 1
             for (uint32_t i = warp; i < cnt; i += kNT / 32) {
                 const uint32_t tok = dlist[i] >> 16;
-                fe_quant_token(p.fe.hidden + static_cast<size_t>(tok) * p.H, p.H, kVec == 32 ? 0 : 1, p.fe.x_gs,
+                fe_quant_token(p.fe.hidden + static_cast<size_t>(tok) * p.H, p.H, kA8 ? 2 : (kVec == 32 ? 0 : 1), p.fe.x_gs,
                                buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes,
                                buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes, lane);
             }

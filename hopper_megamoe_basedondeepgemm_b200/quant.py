@@ -53,6 +53,21 @@ def cast_rows_to_fp4(t: torch.Tensor, fmt: str, global_scale: float = 1.0
     return packed, sf, sf_b.contiguous().view(torch.int32)
 
 
+def cast_rows_to_fp8(t: torch.Tensor) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """[M, K] -> (E4M3 [M, K], scales fp32 [M, K/32], scales int32 [M, K/128], 4 UE8M0 bytes per word).
+
+    `per_token_cast_to_fp8(x, use_ue8m0=True, gran_k=32)` of `deep_gemm/utils/math.py:26-38`: block maxima clamped at
+    1e-4, scale 2^ceil(log2(amax / 448)).
+    """
+    m, k = t.shape
+    g = t.float().view(m, k // 32, 32)
+    amax = g.abs().amax(dim=-1).clamp_min(1e-4)
+    sf = ceil_to_ue8m0(amax / 448.0)
+    sf_b = (sf.view(torch.int32) >> 23).to(torch.uint8)
+    q = (g * (1.0 / sf.unsqueeze(-1))).clamp(-448.0, 448.0).to(torch.float8_e4m3fn).view(m, k)
+    return q, sf, sf_b.contiguous().view(torch.int32)
+
+
 def cast_grouped_weights_to_fp4(w: torch.Tensor, fmt: str, global_scale: float = 1.0
                                 ) -> Tuple[torch.Tensor, torch.Tensor]:
     """bf16 [E, N, K] -> (packed int8 [E, N, K/2], scales int32 [E, N, K/(4 vec)] stored MN-major).

@@ -47,10 +47,10 @@ def make_layer_weights(e_local: int, hidden: int, inter: int, fmt: str, seed: in
 
 
 def make_tokens(num_tokens: int, hidden: int, fmt: str, seed: int, device='cuda', global_scale: float = 1.0):
-    """bf16 tokens ~ N(0, 1) and their quantised form (packed int8, scale words int32)."""
+    """bf16 tokens ~ N(0, 1) and their quantised form (packed E2M1 as int8, or E4M3 for 'fp8'; scale words int32)."""
     g = torch.Generator(device=device).manual_seed(seed)
     x = torch.randn((num_tokens, hidden), generator=g, device=device, dtype=torch.float32).to(torch.bfloat16)
-    packed, _, words = quant.cast_rows_to_fp4(x, fmt, global_scale)
+    packed, _, words = quant.cast_rows_to_fp8(x) if fmt == 'fp8' else quant.cast_rows_to_fp4(x, fmt, global_scale)
     return x, packed, words
 
 

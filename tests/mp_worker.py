@@ -43,8 +43,8 @@ def main():
         y = torch.empty((tokens[rank], hidden), dtype=torch.bfloat16, device='cuda')
         stats = torch.zeros(e_local, dtype=torch.int32, device='cuda')
         dist.barrier()
-        mm.fp4_fp4_mega_moe(y, l1, l2, buf, cumulative_local_expert_recv_stats=stats, activation_clamp=10.0,
-                            engine=engine, timeout_ms=2000.0)
+        op = mm.fp8_fp4_mega_moe if fmt == 'fp8' else mm.fp4_fp4_mega_moe
+        op(y, l1, l2, buf, cumulative_local_expert_recv_stats=stats, activation_clamp=10.0, engine=engine, timeout_ms=2000.0)
         st, words = buf.device_status()
         if st != 0:
             print(f'rank {rank}: device status {st} {[hex(v) for v in words[:4]]}', flush=True)
@@ -65,8 +65,9 @@ def main():
         for e, cnt in enumerate(ref.counts[rank].tolist()):
             if cnt == 0:
                 continue
-            got = O.dequant_fp4_rows(mid[base:base + cnt], O.sf_bytes_to_float(mid_sf[base:base + cnt, :inter // vec], fmt), vec)
-            want = O.dequant_fp4_rows(ref.mid_q[rank][e], O.sf_bytes_to_float(ref.mid_sf[rank][e], fmt), vec)
+            deq = O.dequant_fp8_rows if fmt == 'fp8' else (lambda q, sf: O.dequant_fp4_rows(q, sf, vec))
+            got = deq(mid[base:base + cnt], O.sf_bytes_to_float(mid_sf[base:base + cnt, :inter // vec], fmt))
+            want = deq(ref.mid_q[rank][e], O.sf_bytes_to_float(ref.mid_sf[rank][e], fmt))
             if O.rel_rmse(got, want) > 0.05:
                 print(f'rank {rank} it {it}: expert {e} intermediate rows differ ({O.rel_rmse(got, want):.3f})', flush=True)
                 ok = False

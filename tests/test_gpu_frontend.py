@@ -9,9 +9,12 @@ from tests import util_moe as U
 pytestmark = pytest.mark.gpu
 
 
-def _canon(packed):
-    """-0 and +0 are the same E2M1 value: clear the sign of zero nibbles before comparing bytes."""
+def _canon(packed, fmt='mxfp4'):
+    """-0 and +0 are the same value: clear the sign of zero nibbles (E2M1) or bytes (E4M3) before comparing."""
     u = packed.view(torch.uint8).clone()
+    if fmt == 'fp8':
+        u[u == 0x80] = 0
+        return u
     lo, hi = u & 0xF, u >> 4
     lo[lo == 8] = 0
     hi[hi == 8] = 0
@@ -55,7 +58,7 @@ def test_frontend_384_experts_through_the_c_abi():
     assert torch.allclose(got_w, w, rtol=2e-6, atol=1e-7)
 
 
-@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4'])
+@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4', 'fp8'])
 @pytest.mark.parametrize('score_mode', [0, 1])
 def test_frontend_matches_oracle(fmt, score_mode):
     tokens, num_experts, hidden = 9, 48, 3072
@@ -82,7 +85,7 @@ def test_frontend_matches_oracle(fmt, score_mode):
     assert same >= tokens - 1
     # quantised tokens
     q, sf, sfb = O.quantise_tokens(x, fmt, rounding='rne', sf_rule='mul', global_scale=x_gs)
-    assert torch.equal(_canon(buf.x[:tokens].cpu()), _canon(q))
+    assert torch.equal(_canon(buf.x[:tokens].cpu(), fmt), _canon(q, fmt))
     got_sf = buf.x_sf[:tokens].cpu().contiguous().view(torch.uint8).view(tokens, -1)
     assert torch.equal(got_sf, sfb)
 
@@ -107,7 +110,7 @@ def test_frontend_then_layer_matches_oracle():
     assert O.rel_rmse(y.cpu(), ref.y[0]) <= 3e-3 and O.cosine(y.cpu(), ref.y[0]) >= 0.9999
 
 
-@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4'])
+@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4', 'fp8'])
 def test_layer_from_hidden_states_in_one_kernel(fmt):
     """Router, top-8, quantisation, dispatch, both GEMMs and the combine in a single launch."""
     tokens, e_local, hidden, inter = 7, 48, 3072, 1280
@@ -131,7 +134,7 @@ def test_layer_from_hidden_states_in_one_kernel(fmt):
     assert torch.equal(buf.topk_idx[:tokens].cpu(), idx)
     q, sf, sfb = O.quantise_tokens(x, fmt, rounding='rne', sf_rule='mul', global_scale=x_gs)
     routed = (idx >= 0).any(dim=1)
-    assert torch.equal(_canon(buf.x[:tokens].cpu())[routed], _canon(q)[routed])
+    assert torch.equal(_canon(buf.x[:tokens].cpu(), fmt)[routed], _canon(q, fmt)[routed])
     ref = O.moe_layer_reference([O.RankInput(q, sf, idx, tw)], [w], fmt, e_local, clamp=10.0, x_global_scale=x_gs,
                                 w1_global_scale=gs1, w2_global_scale=gs2, mid_global_scale=mid_gs)
     assert O.rel_rmse(y.cpu(), ref.y[0]) <= 3e-3 and O.cosine(y.cpu(), ref.y[0]) >= 0.9999

@@ -18,7 +18,7 @@ def _run(nproc, fmt, engine='umma'):
     assert 'MP_OK' in res.stdout, res.stdout[-3000:] + res.stderr[-3000:]
 
 
-@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4'])
+@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4', 'fp8'])
 def test_two_ranks(fmt):
     if torch.cuda.device_count() < 2:
         pytest.skip('needs two GPUs')

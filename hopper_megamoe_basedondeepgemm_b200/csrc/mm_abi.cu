@@ -206,6 +206,7 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.stage_bytes = p.stage_units * p.unit_bytes;
     // two token staging buffers when that leaves at least four stream stages, else one
     p.nab = 2;
+    { const char* d = getenv("MM_NAB"); if (d) p.nab = atoi(d); }
     size_t fixed = p.nab * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes + mm::kVtBytes + xbytes;
     if (fixed + 4 * static_cast<size_t>(p.stage_bytes) > budget) {
         p.nab = 1;
@@ -213,7 +214,15 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     }
     if (fixed + 2 * static_cast<size_t>(p.stage_bytes) > budget) return MM_ERR_UNSUPPORTED;
     int nstage = static_cast<int>((budget - fixed) / p.stage_bytes);
-    if (nstage > mm::kMaxStages) nstage = mm::kMaxStages;
+    // A short ring is faster than a deep one: the loader runs ahead into the next phase's weights, and with many stages
+    // that prefetch competes with the stream the current phase is waiting for (measured: 4 stages beat 8 by 2 us).
+    {
+        int want = mm::kDefaultStages;
+        const char* d = getenv("MM_NSTAGE");
+        if (d) want = atoi(d);
+        if (want > mm::kMaxStages) want = mm::kMaxStages;
+        if (nstage > want) nstage = want;
+    }
     if (nstage < 2) return MM_ERR_UNSUPPORTED;
     p.nstage = nstage;
     { const char* d = getenv("MM_L1_INFLIGHT"); p.l1_inflight = d ? atoi(d) : 0; }

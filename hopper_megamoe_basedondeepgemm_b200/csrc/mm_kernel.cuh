@@ -3,12 +3,16 @@
 //   dispatch  : SM d (< ranks) packs this rank's routed rows for rank d and stores them, densely and in (token, slot)
 //               order, into a region of rank d's receive pool that only this rank writes; one release store of
 //               (epoch, row count) then tells rank d that the rows are complete. No ticket atomics, no collective.
-//   schedule  : every SM reads the R flags, scans the received rows' expert ids and derives the same task list
-//               (L1 tiles of all active experts, then L2 tiles); its own tasks are those of a closed-form owner map.
+//   schedule  : every SM reads the R flags, scans the received rows' expert ids and derives its own task list in closed
+//               form (L1 tiles of all active experts, then L2 tiles). A phase's NT tiles are split in two: the first
+//               NT % SMs tiles are cut along K into equal unit ranges, one per SM (partial sums parked in global memory,
+//               summed in SM order by the last contributor); the rest are whole tiles dealt round-robin.
 //   L1 GEMM   : 128 weight rows x 16 tokens per task, swap-AB block-scaled tcgen05 MMA, accumulators in TMEM. Weights
 //               arrive as pre-tiled 128 B-swizzled units with their scale planes by one bulk async copy per stage.
-//   L1 epilog : SwiGLU * top-k weight, requantise to E2M1 (+ scale byte), store to the local intermediate pool,
-//               release-add on the expert's arrival counter.
+//               FP8-activation variant: four more warps widen every packed unit to byte-wide operand slots in shared
+//               memory (kind::mxf8f6f4 reads 4-bit values from 8-bit containers); HBM still streams the packed form.
+//   L1 epilog : SwiGLU * top-k weight, requantise to E2M1 or E4M3 (+ scale byte), store to the local intermediate
+//               pool, release-add on the expert's arrival counter.
 //   L2 GEMM   : acquires that counter, same main loop on W2, epilogue stores bf16 rows straight into the source
 //               rank's combine buffer over NVLink.
 //   combine   : after all ranks' "L2 done" flags, each token's routes are summed in slot order (fp32) and written to y.
@@ -31,15 +35,16 @@ constexpr int kMaxLocalExperts = 64;
 constexpr int kMaxTasks = 256;          // tasks one SM can own in one launch
 constexpr int kMetaCap = 4096;          // rows one rank can receive in one launch
 constexpr int kMaxStages = 12;
+constexpr int kDefaultStages = 4;       // stages used when shared memory allows more (see the launch code)
 constexpr int kMetaSmemRows = 256;      // received rows whose (token, slot, weight) records are cached in shared memory
 constexpr int kMaxMTiles = kMetaCap / 16 + kMaxLocalExperts;   // 16-token tiles over all local experts
 constexpr int kTileRows = 128;          // UMMA M: weight rows per task
 constexpr int kTileTokens = 16;         // UMMA N: token rows per task
 constexpr int kUnitK = 256;             // K elements per streamed unit (one 128 B swizzle atom of packed E2M1)
 constexpr int kUnitWBytes = kTileRows * 128;
-constexpr int kNumEpiThreads = 128, kNumStagerThreads = 64, kNumDispatchThreads = 192;
-constexpr uint32_t kBarEpi = 1, kBarStager = 2, kBarDispatch = 3, kBarExp = 4;
-constexpr int kNumExpThreads = 128;      // FP8-activation variant: warps 8..11 widen the packed E2M1 weights to 8-bit containers
+constexpr int kNumEpiThreads = 128;
+constexpr uint32_t kBarEpi = 1;          // named barrier of the four epilogue warps
+constexpr int kNumExpThreads = 256;      // FP8-activation variant: warps 8..15 widen the packed E2M1 weights to 8-bit containers
 constexpr uint32_t kXbufBytes = 2 * kUnitWBytes + 1024;   // one widened unit + its two scale planes
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kOtileBytes = 4096;
@@ -139,7 +144,13 @@ struct Ctx {
         *reinterpret_cast<volatile uint32_t*>(&c.abort_flag) = 1u;
     }
     __device__ __forceinline__ bool expired() const { return globaltimer_ns() > deadline; }
-    __device__ __noinline__ bool wait(uint64_t* bar, uint32_t parity, uint32_t code) const {
+    // the first probe is inline (a barrier that is already complete costs a few cycles); the polling loop with its
+    // abort and deadline checks is one out-of-line copy
+    __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, uint32_t code) const {
+        if (mbar_try_wait(bar, parity)) return true;
+        return wait_slow(bar, parity, code);
+    }
+    __device__ __noinline__ bool wait_slow(uint64_t* bar, uint32_t parity, uint32_t code) const {
         uint32_t it = 0;
         while (!mbar_try_wait(bar, parity)) {
             if ((++it & 0xFFu) == 0u) {
@@ -300,30 +311,42 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
 // (128 rows x 128 B, one swizzle atom) into two atoms of 128 rows x 128 B and hand it to the MMA issuer.
 __device__ void role_expander(const Ctx& cx, uint32_t xtid) {
     const KParams& p = cx.p; Ctl& c = cx.c;
+    // two groups of four warps; group g widens the units of parity g into buffer g, so that one unit's copy overlaps
+    // the next unit's barrier round trip
+    constexpr uint32_t kGroupThreads = kNumExpThreads / 2;
+    const uint32_t lane = xtid & 31u, grp = xtid / kGroupThreads, gt = xtid % kGroupThreads;
+    uint8_t* xb = cx.smem + p.sm_xbuf + grp * kXbufBytes;
     uint32_t it = 0;
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
-            const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u, x = it & 1u;
-            if (bar_red_or(kBarExp, kNumExpThreads, !cx.warp_wait(&c.full[s], ph, kErrWaitFull))) return;
-            if (bar_red_or(kBarExp, kNumExpThreads, !cx.warp_wait(&c.xempty[x], ((it >> 1) & 1u) ^ 1u, kErrWaitEmpty))) return;
+            if ((it & 1u) != grp) continue;
+            const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
+            // every warp waits and signals for itself (the barriers count a group's four warps): no block-level barrier per unit
+            if (!cx.warp_wait(&c.full[s], ph, kErrWaitFull)) return;
+            if (!cx.warp_wait(&c.xempty[grp], ((it >> 1) & 1u) ^ 1u, kErrWaitEmpty)) return;
             const uint8_t* wsm = cx.smem + static_cast<size_t>(s) * p.stage_bytes;
-            uint8_t* xb = cx.smem + p.sm_xbuf + x * kXbufBytes;
+            // item = (row r, atom a, slot j): the 8 source bytes (16 values) of slot j. Eight consecutive threads fill one
+            // widened 128 B row and sixteen read one packed 128 B row: both sides are free of bank conflicts.
+            constexpr uint32_t kItems = kTileRows * 16 / kGroupThreads;
+            uint2 v[kItems];
             #pragma unroll
-            for (uint32_t k = 0; k < 8; ++k) {
-                const uint32_t idx = k * kNumExpThreads + xtid, r = idx >> 3, ch = idx & 7u;
-                const uint4 v = *reinterpret_cast<const uint4*>(wsm + r * 128u + ((ch ^ (r & 7u)) << 4));
-                uint8_t* drow = xb + (ch >> 2) * kUnitWBytes + r * 128u;
-                const uint32_t j0 = (2u * ch) & 7u;
-                *reinterpret_cast<uint4*>(drow + ((j0 ^ (r & 7u)) << 4)) = make_uint4(v.x, v.y, 0u, 0u);
-                *reinterpret_cast<uint4*>(drow + (((j0 + 1u) ^ (r & 7u)) << 4)) = make_uint4(v.z, v.w, 0u, 0u);
+            for (uint32_t k = 0; k < kItems; ++k) {
+                const uint32_t idx = k * kGroupThreads + gt, j = idx & 7u, at = (idx >> 3) & 1u, r = idx >> 4;
+                const uint32_t ch = 4u * at + (j >> 1);
+                v[k] = *reinterpret_cast<const uint2*>(wsm + r * 128u + ((ch ^ (r & 7u)) << 4) + (j & 1u) * 8u);
             }
-            if (xtid < 64) *reinterpret_cast<uint4*>(xb + 2 * kUnitWBytes + xtid * 16u) = *reinterpret_cast<const uint4*>(wsm + kUnitWBytes + xtid * 16u);
+            #pragma unroll
+            for (uint32_t k = 0; k < kItems; ++k) {
+                const uint32_t idx = k * kGroupThreads + gt, j = idx & 7u, at = (idx >> 3) & 1u, r = idx >> 4;
+                *reinterpret_cast<uint4*>(xb + at * kUnitWBytes + r * 128u + ((j ^ (r & 7u)) << 4)) = make_uint4(v[k].x, v[k].y, 0u, 0u);
+            }
+            if (gt < 64) *reinterpret_cast<uint4*>(xb + 2 * kUnitWBytes + gt * 16u) = *reinterpret_cast<const uint4*>(wsm + kUnitWBytes + gt * 16u);
             fence_proxy_async_smem();
-            bar_sync(kBarExp, kNumExpThreads);
-            if (xtid == 0) { mbar_arrive(&c.xfull[x]); mbar_arrive(&c.empty[s]); }
+            __syncwarp();
+            if (lane == 0) { mbar_arrive(&c.xfull[grp]); mbar_arrive(&c.empty[s]); }
         }
     }
 }
@@ -689,12 +712,12 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         const uint32_t ep = ctrl32[kCtrlEpoch / 4 + bid];
         ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
         c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u;
-        for (int s = 0; s < p.nstage; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kUmma ? 1 : kNumEpiThreads); }
+        for (int s = 0; s < p.nstage; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
         #pragma unroll 1
         for (int i = 0; i < 2; ++i) {
             mbar_init(&c.acts_full[i], 1); mbar_init(&c.acts_empty[i], kUmma ? 1 : kNumEpiThreads);
             mbar_init(&c.tmem_full[i], 1); mbar_init(&c.tmem_empty[i], kNumEpiThreads);
-            mbar_init(&c.xfull[i], 1); mbar_init(&c.xempty[i], 1);
+            mbar_init(&c.xfull[i], kNumExpThreads / 64); mbar_init(&c.xempty[i], 1);
         }
         mbar_fence_init();
     }

@@ -218,8 +218,8 @@ def main():
         stamps = buf.phase_stamps()
         spans.append((stamps[8] - stamps[0]) / 1e3)
     span_us = statistics.median(spans)
-    phase_names = ['entry', 'dispatched', 'dispatch_flags_seen', 'scheduled', 'tasks_done', 'l2_signalled', 'combine_flags_seen', 'exit', 'last_sm_exit']
-    phases = {n: round((stamps[i] - stamps[0]) / 1e3, 2) for i, n in enumerate(phase_names) if stamps[i]}
+    phase_names = ['entry', 'dispatched', 'dispatch_headers_seen', 'scheduled', 'tasks_done', None, None, 'exit', 'last_sm_exit']
+    phases = {n: round((stamps[i] - stamps[0]) / 1e3, 2) for i, n in enumerate(phase_names) if n and stamps[i]}
     st, words = buf.device_status()
     if st != 0:
         raise RuntimeError(f'device status {st}: {[hex(v) for v in words[:4]]}')

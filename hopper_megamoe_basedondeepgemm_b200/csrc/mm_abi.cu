@@ -104,10 +104,11 @@ int mm_get_layout(const mm_config_t* c, mm_layout_t* out) {
     out->off_x_sf = take(t_max * out->x_sf_row_bytes);
     out->off_topk_idx = take(t_max * c->num_topk * 8);
     out->off_topk_weights = take(t_max * c->num_topk * 4);
-    out->off_rx = take(2 * c->num_ranks * out->rx_cap_rows * out->rx_row_bytes);
+    out->rx_region_bytes = align_up(32 + out->rx_cap_rows * 2 * out->rx_row_bytes, 128);
+    out->off_rx = take(2 * c->num_ranks * out->rx_region_bytes);
     out->off_mid = take(out->mid_rows * out->mid_row_bytes);
     out->off_mid_sf = take(out->mid_rows * out->mid_sf_row_bytes);
-    out->off_comb = take(t_max * c->num_topk * c->hidden * 2);
+    out->off_comb = take(t_max * c->num_topk * c->hidden * 4);
     const int64_t n_max = (2 * c->intermediate > c->hidden ? 2 * c->intermediate : c->hidden) / mm::kTileRows;
     out->cnt_per_phase = (out->mid_rows / mm::kTileTokens) * n_max;
     out->off_red = take(256 /* SMs */ * 2 /* phases */ * 2 /* slots */ * mm::kTileTokens * mm::kTileRows * 4);
@@ -121,8 +122,11 @@ int mm_reset(const mm_config_t* cfg, void* buffer, void* stream) {
     const int st = mm_get_layout(cfg, &L);
     if (st != MM_OK) return st;
     if (buffer == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    // the launch counters restart from zero, so every flagged word of earlier launches must go too: the receive pool
+    // and the combine buffer are cleared with the control block and the split-tile counters
     MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_ctrl, 0, L.off_x - L.off_ctrl, static_cast<cudaStream_t>(stream)));
-    MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_cnt, 0, L.total_bytes - L.off_cnt, static_cast<cudaStream_t>(stream)));
+    MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_rx, 0, L.off_mid - L.off_rx, static_cast<cudaStream_t>(stream)));
+    MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_comb, 0, L.total_bytes - L.off_comb, static_cast<cudaStream_t>(stream)));
     return MM_OK;
 }
 
@@ -171,7 +175,7 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     if (p.n1_tiles > 255 || p.n2_tiles > 255) return MM_ERR_UNSUPPORTED;
     p.unit_bytes = wg.unit_bytes;
     p.x_row_bytes = static_cast<int>(L.x_row_bytes); p.x_sf_row_bytes = static_cast<int>(L.x_sf_row_bytes);
-    p.rx_row_bytes = static_cast<int>(L.rx_row_bytes);
+    p.rx_row_bytes = static_cast<int>(L.rx_row_bytes); p.rx_region = L.rx_region_bytes;
     p.mid_row_bytes = static_cast<int>(L.mid_row_bytes); p.mid_sf_row_bytes = static_cast<int>(L.mid_sf_row_bytes);
     p.has_clamp = (a->activation_clamp >= 0.f && std::isfinite(a->activation_clamp)) ? 1 : 0;
     p.clamp = a->activation_clamp; p.fast_math = a->fast_math;
@@ -201,19 +205,15 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.asf_bytes = static_cast<uint32_t>(align_up(kmax / vec, 16) / 4 * 256);     // 256 B per scale word of the K axis
     const size_t xbytes = a8 ? 2 * mm::kXbufBytes : 0;
     const size_t budget = 232448 - sizeof(mm::Ctl) - 1024 /* alignment slack */ - 768;
-    { const char* d = getenv("MM_STAGE_UNITS"); p.stage_units = d ? atoi(d) : 1; }
-    if (p.stage_units < 1 || p.stage_units > 4 || (a8 && p.stage_units != 1)) return MM_ERR_INVALID_ARGUMENT;
-    p.stage_bytes = p.stage_units * p.unit_bytes;
     // two token staging buffers when that leaves at least four stream stages, else one
     p.nab = 2;
-    { const char* d = getenv("MM_NAB"); if (d) p.nab = atoi(d); }
     size_t fixed = p.nab * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes + mm::kVtBytes + xbytes;
-    if (fixed + 4 * static_cast<size_t>(p.stage_bytes) > budget) {
+    if (fixed + 4 * static_cast<size_t>(p.unit_bytes) > budget) {
         p.nab = 1;
         fixed = p.nab * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes + mm::kVtBytes + xbytes;
     }
-    if (fixed + 2 * static_cast<size_t>(p.stage_bytes) > budget) return MM_ERR_UNSUPPORTED;
-    int nstage = static_cast<int>((budget - fixed) / p.stage_bytes);
+    if (fixed + 2 * static_cast<size_t>(p.unit_bytes) > budget) return MM_ERR_UNSUPPORTED;
+    int nstage = static_cast<int>((budget - fixed) / p.unit_bytes);
     // A short ring is faster than a deep one: the loader runs ahead into the next phase's weights, and with many stages
     // that prefetch competes with the stream the current phase is waiting for (measured: 4 stages beat 8 by 2 us).
     {
@@ -225,8 +225,7 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     }
     if (nstage < 2) return MM_ERR_UNSUPPORTED;
     p.nstage = nstage;
-    { const char* d = getenv("MM_L1_INFLIGHT"); p.l1_inflight = d ? atoi(d) : 0; }
-    p.sm_act = nstage * p.stage_bytes;
+    p.sm_act = nstage * p.unit_bytes;
     p.sm_asf = p.sm_act + p.nab * p.act_bytes;
     p.sm_otile = p.sm_asf + p.nab * p.asf_bytes;
     p.sm_vt = p.sm_otile + mm::kOtileBytes;
@@ -382,9 +381,11 @@ int mm_mega_moe_launch_static_scratch(const mm_config_t* cfg, const mm_static_ar
     unsigned char* scratch = g_static_scratch_addr[dev];
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // the array keeps the previous call's contents: the control block, the arrival flags and the split-tile counters
-    // must start from zero (the launch counters restart with them, so every call runs as the buffer's first launch)
+    // must start from zero (the launch counters restart with them, so every call runs as the buffer's first launch),
+    // and with the counters every flagged word of the receive pool and the combine buffer
     MM_CUDA(cudaMemsetAsync(scratch + L.off_ctrl, 0, L.off_x - L.off_ctrl, s));
-    MM_CUDA(cudaMemsetAsync(scratch + L.off_cnt, 0, L.total_bytes - L.off_cnt, s));
+    MM_CUDA(cudaMemsetAsync(scratch + L.off_rx, 0, L.off_mid - L.off_rx, s));
+    MM_CUDA(cudaMemsetAsync(scratch + L.off_comb, 0, L.total_bytes - L.off_comb, s));
     const size_t t = static_cast<size_t>(a->num_tokens);
     if (t > 0) {
         MM_CUDA(cudaMemcpyAsync(scratch + L.off_x, a->x, t * L.x_row_bytes, cudaMemcpyDeviceToDevice, s));

@@ -1,8 +1,9 @@
 // The fused expert-parallel MoE layer as one persistent sm_100a kernel.
 //
 //   dispatch  : SM d (< ranks) packs this rank's routed rows for rank d and stores them, densely and in (token, slot)
-//               order, into a region of rank d's receive pool that only this rank writes; one release store of
-//               (epoch, row count) then tells rank d that the rows are complete. No ticket atomics, no collective.
+//               order, into a region of rank d's receive pool that only this rank writes. Everything that crosses
+//               NVLink travels as flagged 8-byte words {4 data bytes, launch number}: the consumer polls the words it
+//               needs, so there is no fence, no completion flag and no ticket atomic - one one-way trip per hand-off.
 //   schedule  : every SM reads the R flags, scans the received rows' expert ids and derives its own task list in closed
 //               form (L1 tiles of all active experts, then L2 tiles). A phase's NT tiles are split in two: the first
 //               NT % SMs tiles are cut along K into equal unit ranges, one per SM (partial sums parked in global memory,
@@ -13,9 +14,10 @@
 //               memory (kind::mxf8f6f4 reads 4-bit values from 8-bit containers); HBM still streams the packed form.
 //   L1 epilog : SwiGLU * top-k weight, requantise to E2M1 or E4M3 (+ scale byte), store to the local intermediate
 //               pool, release-add on the expert's arrival counter.
-//   L2 GEMM   : acquires that counter, same main loop on W2, epilogue stores bf16 rows straight into the source
-//               rank's combine buffer over NVLink.
-//   combine   : after all ranks' "L2 done" flags, each token's routes are summed in slot order (fp32) and written to y.
+//   L2 GEMM   : acquires that counter, same main loop on W2, epilogue stores bf16 rows (flagged words) straight into
+//               the source rank's combine buffer over NVLink.
+//   combine   : each thread polls the flagged words of the routes it sums; routes are added in slot order (fp32) and
+//               written to y. No grid-wide or cross-rank barrier anywhere in the launch.
 //
 // Every wait is bounded by a deadline; on expiry the SM records a status word, raises a CTA-wide abort flag and all
 // roles fall through to the common exit (TMEM is always released).
@@ -53,15 +55,11 @@ constexpr uint32_t kVtBytes = kTileTokens * kTileRows * 4;   // fp32 accumulator
 // control-block offsets (bytes from off_ctrl)
 constexpr int kCtrlEpoch = 0;           // u32[256] one launch counter per SM
 constexpr int kCtrlStatus = 1024;       // u32[16]
-constexpr int kCtrlL2Done = 1088;       // u32 SMs that finished their L2 tasks
 constexpr int kCtrlFeArrive = 1092;     // u32 SMs that published their router logits
 constexpr int kCtrlL1Done = 1152;       // u32[2][64] L1 tiles finished per (parity, local expert)
 constexpr int kCtrlStamps = 2048;       // u64[32] phase stamps
 constexpr int kCtrlBytes = 4096;
-// flag-block offsets (bytes from off_flags); written by the peers
-constexpr int kFlagDispatch = 0;        // u64[2][8]: (epoch + 1) << 32 | rows
-constexpr int kFlagCombine = 256;       // u32[2][8]: epoch + 1
-constexpr int kFlagBytes = 1024;
+constexpr int kFlagBytes = 1024;        // reserved block after the control block (no separate arrival flags exist)
 
 // device status codes (low byte of status word 0)
 enum : uint32_t {
@@ -72,7 +70,7 @@ enum : uint32_t {
 // phase stamp slots (SM 0 unless noted)
 enum : int {
     kStampEntry = 0, kStampDispatched = 1, kStampFlagsSeen = 2, kStampScheduled = 3, kStampTasksDone = 4,
-    kStampL2Signalled = 5, kStampCombineFlags = 6, kStampExit = 7, kStampLastExit = 8 /* max over SMs */,
+    kStampExit = 7, kStampLastExit = 8 /* max over SMs */,
     kStampFrontend = 9
 };
 
@@ -81,8 +79,7 @@ struct RowMeta { int32_t src, token, slot; float weight; };
 struct KParams {
     int R, rank, e_local, topk, H, I, T, cap;
     int n1_tiles, n2_tiles, k1_units, k2_units;
-    int nstage, l1_inflight, stage_units;   // a stage holds up to `stage_units` consecutive units
-    uint32_t stage_bytes;
+    int nstage;                          // ring of weight stages, one streamed unit each
     uint32_t unit_bytes;                 // weights + scale planes of one streamed unit
     int x_row_bytes, x_sf_row_bytes, rx_row_bytes, mid_row_bytes, mid_sf_row_bytes;
     float clamp; int has_clamp, fast_math;
@@ -92,6 +89,7 @@ struct KParams {
     __nv_bfloat16* y; int* stats;
     long long off_ctrl, off_flags, off_x, off_x_sf, off_topk_idx, off_topk_w, off_rx, off_mid, off_mid_sf, off_comb, off_red, off_cnt;
     int cnt_per_phase;
+    long long rx_region;                 // bytes of one (parity, source) region of the receive pool
     uint32_t sm_act, sm_asf, sm_otile, sm_vt;   // dynamic shared memory offsets (stages start at 0)
     uint32_t act_bytes, asf_bytes;
     uint32_t sm_xbuf; int nab;           // widened-unit buffers (FP8 variant); number of token staging buffers (1 or 2)
@@ -170,8 +168,21 @@ struct Ctx {
     __device__ __forceinline__ void stamp(int slot) const {
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[slot] = globaltimer_ns();
     }
+    // received row i of source rank `src_rank` (flagged words: payload byte b sits at 2 * (b & ~3) + (b & 3))
     __device__ __forceinline__ uint8_t* rx_row(uint32_t src_rank, uint32_t i) const {
-        return buf + p.off_rx + (static_cast<size_t>(par * p.R + src_rank) * p.cap + i) * p.rx_row_bytes;
+        return buf + p.off_rx + static_cast<size_t>(par * p.R + src_rank) * p.rx_region + 32u + static_cast<size_t>(i) * 2u * p.rx_row_bytes;
+    }
+    // one 16 B payload chunk of flagged words at `src` (32 B): polls until both halves carry this launch's flag
+    __device__ __forceinline__ bool ll_read(const uint8_t* src, uint32_t flag, uint4& out, uint32_t code, uint32_t detail) const {
+        uint32_t spins = 0;
+        for (;;) {
+            const uint4 a = ld_volatile_v4(src), b = ld_volatile_v4(src + 16);
+            if (ll_valid(a, b, flag)) { out = ll_data(a, b); return true; }
+            if ((++spins & 0x3Fu) == 0u) {
+                if (aborted()) return false;
+                if (expired()) { fail(code, detail); return false; }
+            }
+        }
     }
 };
 
@@ -209,21 +220,13 @@ __device__ void role_loader(const Ctx& cx) {
         const uint8_t* src = (type ? p.w2 : p.w1) + (static_cast<size_t>(e) * ntiles + j) * kunits * p.unit_bytes;
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         #pragma unroll 1
-        for (int u = ub, nu; u < ue; u += nu, ++it) {
-            nu = ue - u < p.stage_units ? ue - u : p.stage_units;       // consecutive units are contiguous in the stream
+        for (int u = ub; u < ue; ++u, ++it) {
             const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
             if (!cx.warp_wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
-            if (type == 0u && p.l1_inflight > 0 && it >= static_cast<uint32_t>(p.l1_inflight)) {
-                // L1 units: a short queue per SM keeps the memory system's service order fair between SMs (an expert's L2
-                // needs the L1 tiles of ALL its SMs); W2 units, which are prefetched ahead of their use, may fill the ring
-                const uint32_t j0 = it - p.l1_inflight;
-                if (!cx.warp_wait(&c.empty[j0 % p.nstage], (j0 / p.nstage) & 1u, kErrWaitEmpty)) return;
-            }
             if (elect_one()) {
                 if (it == 0) cx.trace(4);
-                mbar_arrive_expect_tx(&c.full[s], nu * p.unit_bytes);
-                bulk_g2s(cx.smem + static_cast<size_t>(s) * p.stage_bytes, src + static_cast<size_t>(u) * p.unit_bytes,
-                         nu * p.unit_bytes, &c.full[s]);
+                mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
+                bulk_g2s(cx.smem + static_cast<size_t>(s) * p.unit_bytes, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
             }
             __syncwarp();
         }
@@ -242,7 +245,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     constexpr uint32_t kStepsPerAtom = kA8 ? 4u : 4u;           // 128 B of operand bytes per swizzle atom either way
     const uint32_t tm = c.tmem_base;
     const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 16
-    uint32_t it = 0, uc = 0;                                    // stages and units consumed so far
+    uint32_t it = 0;                                            // units consumed so far
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
@@ -252,20 +255,18 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         tc_fence_after();
         const uint32_t act = smem_u32(cx.smem + p.sm_act + ab * p.act_bytes);
         #pragma unroll 1
-        for (int u0 = ub, nu; u0 < ue; u0 += nu, ++it) {
-            nu = ue - u0 < p.stage_units ? ue - u0 : p.stage_units;
+        for (int u = ub; u < ue; ++u, ++it) {
             const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
             uint64_t* ready = kA8 ? &c.xfull[it & 1u] : &c.full[s];
             if (!cx.warp_wait(ready, kA8 ? (it >> 1) & 1u : ph, kErrWaitFull)) return;
             tc_fence_after();
             if (elect_one()) {
               if (it == 0) cx.trace(6);
-              #pragma unroll 1
-              for (int u = u0; u < u0 + nu; ++u, ++uc) {
+              {
                 const uint32_t wsm = kA8 ? smem_u32(cx.smem + p.sm_xbuf + (it & 1u) * kXbufBytes)
-                                         : smem_u32(cx.smem + static_cast<size_t>(s) * p.stage_bytes) + static_cast<uint32_t>(u - u0) * p.unit_bytes;
+                                         : smem_u32(cx.smem + static_cast<size_t>(s) * p.unit_bytes);
                 const uint32_t wsf = wsm + (kA8 ? 2u * kUnitWBytes : static_cast<uint32_t>(kUnitWBytes));
-                const uint32_t sfa = tm + sfa_col + (uc & 1u) * 16u, sfb = tm + sfb_col + (uc & 1u) * 16u;
+                const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u, sfb = tm + sfb_col + (it & 1u) * 16u;
                 const uint32_t asf = smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes) + static_cast<uint32_t>(u) * kPlanes * 256u;
                 #pragma unroll
                 for (uint32_t pl = 0; pl < kPlanes; ++pl) {
@@ -327,7 +328,7 @@ __device__ void role_expander(const Ctx& cx, uint32_t xtid) {
             // every warp waits and signals for itself (the barriers count a group's four warps): no block-level barrier per unit
             if (!cx.warp_wait(&c.full[s], ph, kErrWaitFull)) return;
             if (!cx.warp_wait(&c.xempty[grp], ((it >> 1) & 1u) ^ 1u, kErrWaitEmpty)) return;
-            const uint8_t* wsm = cx.smem + static_cast<size_t>(s) * p.stage_bytes;
+            const uint8_t* wsm = cx.smem + static_cast<size_t>(s) * p.unit_bytes;
             // item = (row r, atom a, slot j): the 8 source bytes (16 values) of slot j. Eight consecutive threads fill one
             // widened 128 B row and sixteen read one packed 128 B row: both sides are free of bank conflicts.
             constexpr uint32_t kItems = kTileRows * 16 / kGroupThreads;
@@ -396,7 +397,8 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
             RowMeta m;
             if (f < kMetaSmemRows) m = c.rx_meta[f];
             else {
-                const uint4 q = ld_cg_v4(cx.rx_row(r, i) + p.rx_row_bytes - 16);
+                uint4 q = make_uint4(0u, 0u, 0u, 0u);
+                cx.ll_read(cx.rx_row(r, i) + 2u * (p.rx_row_bytes - 16), c.epoch + 1u, q, kErrWaitDispatchFlag, r);
                 m = RowMeta{0, static_cast<int32_t>(q.y), static_cast<int32_t>(q.z), __uint_as_float(q.w)};
             }
             m.src = static_cast<int32_t>(r);
@@ -424,20 +426,43 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
         const uint32_t sfchunk = (type ? p.mid_sf_row_bytes : p.x_sf_row_bytes) / 16;      // 16 B chunks of one row's scale bytes
         const uint32_t per_row = nchunk + sfchunk;
         const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
-        // four loads per lane are in flight before the first store: one memory round trip per 128 chunks of a row
+        // four chunks per lane are in flight before the first store: one memory round trip per 128 chunks of a row.
+        // Received rows (L1) are flagged words that may still be on their way: a chunk is re-read until its flags match.
+        const uint32_t flag = c.epoch + 1u;
+        bool bad = false;
         #pragma unroll 1
         for (uint32_t n = 0; n < nv; ++n) {
             const uint8_t* row_src = type ? cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes
                                           : cx.rx_row(rowidx[n] >> 24, rowidx[n] & 0xFFFFFFu);
-            const uint8_t* sf_src = type ? cx.buf + p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes
-                                         : row_src + p.x_row_bytes;
+            const uint8_t* sf_src = cx.buf + p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes;
             #pragma unroll 1
             for (uint32_t base = lane; base < per_row; base += 4 * 32) {
                 uint4 v[4];
-                #pragma unroll
-                for (uint32_t u = 0; u < 4; ++u) {
-                    const uint32_t ci = base + u * 32;
-                    if (ci < per_row) v[u] = ld_cg_v4(ci < nchunk ? row_src + ci * 16u : sf_src + (ci - nchunk) * 16u);
+                if (type) {
+                    #pragma unroll
+                    for (uint32_t u = 0; u < 4; ++u) {
+                        const uint32_t ci = base + u * 32;
+                        if (ci < per_row) v[u] = ld_cg_v4(ci < nchunk ? row_src + ci * 16u : sf_src + (ci - nchunk) * 16u);
+                    }
+                } else {
+                    uint32_t spins = 0;
+                    bool ok;
+                    do {
+                        ok = true;
+                        #pragma unroll
+                        for (uint32_t u = 0; u < 4; ++u) {
+                            const uint32_t ci = base + u * 32;
+                            if (ci < per_row) {
+                                const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
+                                ok = ok && ll_valid(a, b, flag);
+                                v[u] = ll_data(a, b);
+                            }
+                        }
+                        if (!ok && (++spins & 0x3Fu) == 0u) {
+                            if (cx.aborted()) bad = true;
+                            else if (cx.expired()) { cx.fail(kErrWaitDispatchFlag, rowidx[n] >> 24); bad = true; }
+                        }
+                    } while (!ok && !bad);
                 }
                 #pragma unroll
                 for (uint32_t u = 0; u < 4; ++u) {
@@ -455,6 +480,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                 }
             }
         }
+        if (__any_sync(0xffffffffu, bad)) return;
         fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) { mbar_arrive(&c.acts_full[ab]); if (ti == 0) cx.trace(13); if (type == 1u) cx.trace(14); }
@@ -548,15 +574,11 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 const uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
                 const uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
                 #pragma unroll 1
-                for (int u0 = ub, nu; u0 < ue && ok; u0 += nu, ++it) {
-                    nu = ue - u0 < p.stage_units ? ue - u0 : p.stage_units;
+                for (int u = ub; u < ue && ok; ++u, ++it) {
                     const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
                     ok = cx.warp_wait(&c.full[s], ph, kErrWaitFull);
                     if (ok) {
-                        #pragma unroll 1
-                        for (int u = u0; u < u0 + nu; ++u)
-                            check_accumulate<kVec>(cx, cx.smem + static_cast<size_t>(s) * p.stage_bytes + static_cast<size_t>(u - u0) * p.unit_bytes,
-                                                   act, asf, u, row, nv, v);
+                        check_accumulate<kVec>(cx, cx.smem + static_cast<size_t>(s) * p.unit_bytes, act, asf, u, row, nv, v);
                         mbar_arrive(&c.empty[s]);
                     }
                 }
@@ -678,7 +700,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             bar_sync(kBarEpi, kNumEpiThreads);          // orders every thread's stores before the release below
             if (etid == 0) { red_release_gpu_add(l1_done + e, 1u); cx.trace(23); }
         } else {
-            // ---- L2: bf16 rows back to the token's source rank
+            // ---- L2: bf16 rows back to the token's source rank, as flagged words: the combine there polls the data itself
             __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(otile);
             #pragma unroll 1
             for (uint32_t n = 0; n < nv; ++n) ot[n * kTileRows + row] = __float2bfloat16_rn(vt[n * kTileRows] * p.l2_scale);
@@ -688,8 +710,8 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 const uint32_t n = idx >> 4, ch = idx & 15u;
                 const uint4 val = *reinterpret_cast<const uint4*>(otile + n * 256u + ch * 16u);
                 uint8_t* dst = p.peer[meta[n].src] + p.off_comb +
-                    ((static_cast<size_t>(meta[n].token) * p.topk + meta[n].slot) * p.H + j * kTileRows) * 2u + ch * 16u;
-                st_global_v4(dst, val);
+                    ((static_cast<size_t>(meta[n].token) * p.topk + meta[n].slot) * p.H + j * kTileRows) * 4u + ch * 32u;
+                st_ll_16B(dst, val, c.epoch + 1u);
             }
         }
         if (etid == 0) cx.trace(9);
@@ -804,7 +826,12 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             __syncthreads();
         }
         const uint32_t nchunk = p.rx_row_bytes / 16, xq = p.x_row_bytes / 16, xs = p.x_sf_row_bytes / 16;
-        uint8_t* dst_base = p.peer[d] + p.off_rx + static_cast<size_t>(par * p.R + p.rank) * p.cap * p.rx_row_bytes;
+        const uint32_t flag = epoch + 1u;
+        uint8_t* region = p.peer[d] + p.off_rx + static_cast<size_t>(par * p.R + p.rank) * p.rx_region;
+        // the header line carries the row count; like every word of the rows it is self-validating (flagged), so nothing
+        // orders it against the rows and it can leave first
+        if (tid == 0) st_ll_16B(region, make_uint4(cnt, 0u, 0u, 0u), flag);
+        uint8_t* dst_base = region + 32u;
         const float* tw = reinterpret_cast<const float*>(buf + p.off_topk_w);
         // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (four in flight)
         #pragma unroll 1
@@ -812,7 +839,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             const uint32_t ent = dlist[i], tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
             const uint8_t* xs_src = buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
             const uint8_t* sf_src = buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
-            uint8_t* dst = dst_base + static_cast<size_t>(i) * p.rx_row_bytes;
+            uint8_t* dst = dst_base + static_cast<size_t>(i) * 2u * p.rx_row_bytes;
             #pragma unroll 1
             for (uint32_t base = lane; base < nchunk; base += 4 * 32) {
                 uint4 v[4];
@@ -826,16 +853,9 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 #pragma unroll
                 for (uint32_t u = 0; u < 4; ++u) {
                     const uint32_t ci = base + u * 32;
-                    if (ci < nchunk) st_global_v4(dst + ci * 16u, v[u]);
+                    if (ci < nchunk) st_ll_16B(dst + ci * 32u, v[u], flag);
                 }
             }
-        }
-        __syncthreads();
-        if (tid == 0) {
-            // release: the barrier orders every thread's row stores before this fence; the flag store follows it
-            uint64_t* flag = reinterpret_cast<uint64_t*>(p.peer[d] + p.off_flags + kFlagDispatch) + par * kMaxRanks + p.rank;
-            fence_acq_rel_sys();
-            st_relaxed_sys64(flag, (static_cast<uint64_t>(epoch + 1u) << 32) | cnt);
         }
         __syncthreads();
     }
@@ -847,17 +867,11 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     for (uint32_t off = tid * 16u; off < p.nab * (p.act_bytes + p.asf_bytes); off += kNT * 16u)
         *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
 
-    // ---- receive: wait for every source rank's flag, then scan the received rows' records
+    // ---- receive: wait for every source rank's header line, then scan the received rows' records
     if (tid < static_cast<uint32_t>(p.R)) {
-        const uint64_t* flag = reinterpret_cast<const uint64_t*>(buf + p.off_flags + kFlagDispatch) + par * kMaxRanks + tid;
-        uint32_t spins = 0; uint64_t f;
-        while (((f = ld_acquire_sys64(flag)) >> 32) != epoch + 1u) {
-            if ((++spins & 0x3Fu) == 0u) {
-                if (cx.aborted()) break;
-                if (cx.expired()) { cx.fail(kErrWaitDispatchFlag, tid); break; }
-            }
-        }
-        c.rx_count[tid] = static_cast<uint32_t>(f & 0xFFFFFFFFu);
+        uint4 h = make_uint4(0u, 0u, 0u, 0u);
+        cx.ll_read(buf + p.off_rx + static_cast<size_t>(par * p.R + tid) * p.rx_region, epoch + 1u, h, kErrWaitDispatchFlag, tid);
+        c.rx_count[tid] = h.x <= static_cast<uint32_t>(p.cap) ? h.x : 0u;
     }
     __syncthreads();
     uint32_t total = 0;
@@ -878,7 +892,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 uint32_t r = 0;
                 #pragma unroll
                 for (int q = 1; q < kMaxRanks; ++q) r += (q < p.R && f >= pre[q]) ? 1u : 0u;
-                const uint4 m = ld_cg_v4(cx.rx_row(r, f - pre[r]) + p.rx_row_bytes - 16);
+                uint4 m = make_uint4(0u, 0u, 0u, 0u);
+                cx.ll_read(cx.rx_row(r, f - pre[r]) + 2u * (p.rx_row_bytes - 16), epoch + 1u, m, kErrWaitDispatchFlag, r);
                 const uint32_t e = m.x & 0xFFu;
                 c.meta_e[f] = static_cast<uint8_t>(e);
                 if (f < kMetaSmemRows) c.rx_meta[f] = RowMeta{0, static_cast<int32_t>(m.y), static_cast<int32_t>(m.z), __uint_as_float(m.w)};
@@ -983,19 +998,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (bid == 0 && tid == 0) cx.stamp(kStampTasksDone);
     if (tid == 0) cx.trace(10);
 
-    // ---- tell every rank that this rank's expert outputs have been written. The barrier above orders every thread's
-    //      stores before the counter's release; the last SM's fence carries all of them to system scope before the flags.
-    if (tid == 0 && !cx.aborted()) {
-        const uint32_t old = atom_acq_rel_gpu_add(&ctrl32[kCtrlL2Done / 4], 1u);
-        if (old == G - 1) {
-            ctrl32[kCtrlL2Done / 4] = 0u;
-            if (p.R > 1) fence_acq_rel_sys(); else fence_acq_rel_gpu();      // a single rank's flag never leaves this GPU
-            for (int r = 0; r < p.R; ++r)
-                st_relaxed_sys(reinterpret_cast<uint32_t*>(p.peer[r] + p.off_flags + kFlagCombine) + par * kMaxRanks + p.rank, epoch + 1u);
-            cx.stamp(kStampL2Signalled);
-        }
-    }
-    // ---- combine, part 1: which routes of this thread's first (token, 16 B chunk) item are live (fetched before the wait)
+    // ---- combine. No grid-wide or cross-rank barrier precedes it: the expert outputs arrive as flagged words and every
+    //      thread polls exactly the words it sums. First, which routes of this thread's first (token, 16 B chunk) item are live:
     const uint32_t chunks_per_row = p.H / 8, nitems = static_cast<uint32_t>(p.T) * chunks_per_row;
     const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
     const uint32_t first_item = bid + tid * G;
@@ -1005,24 +1009,13 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         for (int sl = 0; sl < p.topk; ++sl) first_mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
     }
 
-    // ---- combine: wait for every rank's flag, then sum each token's routes in slot order
-    if (tid < static_cast<uint32_t>(p.R) && !cx.aborted()) {
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(buf + p.off_flags + kFlagCombine) + par * kMaxRanks + tid;
-        uint32_t spins = 0;
-        while (ld_acquire_sys(flag) != epoch + 1u) {
-            if ((++spins & 0x3Fu) == 0u) {
-                if (cx.aborted()) break;
-                if (cx.expired()) { cx.fail(kErrWaitCombineFlag, tid); break; }
-            }
-        }
-    }
-    __syncthreads();
-    if (bid == 0 && tid == 0) cx.stamp(kStampCombineFlags);
     if (tid == 0) cx.trace(11);
     if (!cx.aborted()) {
+        const uint32_t flag = epoch + 1u;
+        bool bad = false;
         // item idx = (token, 16 B chunk); consecutive items go to different SMs so that a small batch uses the whole GPU
         #pragma unroll 1
-        for (uint32_t idx = first_item; idx < nitems; idx += G * kNT) {
+        for (uint32_t idx = first_item; idx < nitems && !bad; idx += G * kNT) {
             const uint32_t tok = idx / chunks_per_row, ch = idx % chunks_per_row;
             uint32_t mask = first_mask;
             if (idx != first_item) {
@@ -1030,23 +1023,41 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 for (int sl = 0; sl < p.topk; ++sl) mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
             }
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-            const uint8_t* cbase = buf + p.off_comb + (static_cast<size_t>(tok) * p.topk * p.H) * 2u + ch * 16u;
-            const size_t sstride = static_cast<size_t>(p.H) * 2u;
+            const uint8_t* cbase = buf + p.off_comb + (static_cast<size_t>(tok) * p.topk * p.H) * 4u + ch * 32u;
+            const size_t sstride = static_cast<size_t>(p.H) * 4u;
             #pragma unroll 1
-            for (int s0 = 0; s0 < p.topk; s0 += 8) {
-                // eight routes' loads in flight; a masked route contributes +0.0, which leaves the running sums bit-identical
-                uint4 v[8];
+            for (int s0 = 0; s0 < p.topk && !bad; s0 += 4) {
+                // four routes' words in flight, re-read until each live route carries this launch's flag; a masked route
+                // contributes +0.0, which leaves the running sums bit-identical; routes are added in slot order
+                uint4 v[4];
+                uint32_t spins = 0;
+                bool ok;
+                do {
+                    ok = true;
+                    #pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        v[u] = make_uint4(0u, 0u, 0u, 0u);
+                        if ((mask >> (s0 + u)) & 1u) {
+                            const uint8_t* src = cbase + static_cast<size_t>(s0 + u) * sstride;
+                            const uint4 a = ld_volatile_v4(src), b = ld_volatile_v4(src + 16);
+                            ok = ok && ll_valid(a, b, flag);
+                            v[u] = ll_data(a, b);
+                        }
+                    }
+                    if (!ok && (++spins & 0x3Fu) == 0u) {
+                        if (cx.aborted()) bad = true;
+                        else if (cx.expired()) { cx.fail(kErrWaitCombineFlag, tok); bad = true; }
+                    }
+                } while (!ok && !bad);
                 #pragma unroll
-                for (int u = 0; u < 8; ++u)
-                    v[u] = ((mask >> (s0 + u)) & 1u) ? ld_cg_v4(cbase + static_cast<size_t>(s0 + u) * sstride) : make_uint4(0u, 0u, 0u, 0u);
-                #pragma unroll
-                for (int u = 0; u < 8; ++u) {
+                for (int u = 0; u < 4; ++u) {
                     acc[0] += __uint_as_float(v[u].x << 16); acc[1] += __uint_as_float(v[u].x & 0xFFFF0000u);
                     acc[2] += __uint_as_float(v[u].y << 16); acc[3] += __uint_as_float(v[u].y & 0xFFFF0000u);
                     acc[4] += __uint_as_float(v[u].z << 16); acc[5] += __uint_as_float(v[u].z & 0xFFFF0000u);
                     acc[6] += __uint_as_float(v[u].w << 16); acc[7] += __uint_as_float(v[u].w & 0xFFFF0000u);
                 }
             }
+            if (bad) break;
             uint4 o;
             uint32_t* ow = &o.x;
             #pragma unroll

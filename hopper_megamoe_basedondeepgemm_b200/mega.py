@@ -74,14 +74,15 @@ class SymmBuffer:
         self.x_sf = view(L.off_x_sf, t * L.x_sf_row_bytes, torch.int32, (t, hidden // (4 * vec)))
         self.topk_idx = view(L.off_topk_idx, t * num_topk * 8, torch.int64, (t, num_topk))
         self.topk_weights = view(L.off_topk_weights, t * num_topk * 4, torch.float32, (t, num_topk))
-        # receive pool: [parity][source rank][row][packed tokens | scale bytes | 16 B (expert, token, slot, weight)]
-        self.l1_acts = view(L.off_rx, 2 * self.num_ranks * L.rx_cap_rows * L.rx_row_bytes, torch.uint8,
-                            (2, self.num_ranks, int(L.rx_cap_rows), int(L.rx_row_bytes)))
-        self.l1_acts_sf = self.l1_acts[..., int(L.x_row_bytes):int(L.x_row_bytes + L.x_sf_row_bytes)]
+        # receive pool: [parity][source rank][32 B header line, then rows of (tokens | scale bytes | 16 B record)];
+        # every 8 bytes hold 4 data bytes and the launch's flag word
+        self.l1_acts = view(L.off_rx, 2 * self.num_ranks * L.rx_region_bytes, torch.uint8,
+                            (2, self.num_ranks, int(L.rx_region_bytes)))
         self.l2_acts = view(L.off_mid, L.mid_rows * L.mid_row_bytes, torch.uint8, (int(L.mid_rows), int(L.mid_row_bytes)))
         self.l2_acts_sf = view(L.off_mid_sf, L.mid_rows * L.mid_sf_row_bytes, torch.uint8,
                                (int(L.mid_rows), int(L.mid_sf_row_bytes)))
-        self.combine = view(L.off_comb, t * num_topk * hidden * 2, torch.bfloat16, (t, num_topk, hidden))
+        # expert outputs coming back: per (token, slot) hidden / 2 flagged words {2 bf16, launch flag}
+        self.combine = view(L.off_comb, t * num_topk * hidden * 4, torch.int32, (t, num_topk, hidden // 2, 2))
 
     def reset(self):
         """Zero the control block and the flags (after an aborted launch). All ranks call it together."""

@@ -44,15 +44,17 @@ typedef struct mm_config {
 typedef struct mm_layout {
     int64_t total_bytes;
     int64_t off_ctrl;          /* per-SM epochs, device status words, local counters, phase stamps */
-    int64_t off_flags;         /* dispatch / combine arrival flags written by the peers */
+    int64_t off_flags;         /* reserved block (earlier layouts kept arrival flags here) */
     int64_t off_x;             /* [T_max][x_row_bytes]   quantised tokens (caller or frontend writes) */
     int64_t off_x_sf;          /* [T_max][x_sf_row_bytes] one scale byte per `vec` elements, K-major */
     int64_t off_topk_idx;      /* [T_max][topk] int64, -1 = masked slot */
     int64_t off_topk_weights;  /* [T_max][topk] float */
-    int64_t off_rx;            /* [2 parities][num_ranks sources][rx_cap_rows][rx_row_bytes] receive pool */
+    int64_t off_rx;            /* [2 parities][num_ranks sources][rx_region_bytes] receive pool: a 32 B header line (row count), then
+                                  rx_cap_rows rows of 2 * rx_row_bytes; every 8 bytes = {4 data bytes, launch flag} */
     int64_t off_mid;           /* [mid_rows][mid_row_bytes] requantised SwiGLU output (local) */
     int64_t off_mid_sf;        /* [mid_rows][mid_sf_row_bytes] */
-    int64_t off_comb;          /* [T_max][topk][hidden] bf16 expert outputs written back by the peers */
+    int64_t off_comb;          /* [T_max][topk][hidden] bf16 expert outputs written back by the peers, as flagged 8-byte words
+                                  {2 bf16, launch flag}: 4 bytes per element */
     int64_t off_red;           /* [256 SMs][2 phases][2][16][128] float partial sums of weight tiles split between SMs (local) */
     int64_t off_cnt;           /* [2 phases][cnt_per_phase] uint32 contributors that have parked their part of a tile (local) */
     int64_t x_row_bytes, x_sf_row_bytes;
@@ -61,6 +63,7 @@ typedef struct mm_layout {
     int64_t cnt_per_phase;
     int32_t sf_vec;            /* elements per scale byte of the activation format */
     int32_t reserved;
+    int64_t rx_region_bytes;   /* bytes of one (parity, source) region of the receive pool */
 } mm_layout_t;
 
 /* Geometry of the pre-tiled weight stream produced by the load-time transform.

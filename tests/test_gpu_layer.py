@@ -145,6 +145,29 @@ def test_repeated_launches_alternate_parity():
             assert O.rel_rmse(y.cpu(), ref.y[0]) <= REL_RMSE_TOL
 
 
+def test_reset_restarts_the_launch_numbering():
+    """Words that cross between ranks are marked with the launch number. `reset` restarts the numbering, so it must
+    also clear every marked word: after it, launch 1's stale rows (other tokens, other routing) must not be taken for
+    current ones."""
+    dev = 'cuda'
+    fmt, e_local, hidden, inter, topk = 'mxfp4', 4, 512, 256, 2
+    w, _, _ = O.make_expert_weights(e_local, hidden, inter, fmt, seed=1, std=0.05)
+    buf = mm.get_symm_buffer_for_mega_moe(None, e_local, 16, topk, hidden, inter, act_format=fmt)
+    l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(w, fmt, dev))
+    for it, tokens in enumerate([16, 9, 16, 5]):
+        if it == 2:
+            buf.reset()
+        idx, tw = U.random_routing(tokens, e_local, topk, 300 + it)
+        x, inp, sfb = U.make_rank_inputs(tokens, hidden, fmt, 400 + it, idx, tw)
+        ref = O.moe_layer_reference([inp], [w], fmt, e_local, clamp=None, faithful=True)
+        U.write_inputs(buf, inp, sfb)
+        y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
+        mm.fp4_fp4_mega_moe(y, l1, l2, buf, activation_clamp=None, timeout_ms=500.0)
+        st, words = buf.device_status()
+        assert st == 0 and words[1] == (it % 2) + 1
+        assert O.rel_rmse(y.cpu(), ref.y[0]) <= REL_RMSE_TOL
+
+
 def test_bounded_wait_reports_timeout_and_buffer_recovers():
     """A dispatch flag that nothing sets: a two-rank configuration whose second rank never launches. The wait runs
     out after the budget, the status word says which wait, the context stays usable, and after a reset the buffer works."""

@@ -38,7 +38,8 @@ def test_layout_regions_are_ordered_and_sized():
     assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs)
     assert L.x_row_bytes == 1536 and L.x_sf_row_bytes == 96 and L.rx_row_bytes == 1536 + 96 + 16
     assert L.rx_cap_rows == 128 * 8 and L.mid_row_bytes == 640 and L.mid_sf_row_bytes == 48
-    assert L.off_mid - L.off_rx >= 2 * 8 * L.rx_cap_rows * L.rx_row_bytes
+    assert L.rx_region_bytes >= 32 + 2 * L.rx_cap_rows * L.rx_row_bytes
+    assert L.off_mid - L.off_rx >= 2 * 8 * L.rx_region_bytes
     st, L2 = _layout(fmt='nvfp4')
     assert st == 0 and L2.x_sf_row_bytes == 192 and L2.mid_sf_row_bytes == 80 and L2.sf_vec == 16
 

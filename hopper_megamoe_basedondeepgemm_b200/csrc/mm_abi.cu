@@ -206,11 +206,12 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     const size_t xbytes = a8 ? 2 * mm::kXbufBytes : 0;
     const size_t budget = 232448 - sizeof(mm::Ctl) - 1024 /* alignment slack */ - 768;
     // two token staging buffers when that leaves at least four stream stages, else one
+    // (with one, the kernel still runs two 8-row halves when no expert has more than 8 rows: two scale-slot areas always)
     p.nab = 2;
-    size_t fixed = p.nab * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes + mm::kVtBytes + xbytes;
+    size_t fixed = p.nab * p.act_bytes + 2 * p.asf_bytes + mm::kOtileBytes + mm::kVtBytes + xbytes;
     if (fixed + 4 * static_cast<size_t>(p.unit_bytes) > budget) {
         p.nab = 1;
-        fixed = p.nab * (p.act_bytes + p.asf_bytes) + mm::kOtileBytes + mm::kVtBytes + xbytes;
+        fixed = p.nab * p.act_bytes + 2 * p.asf_bytes + mm::kOtileBytes + mm::kVtBytes + xbytes;
     }
     if (fixed + 2 * static_cast<size_t>(p.unit_bytes) > budget) return MM_ERR_UNSUPPORTED;
     int nstage = static_cast<int>((budget - fixed) / p.unit_bytes);
@@ -227,11 +228,12 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.nstage = nstage;
     p.sm_act = nstage * p.unit_bytes;
     p.sm_asf = p.sm_act + p.nab * p.act_bytes;
-    p.sm_otile = p.sm_asf + p.nab * p.asf_bytes;
+    p.sm_otile = p.sm_asf + 2 * p.asf_bytes;
+    p.stage_region = p.sm_otile - p.sm_act;
     p.sm_vt = p.sm_otile + mm::kOtileBytes;
     p.sm_xbuf = static_cast<uint32_t>(align_up(p.sm_vt + mm::kVtBytes, 1024));
     *smem_bytes = (a8 ? p.sm_xbuf + xbytes : p.sm_vt + mm::kVtBytes) + 1024 + 256;
-    if (static_cast<size_t>(p.T) * p.topk * 4 > p.nab * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
+    if (static_cast<size_t>(p.T) * p.topk * 4 > p.stage_region) return MM_ERR_UNSUPPORTED;
     return MM_OK;
 }
 
@@ -313,7 +315,7 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     if (cfg->num_topk != 8 || cfg->num_experts > 1024) return MM_ERR_UNSUPPORTED;
     if (fe->score_mode == 1 && fe->expert_bias == nullptr) return MM_ERR_INVALID_ARGUMENT;
     const bool a8 = cfg->act_format == MM_FMT_FP8;
-    if (static_cast<size_t>(cfg->num_experts) * 4 * ((mm::kThreads + (a8 ? mm::kNumExpThreads : 0)) / 32) > p.nab * static_cast<size_t>(p.act_bytes + p.asf_bytes)) return MM_ERR_UNSUPPORTED;
+    if (static_cast<size_t>(cfg->num_experts) * 4 * ((mm::kThreads + (a8 ? mm::kNumExpThreads : 0)) / 32) > p.stage_region) return MM_ERR_UNSUPPORTED;
     mm_layout_t L;
     mm_get_layout(cfg, &L);
     uint8_t* b = static_cast<uint8_t*>(a->buffer);

@@ -92,7 +92,8 @@ struct KParams {
     long long rx_region;                 // bytes of one (parity, source) region of the receive pool
     uint32_t sm_act, sm_asf, sm_otile, sm_vt;   // dynamic shared memory offsets (stages start at 0)
     uint32_t act_bytes, asf_bytes;
-    uint32_t sm_xbuf; int nab;           // widened-unit buffers (FP8 variant); number of token staging buffers (1 or 2)
+    uint32_t sm_xbuf; int nab;           // widened-unit buffers (FP8 variant); number of 16-row token staging buffers (1 or 2)
+    uint32_t stage_region;               // bytes of the token staging area (tiles + scale slots)
     unsigned long long timeout_ns;
     float* debug_acc; int debug_tasks;   // optional diagnostics: raw accumulators of SM 0's first tasks [task][token][row]
     unsigned long long* trace;           // optional diagnostics: 16 globaltimer stamps per SM
@@ -108,6 +109,10 @@ struct Ctl {
     uint32_t rx_count[kMaxRanks], rx_prefix[kMaxRanks + 1];
     uint32_t exp_count[kMaxLocalExperts], mid_base[kMaxLocalExperts];
     uint32_t nt1, nt2, dcount, pad0;
+    // token staging geometry of this launch: with room for one 16-row buffer only, launches whose experts all have at
+    // most 8 rows split it into two 8-row buffers (the MMA then reads rows 8..15 from rows 0..7: stride 0 between the
+    // 8-row groups; those accumulator columns are never used)
+    uint32_t nab, act_stride, atom_stride, sbo;
     uint32_t tasks[kMaxTasks];           // type << 28 | expert << 20 | token tile << 8 | weight tile
     uint32_t tasks2[kMaxTasks];          // first unit | end unit << 8 | parts of the tile << 16 | first contributing SM << 24
     uint32_t tasks3[kMaxTasks];          // tile index inside its phase (counter slot)
@@ -249,11 +254,11 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
-        const uint32_t ab = ti % p.nab, acc = ti & 1u, use_a = (ti / p.nab) & 1u, use = (ti >> 1) & 1u;
+        const uint32_t ab = ti % c.nab, acc = ti & 1u, use_a = (ti / c.nab) & 1u, use = (ti >> 1) & 1u;
         if (!cx.warp_wait(&c.acts_full[ab], use_a, kErrWaitActsFull)) return;
         if (!cx.warp_wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty)) return;
         tc_fence_after();
-        const uint32_t act = smem_u32(cx.smem + p.sm_act + ab * p.act_bytes);
+        const uint32_t act = smem_u32(cx.smem + p.sm_act + ab * c.act_stride);
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
             const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
@@ -276,13 +281,13 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
                     utccp_32x128b_warpx4(sfb + pl * 4u, smem_desc(asf + pl * 256u, 128u, kLayoutNone));
                 }
                 // token tile: [K atoms][16 rows x 128 B]; an atom holds 256 packed E2M1 or 128 E4M3 elements
-                const uint32_t bsm = act + static_cast<uint32_t>(u) * (kA8 ? 2u : 1u) * (kTileTokens * 128u);
+                const uint32_t bsm = act + static_cast<uint32_t>(u) * (kA8 ? 2u : 1u) * c.atom_stride;
                 #pragma unroll
                 for (uint32_t ks = 0; ks < kUnitK / kStepK; ++ks) {
                     const uint32_t pl = (ks * kStepK) / (4u * kVec), sf_id = ((ks * kStepK) % (4u * kVec)) / kVec;
                     const uint32_t atom = ks / kStepsPerAtom, in_atom = (ks % kStepsPerAtom) * 32u;
                     const uint64_t adesc = smem_desc(wsm + (kA8 ? atom * kUnitWBytes : 0u) + in_atom, 1024u, kLayoutSw128);
-                    const uint64_t bdesc = smem_desc(bsm + (kA8 ? atom * (kTileTokens * 128u) : 0u) + in_atom, 1024u, kLayoutSw128);
+                    const uint64_t bdesc = smem_desc(bsm + (kA8 ? atom * c.atom_stride : 0u) + in_atom, c.sbo, kLayoutSw128);
                     const uint32_t idesc = idesc_with_sf(kIdesc, sf_id, sf_id);
                     const uint32_t accum = (u > ub || ks > 0) ? 1u : 0u;
                     if constexpr (kA8)
@@ -377,12 +382,12 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
     uint32_t* l1_done = reinterpret_cast<uint32_t*>(cx.buf + p.off_ctrl + kCtrlL1Done) + cx.par * kMaxLocalExperts;
     uint32_t* rowref = c.rowref[sw];
     uint32_t* rowidx = c.rowidx[sw];
-    if (sw >= static_cast<uint32_t>(p.nab)) return;
+    if (sw >= c.nab) return;
     #pragma unroll 1
-    for (uint32_t ti = sw; ti < c.ntasks; ti += p.nab) {      // with one staging buffer, stager 0 takes every task
+    for (uint32_t ti = sw; ti < c.ntasks; ti += c.nab) {      // with one staging buffer, stager 0 takes every task
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
-        const uint32_t ab = ti % p.nab, use = (ti / p.nab) & 1u, ring = ti & 3u;
+        const uint32_t ab = ti % c.nab, use = (ti / c.nab) & 1u, ring = ti & 3u;
         if (!cx.warp_wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty)) return;
         find_rows(c, rowref, total, e, mt, lane);
         const uint32_t left = c.exp_count[e] - mt * kTileTokens;
@@ -420,7 +425,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
             }
         }
         if (!__all_sync(0xffffffffu, ok)) return;
-        uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
+        uint8_t* act = cx.smem + p.sm_act + ab * c.act_stride;
         uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
         const uint32_t nchunk = (type ? p.mid_row_bytes : p.x_row_bytes) / 16;             // 16 B chunks of one token row
         const uint32_t sfchunk = (type ? p.mid_sf_row_bytes : p.x_sf_row_bytes) / 16;      // 16 B chunks of one row's scale bytes
@@ -468,7 +473,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                 for (uint32_t u = 0; u < 4; ++u) {
                     const uint32_t ci = base + u * 32;
                     if (ci < nchunk) {
-                        *reinterpret_cast<uint4*>(act + (ci >> 3) * (kTileTokens * 128u) + sw128_off(n, ci & 7u)) = v[u];
+                        *reinterpret_cast<uint4*>(act + (ci >> 3) * c.atom_stride + sw128_off(n, ci & 7u)) = v[u];
                     } else if (ci < per_row) {
                         // four scale words: one 16 B slot per (scale word, token), word g of the row at slot g
                         uint8_t* dst = asf + (ci - nchunk) * 4u * 256u + n * 16u;
@@ -543,7 +548,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF, j = t & 0xFF;
-        const uint32_t ab = ti % p.nab, acc = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u;
+        const uint32_t ab = ti % c.nab, acc = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u;
         // ---- accumulators of the valid tokens -> shared memory (the loops below run over the valid tokens only)
         bool ok;
         uint32_t nv = 0;
@@ -571,7 +576,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 #pragma unroll
                 for (int n = 0; n < kTileTokens; ++n) v[n] = 0.f;
                 const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
-                const uint8_t* act = cx.smem + p.sm_act + ab * p.act_bytes;
+                const uint8_t* act = cx.smem + p.sm_act + ab * c.act_stride;
                 const uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
                 #pragma unroll 1
                 for (int u = ub; u < ue && ok; ++u, ++it) {
@@ -833,7 +838,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         if (tid == 0) st_ll_16B(region, make_uint4(cnt, 0u, 0u, 0u), flag);
         uint8_t* dst_base = region + 32u;
         const float* tw = reinterpret_cast<const float*>(buf + p.off_topk_w);
-        // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (four in flight)
+        // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (eight in flight: one memory round trip for a row of up to 4 KB)
         #pragma unroll 1
         for (uint32_t i = warp; i < cnt; i += kNT / 32) {
             const uint32_t ent = dlist[i], tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
@@ -841,17 +846,17 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             const uint8_t* sf_src = buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
             uint8_t* dst = dst_base + static_cast<size_t>(i) * 2u * p.rx_row_bytes;
             #pragma unroll 1
-            for (uint32_t base = lane; base < nchunk; base += 4 * 32) {
-                uint4 v[4];
+            for (uint32_t base = lane; base < nchunk; base += 8 * 32) {
+                uint4 v[8];
                 #pragma unroll
-                for (uint32_t u = 0; u < 4; ++u) {
+                for (uint32_t u = 0; u < 8; ++u) {
                     const uint32_t ci = base + u * 32;
                     if (ci < xq) v[u] = *reinterpret_cast<const uint4*>(xs_src + ci * 16u);
                     else if (ci < xq + xs) v[u] = *reinterpret_cast<const uint4*>(sf_src + (ci - xq) * 16u);
                     else if (ci < nchunk) v[u] = make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot]));
                 }
                 #pragma unroll
-                for (uint32_t u = 0; u < 4; ++u) {
+                for (uint32_t u = 0; u < 8; ++u) {
                     const uint32_t ci = base + u * 32;
                     if (ci < nchunk) st_ll_16B(dst + ci * 32u, v[u], flag);
                 }
@@ -864,7 +869,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
 
     // ---- the staging buffers start from zero: rows beyond a task's valid tokens only ever hold finite bytes
     #pragma unroll 1
-    for (uint32_t off = tid * 16u; off < p.nab * (p.act_bytes + p.asf_bytes); off += kNT * 16u)
+    for (uint32_t off = tid * 16u; off < p.stage_region; off += kNT * 16u)
         *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
 
     // ---- receive: wait for every source rank's header line, then scan the received rows' records
@@ -916,6 +921,14 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             if (static_cast<int>(lane) >= o) { i0 += v0; i1 += v1; }
         }
         const uint32_t tot0 = __shfl_sync(0xffffffffu, i0, 31), M = tot0 + __shfl_sync(0xffffffffu, i1, 31);
+        const bool big = __any_sync(0xffffffffu, c0 > 8u || c1 > 8u);
+        if (lane == 0) {
+            const bool split = p.nab == 1 && !big;
+            c.nab = split ? 2u : static_cast<uint32_t>(p.nab);
+            c.act_stride = split ? p.act_bytes / 2u : p.act_bytes;
+            c.atom_stride = split ? 8u * 128u : kTileTokens * 128u;
+            c.sbo = split ? 0u : 1024u;
+        }
         const uint32_t x0 = i0 - m0, x1 = tot0 + i1 - m1;
         if (lane < el) c.mid_base[lane] = x0 * kTileTokens;
         if (lane + 32 < el) c.mid_base[lane + 32] = x1 * kTileTokens;

@@ -195,7 +195,6 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     const double tmo = a->timeout_ms > 0.f ? a->timeout_ms : 2000.0;
     p.timeout_ns = static_cast<unsigned long long>(tmo * 1e6);
     p.trace = static_cast<unsigned long long*>(a->debug_trace);
-    { const char* d = getenv("MM_DBG"); p.dbg = d ? atoi(d) : 0; }
     p.debug_acc = static_cast<float*>(a->debug_accumulators); p.debug_tasks = a->debug_accumulators ? a->debug_num_tasks : 0;
     // shared memory plan: [stages][token tiles][token scale chunks][output tile][accumulator tile][widened units (FP8)]
     const int kmax = p.H > p.I ? p.H : p.I;
@@ -217,13 +216,7 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     int nstage = static_cast<int>((budget - fixed) / p.unit_bytes);
     // A short ring is faster than a deep one: the loader runs ahead into the next phase's weights, and with many stages
     // that prefetch competes with the stream the current phase is waiting for (measured: 4 stages beat 8 by 2 us).
-    {
-        int want = mm::kDefaultStages;
-        const char* d = getenv("MM_NSTAGE");
-        if (d) want = atoi(d);
-        if (want > mm::kMaxStages) want = mm::kMaxStages;
-        if (nstage > want) nstage = want;
-    }
+    if (nstage > mm::kDefaultStages) nstage = mm::kDefaultStages;
     if (nstage < 2) return MM_ERR_UNSUPPORTED;
     p.nstage = nstage;
     p.sm_act = nstage * p.unit_bytes;

@@ -97,7 +97,6 @@ struct KParams {
     unsigned long long timeout_ns;
     float* debug_acc; int debug_tasks;   // optional diagnostics: raw accumulators of SM 0's first tasks [task][token][row]
     unsigned long long* trace;           // optional diagnostics: 16 globaltimer stamps per SM
-    int dbg;
     FeParams fe; int fe_enabled;         // router frontend run at the head of the same launch (optional)
 };
 
@@ -168,7 +167,7 @@ struct Ctx {
         return __all_sync(0xffffffffu, wait(bar, parity, code));
     }
     __device__ __forceinline__ void trace(int slot) const {
-        if (p.trace != nullptr && (!(p.dbg & 8) || ((0x0680FDF9u >> slot) & 1u))) p.trace[blockIdx.x * 96 + slot] = globaltimer_ns();
+        if (p.trace != nullptr) p.trace[blockIdx.x * 96 + slot] = globaltimer_ns();
     }
     __device__ __forceinline__ void stamp(int slot) const {
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[slot] = globaltimer_ns();
@@ -421,7 +420,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                         if (cx.expired()) { cx.fail(kErrWaitL1Done, e); ok = false; break; }
                     }
                 }
-                if (p.trace != nullptr && !(p.dbg & 8) && p.trace[blockIdx.x * 96 + 24] == 0) cx.trace(24);
+                if (p.trace != nullptr && p.trace[blockIdx.x * 96 + 24] == 0) cx.trace(24);
             }
         }
         if (!__all_sync(0xffffffffu, ok)) return;

@@ -17,6 +17,46 @@ from oracle import megamoe_oracle as O                     # noqa: E402
 from tests import util_moe as U                            # noqa: E402
 
 
+def run_from_hidden(rank, world, group, fmt):
+    """The whole layer from bf16 hidden states (router + top-8 + quantisation fused at the head of the kernel)."""
+    e_local, hidden, inter, topk = 8, 1024, 512, 8
+    num_experts = e_local * world
+    tokens = [5 + 2 * r for r in range(world)]
+    ok = True
+    buf = mm.get_symm_buffer_for_mega_moe(group, num_experts, 16, topk, hidden, inter, act_format=fmt)
+    weights = [O.make_expert_weights(e_local, hidden, inter, fmt, seed=70 + r, std=0.05)[0] for r in range(world)]
+    l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(weights[rank], fmt, 'cuda'))
+    ws = torch.zeros(mm.fe_workspace_bytes(buf), dtype=torch.uint8, device='cuda')
+    g = torch.Generator().manual_seed(7)
+    wr = (torch.randn((num_experts, hidden), generator=g) / hidden ** 0.5).to(torch.bfloat16)
+    for it in range(2):
+        xs, inputs = [], []
+        for r in range(world):
+            gx = torch.Generator().manual_seed(1000 * it + r)
+            x = torch.randn((tokens[r], hidden), generator=gx).to(torch.bfloat16)
+            idx, tw = O.route_from_logits(O.router_logits_device_order(x, wr), x, topk)
+            q, sf, _ = O.quantise_tokens(x, fmt, rounding='rne', sf_rule='mul')
+            xs.append(x); inputs.append(O.RankInput(q, sf, idx, tw))
+        ref = O.moe_layer_reference(inputs, weights, fmt, num_experts, clamp=10.0)
+        y = torch.empty((tokens[rank], hidden), dtype=torch.bfloat16, device='cuda')
+        dist.barrier()
+        mm.mega_moe_from_hidden(y, xs[rank].cuda(), wr.cuda(), l1, l2, buf, ws, activation_clamp=10.0, timeout_ms=2000.0)
+        st, words = buf.device_status()
+        if st != 0:
+            print(f'rank {rank}: device status {st} {[hex(v) for v in words[:4]]}', flush=True)
+            return False
+        if not torch.equal(buf.topk_idx[:tokens[rank]].cpu(), inputs[rank].topk_idx):
+            print(f'rank {rank} it {it}: top-8 differs from the oracle', flush=True)
+            ok = False
+        err, cos = O.rel_rmse(y.cpu(), ref.y[rank]), O.cosine(y.cpu(), ref.y[rank])
+        if not (err <= 3e-3 and cos >= 0.9999):
+            print(f'rank {rank} it {it}: rel_rmse {err:.4e} cos {cos:.6f}', flush=True)
+            ok = False
+        torch.cuda.synchronize()
+        dist.barrier()
+    return ok
+
+
 def main():
     rank, world = int(os.environ['RANK']), int(os.environ['WORLD_SIZE'])
     torch.cuda.set_device(int(os.environ.get('LOCAL_RANK', rank)))
@@ -24,6 +64,14 @@ def main():
     group = dist.group.WORLD
     fmt = os.environ.get('MP_FORMAT', 'mxfp4')
     engine = os.environ.get('MP_ENGINE', 'umma')
+    if os.environ.get('MP_MODE', 'routed') == 'from_hidden':
+        flag = torch.tensor([1 if run_from_hidden(rank, world, group, fmt) else 0], device='cuda')
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if rank == 0:
+            print('MP_OK' if int(flag) == 1 else 'MP_FAIL', flush=True)
+        dist.barrier()
+        dist.destroy_process_group()
+        return
     e_local, hidden, inter, topk = 8, 1024, 512, 4
     num_experts = e_local * world
     tokens = [(5 + 3 * r) % 7 for r in range(world)]          # ragged, some ranks may have 0 tokens

@@ -10,8 +10,8 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(nproc, fmt, engine='umma'):
-    env = dict(os.environ, MP_FORMAT=fmt, MP_ENGINE=engine)
+def _run(nproc, fmt, engine='umma', mode='routed'):
+    env = dict(os.environ, MP_FORMAT=fmt, MP_ENGINE=engine, MP_MODE=mode)
     cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={nproc}',
            '--master-addr', '127.0.0.1', '--master-port', '29531', os.path.join(ROOT, 'tests', 'mp_worker.py')]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
@@ -23,6 +23,12 @@ def test_two_ranks(fmt):
     if torch.cuda.device_count() < 2:
         pytest.skip('needs two GPUs')
     _run(2, fmt)
+
+
+def test_two_ranks_from_hidden_states():
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    _run(2, 'mxfp4', mode='from_hidden')
 
 
 def test_all_ranks_of_the_node():

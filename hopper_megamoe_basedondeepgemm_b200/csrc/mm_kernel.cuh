@@ -115,7 +115,6 @@ struct Ctl {
     uint32_t tasks[kMaxTasks];           // type << 28 | expert << 20 | token tile << 8 | weight tile
     uint32_t tasks2[kMaxTasks];          // first unit | end unit << 8 | parts of the tile << 16 | first contributing SM << 24
     uint32_t tasks3[kMaxTasks];          // tile index inside its phase (counter slot)
-    uint32_t sk_q[2], sk_rem[2];         // unit ranges of the phases: the first `rem` SMs own q + 1 units, the others q
     uint32_t red_old;
     RowMeta row_meta[4][kTileTokens];
     RowMeta epi_meta[2][kTileTokens];
@@ -190,13 +189,6 @@ struct Ctx {
     }
 };
 
-// unit ranges: SM g owns units [sk_lo(g), sk_lo(g + 1)) of a phase
-__device__ __forceinline__ uint32_t sk_lo(uint32_t g, uint32_t q, uint32_t rem) { return g * q + (g < rem ? g : rem); }
-__device__ __forceinline__ uint32_t sk_owner(uint32_t unit, uint32_t q, uint32_t rem) {
-    const uint32_t head = rem * (q + 1u);
-    return unit < head ? unit / (q + 1u) : rem + (unit - head) / q;
-}
-
 // position of 16 B chunk `c` of row `r` inside a 128 B-swizzled [rows x 128 B] tile
 __device__ __forceinline__ uint32_t sw128_off(uint32_t r, uint32_t c) {
     return (r >> 3) * 1024u + (r & 7u) * 128u + ((c ^ (r & 7u)) << 4);
@@ -215,7 +207,7 @@ __device__ __forceinline__ float sf_value(uint32_t byte) {
 // ============================================================================================= weight loader
 __device__ void role_loader(const Ctx& cx) {
     const KParams& p = cx.p; Ctl& c = cx.c;
-    uint32_t it = 0;
+    uint32_t it = 0, s = 0, ph = 0;                              // units issued; ring stage and its phase bit
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
@@ -225,7 +217,6 @@ __device__ void role_loader(const Ctx& cx) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
-            const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
             if (!cx.warp_wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
             if (elect_one()) {
                 if (it == 0) cx.trace(4);
@@ -233,6 +224,7 @@ __device__ void role_loader(const Ctx& cx) {
                 bulk_g2s(cx.smem + static_cast<size_t>(s) * p.unit_bytes, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
             }
             __syncwarp();
+            if (++s == static_cast<uint32_t>(p.nstage)) { s = 0; ph ^= 1u; }
         }
     }
     if ((threadIdx.x & 31u) == 0u) cx.trace(5);
@@ -249,18 +241,18 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     constexpr uint32_t kStepsPerAtom = kA8 ? 4u : 4u;           // 128 B of operand bytes per swizzle atom either way
     const uint32_t tm = c.tmem_base;
     const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 16
-    uint32_t it = 0;                                            // units consumed so far
+    uint32_t it = 0, s = 0, ph = 0;                             // units consumed so far; ring stage and its phase bit
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
-        const uint32_t ab = ti % c.nab, acc = ti & 1u, use_a = (ti / c.nab) & 1u, use = (ti >> 1) & 1u;
+        const uint32_t acc = ti & 1u, use = (ti >> 1) & 1u;
+        const uint32_t ab = c.nab == 2u ? acc : 0u, use_a = c.nab == 2u ? use : acc;
         if (!cx.warp_wait(&c.acts_full[ab], use_a, kErrWaitActsFull)) return;
         if (!cx.warp_wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty)) return;
         tc_fence_after();
         const uint32_t act = smem_u32(cx.smem + p.sm_act + ab * c.act_stride);
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
-            const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
             uint64_t* ready = kA8 ? &c.xfull[it & 1u] : &c.full[s];
             if (!cx.warp_wait(ready, kA8 ? (it >> 1) & 1u : ph, kErrWaitFull)) return;
             tc_fence_after();
@@ -300,6 +292,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
               tc_commit(kA8 ? &c.xempty[it & 1u] : &c.empty[s]);
             }
             __syncwarp();
+            if (++s == static_cast<uint32_t>(p.nstage)) { s = 0; ph ^= 1u; }
         }
         if (elect_one()) {
             tc_commit(&c.tmem_full[acc]);
@@ -321,14 +314,15 @@ __device__ void role_expander(const Ctx& cx, uint32_t xtid) {
     constexpr uint32_t kGroupThreads = kNumExpThreads / 2;
     const uint32_t lane = xtid & 31u, grp = xtid / kGroupThreads, gt = xtid % kGroupThreads;
     uint8_t* xb = cx.smem + p.sm_xbuf + grp * kXbufBytes;
-    uint32_t it = 0;
+    uint32_t it = 0, s_next = 0, ph_next = 0;
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
+            const uint32_t s = s_next, ph = ph_next;
+            if (++s_next == static_cast<uint32_t>(p.nstage)) { s_next = 0; ph_next ^= 1u; }
             if ((it & 1u) != grp) continue;
-            const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
             // every warp waits and signals for itself (the barriers count a group's four warps): no block-level barrier per unit
             if (!cx.warp_wait(&c.full[s], ph, kErrWaitFull)) return;
             if (!cx.warp_wait(&c.xempty[grp], ((it >> 1) & 1u) ^ 1u, kErrWaitEmpty)) return;
@@ -386,7 +380,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
     for (uint32_t ti = sw; ti < c.ntasks; ti += c.nab) {      // with one staging buffer, stager 0 takes every task
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
-        const uint32_t ab = ti % c.nab, use = (ti / c.nab) & 1u, ring = ti & 3u;
+        const uint32_t ab = c.nab == 2u ? (ti & 1u) : 0u, use = c.nab == 2u ? (ti >> 1) & 1u : (ti & 1u), ring = ti & 3u;
         if (!cx.warp_wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty)) return;
         find_rows(c, rowref, total, e, mt, lane);
         const uint32_t left = c.exp_count[e] - mt * kTileTokens;
@@ -547,7 +541,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF, j = t & 0xFF;
-        const uint32_t ab = ti % c.nab, acc = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u;
+        const uint32_t acc = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u, ab = c.nab == 2u ? acc : 0u;
         // ---- accumulators of the valid tokens -> shared memory (the loops below run over the valid tokens only)
         bool ok;
         uint32_t nv = 0;
@@ -579,7 +573,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 const uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
                 #pragma unroll 1
                 for (int u = ub; u < ue && ok; ++u, ++it) {
-                    const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;
+                    const uint32_t s = it % p.nstage, ph = (it / p.nstage) & 1u;      // cross-check engine: not a fast path
                     ok = cx.warp_wait(&c.full[s], ph, kErrWaitFull);
                     if (ok) {
                         check_accumulate<kVec>(cx, cx.smem + static_cast<size_t>(s) * p.unit_bytes, act, asf, u, row, nv, v);
@@ -601,11 +595,9 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
         if (np > 1u) {
             // this SM covered only part of the tile's K range: park the partial sums, count in, and let the last
             // contributor add the parts in SM order (a fixed order: the result does not depend on who arrives last)
-            const uint32_t kunits = type ? p.k2_units : p.k1_units, tile = c.tasks3[ti], cfirst = c.tasks2[ti] >> 24;
-            const uint32_t q = c.sk_q[type], rem = c.sk_rem[type];
+            const uint32_t tile = c.tasks3[ti], cfirst = c.tasks2[ti] >> 24;
             float* red = reinterpret_cast<float*>(cx.buf + p.off_red);
-            const uint32_t my_slot = (sk_lo(blockIdx.x, q, rem) / kunits == tile) ? 0u : 1u;
-            float* mine = red + ((static_cast<size_t>(blockIdx.x) * 2u + type) * 2u + my_slot) * (kTileTokens * kTileRows) + row;
+            float* mine = red + ((static_cast<size_t>(blockIdx.x) * 2u + type) * 2u) * (kTileTokens * kTileRows) + row;
             #pragma unroll 1
             for (uint32_t n = 0; n < nv; ++n) mine[n * kTileRows] = vt[n * kTileRows];
             bar_sync(kBarEpi, kNumEpiThreads);
@@ -628,8 +620,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                         const uint32_t g = cfirst + pc0 + d;
                         part_v[d] = 0.f;
                         if (pc0 + d < np) {
-                            const uint32_t slot = (sk_lo(g, q, rem) / kunits == tile) ? 0u : 1u;
-                            const float* part = red + ((static_cast<size_t>(g) * 2u + type) * 2u + slot) * (kTileTokens * kTileRows);
+                            const float* part = red + ((static_cast<size_t>(g) * 2u + type) * 2u) * (kTileTokens * kTileRows);
                             part_v[d] = __uint_as_float(ld_cg_u32(part + n * kTileRows + row));
                         }
                     }
@@ -809,15 +800,32 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             for (uint32_t base = 0; base < n; base += 32) {
                 const uint32_t i = base + lane;
                 const long long ex = i < n ? tk[i] : -1;
-                const bool m = ex >= 0 && static_cast<uint32_t>(ex / p.e_local) == d;
+                const uint32_t ex32 = ex >= 0 && ex < 0x10000 ? static_cast<uint32_t>(ex) : 0u;
+                const uint32_t dest = udiv_small(ex32, p.e_local), tok = udiv_small(i, p.topk);
+                const bool m = ex >= 0 && ex < 0x10000 && dest == d;
                 const uint32_t b = __ballot_sync(0xffffffffu, m);
-                if (m) dlist[cnt + __popc(b & ((1u << lane) - 1u))] = ((i / p.topk) << 16) | ((i % p.topk) << 8) | static_cast<uint32_t>(ex % p.e_local);
+                if (m) dlist[cnt + __popc(b & ((1u << lane) - 1u))] = (tok << 16) | ((i - tok * p.topk) << 8) | (ex32 - dest * p.e_local);
                 cnt += __popc(b);
             }
             if (lane == 0) c.dcount = cnt;
         }
         __syncthreads();
         const uint32_t cnt = c.dcount;
+        const uint32_t nchunk = (p.rx_row_bytes - 16) / 16, xq = p.x_row_bytes / 16;      // payload chunks of a row: tokens, then scale bytes
+        const uint32_t flag = epoch + 1u;
+        uint8_t* region = p.peer[d] + p.off_rx + static_cast<size_t>(par * p.R + p.rank) * p.rx_region;
+        uint8_t* dst_base = region + 32u;
+        const float* tw = reinterpret_cast<const float*>(buf + p.off_topk_w);
+        // Header line (row count) and the rows' 16 B records (expert, token, slot, weight) leave first: they are all the
+        // receiver's scheduler needs, and they do not depend on the token data. Every word is self-validating (flagged),
+        // so nothing has to order these stores against the payload that follows.
+        if (tid == 0) st_ll_16B(region, make_uint4(cnt, 0u, 0u, 0u), flag);
+        #pragma unroll 1
+        for (uint32_t i = tid; i < cnt; i += kNT) {
+            const uint32_t ent = dlist[i], tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
+            st_ll_16B(dst_base + static_cast<size_t>(i) * 2u * p.rx_row_bytes + 2u * (p.rx_row_bytes - 16),
+                      make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot])), flag);
+        }
         if constexpr (kFe) {
             // quantise the tokens this SM is about to send into the x / x_sf views (the same bytes whichever SM writes them)
             #pragma unroll 1
@@ -829,18 +837,11 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             }
             __syncthreads();
         }
-        const uint32_t nchunk = p.rx_row_bytes / 16, xq = p.x_row_bytes / 16, xs = p.x_sf_row_bytes / 16;
-        const uint32_t flag = epoch + 1u;
-        uint8_t* region = p.peer[d] + p.off_rx + static_cast<size_t>(par * p.R + p.rank) * p.rx_region;
-        // the header line carries the row count; like every word of the rows it is self-validating (flagged), so nothing
-        // orders it against the rows and it can leave first
-        if (tid == 0) st_ll_16B(region, make_uint4(cnt, 0u, 0u, 0u), flag);
-        uint8_t* dst_base = region + 32u;
-        const float* tw = reinterpret_cast<const float*>(buf + p.off_topk_w);
-        // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (eight in flight: one memory round trip for a row of up to 4 KB)
+        // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (eight in flight: one memory round trip for
+        // a row of up to 4 KB)
         #pragma unroll 1
         for (uint32_t i = warp; i < cnt; i += kNT / 32) {
-            const uint32_t ent = dlist[i], tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
+            const uint32_t tok = dlist[i] >> 16;
             const uint8_t* xs_src = buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
             const uint8_t* sf_src = buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
             uint8_t* dst = dst_base + static_cast<size_t>(i) * 2u * p.rx_row_bytes;
@@ -851,8 +852,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 for (uint32_t u = 0; u < 8; ++u) {
                     const uint32_t ci = base + u * 32;
                     if (ci < xq) v[u] = *reinterpret_cast<const uint4*>(xs_src + ci * 16u);
-                    else if (ci < xq + xs) v[u] = *reinterpret_cast<const uint4*>(sf_src + (ci - xq) * 16u);
-                    else if (ci < nchunk) v[u] = make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot]));
+                    else if (ci < nchunk) v[u] = *reinterpret_cast<const uint4*>(sf_src + (ci - xq) * 16u);
                 }
                 #pragma unroll
                 for (uint32_t u = 0; u < 8; ++u) {
@@ -871,10 +871,20 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     for (uint32_t off = tid * 16u; off < p.stage_region; off += kNT * 16u)
         *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
 
-    // ---- receive: wait for every source rank's header line, then scan the received rows' records
+    // ---- receive: wait for every source rank's header line, then scan the received rows' records. The first 32 records
+    //      of every source are fetched speculatively in the same memory round trip as the headers (thread 32 r + i takes
+    //      record i of source r); a record that was not there yet, and any record beyond the first 32, is polled afterwards.
+    const uint32_t flag_rx = epoch + 1u;
+    const uint32_t spec_r = tid >> 5, spec_i = tid & 31u;
+    const bool spec = tid < 32u * static_cast<uint32_t>(p.R) && spec_i < static_cast<uint32_t>(p.cap);
+    uint4 spec_a = make_uint4(0u, 0u, 0u, 0u), spec_b = spec_a;
+    if (spec) {
+        const uint8_t* src = cx.rx_row(spec_r, spec_i) + 2u * (p.rx_row_bytes - 16);
+        spec_a = ld_volatile_v4(src); spec_b = ld_volatile_v4(src + 16);
+    }
     if (tid < static_cast<uint32_t>(p.R)) {
         uint4 h = make_uint4(0u, 0u, 0u, 0u);
-        cx.ll_read(buf + p.off_rx + static_cast<size_t>(par * p.R + tid) * p.rx_region, epoch + 1u, h, kErrWaitDispatchFlag, tid);
+        cx.ll_read(buf + p.off_rx + static_cast<size_t>(par * p.R + tid) * p.rx_region, flag_rx, h, kErrWaitDispatchFlag, tid);
         c.rx_count[tid] = h.x <= static_cast<uint32_t>(p.cap) ? h.x : 0u;
     }
     __syncthreads();
@@ -891,17 +901,27 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             cx.trace(2);
         }
         if (total <= kMetaCap) {
+            auto take = [&](uint32_t f, const uint4& m) {
+                const uint32_t e = m.x & 0xFFu;
+                c.meta_e[f] = static_cast<uint8_t>(e);
+                if (f < kMetaSmemRows) c.rx_meta[f] = RowMeta{0, static_cast<int32_t>(m.y), static_cast<int32_t>(m.z), __uint_as_float(m.w)};
+                atomicAdd(&c.exp_count[e < kMaxLocalExperts ? e : 0], 1u);
+            };
+            if (spec && spec_i < c.rx_count[spec_r]) {
+                uint4 m = ll_data(spec_a, spec_b);
+                if (!ll_valid(spec_a, spec_b, flag_rx))
+                    cx.ll_read(cx.rx_row(spec_r, spec_i) + 2u * (p.rx_row_bytes - 16), flag_rx, m, kErrWaitDispatchFlag, spec_r);
+                take(pre[spec_r] + spec_i, m);
+            }
             #pragma unroll 1
             for (uint32_t f = tid; f < total; f += kNT) {
                 uint32_t r = 0;
                 #pragma unroll
                 for (int q = 1; q < kMaxRanks; ++q) r += (q < p.R && f >= pre[q]) ? 1u : 0u;
+                if (f - pre[r] < 32u) continue;                      // taken by the speculative read above
                 uint4 m = make_uint4(0u, 0u, 0u, 0u);
-                cx.ll_read(cx.rx_row(r, f - pre[r]) + 2u * (p.rx_row_bytes - 16), epoch + 1u, m, kErrWaitDispatchFlag, r);
-                const uint32_t e = m.x & 0xFFu;
-                c.meta_e[f] = static_cast<uint8_t>(e);
-                if (f < kMetaSmemRows) c.rx_meta[f] = RowMeta{0, static_cast<int32_t>(m.y), static_cast<int32_t>(m.z), __uint_as_float(m.w)};
-                atomicAdd(&c.exp_count[e < kMaxLocalExperts ? e : 0], 1u);
+                cx.ll_read(cx.rx_row(r, f - pre[r]) + 2u * (p.rx_row_bytes - 16), flag_rx, m, kErrWaitDispatchFlag, r);
+                take(f, m);
             }
         }
     }
@@ -938,33 +958,30 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             for (uint32_t mt = 0; mt < m1; ++mt) c.mtl[x1 + mt] = ((lane + 32) << 16) | mt;
         }
         __syncwarp();
-        // A phase has NT = M * n weight-tile tasks of k units each. The first NT % G tiles are the remainder: their units
-        // form one line of which every SM takes an equal contiguous share (split tiles, parts reduced by the last
-        // contributor); they run first. Then SM g runs the whole tiles NT % G + g, + G, ... Every SM streams the same
-        // number of units (+-1) and the epilogue that ends a phase is a whole-tile one.
+        // A phase has NT = M * n weight-tile tasks of k units each. The first r = NT % G tiles are the remainder: tile t of
+        // them is shared by the SMs [ceil(t G / r), ceil((t + 1) G / r)), each taking one contiguous range of the tile's K
+        // units (sizes differ by at most one; parts are reduced by the last contributor). Every SM has at most one such
+        // partial task per phase, and it runs first. Then SM g runs the whole tiles r + g, + G, ...
         uint32_t nmine = 0;
         if (M <= kMaxMTiles) {
             #pragma unroll 1
             for (uint32_t type = 0; type < 2; ++type) {
                 const uint32_t n = type ? p.n2_tiles : p.n1_tiles, k = type ? p.k2_units : p.k1_units;
-                const uint32_t NT = M * n, r = NT % G, U = r * k, q = U / G, rem = U % G;
-                if (lane == 0) { c.sk_q[type] = q; c.sk_rem[type] = rem; }
-                const uint32_t lo = sk_lo(bid, q, rem), hi = sk_lo(bid + 1u, q, rem);
-                if (hi > lo) {
-                    const uint32_t t_first = lo / k, t_last = (hi - 1u) / k;      // at most two tiles: the share is < k units
-                    const uint32_t t = t_first + lane;
-                    const bool m = t <= t_last;
-                    const uint32_t b = __ballot_sync(0xffffffffu, m);
-                    const uint32_t pos = nmine + __popc(b & ((1u << lane) - 1u));
-                    if (m && pos < kMaxTasks) {
-                        const uint32_t ub = (lo > t * k ? lo : t * k) - t * k, ue = (hi < (t + 1u) * k ? hi : (t + 1u) * k) - t * k;
-                        const uint32_t cfirst = sk_owner(t * k, q, rem), clast = sk_owner((t + 1u) * k - 1u, q, rem);
-                        const uint32_t ent = c.mtl[t / n];
-                        c.tasks[pos] = task_pack(type, ent >> 16, ent & 0xFFFFu, t % n);
-                        c.tasks2[pos] = ub | (ue << 8) | ((clast - cfirst + 1u) << 16) | (cfirst << 24);
-                        c.tasks3[pos] = t;
+                const uint32_t NT = M * n, r = NT - udiv_small(NT, G) * G;
+                if (r > 0u) {
+                    const uint32_t t = udiv_small(bid * r, G);
+                    const uint32_t gs = udiv_small(t * G + r - 1u, r), ge = udiv_small((t + 1u) * G + r - 1u, r);
+                    const uint32_t S = ge - gs, li = bid - gs, base = udiv_small(k, S), extra = k - base * S;
+                    const uint32_t ub = li * base + (li < extra ? li : extra), ue = ub + base + (li < extra ? 1u : 0u);
+                    if (ue > ub) {
+                        if (lane == 0 && nmine < kMaxTasks) {
+                            const uint32_t mi = udiv_small(t, n), ent = c.mtl[mi];
+                            c.tasks[nmine] = task_pack(type, ent >> 16, ent & 0xFFFFu, t - mi * n);
+                            c.tasks2[nmine] = ub | (ue << 8) | ((S < k ? S : k) << 16) | (gs << 24);
+                            c.tasks3[nmine] = t;
+                        }
+                        nmine += 1u;
                     }
-                    nmine += __popc(b);
                 }
                 #pragma unroll 1
                 for (uint32_t i0 = 0;; i0 += 32) {
@@ -974,8 +991,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                     if (b == 0u) break;
                     const uint32_t pos = nmine + __popc(b & ((1u << lane) - 1u));
                     if (m && pos < kMaxTasks) {
-                        const uint32_t ent = c.mtl[t / n];
-                        c.tasks[pos] = task_pack(type, ent >> 16, ent & 0xFFFFu, t % n);
+                        const uint32_t mi = udiv_small(t, n), ent = c.mtl[mi];
+                        c.tasks[pos] = task_pack(type, ent >> 16, ent & 0xFFFFu, t - mi * n);
                         c.tasks2[pos] = (k << 8) | (1u << 16);
                         c.tasks3[pos] = t;
                     }
@@ -1017,7 +1034,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     const uint32_t first_item = bid + tid * G;
     uint32_t first_mask = 0u;
     if (first_item < nitems) {
-        const uint32_t tok = first_item / chunks_per_row;
+        const uint32_t tok = udiv_small(first_item, chunks_per_row);
         for (int sl = 0; sl < p.topk; ++sl) first_mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
     }
 
@@ -1028,7 +1045,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         // item idx = (token, 16 B chunk); consecutive items go to different SMs so that a small batch uses the whole GPU
         #pragma unroll 1
         for (uint32_t idx = first_item; idx < nitems && !bad; idx += G * kNT) {
-            const uint32_t tok = idx / chunks_per_row, ch = idx % chunks_per_row;
+            const uint32_t tok = udiv_small(idx, chunks_per_row), ch = idx - tok * chunks_per_row;
             uint32_t mask = first_mask;
             if (idx != first_item) {
                 mask = 0u;

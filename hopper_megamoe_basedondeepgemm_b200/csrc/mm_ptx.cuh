@@ -200,6 +200,16 @@ __device__ __forceinline__ void st_global_v4(void* p, uint4 v) {
     asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
+// ----------------------------------------------------------------------------- small integer division
+// a / b for a < 2^23, b > 0 through one approximate float division and a +-1 correction: about a dozen instructions
+// instead of the ~100-cycle integer division sequence (these sit on per-unit and per-launch critical paths).
+__device__ __forceinline__ uint32_t udiv_small(uint32_t a, uint32_t b) {
+    uint32_t q = __float2uint_rz(__fdividef(static_cast<float>(a), static_cast<float>(b)));
+    const int32_t r = static_cast<int32_t>(a - q * b);
+    if (r < 0) --q; else if (static_cast<uint32_t>(r) >= b) ++q;
+    return q;
+}
+
 // ----------------------------------------------------------------------------- numeric conversions
 // two floats -> one byte of two E2M1 codes (round to nearest even, saturating); `lo` lands in the low nibble
 __device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {

@@ -106,8 +106,8 @@ int mm_get_layout(const mm_config_t* c, mm_layout_t* out) {
     out->off_topk_weights = take(t_max * c->num_topk * 4);
     out->rx_region_bytes = align_up(32 + out->rx_cap_rows * 2 * out->rx_row_bytes, 128);
     out->off_rx = take(2 * c->num_ranks * out->rx_region_bytes);
-    out->off_mid = take(out->mid_rows * out->mid_row_bytes);
-    out->off_mid_sf = take(out->mid_rows * out->mid_sf_row_bytes);
+    out->off_mid = take(out->mid_rows * 2 * out->mid_row_bytes);                 // flagged words: twice the payload
+    out->off_mid_sf = take(out->mid_rows * (c->intermediate / 64) * 8);         // one flagged word per (row, L1 tile)
     out->off_comb = take(t_max * c->num_topk * c->hidden * 4);
     const int64_t n_max = (2 * c->intermediate > c->hidden ? 2 * c->intermediate : c->hidden) / mm::kTileRows;
     out->cnt_per_phase = (out->mid_rows / mm::kTileTokens) * n_max;
@@ -122,11 +122,10 @@ int mm_reset(const mm_config_t* cfg, void* buffer, void* stream) {
     const int st = mm_get_layout(cfg, &L);
     if (st != MM_OK) return st;
     if (buffer == nullptr) return MM_ERR_INVALID_ARGUMENT;
-    // the launch counters restart from zero, so every flagged word of earlier launches must go too: the receive pool
-    // and the combine buffer are cleared with the control block and the split-tile counters
+    // the launch counters restart from zero, so every flagged word of earlier launches must go too: the receive pool,
+    // the intermediate pool and the combine buffer are cleared with the control block and the split-tile counters
     MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_ctrl, 0, L.off_x - L.off_ctrl, static_cast<cudaStream_t>(stream)));
-    MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_rx, 0, L.off_mid - L.off_rx, static_cast<cudaStream_t>(stream)));
-    MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_comb, 0, L.total_bytes - L.off_comb, static_cast<cudaStream_t>(stream)));
+    MM_CUDA(cudaMemsetAsync(static_cast<uint8_t*>(buffer) + L.off_rx, 0, L.total_bytes - L.off_rx, static_cast<cudaStream_t>(stream)));
     return MM_OK;
 }
 
@@ -379,8 +378,7 @@ int mm_mega_moe_launch_static_scratch(const mm_config_t* cfg, const mm_static_ar
     // must start from zero (the launch counters restart with them, so every call runs as the buffer's first launch),
     // and with the counters every flagged word of the receive pool and the combine buffer
     MM_CUDA(cudaMemsetAsync(scratch + L.off_ctrl, 0, L.off_x - L.off_ctrl, s));
-    MM_CUDA(cudaMemsetAsync(scratch + L.off_rx, 0, L.off_mid - L.off_rx, s));
-    MM_CUDA(cudaMemsetAsync(scratch + L.off_comb, 0, L.total_bytes - L.off_comb, s));
+    MM_CUDA(cudaMemsetAsync(scratch + L.off_rx, 0, L.total_bytes - L.off_rx, s));
     const size_t t = static_cast<size_t>(a->num_tokens);
     if (t > 0) {
         MM_CUDA(cudaMemcpyAsync(scratch + L.off_x, a->x, t * L.x_row_bytes, cudaMemcpyDeviceToDevice, s));

@@ -56,7 +56,6 @@ constexpr uint32_t kVtBytes = kTileTokens * kTileRows * 4;   // fp32 accumulator
 constexpr int kCtrlEpoch = 0;           // u32[256] one launch counter per SM
 constexpr int kCtrlStatus = 1024;       // u32[16]
 constexpr int kCtrlFeArrive = 1092;     // u32 SMs that published their router logits
-constexpr int kCtrlL1Done = 1152;       // u32[2][64] L1 tiles finished per (parity, local expert)
 constexpr int kCtrlStamps = 2048;       // u64[32] phase stamps
 constexpr int kCtrlBytes = 4096;
 constexpr int kFlagBytes = 1024;        // reserved block after the control block (no separate arrival flags exist)
@@ -122,6 +121,7 @@ struct Ctl {
     uint32_t rowref[2][kTileTokens];
     uint32_t rowidx[2][kTileTokens];
     float amax_x[4][kTileTokens];
+    uint32_t sfb[4][kTileTokens];        // L1 epilogue: one scale byte per (warp, token), gathered into one flagged word
     uint32_t mtl[kMaxMTiles];            // (expert << 16 | token tile) of every 16-token tile, expert-major
     RowMeta rx_meta[kMetaSmemRows];
     uint8_t meta_e[kMetaCap];
@@ -372,7 +372,6 @@ __device__ __forceinline__ void find_rows(Ctl& c, uint32_t* rowref, uint32_t tot
 __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
     const KParams& p = cx.p; Ctl& c = cx.c;
     const uint32_t total = c.rx_prefix[p.R];
-    uint32_t* l1_done = reinterpret_cast<uint32_t*>(cx.buf + p.off_ctrl + kCtrlL1Done) + cx.par * kMaxLocalExperts;
     uint32_t* rowref = c.rowref[sw];
     uint32_t* rowidx = c.rowidx[sw];
     if (sw >= c.nab) return;
@@ -403,65 +402,42 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
             c.row_meta[ring][lane] = m;
             rowidx[lane] = (r << 24) | i;
         }
-        bool ok = true;
-        if (type == 1u) {
-            if (lane == 0) {
-                const uint32_t need = static_cast<uint32_t>(p.n1_tiles) * ((c.exp_count[e] + kTileTokens - 1) / kTileTokens);
-                uint32_t spins = 0;
-                while (ld_acquire_gpu(l1_done + e) < need) {
-                    if ((++spins & 0x3Fu) == 0u) {
-                        if (cx.aborted()) { ok = false; break; }
-                        if (cx.expired()) { cx.fail(kErrWaitL1Done, e); ok = false; break; }
-                    }
-                }
-                if (p.trace != nullptr && p.trace[blockIdx.x * 96 + 24] == 0) cx.trace(24);
-            }
-        }
-        if (!__all_sync(0xffffffffu, ok)) return;
         uint8_t* act = cx.smem + p.sm_act + ab * c.act_stride;
         uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
+        // Both kinds of rows are flagged words that may still be on their way (received tokens for L1, the L1 epilogues'
+        // output of other SMs for L2): a chunk is re-read until its flags match. Received rows carry their scale bytes
+        // behind the tokens; intermediate rows keep theirs as one flagged word per (row, L1 tile).
         const uint32_t nchunk = (type ? p.mid_row_bytes : p.x_row_bytes) / 16;             // 16 B chunks of one token row
-        const uint32_t sfchunk = (type ? p.mid_sf_row_bytes : p.x_sf_row_bytes) / 16;      // 16 B chunks of one row's scale bytes
-        const uint32_t per_row = nchunk + sfchunk;
+        const uint32_t per_row = nchunk + (type ? 0u : p.x_sf_row_bytes / 16);
         const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
-        // four chunks per lane are in flight before the first store: one memory round trip per 128 chunks of a row.
-        // Received rows (L1) are flagged words that may still be on their way: a chunk is re-read until its flags match.
-        const uint32_t flag = c.epoch + 1u;
+        const uint32_t flag = c.epoch + 1u, wait_code = type ? kErrWaitL1Done : kErrWaitDispatchFlag;
         bool bad = false;
         #pragma unroll 1
         for (uint32_t n = 0; n < nv; ++n) {
-            const uint8_t* row_src = type ? cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes
+            const uint8_t* row_src = type ? cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * 2u * p.mid_row_bytes
                                           : cx.rx_row(rowidx[n] >> 24, rowidx[n] & 0xFFFFFFu);
-            const uint8_t* sf_src = cx.buf + p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes;
+            // four chunks per lane are in flight before the first store: one memory round trip per 128 chunks of a row
             #pragma unroll 1
             for (uint32_t base = lane; base < per_row; base += 4 * 32) {
                 uint4 v[4];
-                if (type) {
+                uint32_t spins = 0;
+                bool ok;
+                do {
+                    ok = true;
                     #pragma unroll
                     for (uint32_t u = 0; u < 4; ++u) {
                         const uint32_t ci = base + u * 32;
-                        if (ci < per_row) v[u] = ld_cg_v4(ci < nchunk ? row_src + ci * 16u : sf_src + (ci - nchunk) * 16u);
+                        if (ci < per_row) {
+                            const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
+                            ok = ok && ll_valid(a, b, flag);
+                            v[u] = ll_data(a, b);
+                        }
                     }
-                } else {
-                    uint32_t spins = 0;
-                    bool ok;
-                    do {
-                        ok = true;
-                        #pragma unroll
-                        for (uint32_t u = 0; u < 4; ++u) {
-                            const uint32_t ci = base + u * 32;
-                            if (ci < per_row) {
-                                const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
-                                ok = ok && ll_valid(a, b, flag);
-                                v[u] = ll_data(a, b);
-                            }
-                        }
-                        if (!ok && (++spins & 0x3Fu) == 0u) {
-                            if (cx.aborted()) bad = true;
-                            else if (cx.expired()) { cx.fail(kErrWaitDispatchFlag, rowidx[n] >> 24); bad = true; }
-                        }
-                    } while (!ok && !bad);
-                }
+                    if (!ok && (++spins & 0x3Fu) == 0u) {
+                        if (cx.aborted()) bad = true;
+                        else if (cx.expired()) { cx.fail(wait_code, type ? e : rowidx[n] >> 24); bad = true; }
+                    }
+                } while (!ok && !bad);
                 #pragma unroll
                 for (uint32_t u = 0; u < 4; ++u) {
                     const uint32_t ci = base + u * 32;
@@ -476,6 +452,28 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                         *reinterpret_cast<uint32_t*>(dst + 768u) = v[u].w;
                     }
                 }
+            }
+            if (type) {
+                // scale bytes of the intermediate row: L1 tile w wrote {2 bytes (one per 32 columns) or 4 bytes (one per 16), flag}
+                const uint8_t* sf_src = cx.buf + p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.n1_tiles * 8u;
+                #pragma unroll 1
+                for (uint32_t w = lane; w < static_cast<uint32_t>(p.n1_tiles); w += 32) {
+                    uint32_t spins = 0;
+                    uint2 q;
+                    for (;;) {
+                        q = ld_volatile_v2(sf_src + w * 8u);
+                        if (q.y == flag || bad) break;
+                        if ((++spins & 0x3Fu) == 0u) {
+                            if (cx.aborted()) bad = true;
+                            else if (cx.expired()) { cx.fail(kErrWaitL1Done, e); bad = true; }
+                        }
+                    }
+                    if (p.x_sf_row_bytes * 16 == p.H)           // one scale byte per 16 elements: four bytes per tile, one scale word
+                        *reinterpret_cast<uint32_t*>(asf + w * 256u + n * 16u) = q.x;
+                    else                                          // per 32 elements: two bytes per tile, half a scale word
+                        *reinterpret_cast<uint16_t*>(asf + (w >> 1) * 256u + n * 16u + (w & 1u) * 2u) = static_cast<uint16_t>(q.x);
+                }
+                if (lane == 0 && n == 0 && p.trace != nullptr && p.trace[blockIdx.x * 96 + 24] == 0) cx.trace(24);
             }
         }
         if (__any_sync(0xffffffffu, bad)) return;
@@ -535,7 +533,6 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     const uint32_t ew = etid >> 5, lane = etid & 31u, row = etid;
     uint8_t* otile = cx.smem + p.sm_otile;
     float* vt = reinterpret_cast<float*>(cx.smem + p.sm_vt) + row;      // this thread's accumulators: vt[n * 128], token n
-    uint32_t* l1_done = reinterpret_cast<uint32_t*>(cx.buf + p.off_ctrl + kCtrlL1Done) + cx.par * kMaxLocalExperts;
     uint32_t it = 0;
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
@@ -678,22 +675,27 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                     else
                         otile[n * 32 + ew * 8u + (lane >> 4) * 4u + ((lane & 7u) >> 1)] = static_cast<uint8_t>(cvt_e2m1x2(scaled, nb));
                 }
-                if (lane == 0 && (kVec == 16 || (ew & 1u) == 0u)) {
-                    const uint32_t sfi = kVec == 32 ? 2u * j + (ew >> 1) : 4u * j + ew;
-                    cx.buf[p.off_mid_sf + static_cast<size_t>(midrow0 + n) * p.mid_sf_row_bytes + sfi] = static_cast<uint8_t>(sf_byte);
-                }
+                if (lane == 0) c.sfb[ew][n] = sf_byte;
             }
             bar_sync(kBarEpi, kNumEpiThreads);
             {
-                constexpr uint32_t kChunks = kA8 ? 4u : 2u;                    // 16 B chunks of one token's 64 output columns
+                // The intermediate rows go out as flagged words (the L2 stagers of all SMs poll the data itself: no
+                // counter, no release fence): 16 B chunks of the token's 64 output columns, and one word with this
+                // tile's scale bytes.
+                constexpr uint32_t kChunks = kA8 ? 4u : 2u;
+                const uint32_t flag = c.epoch + 1u;
                 if (etid < nv * kChunks) {
                     const uint32_t n = etid / kChunks, q16 = etid % kChunks;
                     const uint4 val = *reinterpret_cast<const uint4*>(otile + (n * kChunks + q16) * 16u);
-                    st_global_v4(cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * p.mid_row_bytes + (j * kChunks + q16) * 16u, val);
+                    st_ll_16B(cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * 2u * p.mid_row_bytes + (j * kChunks + q16) * 32u, val, flag);
+                } else if (etid >= 64u && etid - 64u < nv) {
+                    const uint32_t n = etid - 64u;
+                    const uint32_t word = kVec == 16 ? (c.sfb[0][n] | (c.sfb[1][n] << 8) | (c.sfb[2][n] << 16) | (c.sfb[3][n] << 24))
+                                                     : (c.sfb[0][n] | (c.sfb[2][n] << 8));
+                    st_volatile_v2(cx.buf + p.off_mid_sf + (static_cast<size_t>(midrow0 + n) * p.n1_tiles + j) * 8u, word, flag);
                 }
             }
-            bar_sync(kBarEpi, kNumEpiThreads);          // orders every thread's stores before the release below
-            if (etid == 0) { red_release_gpu_add(l1_done + e, 1u); cx.trace(23); }
+            if (etid == 0) cx.trace(23);
         } else {
             // ---- L2: bf16 rows back to the token's source rank, as flagged words: the combine there polls the data itself
             __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(otile);
@@ -755,9 +757,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         const size_t cnt_bytes = static_cast<size_t>(2) * p.cnt_per_phase * 4;
         #pragma unroll 1
         for (size_t off = static_cast<size_t>(g) * 128u; off < (cnt_bytes < 65536 ? cnt_bytes : 65536); off += gn * 128u) prefetch_l2_line(buf + p.off_cnt + off);
-        const size_t sf_bytes = static_cast<size_t>(p.mid_sf_row_bytes) * 16 * kMaxLocalExperts;
-        #pragma unroll 1
-        for (size_t off = static_cast<size_t>(g) * 128u; off < sf_bytes; off += gn * 128u) prefetch_l2_line(buf + p.off_mid_sf + off);
     }
 
     // ---- router frontend (optional): all SMs compute logits; the dispatching SMs select the top-8 of every token
@@ -1012,8 +1011,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (tid == 0) { cx.trace(3); if (p.trace != nullptr) p.trace[bid * 96 + 15] = c.ntasks; }
     if (bid == 0 && tid < static_cast<uint32_t>(p.e_local) && p.stats != nullptr && !cx.aborted())
         p.stats[tid] += static_cast<int>(c.exp_count[tid]);
-    // the other parity's L1 counters are idle during this launch: clear them for the next one
-    if (bid == G - 1 && tid < kMaxLocalExperts) ctrl32[kCtrlL1Done / 4 + (par ^ 1u) * kMaxLocalExperts + tid] = 0u;
 
     // ---- roles
     if (!cx.aborted()) {
@@ -1055,16 +1052,16 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             const uint8_t* cbase = buf + p.off_comb + (static_cast<size_t>(tok) * p.topk * p.H) * 4u + ch * 32u;
             const size_t sstride = static_cast<size_t>(p.H) * 4u;
             #pragma unroll 1
-            for (int s0 = 0; s0 < p.topk && !bad; s0 += 4) {
-                // four routes' words in flight, re-read until each live route carries this launch's flag; a masked route
+            for (int s0 = 0; s0 < p.topk && !bad; s0 += 8) {
+                // eight routes' words in flight, re-read until each live route carries this launch's flag; a masked route
                 // contributes +0.0, which leaves the running sums bit-identical; routes are added in slot order
-                uint4 v[4];
+                uint4 v[8];
                 uint32_t spins = 0;
                 bool ok;
                 do {
                     ok = true;
                     #pragma unroll
-                    for (int u = 0; u < 4; ++u) {
+                    for (int u = 0; u < 8; ++u) {
                         v[u] = make_uint4(0u, 0u, 0u, 0u);
                         if ((mask >> (s0 + u)) & 1u) {
                             const uint8_t* src = cbase + static_cast<size_t>(s0 + u) * sstride;
@@ -1079,7 +1076,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                     }
                 } while (!ok && !bad);
                 #pragma unroll
-                for (int u = 0; u < 4; ++u) {
+                for (int u = 0; u < 8; ++u) {
                     acc[0] += __uint_as_float(v[u].x << 16); acc[1] += __uint_as_float(v[u].x & 0xFFFF0000u);
                     acc[2] += __uint_as_float(v[u].y << 16); acc[3] += __uint_as_float(v[u].y & 0xFFFF0000u);
                     acc[4] += __uint_as_float(v[u].z << 16); acc[5] += __uint_as_float(v[u].z & 0xFFFF0000u);

@@ -191,6 +191,14 @@ __device__ __forceinline__ void st_ll_16B(void* dst, uint4 data, uint32_t flag) 
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" :: "l"(dst), "r"(data.x), "r"(flag), "r"(data.y), "r"(flag) : "memory");
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" :: "l"(static_cast<uint8_t*>(dst) + 16), "r"(data.z), "r"(flag), "r"(data.w), "r"(flag) : "memory");
 }
+__device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_volatile_v2(void* p, uint32_t data, uint32_t flag) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" :: "l"(p), "r"(data), "r"(flag) : "memory");
+}
 __device__ __forceinline__ bool ll_valid(const uint4& a, const uint4& b, uint32_t flag) {
     return a.y == flag && a.w == flag && b.y == flag && b.w == flag;
 }

@@ -78,11 +78,26 @@ class SymmBuffer:
         # every 8 bytes hold 4 data bytes and the launch's flag word
         self.l1_acts = view(L.off_rx, 2 * self.num_ranks * L.rx_region_bytes, torch.uint8,
                             (2, self.num_ranks, int(L.rx_region_bytes)))
-        self.l2_acts = view(L.off_mid, L.mid_rows * L.mid_row_bytes, torch.uint8, (int(L.mid_rows), int(L.mid_row_bytes)))
-        self.l2_acts_sf = view(L.off_mid_sf, L.mid_rows * L.mid_sf_row_bytes, torch.uint8,
-                               (int(L.mid_rows), int(L.mid_sf_row_bytes)))
+        # intermediate pool (flagged words too): rows of 2 * mid_row_bytes, and per (row, L1 tile of 64 columns) one
+        # word {scale bytes, launch flag}; `l2_acts_payload()` / `l2_acts_sf_payload()` strip the flags
+        self.l2_acts = view(L.off_mid, L.mid_rows * 2 * L.mid_row_bytes, torch.uint8,
+                            (int(L.mid_rows), 2 * int(L.mid_row_bytes)))
+        self.l2_acts_sf = view(L.off_mid_sf, L.mid_rows * (intermediate_hidden // 64) * 8, torch.uint8,
+                               (int(L.mid_rows), (intermediate_hidden // 64) * 8))
         # expert outputs coming back: per (token, slot) hidden / 2 flagged words {2 bf16, launch flag}
         self.combine = view(L.off_comb, t * num_topk * hidden * 4, torch.int32, (t, num_topk, hidden // 2, 2))
+
+    def l2_acts_payload(self) -> torch.Tensor:
+        """The intermediate rows without their flag words: uint8 [mid_rows, mid_row_bytes]."""
+        rows = self.l2_acts.size(0)
+        return self.l2_acts.view(torch.int32).view(rows, -1, 2)[..., 0].contiguous().view(torch.uint8).view(rows, -1)
+
+    def l2_acts_sf_payload(self) -> torch.Tensor:
+        """The intermediate rows' scale bytes, K-major: uint8 [mid_rows, intermediate / vec]."""
+        rows = self.l2_acts_sf.size(0)
+        words = self.l2_acts_sf.view(torch.int32).view(rows, -1, 2)[..., 0].contiguous().view(torch.uint8).view(rows, -1, 4)
+        per_tile = 64 // int(self.layout.sf_vec)
+        return words[..., :per_tile].contiguous().view(rows, -1)
 
     def reset(self):
         """Zero the control block and the flags (after an aborted launch). All ranks call it together."""

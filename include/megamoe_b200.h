@@ -51,8 +51,8 @@ typedef struct mm_layout {
     int64_t off_topk_weights;  /* [T_max][topk] float */
     int64_t off_rx;            /* [2 parities][num_ranks sources][rx_region_bytes] receive pool: a 32 B header line (row count), then
                                   rx_cap_rows rows of 2 * rx_row_bytes; every 8 bytes = {4 data bytes, launch flag} */
-    int64_t off_mid;           /* [mid_rows][mid_row_bytes] requantised SwiGLU output (local) */
-    int64_t off_mid_sf;        /* [mid_rows][mid_sf_row_bytes] */
+    int64_t off_mid;           /* [mid_rows][2 * mid_row_bytes] requantised SwiGLU output (local), flagged 8-byte words */
+    int64_t off_mid_sf;        /* [mid_rows][intermediate / 64] flagged words {scale bytes of 64 columns, launch flag} */
     int64_t off_comb;          /* [T_max][topk][hidden] bf16 expert outputs written back by the peers, as flagged 8-byte words
                                   {2 bf16, launch flag}: 4 bytes per element */
     int64_t off_red;           /* [256 SMs][2 phases][2][16][128] float partial sums of weight tiles split between SMs (local) */

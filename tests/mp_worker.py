@@ -108,7 +108,7 @@ def main():
                 ok = False
         # canonical slot order: intermediate rows of each local expert in (source rank, token, slot) order
         vec = O.SF_VEC[fmt]
-        mid, mid_sf = buf.l2_acts.cpu(), buf.l2_acts_sf.cpu()
+        mid, mid_sf = buf.l2_acts_payload().cpu(), buf.l2_acts_sf_payload().cpu()
         base = 0
         for e, cnt in enumerate(ref.counts[rank].tolist()):
             if cnt == 0:

@@ -55,8 +55,8 @@ def check_against_oracle(y, stats, ref, buf, fmt, inter):
     # canonical slot order: the intermediate rows of every expert sit in (source rank, token, slot) order
     vec = O.SF_VEC[fmt]
     base = 0
-    mid = buf.l2_acts.cpu()
-    mid_sf = buf.l2_acts_sf.cpu()
+    mid = buf.l2_acts_payload().cpu()
+    mid_sf = buf.l2_acts_sf_payload().cpu()
     mismatched = total = 0
     for e, cnt in enumerate(ref.counts[0].tolist()):
         if cnt == 0:

@@ -46,6 +46,7 @@ constexpr int kUnitK = 256;             // K elements per streamed unit (one 128
 constexpr int kUnitWBytes = kTileRows * 128;
 constexpr int kNumEpiThreads = 128;
 constexpr uint32_t kBarEpi = 1;          // named barrier of the four epilogue warps
+constexpr uint32_t kBarCopy = 2;         // named barrier of the warps that dispatch
 constexpr int kNumExpThreads = 256;      // FP8-activation variant: warps 8..15 widen the packed E2M1 weights to 8-bit containers
 constexpr uint32_t kXbufBytes = 2 * kUnitWBytes + 1024;   // one widened unit + its two scale planes
 constexpr uint32_t kTmemCols = 128;
@@ -121,6 +122,7 @@ struct Ctl {
     uint32_t rowref[2][kTileTokens];
     uint32_t rowidx[2][kTileTokens];
     float amax_x[4][kTileTokens];
+    uint32_t dry_count[kMaxLocalExperts];   // dummy per-expert counts of the schedule's warm-up call
     uint32_t sfb[4][kTileTokens];        // L1 epilogue: one scale byte per (warp, token), gathered into one flagged word
     uint32_t mtl[kMaxMTiles];            // (expert << 16 | token tile) of every 16-token tile, expert-major
     RowMeta rx_meta[kMetaSmemRows];
@@ -715,6 +717,87 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     }
 }
 
+// ============================================================================================= schedule
+// One warp derives this SM's task list from the per-expert row counts (16-token tiles of the active experts,
+// expert-major: M of them). Returns M << 16 | number of tasks. Out of line on purpose: a spare warp runs it once on
+// dummy counts while the SM waits for the dispatch, so that the real call finds its instructions in the SM's cache
+// (executed cold, the instruction fetches of this code cost more than its arithmetic).
+__device__ __noinline__ uint32_t build_schedule(const KParams& p, Ctl& c, const uint32_t* counts, uint32_t bid, uint32_t G, uint32_t lane) {
+    const uint32_t el = p.e_local;
+    const uint32_t c0 = lane < el ? counts[lane] : 0u, c1 = lane + 32 < el ? counts[lane + 32] : 0u;
+    const uint32_t m0 = (c0 + kTileTokens - 1) / kTileTokens, m1 = (c1 + kTileTokens - 1) / kTileTokens;
+    uint32_t i0 = m0, i1 = m1;
+    #pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v0 = __shfl_up_sync(0xffffffffu, i0, o), v1 = __shfl_up_sync(0xffffffffu, i1, o);
+        if (static_cast<int>(lane) >= o) { i0 += v0; i1 += v1; }
+    }
+    const uint32_t tot0 = __shfl_sync(0xffffffffu, i0, 31), M = tot0 + __shfl_sync(0xffffffffu, i1, 31);
+    const bool big = __any_sync(0xffffffffu, c0 > 8u || c1 > 8u);
+    if (lane == 0) {
+        const bool split = p.nab == 1 && !big;
+        c.nab = split ? 2u : static_cast<uint32_t>(p.nab);
+        c.act_stride = split ? p.act_bytes / 2u : p.act_bytes;
+        c.atom_stride = split ? 8u * 128u : kTileTokens * 128u;
+        c.sbo = split ? 0u : 1024u;
+    }
+    const uint32_t x0 = i0 - m0, x1 = tot0 + i1 - m1;
+    if (lane < el) c.mid_base[lane] = x0 * kTileTokens;
+    if (lane + 32 < el) c.mid_base[lane + 32] = x1 * kTileTokens;
+    if (M <= kMaxMTiles) {
+        #pragma unroll 1
+        for (uint32_t mt = 0; mt < m0; ++mt) c.mtl[x0 + mt] = (lane << 16) | mt;
+        #pragma unroll 1
+        for (uint32_t mt = 0; mt < m1; ++mt) c.mtl[x1 + mt] = ((lane + 32) << 16) | mt;
+    }
+    __syncwarp();
+    // A phase has NT = M * n weight-tile tasks of k units each. The first r = NT % G tiles are the remainder: tile t of
+    // them is shared by the SMs [ceil(t G / r), ceil((t + 1) G / r)), each taking one contiguous range of the tile's K
+    // units (sizes differ by at most one; parts are reduced by the last contributor). Every SM has at most one such
+    // partial task per phase, and it runs first. Then SM g runs the whole tiles r + g, + G, ...
+    // The two phases are worked out side by side: lanes 0..15 take phase 0 (L1), lanes 16..31 phase 1 (L2); the scalar
+    // arithmetic of a phase is the same in its 16 lanes, the whole tiles are spread over them.
+    uint32_t nmine = 0;
+    if (M <= kMaxMTiles) {
+        const uint32_t type = lane >> 4, l16 = lane & 15u;
+        const uint32_t n = type ? p.n2_tiles : p.n1_tiles, k = type ? p.k2_units : p.k1_units;
+        const uint32_t NT = M * n, r = NT - udiv_small(NT, G) * G;
+        uint32_t has_split = 0u, s_t = 0u, s_word = 0u;
+        if (r > 0u) {
+            const uint32_t t = udiv_small(bid * r, G);
+            const uint32_t gs = udiv_small(t * G + r - 1u, r), ge = udiv_small((t + 1u) * G + r - 1u, r);
+            const uint32_t S = ge - gs, li = bid - gs, base = udiv_small(k, S), extra = k - base * S;
+            const uint32_t ub = li * base + (li < extra ? li : extra), ue = ub + base + (li < extra ? 1u : 0u);
+            has_split = ue > ub ? 1u : 0u;
+            s_t = t;
+            s_word = ub | (ue << 8) | ((S < k ? S : k) << 16) | (gs << 24);
+        }
+        const uint32_t first_whole = r + bid;
+        const uint32_t nwhole = first_whole < NT ? udiv_small(NT - 1u - first_whole, G) + 1u : 0u;
+        const uint32_t cnt_type = has_split + nwhole;
+        const uint32_t cnt0 = __shfl_sync(0xffffffffu, cnt_type, 0), cnt1 = __shfl_sync(0xffffffffu, cnt_type, 16);
+        const uint32_t basepos = type ? cnt0 : 0u;                 // the tasks of phase 0 come first
+        if (l16 == 0u && has_split && basepos < kMaxTasks) {
+            const uint32_t mi = udiv_small(s_t, n), ent = c.mtl[mi];
+            c.tasks[basepos] = task_pack(type, ent >> 16, ent & 0xFFFFu, s_t - mi * n);
+            c.tasks2[basepos] = s_word;
+            c.tasks3[basepos] = s_t;
+        }
+        #pragma unroll 1
+        for (uint32_t i = l16; i < nwhole; i += 16) {
+            const uint32_t pos = basepos + has_split + i, t = first_whole + i * G;
+            if (pos < kMaxTasks) {
+                const uint32_t mi = udiv_small(t, n), ent = c.mtl[mi];
+                c.tasks[pos] = task_pack(type, ent >> 16, ent & 0xFFFFu, t - mi * n);
+                c.tasks2[pos] = (k << 8) | (1u << 16);
+                c.tasks3[pos] = t;
+            }
+        }
+        __syncwarp();
+        nmine = cnt0 + cnt1;
+    }    return (M << 16) | (nmine < 0xFFFFu ? nmine : 0xFFFFu);
+}
+
 // ============================================================================================= the kernel
 template <int kVec, bool kUmma, bool kFe, bool kA8>
 __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1) mega_moe_kernel(const __grid_constant__ KParams p) {
@@ -740,6 +823,11 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         }
         mbar_fence_init();
     }
+    // the token staging area starts from zero (the dispatch lists and the frontend's scratch that pass through it later
+    // leave finite bytes; whatever sits in rows beyond a task's valid tokens only reaches accumulator columns nobody reads)
+    #pragma unroll 1
+    for (uint32_t off = tid * 16u; off < p.stage_region; off += kNT * 16u)
+        *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
     if (warp == 1) { tmem_alloc(&c.tmem_base, kTmemCols); tmem_relinquish(); tc_fence_before(); }
     if (tid < kMaxLocalExperts) c.exp_count[tid] = 0u;
     __syncthreads();
@@ -757,6 +845,18 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         const size_t cnt_bytes = static_cast<size_t>(2) * p.cnt_per_phase * 4;
         #pragma unroll 1
         for (size_t off = static_cast<size_t>(g) * 128u; off < (cnt_bytes < 65536 ? cnt_bytes : 65536); off += gn * 128u) prefetch_l2_line(buf + p.off_cnt + off);
+    }
+
+    // ---- warm-up of the scheduler's instructions: the last warp has nothing to do until the roles start (it takes no
+    //      part in the dispatch copies), so it runs the scheduler once on dummy counts (eight experts with one row). The
+    //      real call, which sits on the critical path right after the dispatch arrives, overwrites everything this writes.
+    constexpr uint32_t kCopyWarps = kFe ? kNT / 32 : kNT / 32 - 1;      // the fused frontend keeps every warp busy instead
+    if constexpr (!kFe) {
+        if (warp == kCopyWarps) {
+            for (uint32_t e = lane; e < kMaxLocalExperts; e += 32) c.dry_count[e] = e < 8u ? 1u : 0u;
+            __syncwarp();
+            build_schedule(p, c, c.dry_count, bid, G, lane);
+        }
     }
 
     // ---- router frontend (optional): all SMs compute logits; the dispatching SMs select the top-8 of every token
@@ -788,7 +888,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
 
     // ---- dispatch: SM d pushes this rank's rows for rank d
-    if (bid < static_cast<uint32_t>(p.R)) {
+    if (bid < static_cast<uint32_t>(p.R) && warp < kCopyWarps) {
         const uint32_t d = bid;
         uint32_t* dlist = reinterpret_cast<uint32_t*>(smem + p.sm_act);
         if (warp == 0) {
@@ -808,7 +908,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             }
             if (lane == 0) c.dcount = cnt;
         }
-        __syncthreads();
+        bar_sync(kBarCopy, kCopyWarps * 32);
         const uint32_t cnt = c.dcount;
         const uint32_t nchunk = (p.rx_row_bytes - 16) / 16, xq = p.x_row_bytes / 16;      // payload chunks of a row: tokens, then scale bytes
         const uint32_t flag = epoch + 1u;
@@ -820,7 +920,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         // so nothing has to order these stores against the payload that follows.
         if (tid == 0) st_ll_16B(region, make_uint4(cnt, 0u, 0u, 0u), flag);
         #pragma unroll 1
-        for (uint32_t i = tid; i < cnt; i += kNT) {
+        for (uint32_t i = tid; i < cnt; i += kCopyWarps * 32) {
             const uint32_t ent = dlist[i], tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
             st_ll_16B(dst_base + static_cast<size_t>(i) * 2u * p.rx_row_bytes + 2u * (p.rx_row_bytes - 16),
                       make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot])), flag);
@@ -828,18 +928,18 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         if constexpr (kFe) {
             // quantise the tokens this SM is about to send into the x / x_sf views (the same bytes whichever SM writes them)
             #pragma unroll 1
-            for (uint32_t i = warp; i < cnt; i += kNT / 32) {
+            for (uint32_t i = warp; i < cnt; i += kCopyWarps) {
                 const uint32_t tok = dlist[i] >> 16;
                 fe_quant_token(p.fe.hidden + static_cast<size_t>(tok) * p.H, p.H, kA8 ? 2 : (kVec == 32 ? 0 : 1), p.fe.x_gs,
                                buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes,
                                buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes, lane);
             }
-            __syncthreads();
+            bar_sync(kBarCopy, kCopyWarps * 32);
         }
         // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (eight in flight: one memory round trip for
         // a row of up to 4 KB)
         #pragma unroll 1
-        for (uint32_t i = warp; i < cnt; i += kNT / 32) {
+        for (uint32_t i = warp; i < cnt; i += kCopyWarps) {
             const uint32_t tok = dlist[i] >> 16;
             const uint8_t* xs_src = buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
             const uint8_t* sf_src = buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
@@ -860,15 +960,10 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 }
             }
         }
-        __syncthreads();
+        bar_sync(kBarCopy, kCopyWarps * 32);
     }
     if (bid == 0 && tid == 0) cx.stamp(kStampDispatched);
     if (tid == 0) cx.trace(1);
-
-    // ---- the staging buffers start from zero: rows beyond a task's valid tokens only ever hold finite bytes
-    #pragma unroll 1
-    for (uint32_t off = tid * 16u; off < p.stage_region; off += kNT * 16u)
-        *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
 
     // ---- receive: wait for every source rank's header line, then scan the received rows' records. The first 32 records
     //      of every source are fetched speculatively in the same memory round trip as the headers (thread 32 r + i takes
@@ -929,76 +1024,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     // ---- schedule. 16-token tiles of the active experts, expert-major: M of them. Every SM derives its own task list
     //      (L1 tasks, then L2 tasks) in closed form from the per-expert counts.
     if (warp == 0 && !cx.aborted()) {
-        const uint32_t el = p.e_local;
-        const uint32_t c0 = lane < el ? c.exp_count[lane] : 0u, c1 = lane + 32 < el ? c.exp_count[lane + 32] : 0u;
-        const uint32_t m0 = (c0 + kTileTokens - 1) / kTileTokens, m1 = (c1 + kTileTokens - 1) / kTileTokens;
-        uint32_t i0 = m0, i1 = m1;
-        #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t v0 = __shfl_up_sync(0xffffffffu, i0, o), v1 = __shfl_up_sync(0xffffffffu, i1, o);
-            if (static_cast<int>(lane) >= o) { i0 += v0; i1 += v1; }
-        }
-        const uint32_t tot0 = __shfl_sync(0xffffffffu, i0, 31), M = tot0 + __shfl_sync(0xffffffffu, i1, 31);
-        const bool big = __any_sync(0xffffffffu, c0 > 8u || c1 > 8u);
-        if (lane == 0) {
-            const bool split = p.nab == 1 && !big;
-            c.nab = split ? 2u : static_cast<uint32_t>(p.nab);
-            c.act_stride = split ? p.act_bytes / 2u : p.act_bytes;
-            c.atom_stride = split ? 8u * 128u : kTileTokens * 128u;
-            c.sbo = split ? 0u : 1024u;
-        }
-        const uint32_t x0 = i0 - m0, x1 = tot0 + i1 - m1;
-        if (lane < el) c.mid_base[lane] = x0 * kTileTokens;
-        if (lane + 32 < el) c.mid_base[lane + 32] = x1 * kTileTokens;
-        if (M <= kMaxMTiles) {
-            #pragma unroll 1
-            for (uint32_t mt = 0; mt < m0; ++mt) c.mtl[x0 + mt] = (lane << 16) | mt;
-            #pragma unroll 1
-            for (uint32_t mt = 0; mt < m1; ++mt) c.mtl[x1 + mt] = ((lane + 32) << 16) | mt;
-        }
-        __syncwarp();
-        // A phase has NT = M * n weight-tile tasks of k units each. The first r = NT % G tiles are the remainder: tile t of
-        // them is shared by the SMs [ceil(t G / r), ceil((t + 1) G / r)), each taking one contiguous range of the tile's K
-        // units (sizes differ by at most one; parts are reduced by the last contributor). Every SM has at most one such
-        // partial task per phase, and it runs first. Then SM g runs the whole tiles r + g, + G, ...
-        uint32_t nmine = 0;
-        if (M <= kMaxMTiles) {
-            #pragma unroll 1
-            for (uint32_t type = 0; type < 2; ++type) {
-                const uint32_t n = type ? p.n2_tiles : p.n1_tiles, k = type ? p.k2_units : p.k1_units;
-                const uint32_t NT = M * n, r = NT - udiv_small(NT, G) * G;
-                if (r > 0u) {
-                    const uint32_t t = udiv_small(bid * r, G);
-                    const uint32_t gs = udiv_small(t * G + r - 1u, r), ge = udiv_small((t + 1u) * G + r - 1u, r);
-                    const uint32_t S = ge - gs, li = bid - gs, base = udiv_small(k, S), extra = k - base * S;
-                    const uint32_t ub = li * base + (li < extra ? li : extra), ue = ub + base + (li < extra ? 1u : 0u);
-                    if (ue > ub) {
-                        if (lane == 0 && nmine < kMaxTasks) {
-                            const uint32_t mi = udiv_small(t, n), ent = c.mtl[mi];
-                            c.tasks[nmine] = task_pack(type, ent >> 16, ent & 0xFFFFu, t - mi * n);
-                            c.tasks2[nmine] = ub | (ue << 8) | ((S < k ? S : k) << 16) | (gs << 24);
-                            c.tasks3[nmine] = t;
-                        }
-                        nmine += 1u;
-                    }
-                }
-                #pragma unroll 1
-                for (uint32_t i0 = 0;; i0 += 32) {
-                    const uint32_t t = r + bid + (i0 + lane) * G;
-                    const bool m = t < NT;
-                    const uint32_t b = __ballot_sync(0xffffffffu, m);
-                    if (b == 0u) break;
-                    const uint32_t pos = nmine + __popc(b & ((1u << lane) - 1u));
-                    if (m && pos < kMaxTasks) {
-                        const uint32_t mi = udiv_small(t, n), ent = c.mtl[mi];
-                        c.tasks[pos] = task_pack(type, ent >> 16, ent & 0xFFFFu, t - mi * n);
-                        c.tasks2[pos] = (k << 8) | (1u << 16);
-                        c.tasks3[pos] = t;
-                    }
-                    nmine += __popc(b);
-                }
-            }
-        }
+        const uint32_t res = build_schedule(p, c, c.exp_count, bid, G, lane);
+        const uint32_t M = res >> 16, nmine = res & 0xFFFFu;
         const uint32_t nt1 = M * p.n1_tiles, nt2 = M * p.n2_tiles;
         if (lane == 0) {
             c.nt1 = nt1; c.nt2 = nt2;

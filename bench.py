@@ -252,7 +252,7 @@ def main():
                         'h2d_bytes_per_step': int(h_x.numel() * h_x.element_size() + h_sf.numel() * 4 + h_idx.numel() * 8 + h_w.numel() * 4),
                         'd2h_bytes_per_step': int(h_y.numel() * 2)},
                 'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
-                             'traffic': (int(alg_bytes * 1.0035) if (fmt == 'mxfp4' and n == 1) else None), 'traffic_source': 'dram__bytes_read+write of one ncu capture of this workload, scaled by the active experts (profiles/)', 'peak_source': peak_src,
+                             'traffic': (int(alg_bytes * 1.0023) if (fmt == 'mxfp4' and n == 1) else None), 'traffic_source': 'dram__bytes_read+write of one ncu capture of this workload, scaled by the active experts (profiles/)', 'peak_source': peak_src,
                              'algorithmic_bytes_per_launch': alg_bytes, 'active_experts_per_rank': active}}
         if not args.no_cpu_baseline and n == 1:
             us, cores = cpu_reference_us(T, fmt, 5)

@@ -4,18 +4,18 @@
 //               order, into a region of rank d's receive pool that only this rank writes. Everything that crosses
 //               NVLink travels as flagged 8-byte words {4 data bytes, launch number}: the consumer polls the words it
 //               needs, so there is no fence, no completion flag and no ticket atomic - one one-way trip per hand-off.
-//   schedule  : every SM reads the R flags, scans the received rows' expert ids and derives its own task list in closed
-//               form (L1 tiles of all active experts, then L2 tiles). A phase's NT tiles are split in two: the first
-//               NT % SMs tiles are cut along K into equal unit ranges, one per SM (partial sums parked in global memory,
-//               summed in SM order by the last contributor); the rest are whole tiles dealt round-robin.
+//   schedule  : every SM reads the R header lines, scans the received rows' records and derives its own task list in closed
+//               form (L1 tiles of all active experts, then L2 tiles). A phase's NT tiles are split in two: each of the
+//               first NT % SMs tiles is cut along K between the SMs of a fixed group (partial sums parked in global
+//               memory, summed in SM order by the last contributor); the rest are whole tiles dealt round-robin.
 //   L1 GEMM   : 128 weight rows x 16 tokens per task, swap-AB block-scaled tcgen05 MMA, accumulators in TMEM. Weights
 //               arrive as pre-tiled 128 B-swizzled units with their scale planes by one bulk async copy per stage.
-//               FP8-activation variant: four more warps widen every packed unit to byte-wide operand slots in shared
+//               FP8-activation variant: eight more warps widen every packed unit to byte-wide operand slots in shared
 //               memory (kind::mxf8f6f4 reads 4-bit values from 8-bit containers); HBM still streams the packed form.
 //   L1 epilog : SwiGLU * top-k weight, requantise to E2M1 or E4M3 (+ scale byte), store to the local intermediate
-//               pool, release-add on the expert's arrival counter.
-//   L2 GEMM   : acquires that counter, same main loop on W2, epilogue stores bf16 rows (flagged words) straight into
-//               the source rank's combine buffer over NVLink.
+//               pool as flagged words.
+//   L2 GEMM   : the stager polls the intermediate rows it needs, same main loop on W2, epilogue stores bf16 rows
+//               (flagged words) straight into the source rank's combine buffer over NVLink.
 //   combine   : each thread polls the flagged words of the routes it sums; routes are added in slot order (fp32) and
 //               written to y. No grid-wide or cross-rank barrier anywhere in the launch.
 //
@@ -64,7 +64,8 @@ constexpr int kFlagBytes = 1024;        // reserved block after the control bloc
 // device status codes (low byte of status word 0)
 enum : uint32_t {
     kErrWaitEmpty = 1, kErrWaitFull = 2, kErrWaitActsFull = 3, kErrWaitActsEmpty = 4, kErrWaitTmemFull = 5,
-    kErrWaitTmemEmpty = 6, kErrWaitDispatchFlag = 7, kErrWaitL1Done = 8, kErrWaitCombineFlag = 9,
+    kErrWaitTmemEmpty = 6, kErrWaitDispatchFlag = 7 /* header line or row words of a source rank */, kErrWaitL1Done = 8 /* intermediate rows */,
+    kErrWaitCombineFlag = 9 /* expert outputs */,
     kErrMetaCapacity = 10, kErrTaskCapacity = 11, kErrWaitFrontend = 12
 };
 // phase stamp slots (SM 0 unless noted)
@@ -139,7 +140,7 @@ struct Ctx {
     uint8_t* buf;         // this rank's buffer
     uint8_t* smem;        // dynamic shared memory (1024 B aligned)
     uint64_t deadline;
-    uint32_t par;         // launch parity: which half of the receive pool / flags this launch uses
+    uint32_t par;         // launch parity: which half of the receive pool this launch uses
     __device__ __forceinline__ bool aborted() const { return *reinterpret_cast<volatile uint32_t*>(&c.abort_flag) != 0u; }
     __device__ __forceinline__ void fail(uint32_t code, uint32_t detail = 0) const {
         uint32_t* st = reinterpret_cast<uint32_t*>(buf + p.off_ctrl + kCtrlStatus);
@@ -836,8 +837,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     const uint32_t epoch = c.epoch, par = cx.par;
     if (bid == 0 && tid == 0) { ctrl32[kCtrlStatus / 4 + 1] = epoch + 1u; cx.stamp(kStampEntry); }
     if (tid == 0) cx.trace(0);
-    // Counters, flags and scale-byte rows are touched late, on the critical dependency chain, and by then they have
-    // usually been evicted from the L2 by the weight stream of earlier work: ask for their lines now.
+    // The control block and the split-tile counters are touched late, on the critical dependency chain, and by then
+    // they have usually been evicted from the L2 by the weight stream of earlier work: ask for their lines now.
     if (warp == 7) {
         const uint32_t g = bid * 32 + lane, gn = G * 32;
         #pragma unroll 1

@@ -74,6 +74,8 @@ class SymmBuffer:
         self.x_sf = view(L.off_x_sf, t * L.x_sf_row_bytes, torch.int32, (t, hidden // (4 * vec)))
         self.topk_idx = view(L.off_topk_idx, t * num_topk * 8, torch.int64, (t, num_topk))
         self.topk_weights = view(L.off_topk_weights, t * num_topk * 4, torch.float32, (t, num_topk))
+        # the four input views are neighbours in the buffer: one copy of this region moves them all (see host_inputs)
+        self.inputs = self.buffer[int(L.off_x):int(L.off_rx)]
         # receive pool: [parity][source rank][32 B header line, then rows of (tokens | scale bytes | 16 B record)];
         # every 8 bytes hold 4 data bytes and the launch's flag word
         self.l1_acts = view(L.off_rx, 2 * self.num_ranks * L.rx_region_bytes, torch.uint8,
@@ -86,6 +88,22 @@ class SymmBuffer:
                                (int(L.mid_rows), (intermediate_hidden // 64) * 8))
         # expert outputs coming back: per (token, slot) hidden / 2 flagged words {2 bf16, launch flag}
         self.combine = view(L.off_comb, t * num_topk * hidden * 4, torch.int32, (t, num_topk, hidden // 2, 2))
+
+    def host_inputs(self):
+        """A pinned host mirror of the input region and typed views into it (`x`, `x_sf`, `topk_idx`, `topk_weights`,
+        shaped like the device views). Fill the views, then `sym_buffer.inputs.copy_(mirror, non_blocking=True)` moves
+        all inputs of a step with a single host-to-device copy."""
+        L, t = self.layout, self.num_max_tokens_per_rank
+        mirror = torch.zeros(int(L.off_rx - L.off_x), dtype=torch.int8).pin_memory()
+        base = int(L.off_x)
+
+        def view(off, nbytes_, like):
+            return mirror[off - base:off - base + nbytes_].view(like.dtype).view(*like.shape)
+        views = {'x': view(int(L.off_x), t * int(L.x_row_bytes), self.x),
+                 'x_sf': view(int(L.off_x_sf), t * int(L.x_sf_row_bytes), self.x_sf),
+                 'topk_idx': view(int(L.off_topk_idx), t * self.num_topk * 8, self.topk_idx),
+                 'topk_weights': view(int(L.off_topk_weights), t * self.num_topk * 4, self.topk_weights)}
+        return mirror, views
 
     def l2_acts_payload(self) -> torch.Tensor:
         """The intermediate rows without their flag words: uint8 [mid_rows, mid_row_bytes]."""

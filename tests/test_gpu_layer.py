@@ -145,6 +145,28 @@ def test_repeated_launches_alternate_parity():
             assert O.rel_rmse(y.cpu(), ref.y[0]) <= REL_RMSE_TOL
 
 
+def test_inputs_through_the_pinned_host_mirror():
+    """All four input views arrive with one host-to-device copy of the buffer's input region."""
+    dev = 'cuda'
+    fmt, e_local, hidden, inter, topk, tokens = 'fp8', 4, 512, 256, 2, 6
+    w, _, _ = O.make_expert_weights(e_local, hidden, inter, fmt, seed=1, std=0.05)
+    buf = mm.get_symm_buffer_for_mega_moe(None, e_local, 16, topk, hidden, inter, act_format=fmt)
+    l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(w, fmt, dev))
+    idx, tw = U.random_routing(tokens, e_local, topk, 77)
+    x, inp, sfb = U.make_rank_inputs(tokens, hidden, fmt, 78, idx, tw)
+    ref = O.moe_layer_reference([inp], [w], fmt, e_local, clamp=None, faithful=True)
+    mirror, views = buf.host_inputs()
+    views['x'][:tokens].copy_(inp.x_q.view(views['x'].dtype))
+    views['x_sf'][:tokens].copy_(sfb.contiguous().view(torch.int32))
+    views['topk_idx'][:tokens].copy_(inp.topk_idx)
+    views['topk_weights'][:tokens].copy_(inp.topk_weights)
+    buf.inputs.copy_(mirror, non_blocking=True)
+    y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
+    mm.fp8_fp4_mega_moe(y, l1, l2, buf, activation_clamp=None, timeout_ms=500.0)
+    assert buf.device_status()[0] == 0
+    assert O.rel_rmse(y.cpu(), ref.y[0]) <= REL_RMSE_TOL
+
+
 def test_reset_restarts_the_launch_numbering():
     """Words that cross between ranks are marked with the launch number. `reset` restarts the numbering, so it must
     also clear every marked word: after it, launch 1's stale rows (other tokens, other routing) must not be taken for

@@ -37,8 +37,8 @@ class MMLaunchArgs(ctypes.Structure):
         ('activation_clamp', ctypes.c_float), ('fast_math', ctypes.c_int32),
         ('x_global_scale', ctypes.c_float), ('l1_global_scale', ctypes.c_float),
         ('l2_global_scale', ctypes.c_float), ('mid_global_scale', ctypes.c_float),
-        ('timeout_ms', ctypes.c_float), ('debug_accumulators', ctypes.c_void_p),
-        ('debug_num_tasks', ctypes.c_int32), ('reserved', ctypes.c_int32), ('debug_trace', ctypes.c_void_p)]
+        ('timeout_ms', ctypes.c_float), ('reserved_ptr0', ctypes.c_void_p),
+        ('reserved0', ctypes.c_int32), ('reserved1', ctypes.c_int32), ('reserved_ptr1', ctypes.c_void_p)]
 
 
 class MMFrontendArgs(ctypes.Structure):

@@ -193,8 +193,6 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.off_red = L.off_red; p.off_cnt = L.off_cnt; p.cnt_per_phase = static_cast<int>(L.cnt_per_phase);
     const double tmo = a->timeout_ms > 0.f ? a->timeout_ms : 2000.0;
     p.timeout_ns = static_cast<unsigned long long>(tmo * 1e6);
-    p.trace = static_cast<unsigned long long*>(a->debug_trace);
-    p.debug_acc = static_cast<float*>(a->debug_accumulators); p.debug_tasks = a->debug_accumulators ? a->debug_num_tasks : 0;
     // shared memory plan: [stages][token tiles][token scale chunks][output tile][accumulator tile][widened units (FP8)]
     const int kmax = p.H > p.I ? p.H : p.I;
     const int vec = sf_vec_of(cfg->act_format);

@@ -96,8 +96,6 @@ struct KParams {
     uint32_t sm_xbuf; int nab;           // widened-unit buffers (FP8 variant); number of 16-row token staging buffers (1 or 2)
     uint32_t stage_region;               // bytes of the token staging area (tiles + scale slots)
     unsigned long long timeout_ns;
-    float* debug_acc; int debug_tasks;   // optional diagnostics: raw accumulators of SM 0's first tasks [task][token][row]
-    unsigned long long* trace;           // optional diagnostics: 16 globaltimer stamps per SM
     FeParams fe; int fe_enabled;         // router frontend run at the head of the same launch (optional)
 };
 
@@ -142,7 +140,7 @@ struct Ctx {
     uint64_t deadline;
     uint32_t par;         // launch parity: which half of the receive pool this launch uses
     __device__ __forceinline__ bool aborted() const { return *reinterpret_cast<volatile uint32_t*>(&c.abort_flag) != 0u; }
-    __device__ __forceinline__ void fail(uint32_t code, uint32_t detail = 0) const {
+    __device__ __noinline__ void fail(uint32_t code, uint32_t detail = 0) const {      // cold: keep it out of the callers' code
         uint32_t* st = reinterpret_cast<uint32_t*>(buf + p.off_ctrl + kCtrlStatus);
         atomicCAS(st, 0u, code | (blockIdx.x << 8) | (detail << 16));
         *reinterpret_cast<volatile uint32_t*>(&c.abort_flag) = 1u;
@@ -167,9 +165,6 @@ struct Ctx {
     // every lane waits; the warp agrees on the outcome
     __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, uint32_t code) const {
         return __all_sync(0xffffffffu, wait(bar, parity, code));
-    }
-    __device__ __forceinline__ void trace(int slot) const {
-        if (p.trace != nullptr) p.trace[blockIdx.x * 96 + slot] = globaltimer_ns();
     }
     __device__ __forceinline__ void stamp(int slot) const {
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[slot] = globaltimer_ns();
@@ -222,7 +217,6 @@ __device__ void role_loader(const Ctx& cx) {
         for (int u = ub; u < ue; ++u, ++it) {
             if (!cx.warp_wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
             if (elect_one()) {
-                if (it == 0) cx.trace(4);
                 mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
                 bulk_g2s(cx.smem + static_cast<size_t>(s) * p.unit_bytes, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
             }
@@ -230,7 +224,6 @@ __device__ void role_loader(const Ctx& cx) {
             if (++s == static_cast<uint32_t>(p.nstage)) { s = 0; ph ^= 1u; }
         }
     }
-    if ((threadIdx.x & 31u) == 0u) cx.trace(5);
 }
 
 // ============================================================================================= MMA issuer
@@ -260,7 +253,6 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
             if (!cx.warp_wait(ready, kA8 ? (it >> 1) & 1u : ph, kErrWaitFull)) return;
             tc_fence_after();
             if (elect_one()) {
-              if (it == 0) cx.trace(6);
               {
                 const uint32_t wsm = kA8 ? smem_u32(cx.smem + p.sm_xbuf + (it & 1u) * kXbufBytes)
                                          : smem_u32(cx.smem + static_cast<size_t>(s) * p.unit_bytes);
@@ -300,7 +292,6 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         if (elect_one()) {
             tc_commit(&c.tmem_full[acc]);
             tc_commit(&c.acts_empty[ab]);
-            cx.trace(7);
         }
         __syncwarp();
     }
@@ -476,13 +467,12 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                     else                                          // per 32 elements: two bytes per tile, half a scale word
                         *reinterpret_cast<uint16_t*>(asf + (w >> 1) * 256u + n * 16u + (w & 1u) * 2u) = static_cast<uint16_t>(q.x);
                 }
-                if (lane == 0 && n == 0 && p.trace != nullptr && p.trace[blockIdx.x * 96 + 24] == 0) cx.trace(24);
             }
         }
         if (__any_sync(0xffffffffu, bad)) return;
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) { mbar_arrive(&c.acts_full[ab]); if (ti == 0) cx.trace(13); if (type == 1u) cx.trace(14); }
+        if (lane == 0) mbar_arrive(&c.acts_full[ab]);
     }
 }
 
@@ -549,7 +539,6 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             ok = cx.warp_wait(&c.tmem_full[acc], use, kErrWaitTmemFull);
             if (ok) {
                 tc_fence_after();
-                if (etid == 0) { if (ti == 0) cx.trace(8); cx.trace(type ? 26 : 25); }
                 if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
                 nv = c.nvalid[ring];
                 uint32_t raw[kTileTokens];
@@ -586,9 +575,6 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             }
         }
         if (bar_red_or(kBarEpi, kNumEpiThreads, !ok)) return;        // also publishes epi_meta
-        if (p.debug_acc != nullptr && blockIdx.x == 0 && ti < static_cast<uint32_t>(p.debug_tasks))
-            #pragma unroll 1
-            for (uint32_t n = 0; n < nv; ++n) p.debug_acc[(static_cast<size_t>(ti) * kTileTokens + n) * kTileRows + row] = vt[n * kTileRows];
         const RowMeta* meta = c.epi_meta[acc];
         const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
         const uint32_t np = (c.tasks2[ti] >> 16) & 0xFFu;
@@ -698,7 +684,6 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                     st_volatile_v2(cx.buf + p.off_mid_sf + (static_cast<size_t>(midrow0 + n) * p.n1_tiles + j) * 8u, word, flag);
                 }
             }
-            if (etid == 0) cx.trace(23);
         } else {
             // ---- L2: bf16 rows back to the token's source rank, as flagged words: the combine there polls the data itself
             __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(otile);
@@ -714,7 +699,6 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 st_ll_16B(dst, val, c.epoch + 1u);
             }
         }
-        if (etid == 0) cx.trace(9);
     }
 }
 
@@ -836,7 +820,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, c.epoch & 1u};
     const uint32_t epoch = c.epoch, par = cx.par;
     if (bid == 0 && tid == 0) { ctrl32[kCtrlStatus / 4 + 1] = epoch + 1u; cx.stamp(kStampEntry); }
-    if (tid == 0) cx.trace(0);
     // The control block and the split-tile counters are touched late, on the critical dependency chain, and by then
     // they have usually been evicted from the L2 by the weight stream of earlier work: ask for their lines now.
     if (warp == 7) {
@@ -964,7 +947,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         bar_sync(kBarCopy, kCopyWarps * 32);
     }
     if (bid == 0 && tid == 0) cx.stamp(kStampDispatched);
-    if (tid == 0) cx.trace(1);
 
     // ---- receive: wait for every source rank's header line, then scan the received rows' records. The first 32 records
     //      of every source are fetched speculatively in the same memory round trip as the headers (thread 32 r + i takes
@@ -993,7 +975,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         if (tid == 0) {
             if (total > kMetaCap) cx.fail(kErrMetaCapacity, total >> 4);
             if (bid == 0) cx.stamp(kStampFlagsSeen);
-            cx.trace(2);
         }
         if (total <= kMetaCap) {
             auto take = [&](uint32_t f, const uint4& m) {
@@ -1036,7 +1017,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
     __syncthreads();
     if (bid == 0 && tid == 0) cx.stamp(kStampScheduled);
-    if (tid == 0) { cx.trace(3); if (p.trace != nullptr) p.trace[bid * 96 + 15] = c.ntasks; }
     if (bid == 0 && tid < static_cast<uint32_t>(p.e_local) && p.stats != nullptr && !cx.aborted())
         p.stats[tid] += static_cast<int>(c.exp_count[tid]);
 
@@ -1050,7 +1030,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
     __syncthreads();
     if (bid == 0 && tid == 0) cx.stamp(kStampTasksDone);
-    if (tid == 0) cx.trace(10);
 
     // ---- combine. No grid-wide or cross-rank barrier precedes it: the expert outputs arrive as flagged words and every
     //      thread polls exactly the words it sums. First, which routes of this thread's first (token, 16 B chunk) item are live:
@@ -1063,7 +1042,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         for (int sl = 0; sl < p.topk; ++sl) first_mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
     }
 
-    if (tid == 0) cx.trace(11);
     if (!cx.aborted()) {
         const uint32_t flag = epoch + 1u;
         bool bad = false;
@@ -1130,7 +1108,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (warp == 1) { tc_fence_after(); tmem_dealloc(c.tmem_base, kTmemCols); }
     if (tid == 0) {
         if (bid == 0) cx.stamp(kStampExit);
-        cx.trace(12);
         atomicMax(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps) + kStampLastExit, globaltimer_ns());
     }
 }

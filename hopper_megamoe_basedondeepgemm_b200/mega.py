@@ -182,7 +182,7 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
 
 
 def _launch(y, l1_weights, l2_weights, sym_buffer: SymmBuffer, stats, recipe, activation, activation_clamp, fast_math,
-            engine='umma', global_scales=(1.0, 1.0, 1.0, 1.0), timeout_ms=0.0, debug_accumulators=None, debug_trace=None):
+            engine='umma', global_scales=(1.0, 1.0, 1.0, 1.0), timeout_ms=0.0):
     lib = _lib.load()
     if activation != 'swiglu':
         raise RuntimeError('only the swiglu activation is supported')
@@ -208,10 +208,7 @@ def _launch(y, l1_weights, l2_weights, sym_buffer: SymmBuffer, stats, recipe, ac
         b.buffer.data_ptr(), b._peer_array, w1.data_ptr(), w2.data_ptr(), y.data_ptr() if y.numel() else None,
         y.size(0), _lib.ENGINE[engine], stats.data_ptr() if stats is not None else None,
         float(activation_clamp) if activation_clamp is not None else -1.0, int(bool(fast_math)),
-        *[float(g) for g in global_scales], float(timeout_ms),
-        debug_accumulators.data_ptr() if debug_accumulators is not None else None,
-        debug_accumulators.size(0) if debug_accumulators is not None else 0, 0,
-        debug_trace.data_ptr() if debug_trace is not None else None)
+        *[float(g) for g in global_scales], float(timeout_ms), None, 0, 0, None)
     _lib.check(lib.mm_mega_moe_launch(ctypes.byref(b.cfg), ctypes.byref(args), torch.cuda.current_stream().cuda_stream),
                'mega_moe launch')
 
@@ -221,8 +218,7 @@ def fp4_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBu
                      recipe: Optional[Tuple[int, int, int]] = None, activation: str = 'swiglu',
                      activation_clamp: Optional[float] = None, fast_math: bool = True, *,
                      x_global_scale: float = 1.0, l1_global_scale: float = 1.0, l2_global_scale: float = 1.0,
-                     mid_global_scale: float = 1.0, engine: str = 'umma', timeout_ms: float = 0.0,
-                     debug_accumulators: Optional[torch.Tensor] = None, debug_trace: Optional[torch.Tensor] = None):
+                     mid_global_scale: float = 1.0, engine: str = 'umma', timeout_ms: float = 0.0):
     """W4A4 MegaMoE, packed E2M1 activations and weights (`sm100_b200/mega___init__.py:244-274`).
 
     The caller has written `x`, `x_sf`, `topk_idx`, `topk_weights[:y.size(0)]` into the buffer views; the launch is
@@ -236,15 +232,14 @@ def fp4_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBu
     assert recipe[2] == sym_buffer.act_sf_vec_size
     _launch(y, l1_weights, l2_weights, sym_buffer, cumulative_local_expert_recv_stats, recipe, activation,
             activation_clamp, fast_math, engine, (x_global_scale, l1_global_scale, l2_global_scale, mid_global_scale),
-            timeout_ms, debug_accumulators, debug_trace)
+            timeout_ms)
 
 
 def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
                      cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
                      recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = 'swiglu',
                      activation_clamp: Optional[float] = None, fast_math: bool = True, *,
-                     engine: str = 'umma', timeout_ms: float = 0.0,
-                     debug_accumulators: Optional[torch.Tensor] = None, debug_trace: Optional[torch.Tensor] = None):
+                     engine: str = 'umma', timeout_ms: float = 0.0):
     """W-MXFP4 x A-FP8 MegaMoE (`sm100_b200/mega___init__.py:221-241`).
 
     Tokens are E4M3 with one UE8M0 scale per 32 elements, the intermediate is requantised the same way, weights are
@@ -254,7 +249,7 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBu
     """
     assert sym_buffer.act_format == 'fp8', 'buffer must be created with act_format fp8'
     _launch(y, l1_weights, l2_weights, sym_buffer, cumulative_local_expert_recv_stats, recipe, activation,
-            activation_clamp, fast_math, engine, (1.0, 1.0, 1.0, 1.0), timeout_ms, debug_accumulators, debug_trace)
+            activation_clamp, fast_math, engine, (1.0, 1.0, 1.0, 1.0), timeout_ms)
 
 
 def mega_moe_from_hidden(y: torch.Tensor, hidden: torch.Tensor, router_weight: torch.Tensor, l1_weights, l2_weights,

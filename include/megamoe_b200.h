@@ -90,11 +90,9 @@ typedef struct mm_launch_args {
     int32_t fast_math;               /* 1: __expf + approximate reciprocal in the SwiGLU */
     float x_global_scale, l1_global_scale, l2_global_scale, mid_global_scale;   /* NVFP4 per-tensor scales; 1.0 otherwise */
     float timeout_ms;                /* budget of every device-side wait; <= 0: 2000 ms */
-    void* debug_accumulators;        /* optional diagnostics: float [debug_num_tasks][16][128], the raw fp32 accumulators
-                                        of the first tasks of SM 0 (meaningful with num_sms = 1); NULL in production */
-    int32_t debug_num_tasks;
-    int32_t reserved;
-    void* debug_trace;               /* optional diagnostics: uint64 [num_sms][16] globaltimer stamps per SM; NULL in production */
+    void* reserved_ptr0;             /* reserved, NULL */
+    int32_t reserved0, reserved1;    /* reserved, 0 */
+    void* reserved_ptr1;             /* reserved, NULL */
 } mm_launch_args_t;
 
 /* Router frontend: bf16 router GEMM, top-k selection, token quantisation into the buffer views.

@@ -218,7 +218,8 @@ def main():
         stamps = buf.phase_stamps()
         spans.append((stamps[8] - stamps[0]) / 1e3)
     span_us = statistics.median(spans)
-    phase_names = ['entry', 'dispatched', 'dispatch_headers_seen', 'scheduled', 'tasks_done', None, None, 'exit', 'last_sm_exit']
+    phase_names = ['entry', 'dispatched', 'dispatch_headers_seen', 'scheduled', 'tasks_done', None, None, 'exit', 'last_sm_exit',
+                   None, 'last_sm_tasks_done', 'last_sm_scheduled']
     phases = {n: round((stamps[i] - stamps[0]) / 1e3, 2) for i, n in enumerate(phase_names) if n and stamps[i]}
     st, words = buf.device_status()
     if st != 0:

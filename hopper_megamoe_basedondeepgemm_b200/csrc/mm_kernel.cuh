@@ -72,7 +72,7 @@ enum : uint32_t {
 enum : int {
     kStampEntry = 0, kStampDispatched = 1, kStampFlagsSeen = 2, kStampScheduled = 3, kStampTasksDone = 4,
     kStampExit = 7, kStampLastExit = 8 /* max over SMs */,
-    kStampFrontend = 9
+    kStampFrontend = 9, kStampLastTasksDone = 10 /* max over SMs */, kStampLastScheduled = 11 /* max over SMs */
 };
 
 struct RowMeta { int32_t src, token, slot; float weight; };
@@ -1017,6 +1017,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
     __syncthreads();
     if (bid == 0 && tid == 0) cx.stamp(kStampScheduled);
+    if (tid == 0) atomicMax(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps) + kStampLastScheduled, globaltimer_ns());
     if (bid == 0 && tid < static_cast<uint32_t>(p.e_local) && p.stats != nullptr && !cx.aborted())
         p.stats[tid] += static_cast<int>(c.exp_count[tid]);
 
@@ -1029,7 +1030,10 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         else { if constexpr (kA8) role_expander(cx, tid - kThreads); }
     }
     __syncthreads();
-    if (bid == 0 && tid == 0) cx.stamp(kStampTasksDone);
+    if (tid == 0) {
+        if (bid == 0) cx.stamp(kStampTasksDone);
+        atomicMax(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps) + kStampLastTasksDone, globaltimer_ns());
+    }
 
     // ---- combine. No grid-wide or cross-rank barrier precedes it: the expert outputs arrive as flagged words and every
     //      thread polls exactly the words it sums. First, which routes of this thread's first (token, 16 B chunk) item are live:

@@ -122,13 +122,15 @@ int64_t mm_frontend_workspace_bytes(const mm_config_t* cfg);
 /* Router frontend and layer as ONE persistent kernel (the frontend's outputs still land in the buffer views). */
 int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_t* args,
                                    const mm_frontend_args_t* fe, void* stream);
-/* Zero the control block and the arrival flags (after an aborted launch or at creation). The reference's
- * only remedy is re-creating the buffer (sm100_b200/mega___init__.py:43-47). Callers synchronise the ranks around it. */
+/* Zero the control block and every flagged region: the launch numbering restarts (after an aborted launch or at
+ * creation). The reference's only remedy is re-creating the buffer (sm100_b200/mega___init__.py:43-47). Callers synchronise the ranks around it. */
 int mm_reset(const mm_config_t* cfg, void* buffer, void* stream);
 /* Synchronises `stream`, then copies the 16 device status words: [0] first failure (0 = none; code | sm << 8 |
  * detail << 16), [1] launches seen, [2..] diagnostics. The reference traps instead (sm100_b200/layout_mega_moe.cuh:13-19). */
 int mm_read_device_status(const mm_config_t* cfg, const void* buffer, uint32_t out_words[16], void* stream);
-/* Synchronises `stream`, then copies the 32 phase stamps (globaltimer ns) of the last launch.
+/* Synchronises `stream`, then copies the 32 phase stamps (globaltimer ns) of the last launch. Slots, SM 0 unless
+ * noted: 0 entry, 1 dispatched, 2 header lines of all ranks seen, 3 scheduled, 4 tasks done, 7 exit, 8 last SM out,
+ * 9 fused frontend done, 10 last SM's tasks done, 11 last SM scheduled (8, 10, 11: running maxima over the SMs).
  * Replaces the `DG_SM100_PHASE_STAMPS_PTR` facility (sm100_b200/sm100_fp4_fp4_mega_moe.cuh:97-128). */
 int mm_read_phase_stamps(const mm_config_t* cfg, const void* buffer, uint64_t out_stamps[32], void* stream);
 /* Bytes of the library's built-in working memory (one array per GPU, resident from library load to process exit). */

@@ -209,7 +209,8 @@ __device__ __forceinline__ void st_global_v4(void* p, uint4 v) {
 }
 
 // ----------------------------------------------------------------------------- small integer division
-// a / b for a < 2^23, b > 0 through one approximate float division and a +-1 correction: about a dozen instructions
+// a / b for a < 2^24, b > 0 and a / b < 2^21 (tile, unit, SM, token and chunk indices are far below that) through one
+// approximate float division (2 ulp) and a +-1 correction: about a dozen instructions
 // instead of the ~100-cycle integer division sequence (these sit on per-unit and per-launch critical paths).
 __device__ __forceinline__ uint32_t udiv_small(uint32_t a, uint32_t b) {
     uint32_t q = __float2uint_rz(__fdividef(static_cast<float>(a), static_cast<float>(b)));

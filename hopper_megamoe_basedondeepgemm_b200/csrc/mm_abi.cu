@@ -216,6 +216,13 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     if (nstage > mm::kDefaultStages) nstage = mm::kDefaultStages;
     if (nstage < 2) return MM_ERR_UNSUPPORTED;
     p.nstage = nstage;
+    // dispatching SMs per destination: one per ~16 expected rows, at most G / R (and at most 32)
+    {
+        int nd = (p.T * p.topk) / (p.R * 16);
+        if (nd > *grid / p.R) nd = *grid / p.R;
+        if (nd > 32) nd = 32;
+        p.ndisp = nd < 1 ? 1 : nd;
+    }
     p.sm_act = nstage * p.unit_bytes;
     p.sm_asf = p.sm_act + p.nab * p.act_bytes;
     p.sm_otile = p.sm_asf + 2 * p.asf_bytes;
@@ -323,6 +330,7 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     q.topk_w = reinterpret_cast<float*>(b + L.off_topk_weights);
     q.x_row_bytes = static_cast<int>(L.x_row_bytes); q.x_sf_row_bytes = static_cast<int>(L.x_sf_row_bytes);
     p.fe_enabled = 1;
+    p.ndisp = 1;                          // the dispatching SMs also select the routes: one per destination
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (a->engine != MM_ENGINE_UMMA) return MM_ERR_UNSUPPORTED;     // the cross-check engine takes pre-routed inputs only
     if (a8) return fe->num_tokens == 0 ? launch_variant<32, true, false, true>(p, grid, smem_bytes, s)

@@ -93,6 +93,7 @@ struct KParams {
     long long rx_region;                 // bytes of one (parity, source) region of the receive pool
     uint32_t sm_act, sm_asf, sm_otile, sm_vt;   // dynamic shared memory offsets (stages start at 0)
     uint32_t act_bytes, asf_bytes;
+    int ndisp;                           // SMs that share the dispatch to one destination rank (1 with the fused frontend)
     uint32_t sm_xbuf; int nab;           // widened-unit buffers (FP8 variant); number of 16-row token staging buffers (1 or 2)
     uint32_t stage_region;               // bytes of the token staging area (tiles + scale slots)
     unsigned long long timeout_ns;
@@ -871,9 +872,11 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         if (bid == 0 && tid == 0) cx.stamp(kStampFrontend);
     }
 
-    // ---- dispatch: SM d pushes this rank's rows for rank d
-    if (bid < static_cast<uint32_t>(p.R) && warp < kCopyWarps) {
-        const uint32_t d = bid;
+    // ---- dispatch: the SMs d, d + R, d + 2R, ... (`ndisp` of them: one at decode sizes, more when a destination gets many
+    //      rows) push this rank's rows for rank d; each builds the same row list and takes the rows i = part (mod ndisp)
+    const uint32_t ndisp = static_cast<uint32_t>(p.ndisp);
+    if (bid < static_cast<uint32_t>(p.R) * ndisp && warp < kCopyWarps) {
+        const uint32_t part = udiv_small(bid, p.R), d = bid - part * p.R;
         uint32_t* dlist = reinterpret_cast<uint32_t*>(smem + p.sm_act);
         if (warp == 0) {
             const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
@@ -902,9 +905,9 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         // Header line (row count) and the rows' 16 B records (expert, token, slot, weight) leave first: they are all the
         // receiver's scheduler needs, and they do not depend on the token data. Every word is self-validating (flagged),
         // so nothing has to order these stores against the payload that follows.
-        if (tid == 0) st_ll_16B(region, make_uint4(cnt, 0u, 0u, 0u), flag);
+        if (tid == 0 && part == 0u) st_ll_16B(region, make_uint4(cnt, 0u, 0u, 0u), flag);
         #pragma unroll 1
-        for (uint32_t i = tid; i < cnt; i += kCopyWarps * 32) {
+        for (uint32_t i = part + tid * ndisp; i < cnt; i += kCopyWarps * 32 * ndisp) {
             const uint32_t ent = dlist[i], tok = ent >> 16, slot = (ent >> 8) & 0xFFu;
             st_ll_16B(dst_base + static_cast<size_t>(i) * 2u * p.rx_row_bytes + 2u * (p.rx_row_bytes - 16),
                       make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot])), flag);
@@ -923,7 +926,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (eight in flight: one memory round trip for
         // a row of up to 4 KB)
         #pragma unroll 1
-        for (uint32_t i = warp; i < cnt; i += kCopyWarps) {
+        for (uint32_t i = part + warp * ndisp; i < cnt; i += kCopyWarps * ndisp) {
             const uint32_t tok = dlist[i] >> 16;
             const uint8_t* xs_src = buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
             const uint8_t* sf_src = buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;

@@ -10,8 +10,10 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(nproc, fmt, engine='umma', mode='routed'):
+def _run(nproc, fmt, engine='umma', mode='routed', tokens=None):
     env = dict(os.environ, MP_FORMAT=fmt, MP_ENGINE=engine, MP_MODE=mode)
+    if tokens:
+        env['MP_TOKENS'] = str(tokens)
     cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={nproc}',
            '--master-addr', '127.0.0.1', '--master-port', '29531', os.path.join(ROOT, 'tests', 'mp_worker.py')]
     res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
@@ -23,6 +25,13 @@ def test_two_ranks(fmt):
     if torch.cuda.device_count() < 2:
         pytest.skip('needs two GPUs')
     _run(2, fmt)
+
+
+def test_two_ranks_many_tokens():
+    """48 and 45 tokens x top-4: ~96 rows per destination, so several SMs share each dispatch."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    _run(2, 'mxfp4', tokens=48)
 
 
 def test_two_ranks_from_hidden_states():

@@ -147,7 +147,9 @@ def moe_vectors(rm, act_format):
 
 
 if __name__ == '__main__':
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else '/root/reference'
+    if len(sys.argv) != 2:
+        sys.exit('usage: python tests/golden/make_golden.py <path of the reference checkout>')
+    ref_root = sys.argv[1]
     rm = load_reference_math(ref_root)
     helper_vectors(rm)
     for fmt in ('mxfp4', 'nvfp4', 'fp8'):

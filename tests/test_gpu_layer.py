@@ -145,6 +145,36 @@ def test_repeated_launches_alternate_parity():
             assert O.rel_rmse(y.cpu(), ref.y[0]) <= REL_RMSE_TOL
 
 
+def test_launch_inside_a_cuda_graph():
+    """The launch is one kernel on the current stream with all per-launch state on the device (launch counters in the
+    buffer): captured once, it replays on new inputs, as the reference's serving path does."""
+    dev = 'cuda'
+    fmt, e_local, hidden, inter, topk, tokens = 'mxfp4', 4, 512, 256, 2, 7
+    w, _, _ = O.make_expert_weights(e_local, hidden, inter, fmt, seed=1, std=0.05)
+    buf = mm.get_symm_buffer_for_mega_moe(None, e_local, 16, topk, hidden, inter, act_format=fmt)
+    l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(w, fmt, dev))
+    y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device=dev)
+    idx, tw = U.random_routing(tokens, e_local, topk, 500)
+    _, inp, sfb = U.make_rank_inputs(tokens, hidden, fmt, 501, idx, tw)
+    U.write_inputs(buf, inp, sfb)
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):                                   # warm-up launch outside the capture
+        mm.fp4_fp4_mega_moe(y, l1, l2, buf, activation_clamp=None, timeout_ms=500.0)
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        mm.fp4_fp4_mega_moe(y, l1, l2, buf, activation_clamp=None, timeout_ms=500.0)
+    for it in range(3):
+        idx, tw = U.random_routing(tokens, e_local, topk, 510 + it)
+        _, inp, sfb = U.make_rank_inputs(tokens, hidden, fmt, 520 + it, idx, tw)
+        ref = O.moe_layer_reference([inp], [w], fmt, e_local, clamp=None, faithful=True)
+        U.write_inputs(buf, inp, sfb)
+        graph.replay()
+        torch.cuda.synchronize()
+        assert buf.device_status()[0] == 0
+        assert O.rel_rmse(y.cpu(), ref.y[0]) <= REL_RMSE_TOL
+
+
 def test_inputs_through_the_pinned_host_mirror():
     """All four input views arrive with one host-to-device copy of the buffer's input region."""
     dev = 'cuda'

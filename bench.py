@@ -108,8 +108,9 @@ def run_reference(args):
 
 def workload_config(args, n):
     return {'workload': f'EP{n} {"W4A8 (MXFP4 x FP8)" if args.format == "fp8" else "W4A4 " + args.format.upper()} MegaMoE layer, E={E_LOCAL * n} ({E_LOCAL}/rank), H={HIDDEN}, '
-                        f'I={INTER}, top-{TOPK}, forced-balanced routing, {args.tokens_per_rank} token(s) per rank '
-                        f'(global M={args.tokens_per_rank * n}), weights ~N(0,0.02)',
+                        f'I={INTER}, top-{TOPK}, {"router-picked" if getattr(args, "from_hidden", False) else "forced-balanced"} routing, {args.tokens_per_rank} token(s) per rank '
+                        f'(global M={args.tokens_per_rank * n}), weights ~N(0,0.02)'
+                        + (', from bf16 hidden states: router GEMM, top-8 and token quantisation fused into the same kernel (routing as the router picks it)' if getattr(args, 'from_hidden', False) else ''),
             'l2': 'flushed by a 256 MiB write before every timed step; then the inputs are copied into the buffer views', 'parallelism': f'ep{n}'}
 
 
@@ -123,6 +124,8 @@ def main():
     ap.add_argument('--format', default='mxfp4', choices=['mxfp4', 'nvfp4', 'fp8'])
     ap.add_argument('--no-cpu-baseline', action='store_true')
     ap.add_argument('--num-sms', type=int, default=0)
+    ap.add_argument('--from-hidden', action='store_true',
+                    help='time the single-kernel layer from bf16 hidden states (router + top-8 + quantisation fused in)')
     args = ap.parse_args()
     if args.impl == 'reference':
         return run_reference(args)
@@ -169,6 +172,37 @@ def main():
         else:
             mm.fp4_fp4_mega_moe(y, l1, l2, buf, activation_clamp=10.0, fast_math=True, x_global_scale=x_gs,
                                 l1_global_scale=gs1, l2_global_scale=gs2, mid_global_scale=mid_gs)
+
+    if args.from_hidden:
+        # router over all experts (the same weights on every rank), hidden states ~ N(0, 1); the routing is whatever the
+        # router picks (top-8 of softmax), so the active experts per rank are counted from the receive statistics
+        g = torch.Generator(device='cuda').manual_seed(77)
+        wr = (torch.randn((num_experts, HIDDEN), generator=g, device='cuda') / HIDDEN ** 0.5).to(torch.bfloat16)
+        g = torch.Generator(device='cuda').manual_seed(3000 + rank)
+        hidden_src = torch.randn((T, HIDDEN), generator=g, device='cuda').to(torch.bfloat16)
+        hidden_dev = hidden_src.clone()
+        h_hidden = hidden_src.cpu().pin_memory()
+        ws = torch.zeros(mm.fe_workspace_bytes(buf), dtype=torch.uint8, device='cuda')
+        stats = torch.zeros(E_LOCAL, dtype=torch.int32, device='cuda')
+
+        def write_inputs_from_device():                 # noqa: F811
+            hidden_dev.copy_(hidden_src)
+
+        def launch(stats_arg=None):                     # noqa: F811
+            mm.mega_moe_from_hidden(y, hidden_dev, wr, l1, l2, buf, ws, cumulative_local_expert_recv_stats=stats_arg,
+                                    activation_clamp=10.0, fast_math=True, x_global_scale=x_gs, l1_global_scale=gs1,
+                                    l2_global_scale=gs2, mid_global_scale=mid_gs)
+        if world > 1:
+            dist.barrier()
+        launch(stats)
+        torch.cuda.synchronize()
+        mine = torch.tensor([int((stats > 0).sum())], device='cuda')
+        if world > 1:
+            gathered = [torch.zeros_like(mine) for _ in range(world)]
+            dist.all_gather(gathered, mine)
+            active = [int(v) for v in gathered]
+        else:
+            active = [int(mine)]
 
     def timed(step_fn, steps, warm, e2e=False):
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
@@ -219,7 +253,7 @@ def main():
         spans.append((stamps[8] - stamps[0]) / 1e3)
     span_us = statistics.median(spans)
     phase_names = ['entry', 'dispatched', 'dispatch_headers_seen', 'scheduled', 'tasks_done', None, None, 'exit', 'last_sm_exit',
-                   None, 'last_sm_tasks_done', 'last_sm_scheduled']
+                   'frontend_done', 'last_sm_tasks_done', 'last_sm_scheduled']
     phases = {n: round((stamps[i] - stamps[0]) / 1e3, 2) for i, n in enumerate(phase_names) if n and stamps[i]}
     st, words = buf.device_status()
     if st != 0:
@@ -236,6 +270,11 @@ def main():
         buf.inputs.copy_(h_in, non_blocking=True)
         launch()
         h_y.copy_(y, non_blocking=True)
+    if args.from_hidden:
+        def e2e_step():                                 # noqa: F811  (hidden states are the step's only input)
+            hidden_dev.copy_(h_hidden, non_blocking=True)
+            launch()
+            h_y.copy_(y, non_blocking=True)
     es = timed(e2e_step, args.steps, 3, e2e=True)
 
     mean_us, e2e_us = sum(ks) / len(ks), sum(es) / len(es)
@@ -255,7 +294,7 @@ def main():
                 'median_us': med_us, 'device_span_us_median': span_us, 'phases_us_sm0_last_launch': phases, 'wall_s': t_wall,
                 'clocks': clocks, 'gpu_launches': args.steps,
                 'e2e': {'value': e2e_us, 'unit': 'us',
-                        'h2d_bytes_per_step': int(h_in.numel()),
+                        'h2d_bytes_per_step': int(h_hidden.numel() * 2 if args.from_hidden else h_in.numel()),
                         'd2h_bytes_per_step': int(h_y.numel() * 2)},
                 'roofline': {'bound': 'hbm', 'achieved': achieved, 'peak': peak, 'unit': 'GB/s', 'frac': achieved / peak,
                              'traffic': (int(alg_bytes * 1.0023) if (fmt == 'mxfp4' and n == 1) else None), 'traffic_source': 'dram__bytes_read+write of one ncu capture of this workload, scaled by the active experts (profiles/)', 'peak_source': peak_src,

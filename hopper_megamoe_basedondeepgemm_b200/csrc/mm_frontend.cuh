@@ -34,16 +34,36 @@ __device__ __forceinline__ void fe_logits_items(const FeParams& q, uint32_t warp
         const uint32_t nt = min(4u, static_cast<uint32_t>(q.T) - t0);
         float acc[4] = {0.f, 0.f, 0.f, 0.f};
         const uint4* wrow = reinterpret_cast<const uint4*>(q.router_w + static_cast<size_t>(e) * q.H);
-        for (uint32_t ch = lane; ch < nchunk; ch += 32) {
-            float w[8];
-            unpack_bf16x8(__ldg(wrow + ch), w);
+        // six chunks per lane are fetched before the first multiply-add (one memory round trip per 6 x 32 chunks of the
+        // row instead of one per 32); the multiply-adds then run in the same order as a chunk-by-chunk loop would
+        constexpr uint32_t kAhead = 6;
+        #pragma unroll 1
+        for (uint32_t ch0 = lane; ch0 < nchunk; ch0 += 32 * kAhead) {
+            uint4 wq[kAhead], xq[4][kAhead];
             #pragma unroll
-            for (uint32_t t = 0; t < 4; ++t) {
-                if (t < nt) {
-                    float x[8];
-                    unpack_bf16x8(__ldg(reinterpret_cast<const uint4*>(q.hidden + static_cast<size_t>(t0 + t) * q.H) + ch), x);
+            for (uint32_t b = 0; b < kAhead; ++b) {
+                const uint32_t ch = ch0 + 32 * b;
+                if (ch < nchunk) {
+                    wq[b] = __ldg(wrow + ch);
                     #pragma unroll
-                    for (int k = 0; k < 8; ++k) acc[t] = fmaf(x[k], w[k], acc[t]);
+                    for (uint32_t t = 0; t < 4; ++t)
+                        if (t < nt) xq[t][b] = __ldg(reinterpret_cast<const uint4*>(q.hidden + static_cast<size_t>(t0 + t) * q.H) + ch);
+                }
+            }
+            #pragma unroll
+            for (uint32_t b = 0; b < kAhead; ++b) {
+                if (ch0 + 32 * b < nchunk) {
+                    float w[8];
+                    unpack_bf16x8(wq[b], w);
+                    #pragma unroll
+                    for (uint32_t t = 0; t < 4; ++t) {
+                        if (t < nt) {
+                            float x[8];
+                            unpack_bf16x8(xq[t][b], x);
+                            #pragma unroll
+                            for (int k = 0; k < 8; ++k) acc[t] = fmaf(x[k], w[k], acc[t]);
+                        }
+                    }
                 }
             }
         }
@@ -120,11 +140,18 @@ __device__ __forceinline__ bool fe_quant_token(const __nv_bfloat16* xrow, int H,
 
 // One warp: is any element of the bf16 row non-zero?
 __device__ __forceinline__ bool fe_row_nonzero(const __nv_bfloat16* xrow, int H, uint32_t lane) {
-    bool nz = false;
-    for (int k0 = lane * 8; k0 < H; k0 += 256) {
-        const uint4 v = *reinterpret_cast<const uint4*>(xrow + k0);
-        nz |= ((v.x | v.y | v.z | v.w) & 0x7FFF7FFFu) != 0u;
+    // all loads of the row are issued before the first is used (one memory round trip, not one per 256 elements); the
+    // row then sits in this SM's L1 for the quantisation pass that follows with the same lane mapping
+    uint32_t any = 0u;
+    #pragma unroll
+    for (int i = 0; i < 16; ++i) {                        // H <= 4096
+        const int k0 = lane * 8 + i * 256;
+        if (k0 < H) {
+            const uint4 v = *reinterpret_cast<const uint4*>(xrow + k0);
+            any |= v.x | v.y | v.z | v.w;
+        }
     }
+    const bool nz = (any & 0x7FFF7FFFu) != 0u;
     return __any_sync(0xffffffffu, nz);
 }
 

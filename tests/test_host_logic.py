@@ -104,3 +104,43 @@ def test_transform_weights_shapes():
                                                quant.cast_grouped_weights_to_fp4(w2, 'mxfp4'))
     assert l1[0].shape == (2, 4, 2, 17408) and l1[1].tolist() == [512, 512, 32]
     assert l2[0].shape == (2, 4, 1, 17408) and l2[1].tolist() == [512, 256, 32]
+
+
+def test_ctypes_mirror_matches_the_header(tmp_path):
+    """Compile a C program against include/megamoe_b200.h and compare every struct's size and field offsets with the
+    ctypes mirror the Python binding uses."""
+    import shutil
+    import subprocess
+    if shutil.which('gcc') is None:
+        pytest.skip('no C compiler')
+    structs = {'mm_config_t': _lib.MMConfig, 'mm_layout_t': _lib.MMLayout, 'mm_weight_geometry_t': _lib.MMWeightGeometry,
+               'mm_launch_args_t': _lib.MMLaunchArgs, 'mm_frontend_args_t': _lib.MMFrontendArgs,
+               'mm_static_args_t': _lib.MMStaticArgs}
+    header = re.sub(r'/\*.*?\*/', '', open(os.path.join(ROOT, 'include', 'megamoe_b200.h')).read(), flags=re.S)
+    lines = ['#include <stdio.h>', '#include <stddef.h>', '#include "megamoe_b200.h"', 'int main(void) {']
+    fields = {}
+    for cname, ct in structs.items():
+        body = re.search(r'typedef struct \w+ \{([^}]*)\} ' + cname + ';', header).group(1)
+        names = []
+        for decl in body.split(';'):
+            decl = decl.strip()
+            if not decl:
+                continue
+            for part in decl.split(','):
+                names.append(re.findall(r'[A-Za-z_][A-Za-z0-9_]*', part)[-1])
+        fields[cname] = names
+        lines.append(f'printf("{cname} %zu\\n", sizeof({cname}));')
+        for f in names:
+            lines.append(f'printf("{cname}.{f} %zu\\n", offsetof({cname}, {f}));')
+    lines += ['return 0;', '}']
+    src = tmp_path / 'abi.c'
+    src.write_text('\n'.join(lines))
+    exe = tmp_path / 'abi'
+    subprocess.run(['gcc', '-I', os.path.join(ROOT, 'include'), '-o', str(exe), str(src)], check=True)
+    out = dict(line.split() for line in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.splitlines())
+    for cname, ct in structs.items():
+        assert int(out[cname]) == ctypes.sizeof(ct), cname
+        mirror = [f[0] for f in ct._fields_]
+        assert mirror == fields[cname], (cname, mirror, fields[cname])
+        for f in mirror:
+            assert int(out[f'{cname}.{f}']) == getattr(ct, f).offset, (cname, f)

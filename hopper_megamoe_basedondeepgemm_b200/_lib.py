@@ -17,9 +17,9 @@ class MMConfig(ctypes.Structure):
 
 class MMLayout(ctypes.Structure):
     _fields_ = [(n, ctypes.c_int64) for n in (
-        'total_bytes', 'off_ctrl', 'off_flags', 'off_x', 'off_x_sf', 'off_topk_idx', 'off_topk_weights', 'off_rx',
+        'total_bytes', 'off_ctrl', 'off_x', 'off_x_sf', 'off_topk_idx', 'off_topk_weights', 'off_rx',
         'off_mid', 'off_mid_sf', 'off_comb', 'off_red', 'off_cnt', 'x_row_bytes', 'x_sf_row_bytes', 'rx_row_bytes', 'rx_cap_rows',
-        'mid_rows', 'mid_row_bytes', 'mid_sf_row_bytes', 'cnt_per_phase')] + [('sf_vec', ctypes.c_int32), ('reserved', ctypes.c_int32),
+        'mid_rows', 'mid_row_bytes', 'mid_sf_row_bytes', 'cnt_per_phase')] + [('sf_vec', ctypes.c_int32), ('ctrl_bytes', ctypes.c_int32),
                                                    ('rx_region_bytes', ctypes.c_int64)]
 
 
@@ -37,8 +37,7 @@ class MMLaunchArgs(ctypes.Structure):
         ('activation_clamp', ctypes.c_float), ('fast_math', ctypes.c_int32),
         ('x_global_scale', ctypes.c_float), ('l1_global_scale', ctypes.c_float),
         ('l2_global_scale', ctypes.c_float), ('mid_global_scale', ctypes.c_float),
-        ('timeout_ms', ctypes.c_float), ('reserved_ptr0', ctypes.c_void_p),
-        ('reserved0', ctypes.c_int32), ('reserved1', ctypes.c_int32), ('reserved_ptr1', ctypes.c_void_p)]
+        ('timeout_ms', ctypes.c_float), ('input_region', ctypes.c_void_p)]
 
 
 class MMFrontendArgs(ctypes.Structure):
@@ -60,11 +59,13 @@ class MMStaticArgs(ctypes.Structure):
 
 
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
+TUNE = {'knobs': 0, 'stages': 1, 'prefetch_w1_experts': 2, 'prefetch_w2_experts': 3}
+KNOB_PREFETCH, KNOB_OWN_ROWS, KNOB_EARLY_COMBINE = 1, 2, 4
 
 EXPORTS = ('mm_get_layout', 'mm_get_weight_geometry', 'mm_get_token_alignment', 'mm_mega_moe_launch',
            'mm_frontend_launch', 'mm_frontend_workspace_bytes', 'mm_mega_moe_from_hidden_launch', 'mm_reset',
            'mm_read_device_status', 'mm_read_phase_stamps', 'mm_status_string', 'mm_last_cuda_error',
-           'mm_mega_moe_launch_static_scratch')
+           'mm_mega_moe_launch_static_scratch', 'mm_set_tuning', 'mm_get_tuning')
 
 _lib = None
 
@@ -88,6 +89,9 @@ def load() -> ctypes.CDLL:
     lib.mm_frontend_workspace_bytes.restype = ctypes.c_int64
     lib.mm_mega_moe_from_hidden_launch.argtypes = [P(MMConfig), P(MMLaunchArgs), P(MMFrontendArgs), ctypes.c_void_p]
     lib.mm_mega_moe_launch_static_scratch.argtypes = [P(MMConfig), P(MMStaticArgs), ctypes.c_void_p]
+    lib.mm_set_tuning.argtypes = [ctypes.c_int32, ctypes.c_int32]
+    lib.mm_get_tuning.argtypes = [ctypes.c_int32]
+    lib.mm_get_tuning.restype = ctypes.c_int32
     lib.mm_reset.argtypes = [P(MMConfig), ctypes.c_void_p, ctypes.c_void_p]
     lib.mm_read_device_status.argtypes = [P(MMConfig), ctypes.c_void_p, P(ctypes.c_uint32), ctypes.c_void_p]
     lib.mm_read_phase_stamps.argtypes = [P(MMConfig), ctypes.c_void_p, P(ctypes.c_uint64), ctypes.c_void_p]

@@ -23,6 +23,10 @@ inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 
 int sf_vec_of(int fmt) { return fmt == MM_FMT_NVFP4 ? 16 : 32; }
 
+// development knobs (mm_set_tuning): kernel feature bits, ring depth (0 = chosen from the shared-memory plan), and how
+// many experts' W1 / W2 the scout may prefetch into the L2 in one launch
+int g_tuning[MM_TUNE_COUNT] = {mm::kKnobPrefetch | mm::kKnobOwnRows | mm::kKnobEarlyCombine, 0, 14, 14};
+
 int check_config(const mm_config_t* c) {
     if (c == nullptr) return MM_ERR_INVALID_ARGUMENT;
     if (c->num_ranks < 1 || c->num_ranks > mm::kMaxRanks || c->rank < 0 || c->rank >= c->num_ranks) return MM_ERR_INVALID_ARGUMENT;
@@ -67,6 +71,14 @@ const char* mm_last_cuda_error(void) { return g_cuda_error; }
 
 int32_t mm_get_token_alignment(void) { return 16; }
 
+int mm_set_tuning(int32_t key, int32_t value) {
+    if (key < 0 || key >= MM_TUNE_COUNT || value < 0) return MM_ERR_INVALID_ARGUMENT;
+    g_tuning[key] = value;
+    return MM_OK;
+}
+
+int32_t mm_get_tuning(int32_t key) { return key >= 0 && key < MM_TUNE_COUNT ? g_tuning[key] : -1; }
+
 int mm_get_weight_geometry(int32_t act_format, mm_weight_geometry_t* out) {
     if (out == nullptr || (act_format != MM_FMT_MXFP4 && act_format != MM_FMT_NVFP4 && act_format != MM_FMT_FP8)) return MM_ERR_INVALID_ARGUMENT;
     const int vec = sf_vec_of(act_format);
@@ -99,7 +111,7 @@ int mm_get_layout(const mm_config_t* c, mm_layout_t* out) {
     int64_t off = 0;
     auto take = [&](int64_t bytes) { const int64_t o = off; off = align_up(off + bytes, 1024); return o; };
     out->off_ctrl = take(mm::kCtrlBytes);
-    out->off_flags = take(mm::kFlagBytes);
+    out->ctrl_bytes = mm::kCtrlBytes;
     out->off_x = take(t_max * out->x_row_bytes);
     out->off_x_sf = take(t_max * out->x_sf_row_bytes);
     out->off_topk_idx = take(t_max * c->num_topk * 8);
@@ -148,6 +160,16 @@ int mm_read_phase_stamps(const mm_config_t* cfg, const void* buffer, uint64_t ou
     if (buffer == nullptr || out_stamps == nullptr) return MM_ERR_INVALID_ARGUMENT;
     MM_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
     MM_CUDA(cudaMemcpy(out_stamps, static_cast<const uint8_t*>(buffer) + L.off_ctrl + mm::kCtrlStamps, 256, cudaMemcpyDeviceToHost));
+    // per-SM records -> slot 12 (first instruction of the earliest SM) and slot 13 (first weight request of any SM)
+    static thread_local uint64_t per_sm[512];
+    MM_CUDA(cudaMemcpy(per_sm, static_cast<const uint8_t*>(buffer) + L.off_ctrl + mm::kCtrlSmEntry, sizeof(per_sm), cudaMemcpyDeviceToHost));
+    uint64_t first_in = ~0ull, first_w = ~0ull;
+    for (int i = 0; i < 256; ++i) {
+        if (per_sm[i] != 0 && per_sm[i] < first_in) first_in = per_sm[i];
+        if (per_sm[256 + i] != 0 && per_sm[256 + i] < first_w) first_w = per_sm[256 + i];
+    }
+    out_stamps[12] = first_in == ~0ull ? 0 : first_in;
+    out_stamps[13] = first_w == ~0ull ? 0 : first_w;
     return MM_OK;
 }
 
@@ -187,7 +209,11 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     }
     p.w1 = static_cast<const uint8_t*>(a->l1_weights); p.w2 = static_cast<const uint8_t*>(a->l2_weights);
     p.y = static_cast<__nv_bfloat16*>(a->y); p.stats = a->cumulative_local_expert_recv_stats;
-    p.off_ctrl = L.off_ctrl; p.off_flags = L.off_flags; p.off_x = L.off_x; p.off_x_sf = L.off_x_sf;
+    p.off_ctrl = L.off_ctrl; p.off_x = L.off_x; p.off_x_sf = L.off_x_sf;
+    p.inp = a->input_region != nullptr ? static_cast<const uint8_t*>(a->input_region) - L.off_x : static_cast<const uint8_t*>(a->buffer);
+    p.knobs = static_cast<uint32_t>(g_tuning[MM_TUNE_KNOBS]);
+    p.pf_w1_max = static_cast<uint32_t>(g_tuning[MM_TUNE_PREFETCH_W1_EXPERTS]);
+    p.pf_w2_max = static_cast<uint32_t>(g_tuning[MM_TUNE_PREFETCH_W2_EXPERTS]);
     p.off_topk_idx = L.off_topk_idx; p.off_topk_w = L.off_topk_weights; p.off_rx = L.off_rx;
     p.off_mid = L.off_mid; p.off_mid_sf = L.off_mid_sf; p.off_comb = L.off_comb;
     p.off_red = L.off_red; p.off_cnt = L.off_cnt; p.cnt_per_phase = static_cast<int>(L.cnt_per_phase);
@@ -213,7 +239,9 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     int nstage = static_cast<int>((budget - fixed) / p.unit_bytes);
     // A short ring is faster than a deep one: the loader runs ahead into the next phase's weights, and with many stages
     // that prefetch competes with the stream the current phase is waiting for (measured: 4 stages beat 8 by 2 us).
-    if (nstage > mm::kDefaultStages) nstage = mm::kDefaultStages;
+    const int want = g_tuning[MM_TUNE_STAGES] > 0 ? g_tuning[MM_TUNE_STAGES] : mm::kDefaultStages;
+    if (nstage > want) nstage = want;
+    if (nstage > mm::kMaxStages) nstage = mm::kMaxStages;
     if (nstage < 2) return MM_ERR_UNSUPPORTED;
     p.nstage = nstage;
     // dispatching SMs per destination: one per ~16 expected rows, at most G / R (and at most 32)
@@ -237,7 +265,14 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
 template <int kVec, bool kUmma, bool kFe = false, bool kA8 = false>
 static int launch_variant(const mm::KParams& p, int grid, size_t smem_bytes, cudaStream_t stream) {
     auto kern = mm::mega_moe_kernel<kVec, kUmma, kFe, kA8>;
-    MM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
+    // the opt-in shared-memory size is a per-device function attribute: set once per (variant, device), raised on demand
+    static int attr_bytes[64] = {};
+    int dev = 0;
+    MM_CUDA(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || attr_bytes[dev] < static_cast<int>(smem_bytes)) {
+        MM_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_bytes)));
+        if (dev >= 0 && dev < 64) attr_bytes[dev] = static_cast<int>(smem_bytes);
+    }
     kern<<<grid, kA8 ? mm::kThreads + mm::kNumExpThreads : mm::kThreads, smem_bytes, stream>>>(p);
     MM_CUDA(cudaGetLastError());
     return MM_OK;
@@ -272,6 +307,7 @@ int mm_frontend_launch(const mm_config_t* cfg, void* buffer, const mm_frontend_a
     if (buffer == nullptr || fe == nullptr || fe->hidden_states == nullptr || fe->router_weight == nullptr || fe->workspace == nullptr) return MM_ERR_INVALID_ARGUMENT;
     if (fe->num_tokens < 0 || fe->num_tokens > cfg->num_max_tokens_per_rank) return MM_ERR_INVALID_ARGUMENT;
     if (cfg->num_topk != 8 || cfg->num_experts > 1024) return MM_ERR_UNSUPPORTED;
+    if (cfg->num_experts < cfg->num_topk) return MM_ERR_INVALID_ARGUMENT;      // fewer experts than routes per token
     if (fe->score_mode == 1 && fe->expert_bias == nullptr) return MM_ERR_INVALID_ARGUMENT;
     if (fe->num_tokens == 0) return MM_OK;
     int grid = 0;
@@ -310,6 +346,7 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     if (fe == nullptr || fe->hidden_states == nullptr || fe->router_weight == nullptr || fe->workspace == nullptr) return MM_ERR_INVALID_ARGUMENT;
     if (fe->num_tokens != a->num_tokens) return MM_ERR_INVALID_ARGUMENT;
     if (cfg->num_topk != 8 || cfg->num_experts > 1024) return MM_ERR_UNSUPPORTED;
+    if (cfg->num_experts < cfg->num_topk) return MM_ERR_INVALID_ARGUMENT;      // fewer experts than routes per token
     if (fe->score_mode == 1 && fe->expert_bias == nullptr) return MM_ERR_INVALID_ARGUMENT;
     const bool a8 = cfg->act_format == MM_FMT_FP8;
     if (static_cast<size_t>(cfg->num_experts) * 4 * ((mm::kThreads + (a8 ? mm::kNumExpThreads : 0)) / 32) > p.stage_region) return MM_ERR_UNSUPPORTED;
@@ -383,8 +420,10 @@ int mm_mega_moe_launch_static_scratch(const mm_config_t* cfg, const mm_static_ar
     // the array keeps the previous call's contents: the control block, the arrival flags and the split-tile counters
     // must start from zero (the launch counters restart with them, so every call runs as the buffer's first launch),
     // and with the counters every flagged word of the receive pool and the combine buffer
+    // (the split-tile partial sums between them are always written before they are read: not cleared)
     MM_CUDA(cudaMemsetAsync(scratch + L.off_ctrl, 0, L.off_x - L.off_ctrl, s));
-    MM_CUDA(cudaMemsetAsync(scratch + L.off_rx, 0, L.total_bytes - L.off_rx, s));
+    MM_CUDA(cudaMemsetAsync(scratch + L.off_rx, 0, L.off_red - L.off_rx, s));
+    MM_CUDA(cudaMemsetAsync(scratch + L.off_cnt, 0, L.total_bytes - L.off_cnt, s));
     const size_t t = static_cast<size_t>(a->num_tokens);
     if (t > 0) {
         MM_CUDA(cudaMemcpyAsync(scratch + L.off_x, a->x, t * L.x_row_bytes, cudaMemcpyDeviceToDevice, s));

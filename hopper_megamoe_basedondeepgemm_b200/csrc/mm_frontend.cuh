@@ -175,13 +175,16 @@ __device__ __forceinline__ void fe_select_token(const FeParams& q, uint32_t t, f
             best = key > best ? key : best;
         }
         best = warp_max_u64(best);
+        // no candidate left (fewer than eight selectable experts: every remaining score is -inf): the slot stays empty
+        const bool found = best != 0ull;
         const uint32_t e_best = 0xFFFFFFFFu - static_cast<uint32_t>(best & 0xFFFFFFFFull);
-        if (lane == 0) sc[e_best] = -INFINITY;
-        if (static_cast<int>(lane) == k) chosen = e_best;
+        if (found && lane == 0) sc[e_best] = -INFINITY;
+        if (static_cast<int>(lane) == k) chosen = found ? e_best : 0xFFFFFFFFull;
         __syncwarp();
     }
-    const int e_sel = static_cast<int>(chosen);
-    const float v_sel = lane < 8 ? __uint_as_float(ld_cg_u32(lg + e_sel)) : -INFINITY;
+    const bool empty_slot = lane < 8 && chosen == 0xFFFFFFFFull;
+    const int e_sel = empty_slot ? 0 : static_cast<int>(chosen);
+    const float v_sel = lane < 8 && !empty_slot ? __uint_as_float(ld_cg_u32(lg + e_sel)) : -INFINITY;
     float wgt;
     if (q.score_mode == 1) {
         const float s = lane < 8 ? 1.0f / (1.0f + expf(-v_sel)) : 0.f;
@@ -200,8 +203,8 @@ __device__ __forceinline__ void fe_select_token(const FeParams& q, uint32_t t, f
         wgt = ex / sum;
     }
     if (lane < 8) {
-        q.topk_idx[static_cast<size_t>(t) * 8 + lane] = nonzero ? e_sel : -1;
-        q.topk_w[static_cast<size_t>(t) * 8 + lane] = nonzero ? wgt : 0.f;
+        q.topk_idx[static_cast<size_t>(t) * 8 + lane] = nonzero && !empty_slot ? e_sel : -1;
+        q.topk_w[static_cast<size_t>(t) * 8 + lane] = nonzero && !empty_slot ? wgt : 0.f;
     }
 }
 

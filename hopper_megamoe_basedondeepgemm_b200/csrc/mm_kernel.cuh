@@ -53,13 +53,23 @@ constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kOtileBytes = 4096;
 constexpr uint32_t kVtBytes = kTileTokens * kTileRows * 4;   // fp32 accumulators of one task, token-major
 
+constexpr int kOwnCap = 256;            // routed rows of this rank's own tokens that every SM lists for itself (see the scout)
+
 // control-block offsets (bytes from off_ctrl)
 constexpr int kCtrlEpoch = 0;           // u32[256] one launch counter per SM
 constexpr int kCtrlStatus = 1024;       // u32[16]
-constexpr int kCtrlFeArrive = 1092;     // u32 SMs that published their router logits
 constexpr int kCtrlStamps = 2048;       // u64[32] phase stamps
-constexpr int kCtrlBytes = 4096;
-constexpr int kFlagBytes = 1024;        // reserved block after the control block (no separate arrival flags exist)
+constexpr int kCtrlFeWords = 3072;      // u32[256] per-SM word: launch number once the SM has published its router logits
+constexpr int kCtrlSmEntry = 4096;      // u64[256] per-SM time of the kernel's first instruction
+constexpr int kCtrlSmWFirst = 6144;     // u64[256] per-SM time of the first weight request (prefetch or load); ~0: none
+constexpr int kCtrlBytes = 8192;
+
+// tuning bits (KParams::knobs)
+enum : uint32_t {
+    kKnobPrefetch = 1u,                 // the scout asks for the weights of every expert it learns to be live (L2 prefetch)
+    kKnobOwnRows = 2u,                  // rows of this rank's own tokens are listed from topk_idx by every SM (no header wait)
+    kKnobEarlyCombine = 4u              // warps start on the combine as soon as their role ends
+};
 
 // device status codes (low byte of status word 0)
 enum : uint32_t {
@@ -70,9 +80,10 @@ enum : uint32_t {
 };
 // phase stamp slots (SM 0 unless noted)
 enum : int {
-    kStampEntry = 0, kStampDispatched = 1, kStampFlagsSeen = 2, kStampScheduled = 3, kStampTasksDone = 4,
+    kStampEntry = 0, kStampDispatched = 1, kStampFlagsSeen = 2, kStampScheduled = 3, kStampTasksDone = 4, kStampPrologue = 5 /* SM 0: shared memory, barriers and TMEM are set up */,
     kStampExit = 7, kStampLastExit = 8 /* max over SMs */,
-    kStampFrontend = 9, kStampLastTasksDone = 10 /* max over SMs */, kStampLastScheduled = 11 /* max over SMs */
+    kStampFrontend = 9, kStampLastTasksDone = 10 /* max over SMs */, kStampLastScheduled = 11 /* max over SMs */,
+    kStampLastWeight = 14 /* max over SMs: the last streamed unit has landed */
 };
 
 struct RowMeta { int32_t src, token, slot; float weight; };
@@ -88,7 +99,8 @@ struct KParams {
     uint8_t* peer[kMaxRanks];
     const uint8_t* w1; const uint8_t* w2;
     __nv_bfloat16* y; int* stats;
-    long long off_ctrl, off_flags, off_x, off_x_sf, off_topk_idx, off_topk_w, off_rx, off_mid, off_mid_sf, off_comb, off_red, off_cnt;
+    const uint8_t* inp;                  // base of the input views: inp + off_x etc. (the buffer itself, or a mapped host mirror of its input region)
+    long long off_ctrl, off_x, off_x_sf, off_topk_idx, off_topk_w, off_rx, off_mid, off_mid_sf, off_comb, off_red, off_cnt;
     int cnt_per_phase;
     long long rx_region;                 // bytes of one (parity, source) region of the receive pool
     uint32_t sm_act, sm_asf, sm_otile, sm_vt;   // dynamic shared memory offsets (stages start at 0)
@@ -97,6 +109,8 @@ struct KParams {
     uint32_t sm_xbuf; int nab;           // widened-unit buffers (FP8 variant); number of 16-row token staging buffers (1 or 2)
     uint32_t stage_region;               // bytes of the token staging area (tiles + scale slots)
     unsigned long long timeout_ns;
+    uint32_t knobs;                      // kKnob* bits
+    uint32_t pf_w1_max, pf_w2_max;       // experts whose W1 / W2 the scout may prefetch in one launch (L2 capacity)
     FeParams fe; int fe_enabled;         // router frontend run at the head of the same launch (optional)
 };
 
@@ -107,7 +121,8 @@ struct Ctl {
     uint32_t tmem_base, epoch, abort_flag, ntasks;
     uint32_t rx_count[kMaxRanks], rx_prefix[kMaxRanks + 1];
     uint32_t exp_count[kMaxLocalExperts], mid_base[kMaxLocalExperts];
-    uint32_t nt1, nt2, dcount, pad0;
+    uint32_t nt1, nt2, dcount, own_cnt;
+    uint32_t comb_next, issued, pad1, pad2; // next combine item of this SM; weight units the loader has issued
     // token staging geometry of this launch: with room for one 16-row buffer only, launches whose experts all have at
     // most 8 rows split it into two 8-row buffers (the MMA then reads rows 8..15 from rows 0..7: stride 0 between the
     // 8-row groups; those accumulator columns are never used)
@@ -126,6 +141,8 @@ struct Ctl {
     uint32_t sfb[4][kTileTokens];        // L1 epilogue: one scale byte per (warp, token), gathered into one flagged word
     uint32_t mtl[kMaxMTiles];            // (expert << 16 | token tile) of every 16-token tile, expert-major
     RowMeta rx_meta[kMetaSmemRows];
+    RowMeta own_meta[kOwnCap];           // records of this rank's own routed rows, listed by the scout from topk_idx
+    uint8_t own_e[kOwnCap];
     uint8_t meta_e[kMetaCap];
 };
 
@@ -169,6 +186,13 @@ struct Ctx {
     }
     __device__ __forceinline__ void stamp(int slot) const {
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[slot] = globaltimer_ns();
+    }
+    __device__ __forceinline__ void stamp_max(int slot, unsigned long long t) const {
+        atomicMax(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps) + slot, t);
+    }
+    // per-SM time of the first weight request of this launch (the scout's first prefetch or the loader's first copy)
+    __device__ __forceinline__ void note_first_weight_request() const {
+        atomicMin(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmWFirst) + blockIdx.x, globaltimer_ns());
     }
     // received row i of source rank `src_rank` (flagged words: payload byte b sits at 2 * (b & ~3) + (b & 3))
     __device__ __forceinline__ uint8_t* rx_row(uint32_t src_rank, uint32_t i) const {
@@ -220,6 +244,8 @@ __device__ void role_loader(const Ctx& cx) {
             if (elect_one()) {
                 mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
                 bulk_g2s(cx.smem + static_cast<size_t>(s) * p.unit_bytes, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
+                c.issued = it + 1u;
+                if (it == 0u) cx.note_first_weight_request();
             }
             __syncwarp();
             if (++s == static_cast<uint32_t>(p.nstage)) { s = 0; ph ^= 1u; }
@@ -239,6 +265,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     const uint32_t tm = c.tmem_base;
     const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 16
     uint32_t it = 0, s = 0, ph = 0;                             // units consumed so far; ring stage and its phase bit
+    unsigned long long t_landed = 0ull;                         // when the latest unit was found in shared memory
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
@@ -253,6 +280,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
             uint64_t* ready = kA8 ? &c.xfull[it & 1u] : &c.full[s];
             if (!cx.warp_wait(ready, kA8 ? (it >> 1) & 1u : ph, kErrWaitFull)) return;
             tc_fence_after();
+            t_landed = globaltimer_ns();
             if (elect_one()) {
               {
                 const uint32_t wsm = kA8 ? smem_u32(cx.smem + p.sm_xbuf + (it & 1u) * kXbufBytes)
@@ -296,6 +324,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         }
         __syncwarp();
     }
+    if (lane == 0 && t_landed != 0ull) cx.stamp_max(kStampLastWeight, t_landed);
 }
 
 // ============================================================================================= weight widener (FP8 variant)
@@ -784,22 +813,149 @@ __device__ __noinline__ uint32_t build_schedule(const KParams& p, Ctl& c, const 
     }    return (M << 16) | (nmine < 0xFFFFu ? nmine : 0xFFFFu);
 }
 
+// ============================================================================================= scout
+// One warp per SM has nothing to do until the roles start. It (a) lists the routed rows of this rank's own tokens
+// straight from topk_idx, so that no SM has to wait for the own-rank header line to learn them, and (b) watches the
+// other ranks' header lines and records as they arrive; for every expert it learns to be live it asks for this SM's
+// share of the expert's W1 and W2 units to be brought into the L2 (units u = SM, SM + G, ... of the expert's stream:
+// all SMs together cover every byte once). The weight stream therefore starts when the first live expert is known,
+// not when the last header has arrived and the schedule is built; the roles' bulk copies then find their units in the
+// L2 or already on their way. The routing entries of the own tokens are loaded before the prologue's barrier.
+struct ScoutRegs { long long tk[kOwnCap / 32]; float tw[kOwnCap / 32]; };
+
+__device__ __forceinline__ void scout_load_own(const KParams& p, const uint8_t* inp, uint32_t lane, ScoutRegs& r) {
+    const long long* tk = reinterpret_cast<const long long*>(inp + p.off_topk_idx);
+    const float* tw = reinterpret_cast<const float*>(inp + p.off_topk_w);
+    const uint32_t n = static_cast<uint32_t>(p.T) * p.topk;
+    #pragma unroll
+    for (uint32_t i = 0; i < kOwnCap / 32; ++i) {
+        const uint32_t idx = i * 32 + lane;
+        r.tk[i] = idx < n ? tk[idx] : -1ll;
+        r.tw[i] = idx < n ? tw[idx] : 0.f;
+    }
+}
+
+__device__ __forceinline__ uint64_t warp_or_u64(uint64_t v) {
+    const uint32_t lo = __reduce_or_sync(0xffffffffu, static_cast<uint32_t>(v));
+    const uint32_t hi = __reduce_or_sync(0xffffffffu, static_cast<uint32_t>(v >> 32));
+    return (static_cast<uint64_t>(hi) << 32) | lo;
+}
+
+__device__ __noinline__ void role_scout(const Ctx& cx, const ScoutRegs& reg, bool own_ok, uint32_t lane, uint32_t G) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    const uint32_t bid = blockIdx.x, R = p.R, flag = c.epoch + 1u;
+    const bool pf = (p.knobs & kKnobPrefetch) != 0u;
+    uint64_t known = 0ull;
+    uint32_t asked = 0;
+    // this SM's share of the weights of the experts in `fresh`: W1 of all of them first (the L1 phase needs it first)
+    auto ask = [&](uint64_t fresh) {
+        if (!pf || fresh == 0ull) return;
+        if (asked == 0u && lane == 0) cx.note_first_weight_request();
+        #pragma unroll 1
+        for (uint32_t layer = 0; layer < 2; ++layer) {
+            const uint32_t per = layer ? p.n2_tiles * p.k2_units : p.n1_tiles * p.k1_units;
+            const uint32_t limit = layer ? p.pf_w2_max : p.pf_w1_max;
+            const uint8_t* base = layer ? p.w2 : p.w1;
+            uint64_t m = fresh;
+            uint32_t n = asked;
+            while (m != 0ull && n < limit) {
+                const uint32_t e = static_cast<uint32_t>(__ffsll(static_cast<long long>(m))) - 1u;
+                m &= m - 1ull;
+                ++n;
+                #pragma unroll 1
+                for (uint32_t u = bid + lane * G; u < per; u += 32u * G)
+                    bulk_prefetch_l2(base + (static_cast<size_t>(e) * per + u) * p.unit_bytes, p.unit_bytes);
+            }
+        }
+        asked += static_cast<uint32_t>(__popcll(fresh));
+    };
+    if (own_ok) {
+        const uint32_t n = static_cast<uint32_t>(p.T) * p.topk;
+        uint32_t cnt = 0;
+        uint64_t m = 0ull;
+        #pragma unroll
+        for (uint32_t i = 0; i < kOwnCap / 32; ++i) {
+            if (i * 32 < n) {
+                const uint32_t idx = i * 32 + lane;
+                const long long ex = reg.tk[i];
+                const uint32_t ex32 = ex >= 0 && ex < 0x10000 ? static_cast<uint32_t>(ex) : 0u;
+                const uint32_t dest = udiv_small(ex32, p.e_local), tok = udiv_small(idx, p.topk);
+                const bool mine = idx < n && ex >= 0 && ex < 0x10000 && dest == static_cast<uint32_t>(p.rank);
+                const uint32_t b = __ballot_sync(0xffffffffu, mine);
+                if (mine) {
+                    const uint32_t pos = cnt + __popc(b & ((1u << lane) - 1u)), el = ex32 - dest * p.e_local;
+                    c.own_e[pos] = static_cast<uint8_t>(el);
+                    c.own_meta[pos] = RowMeta{p.rank, static_cast<int32_t>(tok), static_cast<int32_t>(idx - tok * p.topk), reg.tw[i]};
+                    m |= 1ull << (el & 63u);
+                }
+                cnt += __popc(b);
+            }
+        }
+        if (lane == 0) c.own_cnt = cnt;
+        known = warp_or_u64(m);
+        ask(known);
+    }
+    if (!pf) return;
+    uint32_t pending = (R >= 32u ? 0xFFFFFFFFu : (1u << R) - 1u);
+    if (own_ok) pending &= ~(1u << p.rank);
+    uint32_t passes = 0;
+    while (pending != 0u) {
+        uint64_t fresh = 0ull;
+        #pragma unroll 1
+        for (uint32_t r = 0; r < R; ++r) {
+            if (((pending >> r) & 1u) == 0u) continue;
+            const uint8_t* region = cx.buf + p.off_rx + static_cast<size_t>(cx.par * R + r) * p.rx_region;
+            const uint4 ha = ld_volatile_v4(region), hb = ld_volatile_v4(region + 16);
+            if (!ll_valid(ha, hb, flag)) continue;
+            const uint32_t cnt = ha.x <= static_cast<uint32_t>(p.cap) ? ha.x : 0u;
+            bool all = true;
+            uint64_t m = 0ull;
+            #pragma unroll 1
+            for (uint32_t base = 0; base < cnt; base += 32) {
+                const uint32_t i = base + lane;
+                bool ok = true;
+                if (i < cnt) {
+                    const uint8_t* src = cx.rx_row(r, i) + 2u * (p.rx_row_bytes - 16);
+                    const uint4 a = ld_volatile_v4(src), b = ld_volatile_v4(src + 16);
+                    ok = ll_valid(a, b, flag);
+                    if (ok && (a.x & 0xFFu) < static_cast<uint32_t>(p.e_local)) m |= 1ull << (a.x & 63u);      // only experts this rank holds: the prefetch address must lie inside the weights
+                }
+                all = __all_sync(0xffffffffu, ok) && all;
+            }
+            fresh |= warp_or_u64(m);
+            if (all) pending &= ~(1u << r);
+        }
+        fresh &= ~known;
+        ask(fresh);
+        known |= fresh;
+        if ((++passes & 0xFu) == 0u && (cx.aborted() || cx.expired())) break;   // the header wait of the main path reports the failure
+    }
+}
+
 // ============================================================================================= the kernel
 template <int kVec, bool kUmma, bool kFe, bool kA8>
 __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1) mega_moe_kernel(const __grid_constant__ KParams p) {
     constexpr uint32_t kNT = kA8 ? kThreads + kNumExpThreads : kThreads;       // threads of this instantiation
+    const unsigned long long t_first = globaltimer_ns();
     extern __shared__ uint8_t smem_raw[];
     __shared__ Ctl c;
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023u) & ~static_cast<uintptr_t>(1023u));
     const uint32_t tid = threadIdx.x, warp = tid >> 5, lane = tid & 31u, bid = blockIdx.x, G = gridDim.x;
     uint8_t* buf = p.peer[p.rank];
+    const uint8_t* inp = kFe ? buf : p.inp;          // the fused frontend writes the input views itself (into the buffer)
     uint32_t* ctrl32 = reinterpret_cast<uint32_t*>(buf + p.off_ctrl);
+    // the spare warp: the last one (it takes no part in the dispatch copies); with the fused frontend every warp is busy
+    constexpr uint32_t kCopyWarps = kFe ? kNT / 32 : kNT / 32 - 1;
+    constexpr bool kScout = !kFe;
+    const bool own_ok = kScout && (p.knobs & kKnobOwnRows) != 0u && static_cast<uint32_t>(p.T) * p.topk <= kOwnCap;
 
     // ---- prologue
+    ScoutRegs sreg;
+    if constexpr (kScout) { if (warp == kCopyWarps && own_ok) scout_load_own(p, inp, lane, sreg); }
     if (tid == 0) {
         const uint32_t ep = ctrl32[kCtrlEpoch / 4 + bid];
         ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
-        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u;
+        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.own_cnt = 0u; c.comb_next = 0u; c.issued = 0u;
         for (int s = 0; s < p.nstage; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
         #pragma unroll 1
         for (int i = 0; i < 2; ++i) {
@@ -808,6 +964,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             mbar_init(&c.xfull[i], kNumExpThreads / 64); mbar_init(&c.xempty[i], 1);
         }
         mbar_fence_init();
+        reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmEntry)[bid] = t_first;
+        reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmWFirst)[bid] = ~0ull;
     }
     // the token staging area starts from zero (the dispatch lists and the frontend's scratch that pass through it later
     // leave finite bytes; whatever sits in rows beyond a task's valid tokens only reaches accumulator columns nobody reads)
@@ -820,24 +978,30 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     tc_fence_after();
     Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, c.epoch & 1u};
     const uint32_t epoch = c.epoch, par = cx.par;
-    if (bid == 0 && tid == 0) { ctrl32[kCtrlStatus / 4 + 1] = epoch + 1u; cx.stamp(kStampEntry); }
+    if (bid == 0 && tid == 0) {
+        ctrl32[kCtrlStatus / 4 + 1] = epoch + 1u;
+        reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[kStampEntry] = t_first;
+        cx.stamp(kStampPrologue);
+    }
     // The control block and the split-tile counters are touched late, on the critical dependency chain, and by then
     // they have usually been evicted from the L2 by the weight stream of earlier work: ask for their lines now.
-    if (warp == 7) {
+    if (warp == 6) {
         const uint32_t g = bid * 32 + lane, gn = G * 32;
         #pragma unroll 1
-        for (uint32_t off = g * 128u; off < kCtrlBytes + kFlagBytes; off += gn * 128u) prefetch_l2_line(buf + p.off_ctrl + off);
+        for (uint32_t off = g * 128u; off < kCtrlBytes; off += gn * 128u) prefetch_l2_line(buf + p.off_ctrl + off);
         const size_t cnt_bytes = static_cast<size_t>(2) * p.cnt_per_phase * 4;
         #pragma unroll 1
         for (size_t off = static_cast<size_t>(g) * 128u; off < (cnt_bytes < 65536 ? cnt_bytes : 65536); off += gn * 128u) prefetch_l2_line(buf + p.off_cnt + off);
     }
 
-    // ---- warm-up of the scheduler's instructions: the last warp has nothing to do until the roles start (it takes no
-    //      part in the dispatch copies), so it runs the scheduler once on dummy counts (eight experts with one row). The
-    //      real call, which sits on the critical path right after the dispatch arrives, overwrites everything this writes.
-    constexpr uint32_t kCopyWarps = kFe ? kNT / 32 : kNT / 32 - 1;      // the fused frontend keeps every warp busy instead
+    // ---- warm-up of the scheduler's instructions: on the SMs that do not dispatch, warp 6 is idle until the roles start,
+    //      so it runs the scheduler once on dummy counts (eight experts with one row). The real call, which sits on the
+    //      critical path right after the dispatch arrives, then finds its instructions cached and overwrites everything
+    //      this writes. (On the dispatching SMs warp 6 copies rows; their schedule runs cold.)
+    const uint32_t ndisp = static_cast<uint32_t>(p.ndisp);
+    const bool dispatching = bid < static_cast<uint32_t>(p.R) * ndisp;
     if constexpr (!kFe) {
-        if (warp == kCopyWarps) {
+        if (warp == 6 && !dispatching) {
             for (uint32_t e = lane; e < kMaxLocalExperts; e += 32) c.dry_count[e] = e < 8u ? 1u : 0u;
             __syncwarp();
             build_schedule(p, c, c.dry_count, bid, G, lane);
@@ -848,15 +1012,20 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if constexpr (kFe) {
         fe_logits_items(p.fe, bid * (kNT / 32) + warp, G * (kNT / 32), lane);
         __syncthreads();
-        uint32_t* fe_arrive = ctrl32 + kCtrlFeArrive / 4;
-        if (tid == 0) red_release_gpu_add(fe_arrive, 1u);
+        // Every SM publishes a word with this launch's number once its logits are written; the selecting SMs wait for
+        // all G words (per-launch values: launches of the other variants in between leave nothing to catch up with).
+        uint32_t* few = ctrl32 + kCtrlFeWords / 4;
+        if (tid == 0) st_release_gpu(few + bid, epoch + 1u);
         if (bid < static_cast<uint32_t>(p.R)) {
-            if (tid == 0) {
+            if (warp == 0) {
                 uint32_t spins = 0;
-                while (ld_acquire_gpu(fe_arrive) < G * (epoch + 1u)) {
+                for (;;) {
+                    bool ok = true;
+                    for (uint32_t g = lane; g < G; g += 32) ok = ok && ld_acquire_gpu(few + g) == epoch + 1u;
+                    if (__all_sync(0xffffffffu, ok)) break;
                     if ((++spins & 0x3Fu) == 0u) {
                         if (cx.aborted()) break;
-                        if (cx.expired()) { cx.fail(kErrWaitFrontend); break; }
+                        if (cx.expired()) { if (lane == 0) cx.fail(kErrWaitFrontend); break; }
                     }
                 }
             }
@@ -867,6 +1036,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 const bool nz = fe_row_nonzero(p.fe.hidden + static_cast<size_t>(t) * p.H, p.H, lane);
                 fe_select_token(p.fe, t, sc, nz, lane);
             }
+            __threadfence();                 // the routing written above is read by other SMs of this launch (combine)
             __syncthreads();
         }
         if (bid == 0 && tid == 0) cx.stamp(kStampFrontend);
@@ -874,12 +1044,11 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
 
     // ---- dispatch: the SMs d, d + R, d + 2R, ... (`ndisp` of them: one at decode sizes, more when a destination gets many
     //      rows) push this rank's rows for rank d; each builds the same row list and takes the rows i = part (mod ndisp)
-    const uint32_t ndisp = static_cast<uint32_t>(p.ndisp);
-    if (bid < static_cast<uint32_t>(p.R) * ndisp && warp < kCopyWarps) {
+    if (dispatching && warp < kCopyWarps) {
         const uint32_t part = udiv_small(bid, p.R), d = bid - part * p.R;
         uint32_t* dlist = reinterpret_cast<uint32_t*>(smem + p.sm_act);
         if (warp == 0) {
-            const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
+            const long long* tk = reinterpret_cast<const long long*>(inp + p.off_topk_idx);
             const uint32_t n = static_cast<uint32_t>(p.T) * p.topk;
             uint32_t cnt = 0;
             #pragma unroll 1
@@ -901,7 +1070,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         const uint32_t flag = epoch + 1u;
         uint8_t* region = p.peer[d] + p.off_rx + static_cast<size_t>(par * p.R + p.rank) * p.rx_region;
         uint8_t* dst_base = region + 32u;
-        const float* tw = reinterpret_cast<const float*>(buf + p.off_topk_w);
+        const float* tw = reinterpret_cast<const float*>(inp + p.off_topk_w);
         // Header line (row count) and the rows' 16 B records (expert, token, slot, weight) leave first: they are all the
         // receiver's scheduler needs, and they do not depend on the token data. Every word is self-validating (flagged),
         // so nothing has to order these stores against the payload that follows.
@@ -928,8 +1097,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         #pragma unroll 1
         for (uint32_t i = part + warp * ndisp; i < cnt; i += kCopyWarps * ndisp) {
             const uint32_t tok = dlist[i] >> 16;
-            const uint8_t* xs_src = buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
-            const uint8_t* sf_src = buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
+            const uint8_t* xs_src = inp + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
+            const uint8_t* sf_src = inp + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
             uint8_t* dst = dst_base + static_cast<size_t>(i) * 2u * p.rx_row_bytes;
             #pragma unroll 1
             for (uint32_t base = lane; base < nchunk; base += 8 * 32) {
@@ -954,25 +1123,34 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     // ---- receive: wait for every source rank's header line, then scan the received rows' records. The first 32 records
     //      of every source are fetched speculatively in the same memory round trip as the headers (thread 32 r + i takes
     //      record i of source r); a record that was not there yet, and any record beyond the first 32, is polled afterwards.
+    //      The rows of this rank's own tokens need no header: the scout lists them from topk_idx (`own_ok`).
     const uint32_t flag_rx = epoch + 1u;
     const uint32_t spec_r = tid >> 5, spec_i = tid & 31u;
-    const bool spec = tid < 32u * static_cast<uint32_t>(p.R) && spec_i < static_cast<uint32_t>(p.cap);
+    const bool spec = tid < 32u * static_cast<uint32_t>(p.R) && spec_i < static_cast<uint32_t>(p.cap) &&
+                      !(own_ok && spec_r == static_cast<uint32_t>(p.rank));
     uint4 spec_a = make_uint4(0u, 0u, 0u, 0u), spec_b = spec_a;
     if (spec) {
         const uint8_t* src = cx.rx_row(spec_r, spec_i) + 2u * (p.rx_row_bytes - 16);
         spec_a = ld_volatile_v4(src); spec_b = ld_volatile_v4(src + 16);
     }
-    if (tid < static_cast<uint32_t>(p.R)) {
+    if constexpr (kScout) {
+        if (warp == kCopyWarps) role_scout(cx, sreg, own_ok, lane, G);
+    }
+    if (tid < static_cast<uint32_t>(p.R) && !(own_ok && tid == static_cast<uint32_t>(p.rank))) {
         uint4 h = make_uint4(0u, 0u, 0u, 0u);
         cx.ll_read(buf + p.off_rx + static_cast<size_t>(par * p.R + tid) * p.rx_region, flag_rx, h, kErrWaitDispatchFlag, tid);
         c.rx_count[tid] = h.x <= static_cast<uint32_t>(p.cap) ? h.x : 0u;
     }
     __syncthreads();
+    if constexpr (kFe) __threadfence();
     uint32_t total = 0;
     {
         uint32_t pre[kMaxRanks + 1];
         #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r) { pre[r] = total; if (r < p.R) total += c.rx_count[r]; }
+        for (int r = 0; r < kMaxRanks; ++r) {
+            pre[r] = total;
+            if (r < p.R) total += (own_ok && r == p.rank) ? c.own_cnt : c.rx_count[r];
+        }
         pre[kMaxRanks] = total;
         if (tid <= static_cast<uint32_t>(p.R)) c.rx_prefix[tid] = tid < static_cast<uint32_t>(p.R) ? pre[tid] : total;
         if (tid == 0) {
@@ -986,7 +1164,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 if (f < kMetaSmemRows) c.rx_meta[f] = RowMeta{0, static_cast<int32_t>(m.y), static_cast<int32_t>(m.z), __uint_as_float(m.w)};
                 atomicAdd(&c.exp_count[e < kMaxLocalExperts ? e : 0], 1u);
             };
-            if (spec && spec_i < c.rx_count[spec_r]) {
+            const uint32_t spec_cnt = spec ? c.rx_count[spec_r] : 0u;
+            if (spec && spec_i < spec_cnt) {
                 uint4 m = ll_data(spec_a, spec_b);
                 if (!ll_valid(spec_a, spec_b, flag_rx))
                     cx.ll_read(cx.rx_row(spec_r, spec_i) + 2u * (p.rx_row_bytes - 16), flag_rx, m, kErrWaitDispatchFlag, spec_r);
@@ -997,9 +1176,15 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 uint32_t r = 0;
                 #pragma unroll
                 for (int q = 1; q < kMaxRanks; ++q) r += (q < p.R && f >= pre[q]) ? 1u : 0u;
-                if (f - pre[r] < 32u) continue;                      // taken by the speculative read above
+                const uint32_t i = f - pre[r];
+                if (own_ok && r == static_cast<uint32_t>(p.rank)) {
+                    const RowMeta om = c.own_meta[i];
+                    take(f, make_uint4(c.own_e[i], static_cast<uint32_t>(om.token), static_cast<uint32_t>(om.slot), __float_as_uint(om.weight)));
+                    continue;
+                }
+                if (i < 32u) continue;                               // taken by the speculative read above
                 uint4 m = make_uint4(0u, 0u, 0u, 0u);
-                cx.ll_read(cx.rx_row(r, f - pre[r]) + 2u * (p.rx_row_bytes - 16), flag_rx, m, kErrWaitDispatchFlag, r);
+                cx.ll_read(cx.rx_row(r, i) + 2u * (p.rx_row_bytes - 16), flag_rx, m, kErrWaitDispatchFlag, r);
                 take(f, m);
             }
         }
@@ -1020,7 +1205,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
     __syncthreads();
     if (bid == 0 && tid == 0) cx.stamp(kStampScheduled);
-    if (tid == 0) atomicMax(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps) + kStampLastScheduled, globaltimer_ns());
+    if (tid == 0) cx.stamp_max(kStampLastScheduled, globaltimer_ns());
     if (bid == 0 && tid < static_cast<uint32_t>(p.e_local) && p.stats != nullptr && !cx.aborted())
         p.stats[tid] += static_cast<int>(c.exp_count[tid]);
 
@@ -1032,38 +1217,39 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         else if (warp < 8) role_epilogue<kVec, kUmma, kA8>(cx, tid - 128);
         else { if constexpr (kA8) role_expander(cx, tid - kThreads); }
     }
-    __syncthreads();
-    if (tid == 0) {
+    const bool early = (p.knobs & kKnobEarlyCombine) != 0u;
+    if (!early) __syncthreads();
+    if (tid == 128) {                                   // first epilogue thread: this SM's tasks are finished
         if (bid == 0) cx.stamp(kStampTasksDone);
-        atomicMax(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps) + kStampLastTasksDone, globaltimer_ns());
+        cx.stamp_max(kStampLastTasksDone, globaltimer_ns());
     }
 
     // ---- combine. No grid-wide or cross-rank barrier precedes it: the expert outputs arrive as flagged words and every
-    //      thread polls exactly the words it sums. First, which routes of this thread's first (token, 16 B chunk) item are live:
-    const uint32_t chunks_per_row = p.H / 8, nitems = static_cast<uint32_t>(p.T) * chunks_per_row;
-    const long long* tk = reinterpret_cast<const long long*>(buf + p.off_topk_idx);
-    const uint32_t first_item = bid + tid * G;
-    uint32_t first_mask = 0u;
-    if (first_item < nitems) {
-        const uint32_t tok = udiv_small(first_item, chunks_per_row);
-        for (int sl = 0; sl < p.topk; ++sl) first_mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
-    }
-
+    //      thread polls exactly the words it sums. Item = (token, 16 B chunk of the row); the items b, b + G, ... belong
+    //      to SM b (a small batch uses the whole GPU) and its threads take them one by one. A warp comes here as soon as
+    //      its role has ended, so the first polls (and the first execution of this code) overlap the SM's last tasks.
     if (!cx.aborted()) {
+        const uint32_t chunks_per_row = p.H / 8, nitems = static_cast<uint32_t>(p.T) * chunks_per_row;
+        const long long* tk = reinterpret_cast<const long long*>(inp + p.off_topk_idx);
         const uint32_t flag = epoch + 1u;
+        const size_t sstride = static_cast<size_t>(p.H) * 4u;
         bool bad = false;
-        // item idx = (token, 16 B chunk); consecutive items go to different SMs so that a small batch uses the whole GPU
+        uint32_t static_k = tid;
         #pragma unroll 1
-        for (uint32_t idx = first_item; idx < nitems && !bad; idx += G * kNT) {
+        while (!bad) {
+            uint32_t k;
+            if (early) k = atomicAdd(&c.comb_next, 1u); else { k = static_k; static_k += kNT; }
+            const uint32_t idx = bid + k * G;
+            if (k >= nitems || idx >= nitems) break;
             const uint32_t tok = udiv_small(idx, chunks_per_row), ch = idx - tok * chunks_per_row;
-            uint32_t mask = first_mask;
-            if (idx != first_item) {
-                mask = 0u;
-                for (int sl = 0; sl < p.topk; ++sl) mask |= (tk[tok * p.topk + sl] >= 0 ? 1u : 0u) << sl;
+            uint32_t mask = 0u;
+            for (int sl = 0; sl < p.topk; ++sl) {
+                long long ex;
+                if constexpr (kFe) ex = static_cast<long long>(ld_volatile_u64(tk + tok * p.topk + sl)); else ex = tk[tok * p.topk + sl];
+                mask |= (ex >= 0 ? 1u : 0u) << sl;
             }
             float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
             const uint8_t* cbase = buf + p.off_comb + (static_cast<size_t>(tok) * p.topk * p.H) * 4u + ch * 32u;
-            const size_t sstride = static_cast<size_t>(p.H) * 4u;
             #pragma unroll 1
             for (int s0 = 0; s0 < p.topk && !bad; s0 += 8) {
                 // eight routes' words in flight, re-read until each live route carries this launch's flag; a masked route
@@ -1100,22 +1286,30 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             uint4 o;
             uint32_t* ow = &o.x;
             #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * k]));
-                const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * k + 1]));
-                ow[k] = lo | (hi << 16);
+            for (int q = 0; q < 4; ++q) {
+                const uint32_t lo = __bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * q]));
+                const uint32_t hi = __bfloat16_as_ushort(__float2bfloat16_rn(acc[2 * q + 1]));
+                ow[q] = lo | (hi << 16);
             }
             *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.y) + (static_cast<size_t>(tok) * p.H) * 2u + ch * 16u) = o;
         }
     }
 
-    // ---- exit: an aborted SM lets its bulk copies in flight land before the shared memory goes away
-    if (cx.aborted()) { for (int i = 0; i < 64; ++i) __nanosleep(1000); }
+    // ---- exit: an aborted SM lets the loader's copies in flight land (a bounded wait on the barriers of the stages it
+    //      issued last) before the shared memory goes away
+    if (warp == 0 && cx.aborted()) {
+        const uint32_t issued = *reinterpret_cast<volatile uint32_t*>(&c.issued), nst = static_cast<uint32_t>(p.nstage);
+        #pragma unroll 1
+        for (uint32_t k = issued > nst ? issued - nst : 0u; k < issued; ++k) {
+            const uint32_t s = k % nst, ph = (k / nst) & 1u;
+            for (uint32_t spin = 0; spin < 400000u && !mbar_try_wait(&c.full[s], ph); ++spin) { }
+        }
+    }
     __syncthreads();
     if (warp == 1) { tc_fence_after(); tmem_dealloc(c.tmem_base, kTmemCols); }
     if (tid == 0) {
         if (bid == 0) cx.stamp(kStampExit);
-        atomicMax(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps) + kStampLastExit, globaltimer_ns());
+        cx.stamp_max(kStampLastExit, globaltimer_ns());
     }
 }
 

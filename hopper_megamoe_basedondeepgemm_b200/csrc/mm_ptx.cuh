@@ -57,6 +57,10 @@ __device__ __forceinline__ void bulk_g2s(void* smem_dst, const void* gsrc, uint3
 __device__ __forceinline__ void prefetch_l2_line(const void* p) {
     asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
 }
+// global -> L2 only (no shared-memory destination, no completion to wait for). Address 16 B aligned, size % 16 == 0.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
+}
 // generic-proxy shared-memory writes -> visible to the async proxy (UMMA / UTCCP / bulk copies)
 __device__ __forceinline__ void fence_proxy_async_smem() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -159,6 +163,14 @@ __device__ __forceinline__ void umma_mxf8f6f4(uint32_t d_tmem, uint64_t adesc, u
 __device__ __forceinline__ uint32_t ld_acquire_gpu(const uint32_t* p) {
     uint32_t v;
     asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_gpu(uint32_t* p, uint32_t v) {
+    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_volatile_u64(const void* p) {
+    unsigned long long v;
+    asm volatile("ld.volatile.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
     return v;
 }
 __device__ __forceinline__ void red_release_gpu_add(uint32_t* p, uint32_t v) {

@@ -5,6 +5,7 @@ sm_100a library behind the C ABI of `include/megamoe_b200.h`. PyTorch supplies d
 the symmetric-memory rendezvous only.
 """
 import ctypes
+from types import SimpleNamespace
 from typing import Optional, Tuple
 
 import torch
@@ -49,15 +50,16 @@ class SymmBuffer:
         self.layout = _lib.MMLayout()
         _lib.check(lib.mm_get_layout(ctypes.byref(self.cfg), ctypes.byref(self.layout)), 'get_symm_buffer_for_mega_moe')
         nbytes = int(self.layout.total_bytes)
-        self.handle = None
         if self.num_ranks > 1:
             import torch.distributed._symmetric_memory as symm_mem
             self.buffer = symm_mem.empty(nbytes, dtype=torch.int8, device='cuda')
             self.handle = symm_mem.rendezvous(self.buffer, group=group)
             self.buffer_ptrs = [int(p) for p in self.handle.buffer_ptrs]
         else:
+            # one rank: plain device memory; `handle.buffer_ptrs` exists all the same (the reference's callers read it)
             self.buffer = torch.empty(nbytes, dtype=torch.int8, device='cuda')
             self.buffer_ptrs = [self.buffer.data_ptr()]
+            self.handle = SimpleNamespace(buffer_ptrs=list(self.buffer_ptrs), rank=0, world_size=1)
         self.buffer.zero_()
         if self.num_ranks > 1:
             self.group.barrier()
@@ -116,6 +118,34 @@ class SymmBuffer:
         words = self.l2_acts_sf.view(torch.int32).view(rows, -1, 2)[..., 0].contiguous().view(torch.uint8).view(rows, -1, 4)
         per_tile = 64 // int(self.layout.sf_vec)
         return words[..., :per_tile].contiguous().view(rows, -1)
+
+    def received_records(self):
+        """The routed rows this rank received in its latest launch, as the kernel recorded them in the receive pool:
+        per source rank a list of (local expert, token, slot, top-k weight) in arrival (= row) order. The canonical
+        slot map follows from it: the rows of an expert, by (source rank, token, slot). Synchronises the stream."""
+        st, words = self.device_status()
+        launches = int(words[1])
+        if launches == 0:
+            return [[] for _ in range(self.num_ranks)]
+        flag, parity = launches, (launches - 1) & 1
+        L = self.layout
+        row2, out = 2 * int(L.rx_row_bytes), []
+        pool = self.l1_acts[parity].cpu()
+        for src in range(self.num_ranks):
+            region = pool[src]
+            head = region[:32].view(torch.int32)
+            if int(head[1]) != flag:
+                out.append(None)                       # that source's header line never arrived in this launch
+                continue
+            recs = []
+            for i in range(int(head[0])):
+                w = region[32 + i * row2 + row2 - 32:32 + (i + 1) * row2].view(torch.int32)
+                if any(int(w[k]) != flag for k in (1, 3, 5, 7)):
+                    recs.append(None)
+                    continue
+                recs.append((int(w[0]) & 0xFF, int(w[2]), int(w[4]), float(w[6:7].view(torch.float32))))
+            out.append(recs)
+        return out
 
     def reset(self):
         """Zero the control block and the flags (after an aborted launch). All ranks call it together."""
@@ -181,8 +211,19 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
     return one(l1_weights, True), one(l2_weights, False)
 
 
+def _input_region_ptr(sym_buffer: 'SymmBuffer', host_inputs):
+    """Address of a pinned host mirror of the buffer's input region (from `SymmBuffer.host_inputs()`), or None."""
+    if host_inputs is None:
+        return None
+    L = sym_buffer.layout
+    if (host_inputs.device.type != 'cpu' or not host_inputs.is_pinned() or not host_inputs.is_contiguous()
+            or host_inputs.numel() * host_inputs.element_size() != int(L.off_rx - L.off_x)):
+        raise RuntimeError('host_inputs must be the pinned mirror returned by SymmBuffer.host_inputs()')
+    return host_inputs.data_ptr()
+
+
 def _launch(y, l1_weights, l2_weights, sym_buffer: SymmBuffer, stats, recipe, activation, activation_clamp, fast_math,
-            engine='umma', global_scales=(1.0, 1.0, 1.0, 1.0), timeout_ms=0.0):
+            engine='umma', global_scales=(1.0, 1.0, 1.0, 1.0), timeout_ms=0.0, host_inputs=None):
     lib = _lib.load()
     if activation != 'swiglu':
         raise RuntimeError('only the swiglu activation is supported')
@@ -190,7 +231,8 @@ def _launch(y, l1_weights, l2_weights, sym_buffer: SymmBuffer, stats, recipe, ac
     vec = b.act_sf_vec_size or 32        # FP8 tokens carry one UE8M0 scale per 32 elements, like the MXFP4 weights
     if tuple(recipe) != (1, 1, vec):
         raise RuntimeError(f'recipe {recipe} does not match the buffer format {b.act_format}')
-    if y.dtype != torch.bfloat16 or y.dim() != 2 or y.size(1) != b.hidden or not y.is_contiguous():
+    if y.dtype != torch.bfloat16 or y.dim() != 2 or y.size(1) != b.hidden or not y.is_contiguous() or \
+            not (y.is_cuda or y.is_pinned()):
         raise RuntimeError('y must be a contiguous bf16 [num_tokens, hidden] tensor')
     if y.size(0) > b.num_max_tokens_per_rank:
         raise RuntimeError('more tokens than the buffer was created for')
@@ -208,7 +250,7 @@ def _launch(y, l1_weights, l2_weights, sym_buffer: SymmBuffer, stats, recipe, ac
         b.buffer.data_ptr(), b._peer_array, w1.data_ptr(), w2.data_ptr(), y.data_ptr() if y.numel() else None,
         y.size(0), _lib.ENGINE[engine], stats.data_ptr() if stats is not None else None,
         float(activation_clamp) if activation_clamp is not None else -1.0, int(bool(fast_math)),
-        *[float(g) for g in global_scales], float(timeout_ms), None, 0, 0, None)
+        *[float(g) for g in global_scales], float(timeout_ms), _input_region_ptr(b, host_inputs))
     _lib.check(lib.mm_mega_moe_launch(ctypes.byref(b.cfg), ctypes.byref(args), torch.cuda.current_stream().cuda_stream),
                'mega_moe launch')
 
@@ -218,13 +260,17 @@ def fp4_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBu
                      recipe: Optional[Tuple[int, int, int]] = None, activation: str = 'swiglu',
                      activation_clamp: Optional[float] = None, fast_math: bool = True, *,
                      x_global_scale: float = 1.0, l1_global_scale: float = 1.0, l2_global_scale: float = 1.0,
-                     mid_global_scale: float = 1.0, engine: str = 'umma', timeout_ms: float = 0.0):
+                     mid_global_scale: float = 1.0, engine: str = 'umma', timeout_ms: float = 0.0,
+                     host_inputs: Optional[torch.Tensor] = None):
     """W4A4 MegaMoE, packed E2M1 activations and weights (`sm100_b200/mega___init__.py:244-274`).
 
     The caller has written `x`, `x_sf`, `topk_idx`, `topk_weights[:y.size(0)]` into the buffer views; the launch is
     asynchronous on the current CUDA stream and every rank of the group must make the same call. The keyword-only
     arguments are additions: NVFP4 per-tensor scales (default 1.0 = the reference's behaviour), `engine='check'`
-    (the same kernel with CUDA-core dot products, used as an on-device cross-check) and the device wait budget.
+    (the same kernel with CUDA-core dot products, used as an on-device cross-check), the device wait budget, and
+    `host_inputs`: the pinned mirror of `SymmBuffer.host_inputs()`; when given, the kernel reads this call's inputs
+    straight from that host memory (no host-to-device copy is needed before the launch; `y` may likewise be a pinned
+    host tensor).
     """
     assert sym_buffer.act_format in ('mxfp4', 'nvfp4'), 'buffer must be created with act_format mxfp4/nvfp4'
     if recipe is None:
@@ -232,14 +278,14 @@ def fp4_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBu
     assert recipe[2] == sym_buffer.act_sf_vec_size
     _launch(y, l1_weights, l2_weights, sym_buffer, cumulative_local_expert_recv_stats, recipe, activation,
             activation_clamp, fast_math, engine, (x_global_scale, l1_global_scale, l2_global_scale, mid_global_scale),
-            timeout_ms)
+            timeout_ms, host_inputs)
 
 
 def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBuffer,
                      cumulative_local_expert_recv_stats: Optional[torch.Tensor] = None,
                      recipe: Tuple[int, int, int] = (1, 1, 32), activation: str = 'swiglu',
                      activation_clamp: Optional[float] = None, fast_math: bool = True, *,
-                     engine: str = 'umma', timeout_ms: float = 0.0):
+                     engine: str = 'umma', timeout_ms: float = 0.0, host_inputs: Optional[torch.Tensor] = None):
     """W-MXFP4 x A-FP8 MegaMoE (`sm100_b200/mega___init__.py:221-241`).
 
     Tokens are E4M3 with one UE8M0 scale per 32 elements, the intermediate is requantised the same way, weights are
@@ -249,7 +295,7 @@ def fp8_fp4_mega_moe(y: torch.Tensor, l1_weights, l2_weights, sym_buffer: SymmBu
     """
     assert sym_buffer.act_format == 'fp8', 'buffer must be created with act_format fp8'
     _launch(y, l1_weights, l2_weights, sym_buffer, cumulative_local_expert_recv_stats, recipe, activation,
-            activation_clamp, fast_math, engine, (1.0, 1.0, 1.0, 1.0), timeout_ms)
+            activation_clamp, fast_math, engine, (1.0, 1.0, 1.0, 1.0), timeout_ms, host_inputs)
 
 
 def mega_moe_from_hidden(y: torch.Tensor, hidden: torch.Tensor, router_weight: torch.Tensor, l1_weights, l2_weights,
@@ -278,12 +324,20 @@ def mega_moe_from_hidden(y: torch.Tensor, hidden: torch.Tensor, router_weight: t
         y.size(0), _lib.ENGINE[engine], stats.data_ptr() if stats is not None else None,
         float(activation_clamp) if activation_clamp is not None else -1.0, int(bool(fast_math)),
         float(x_global_scale), float(l1_global_scale), float(l2_global_scale), float(mid_global_scale),
-        float(timeout_ms), None, 0, 0, None)
+        float(timeout_ms), None)
     fe = _lib.MMFrontendArgs(hidden.data_ptr(), router_weight.data_ptr(),
                              expert_bias.data_ptr() if expert_bias is not None else None,
                              hidden.size(0), score_mode, workspace.data_ptr(), float(x_global_scale))
     _lib.check(lib.mm_mega_moe_from_hidden_launch(ctypes.byref(b.cfg), ctypes.byref(args), ctypes.byref(fe),
                                                   torch.cuda.current_stream().cuda_stream), 'mega_moe_from_hidden')
+
+
+def set_tuning(**kwargs) -> None:
+    """Development knobs of the kernel (`mm_set_tuning`): knobs=<bit mask>, stages=<ring depth>,
+    prefetch_w1_experts=<n>, prefetch_w2_experts=<n>. Process-wide; every rank must use the same values."""
+    lib = _lib.load()
+    for k, v in kwargs.items():
+        _lib.check(lib.mm_set_tuning(_lib.TUNE[k], int(v)), f'set_tuning({k})')
 
 
 def fe_workspace_bytes(sym_buffer: SymmBuffer) -> int:

@@ -32,8 +32,10 @@ def balanced_routing(num_tokens: int, rank: int, num_ranks: int, num_experts: in
     return idx, w
 
 
-def make_layer_weights(e_local: int, hidden: int, inter: int, fmt: str, seed: int, std: float = 0.02, device='cuda'):
-    """Random expert weights -> ((l1 stream, shape), (l2 stream, shape), (l1 global scale, l2 global scale))."""
+def make_layer_weights(e_local: int, hidden: int, inter: int, fmt: str, seed: int, std: float = 0.02, device='cuda',
+                       keep_untransformed: bool = False):
+    """Random expert weights -> ((l1 stream, shape), (l2 stream, shape), (l1 global scale, l2 global scale)); with
+    `keep_untransformed` also the operator-format inputs of the transform [(w1, w1_sf), (w2, w2_sf)] (for checkers)."""
     g = torch.Generator(device=device).manual_seed(seed)
     out, scales = [], []
     for n, k in ((2 * inter, hidden), (hidden, inter)):
@@ -43,6 +45,8 @@ def make_layer_weights(e_local: int, hidden: int, inter: int, fmt: str, seed: in
         scales.append(gs)
         del w
     l1, l2 = transform_weights_for_mega_moe(out[0], out[1])
+    if keep_untransformed:
+        return l1, l2, tuple(scales), out
     return l1, l2, tuple(scales)
 
 

@@ -43,8 +43,7 @@ typedef struct mm_config {
  * Replaces `get_symm_buffer_size_for_mega_moe` + its slicing lambda (sm100_b200/apis_mega.hpp:23-171). */
 typedef struct mm_layout {
     int64_t total_bytes;
-    int64_t off_ctrl;          /* per-SM epochs, device status words, local counters, phase stamps */
-    int64_t off_flags;         /* reserved block (earlier layouts kept arrival flags here) */
+    int64_t off_ctrl;          /* per-SM launch counters, device status words, phase stamps, per-SM time records */
     int64_t off_x;             /* [T_max][x_row_bytes]   quantised tokens (caller or frontend writes) */
     int64_t off_x_sf;          /* [T_max][x_sf_row_bytes] one scale byte per `vec` elements, K-major */
     int64_t off_topk_idx;      /* [T_max][topk] int64, -1 = masked slot */
@@ -62,7 +61,7 @@ typedef struct mm_layout {
     int64_t mid_rows, mid_row_bytes, mid_sf_row_bytes;
     int64_t cnt_per_phase;
     int32_t sf_vec;            /* elements per scale byte of the activation format */
-    int32_t reserved;
+    int32_t ctrl_bytes;        /* bytes of the control block at off_ctrl */
     int64_t rx_region_bytes;   /* bytes of one (parity, source) region of the receive pool */
 } mm_layout_t;
 
@@ -90,9 +89,9 @@ typedef struct mm_launch_args {
     int32_t fast_math;               /* 1: __expf + approximate reciprocal in the SwiGLU */
     float x_global_scale, l1_global_scale, l2_global_scale, mid_global_scale;   /* NVFP4 per-tensor scales; 1.0 otherwise */
     float timeout_ms;                /* budget of every device-side wait; <= 0: 2000 ms */
-    void* reserved_ptr0;             /* reserved, NULL */
-    int32_t reserved0, reserved1;    /* reserved, 0 */
-    void* reserved_ptr1;             /* reserved, NULL */
+    const void* input_region;        /* optional: where the kernel reads this call's x / x_sf / topk_idx / topk_weights from,
+                                        laid out like the buffer's bytes [off_x, off_rx). NULL: the buffer's own views. A
+                                        pinned (device-mapped) host mirror here lets one launch replace copy + launch. */
 } mm_launch_args_t;
 
 /* Router frontend: bf16 router GEMM, top-k selection, token quantisation into the buffer views.
@@ -129,10 +128,22 @@ int mm_reset(const mm_config_t* cfg, void* buffer, void* stream);
  * detail << 16), [1] launches seen, [2..] diagnostics. The reference traps instead (sm100_b200/layout_mega_moe.cuh:13-19). */
 int mm_read_device_status(const mm_config_t* cfg, const void* buffer, uint32_t out_words[16], void* stream);
 /* Synchronises `stream`, then copies the 32 phase stamps (globaltimer ns) of the last launch. Slots, SM 0 unless
- * noted: 0 entry, 1 dispatched, 2 header lines of all ranks seen, 3 scheduled, 4 tasks done, 7 exit, 8 last SM out,
- * 9 fused frontend done, 10 last SM's tasks done, 11 last SM scheduled (8, 10, 11: running maxima over the SMs).
+ * noted: 0 first instruction, 1 dispatched, 2 header lines of all ranks seen, 3 scheduled, 4 tasks done, 5 prologue
+ * done, 7 exit, 8 last SM out, 9 fused frontend done, 10 last SM's tasks done, 11 last SM scheduled, 12 first
+ * instruction of the earliest SM, 13 first weight request (L2 prefetch or shared-memory copy) of any SM, 14 last
+ * streamed weight unit found in shared memory by any SM (8, 10, 11, 14: maxima over the SMs; 12, 13: minima).
  * Replaces the `DG_SM100_PHASE_STAMPS_PTR` facility (sm100_b200/sm100_fp4_fp4_mega_moe.cuh:97-128). */
 int mm_read_phase_stamps(const mm_config_t* cfg, const void* buffer, uint64_t out_stamps[32], void* stream);
+/* Development knobs, process-wide, read at every launch. The reference reads its own from DG_SM100_* environment
+ * variables (sm100_b200/sm100_fp4_fp4_mega_moe.hpp:215-248). MM_TUNE_KNOBS is a bit mask: 1 the spare warp asks for a
+ * live expert's weights (L2 prefetch) as soon as it learns of the expert, 2 every SM lists the rows of this rank's own
+ * tokens from topk_idx instead of waiting for the own-rank header line, 4 warps start the combine when their role ends. */
+enum mm_tuning_key { MM_TUNE_KNOBS = 0, MM_TUNE_STAGES = 1 /* ring depth, 0 = default */,
+                     MM_TUNE_PREFETCH_W1_EXPERTS = 2, MM_TUNE_PREFETCH_W2_EXPERTS = 3 /* experts prefetched per launch at most */,
+                     MM_TUNE_COUNT = 4 };
+int mm_set_tuning(int32_t key, int32_t value);
+int32_t mm_get_tuning(int32_t key);
+
 /* Bytes of the library's built-in working memory (one array per GPU, resident from library load to process exit). */
 #define MM_STATIC_SCRATCH_BYTES (16ll * 1024 * 1024)
 
@@ -161,7 +172,8 @@ typedef struct mm_static_args {
  * The call issues memsets, device-to-device copies of the inputs and the kernel on `stream`, and calls no cudaMalloc,
  * cudaFree or other allocating routine. Limits: num_ranks must be 1; a configuration whose mm_layout.total_bytes
  * exceeds MM_STATIC_SCRATCH_BYTES is refused with MM_ERR_UNSUPPORTED (mm_last_cuda_error() says by how much).
- * The first call on each device looks up the array's device address; make that call outside any stream capture.
+ * The first call on each device looks up the array's device address, and the first launch of a format on a device may
+ * load the kernel's module and sets its shared-memory attribute; make that call outside any stream capture.
  * All calls on a GPU share the one array and it keeps the previous call's bytes (the call clears the parts that must
  * start from zero), so two calls that overlap on the GPU, e.g. on different streams, race: serialise them. */
 int mm_mega_moe_launch_static_scratch(const mm_config_t* cfg, const mm_static_args_t* args, void* stream);

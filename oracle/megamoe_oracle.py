@@ -321,11 +321,70 @@ def swiglu_weighted(h: torch.Tensor, inter: int, clamp: Optional[float], w: torc
     return gate * torch.sigmoid(gate) * up * w[:, None]
 
 
+def expert_forward(xs: torch.Tensor, ws: torch.Tensor, w1_q: torch.Tensor, w1_sf: torch.Tensor, w2_q: torch.Tensor,
+                   w2_sf: torch.Tensor, act_format: str, clamp: Optional[float], rounding: str = 'rne',
+                   w1_global_scale: float = 1.0, w2_global_scale: float = 1.0, mid_global_scale: float = 1.0,
+                   dequantised: Optional[Tuple[torch.Tensor, torch.Tensor]] = None):
+    """One expert on its routed rows (`sm100_b200/test_mega_moe.py:447-476`): dequantised `xs` [n, H] and top-k
+    weights `ws` [n] -> (fp32 outputs [n, H], requantised intermediate, its scale bytes). `dequantised` = the
+    expert's (W1, W2) already as fp32 (global scales applied) skips the weight dequantisation."""
+    vec_a = SF_VEC[act_format]
+    vec_w = 32 if act_format == 'fp8' else vec_a
+    inter = w2_q.shape[-1] * 2
+    if dequantised is not None:
+        w1, w2 = dequantised
+    else:
+        w1 = dequant_fp4_rows(w1_q, w1_sf, vec_w) * w1_global_scale
+        w2 = dequant_fp4_rows(w2_q, w2_sf, vec_w) * w2_global_scale
+    act = swiglu_weighted(xs @ w1.t(), inter, clamp, ws)
+    if act_format == 'fp8':
+        q, sf, sfb = quant_fp8_rows(act, amax_floor=1e-30)
+        mid = dequant_fp8_rows(q, sf)
+    else:
+        q, sf, sfb = quant_fp4_rows(act, act_format, rounding=rounding, sf_rule='div', global_scale=mid_global_scale)
+        mid = dequant_fp4_rows(q, sf, vec_a) * mid_global_scale
+    return mid @ w2.t(), q, sfb
+
+
+def moe_rank_routes(inputs: Sequence[RankInput], local_experts: Dict[int, Tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]],
+                    rank: int, act_format: str, num_experts: int, clamp: Optional[float] = 10.0, rounding: str = 'rne',
+                    x_global_scale: float = 1.0, w1_global_scale: float = 1.0, w2_global_scale: float = 1.0,
+                    mid_global_scale: float = 1.0):
+    """One rank's share of `moe_layer_reference` for a multi-process check (`sm100_b200/test_mega_moe.py:438-486`:
+    every rank evaluates its own experts on the gathered tokens, then the partial results are all-reduced).
+
+    `inputs`: all ranks' inputs; `local_experts`: {local expert id: (w1_q, w1_sf, w2_q, w2_sf)} for (at least) the
+    experts of `rank` that receive rows. Returns ({(src rank, token, slot): bf16-rounded fp32 output row [H]},
+    per-expert counts int32 [E_local], the canonical slot map of this rank)."""
+    num_ranks = len(inputs)
+    e_local = num_experts // num_ranks
+    vec_a = SF_VEC[act_format]
+    if act_format == 'fp8':
+        x_dq = [dequant_fp8_rows(i.x_q, i.x_sf) for i in inputs]
+    else:
+        x_dq = [dequant_fp4_rows(i.x_q, i.x_sf, vec_a) * x_global_scale for i in inputs]
+    smap = canonical_slot_map([i.topk_idx for i in inputs], num_experts)[rank]
+    counts = torch.tensor([len(smap[e]) for e in range(e_local)], dtype=torch.int32)
+    routes = {}
+    for e in range(e_local):
+        rows = smap[e]
+        if not rows:
+            continue
+        xs = torch.stack([x_dq[src][t] for (src, t, s) in rows])
+        ws = torch.stack([inputs[src].topk_weights[t, s] for (src, t, s) in rows]).float()
+        out, _, _ = expert_forward(xs, ws, *local_experts[e], act_format, clamp, rounding, w1_global_scale,
+                                   w2_global_scale, mid_global_scale)
+        for n, key in enumerate(rows):
+            routes[key] = out[n].to(torch.bfloat16).float()
+    return routes, counts, smap
+
+
 def moe_layer_reference(inputs: Sequence[RankInput], weights: Sequence[RankWeights], act_format: str,
                         num_experts: int, clamp: Optional[float] = 10.0, faithful: bool = True,
                         rounding: str = 'rne', keep_mid: bool = False,
                         x_global_scale: float = 1.0, w1_global_scale: float = 1.0,
-                        w2_global_scale: float = 1.0, mid_global_scale: float = 1.0) -> LayerResult:
+                        w2_global_scale: float = 1.0, mid_global_scale: float = 1.0,
+                        dequantised: Optional[Dict[Tuple[int, int], Tuple[torch.Tensor, torch.Tensor]]] = None) -> LayerResult:
     """All ranks of the EP layer in one process (`sm100_b200/test_mega_moe.py:411-499`).
 
     Dequantised tokens and weights; per local expert an fp32 `X @ W1^T`, the
@@ -333,7 +392,9 @@ def moe_layer_reference(inputs: Sequence[RankInput], weights: Sequence[RankWeigh
     (`:459-460`), requantisation with the kernel's rule (`:425-437`), fp32
     `@ W2^T`, accumulation per token. The global scales (NVFP4 extension) multiply
     the dequantised operands; `mid_global_scale` divides the intermediate before
-    its requantisation and multiplies it back after.
+    its requantisation and multiplies it back after. `dequantised` optionally maps
+    (rank, local expert) to that expert's (W1, W2) already dequantised to fp32
+    (the reference dequantises all weights once, before its loop, `:411-420`).
     """
     num_ranks = len(inputs)
     e_local = num_experts // num_ranks
@@ -358,17 +419,10 @@ def moe_layer_reference(inputs: Sequence[RankInput], weights: Sequence[RankWeigh
                 continue
             xs = torch.stack([x_dq[src][t] for (src, t, s) in rows])
             ws = torch.stack([inputs[src].topk_weights[t, s] for (src, t, s) in rows]).float()
-            w1 = dequant_fp4_rows(weights[r].w1_q[e], weights[r].w1_sf[e], vec_w) * w1_global_scale
-            w2 = dequant_fp4_rows(weights[r].w2_q[e], weights[r].w2_sf[e], vec_w) * w2_global_scale
-            act = swiglu_weighted(xs @ w1.t(), inter, clamp, ws)
-            if act_format == 'fp8':
-                q, sf, sfb = quant_fp8_rows(act, amax_floor=1e-30)
-                mid = dequant_fp8_rows(q, sf)
-            else:
-                q, sf, sfb = quant_fp4_rows(act, act_format, rounding=rounding, sf_rule='div',
-                                            global_scale=mid_global_scale)
-                mid = dequant_fp4_rows(q, sf, vec_a) * mid_global_scale
-            out = mid @ w2.t()
+            out, q, sfb = expert_forward(xs, ws, weights[r].w1_q[e], weights[r].w1_sf[e], weights[r].w2_q[e],
+                                         weights[r].w2_sf[e], act_format, clamp, rounding, w1_global_scale,
+                                         w2_global_scale, mid_global_scale,
+                                         dequantised.get((r, e)) if dequantised is not None else None)
             if keep_mid:
                 mids[e], midsf[e] = q, sfb
                 routes[e] = out.to(torch.bfloat16)

@@ -108,7 +108,21 @@ def main():
             if not (err <= 3e-3 and cos >= 0.9999):
                 print(f'rank {rank} it {it}: rel_rmse {err:.4e} cos {cos:.6f}', flush=True)
                 ok = False
-        # canonical slot order: intermediate rows of each local expert in (source rank, token, slot) order
+        # slot map: the records kept in the receive pool, grouped per expert in row order, equal the canonical
+        # (source rank, token, slot) order exactly
+        recs = buf.received_records()
+        got_map = [[] for _ in range(e_local)]
+        if any(r is None or any(v is None for v in r) for r in recs):
+            print(f'rank {rank} it {it}: incomplete records in the receive pool', flush=True)
+            ok = False
+        else:
+            for src, rows in enumerate(recs):
+                for (e, t, s, _) in rows:
+                    got_map[e].append((src, t, s))
+            if got_map != [list(v) for v in ref.slot_map[rank]]:
+                print(f'rank {rank} it {it}: slot map differs from the canonical order', flush=True)
+                ok = False
+        # and the intermediate rows sit in that order
         vec = O.SF_VEC[fmt]
         mid, mid_sf = buf.l2_acts_payload().cpu(), buf.l2_acts_sf_payload().cpu()
         base = 0
@@ -118,7 +132,7 @@ def main():
             deq = O.dequant_fp8_rows if fmt == 'fp8' else (lambda q, sf: O.dequant_fp4_rows(q, sf, vec))
             got = deq(mid[base:base + cnt], O.sf_bytes_to_float(mid_sf[base:base + cnt, :inter // vec], fmt))
             want = deq(ref.mid_q[rank][e], O.sf_bytes_to_float(ref.mid_sf[rank][e], fmt))
-            if O.rel_rmse(got, want) > 0.05:
+            if any(O.rel_rmse(got[n], want[n]) > 0.05 for n in range(cnt)):
                 print(f'rank {rank} it {it}: expert {e} intermediate rows differ ({O.rel_rmse(got, want):.3f})', flush=True)
                 ok = False
             base += (cnt + 15) // 16 * 16

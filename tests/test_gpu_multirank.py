@@ -45,3 +45,24 @@ def test_all_ranks_of_the_node():
     if n < 4:
         pytest.skip('needs at least four GPUs')
     _run(8 if n >= 8 else 4, 'mxfp4')
+
+
+@pytest.mark.parametrize('fmt', ['mxfp4', 'nvfp4', 'fp8'])
+def test_full_shape_parity_on_all_gpus(fmt):
+    """The benchmark's own configuration (48 experts per rank, H=3072, I=1280, top-8, forced-balanced routing) on every
+    GPU of the node: the benchmark checks its output, counts and slot maps against the oracle and reports `parity`."""
+    import json
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip('needs two GPUs')
+    n = 8 if n >= 8 else (4 if n >= 4 else 2)
+    cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={n}', '--master-addr', '127.0.0.1',
+           '--master-port', '29533', os.path.join(ROOT, 'bench.py'), '--gpus', str(n), '--steps', '5', '--warmup', '3',
+           '--format', fmt, '--no-cpu-baseline'] + (['--no-sweep'] if fmt != 'mxfp4' else [])
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith('{')]
+    assert res.returncode == 0 and lines, res.stdout[-3000:] + res.stderr[-3000:]
+    out = json.loads(lines[-1])
+    assert out['parity']['ok'] and out['parity']['slot_map_exact'] and out['parity']['counts_exact'], out['parity']
+    if 'm_sweep' in out:
+        assert all(v['parity_ok'] for v in out['m_sweep'].values()), out['m_sweep']

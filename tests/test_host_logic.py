@@ -33,7 +33,7 @@ def _layout(**kw):
 def test_layout_regions_are_ordered_and_sized():
     st, L = _layout()
     assert st == 0
-    offs = [L.off_ctrl, L.off_flags, L.off_x, L.off_x_sf, L.off_topk_idx, L.off_topk_weights, L.off_rx, L.off_mid,
+    offs = [L.off_ctrl, L.off_x, L.off_x_sf, L.off_topk_idx, L.off_topk_weights, L.off_rx, L.off_mid,
             L.off_mid_sf, L.off_comb, L.off_red, L.off_cnt, L.total_bytes]
     assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs)
     assert L.x_row_bytes == 1536 and L.x_sf_row_bytes == 96 and L.rx_row_bytes == 1536 + 96 + 16
@@ -144,3 +144,23 @@ def test_ctypes_mirror_matches_the_header(tmp_path):
         assert mirror == fields[cname], (cname, mirror, fields[cname])
         for f in mirror:
             assert int(out[f'{cname}.{f}']) == getattr(ct, f).offset, (cname, f)
+
+
+def test_frontend_rejects_fewer_experts_than_routes():
+    """Eight routes per token cannot be drawn from fewer than eight experts: refused on the host, before any launch."""
+    lib = _lib.load()
+    cfg = _lib.MMConfig(1, 0, 4, 16, 8, 512, 256, _lib.FMT['mxfp4'], 148)
+    dummy = ctypes.c_void_p(0x1000)                                  # never dereferenced: the argument check fails first
+    fe = _lib.MMFrontendArgs(dummy, dummy, None, 4, 0, dummy, 1.0)
+    assert lib.mm_frontend_launch(ctypes.byref(cfg), dummy, ctypes.byref(fe), None) == 1
+    peers = (ctypes.c_void_p * 1)(0x1000)
+    la = _lib.MMLaunchArgs(dummy, peers, dummy, dummy, dummy, 4, 0, None, -1.0, 1, 1.0, 1.0, 1.0, 1.0, 0.0, None)
+    assert lib.mm_mega_moe_from_hidden_launch(ctypes.byref(cfg), ctypes.byref(la), ctypes.byref(fe), None) == 1
+
+
+def test_tuning_values_round_trip():
+    lib = _lib.load()
+    old = lib.mm_get_tuning(_lib.TUNE['stages'])
+    assert lib.mm_set_tuning(_lib.TUNE['stages'], 6) == 0 and lib.mm_get_tuning(_lib.TUNE['stages']) == 6
+    assert lib.mm_set_tuning(_lib.TUNE['stages'], old) == 0
+    assert lib.mm_set_tuning(99, 1) == 1 and lib.mm_set_tuning(0, -1) == 1 and lib.mm_get_tuning(99) == -1

@@ -46,9 +46,14 @@ def test_static_scratch_entry_matches_regular_entry_twice():
         args = _lib.MMStaticArgs(x_d.data_ptr(), sf_d.data_ptr(), idx_d.data_ptr(), tw_d.data_ptr(),
                                  l1[0].data_ptr(), l2[0].data_ptr(), y.data_ptr(), tokens, 1, None, 10.0,
                                  1.0, 1.0, 1.0, 1.0, 500.0, status.data_ptr())
+        torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info()
         st = lib.mm_mega_moe_launch_static_scratch(ctypes.byref(cfg), ctypes.byref(args), stream)
         assert st == 0, lib.mm_last_cuda_error().decode()
         torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info()
+        if call > 0:                    # (the first call may load the kernel's module; from then on nothing is allocated)
+            assert free_after == free_before, (free_before, free_after)
         assert int(status[0]) == 0, hex(int(status[0]))
         assert O.rel_rmse(y.cpu(), y_ref.cpu()) <= 3e-3 and O.cosine(y.cpu(), y_ref.cpu()) >= 0.9999
         ref = O.moe_layer_reference([inp], [w], fmt, e_local, clamp=10.0)

@@ -65,7 +65,7 @@ KNOB_PREFETCH, KNOB_OWN_ROWS, KNOB_EARLY_COMBINE = 1, 2, 4
 EXPORTS = ('mm_get_layout', 'mm_get_weight_geometry', 'mm_get_token_alignment', 'mm_mega_moe_launch',
            'mm_frontend_launch', 'mm_frontend_workspace_bytes', 'mm_mega_moe_from_hidden_launch', 'mm_reset',
            'mm_read_device_status', 'mm_read_phase_stamps', 'mm_status_string', 'mm_last_cuda_error',
-           'mm_mega_moe_launch_static_scratch', 'mm_set_tuning', 'mm_get_tuning')
+           'mm_mega_moe_launch_static_scratch', 'mm_set_tuning', 'mm_get_tuning', 'mm_read_sm_phases', 'mm_fe_forward', 'mm_fe_workspace_bytes', 'mm_fe_router_ctas', 'mm_transform_weights', 'mm_cast_rows_to_fp4')
 
 _lib = None
 
@@ -95,6 +95,15 @@ def load() -> ctypes.CDLL:
     lib.mm_reset.argtypes = [P(MMConfig), ctypes.c_void_p, ctypes.c_void_p]
     lib.mm_read_device_status.argtypes = [P(MMConfig), ctypes.c_void_p, P(ctypes.c_uint32), ctypes.c_void_p]
     lib.mm_read_phase_stamps.argtypes = [P(MMConfig), ctypes.c_void_p, P(ctypes.c_uint64), ctypes.c_void_p]
+    lib.mm_read_sm_phases.argtypes = [P(MMConfig), ctypes.c_void_p, P(ctypes.c_uint64), ctypes.c_void_p]
+    lib.mm_fe_forward.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int64] + [ctypes.c_int32] * 6 + [ctypes.c_void_p]
+    lib.mm_fe_workspace_bytes.argtypes = [ctypes.c_int32]
+    lib.mm_fe_workspace_bytes.restype = ctypes.c_int64
+    lib.mm_fe_router_ctas.argtypes = [ctypes.c_int32] * 4
+    lib.mm_fe_router_ctas.restype = ctypes.c_int32
+    lib.mm_transform_weights.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64,
+                                         ctypes.c_int64] + [ctypes.c_int32] * 5 + [ctypes.c_void_p, ctypes.c_void_p]
+    lib.mm_cast_rows_to_fp4.argtypes = [ctypes.c_void_p] + [ctypes.c_int32] * 5 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.mm_status_string.argtypes = [ctypes.c_int]
     lib.mm_status_string.restype = ctypes.c_char_p
     lib.mm_last_cuda_error.restype = ctypes.c_char_p

@@ -7,7 +7,7 @@ CSRC = os.path.join(PKG_DIR, 'csrc')
 LIB_NAME = 'libmegamoe_b200.so'
 LIB_PATH = os.path.join(PKG_DIR, LIB_NAME)
 SOURCES = ['mm_abi.cu']
-HEADERS = ['mm_kernel.cuh', 'mm_frontend.cuh', 'mm_ptx.cuh', os.path.join('..', '..', 'include', 'megamoe_b200.h')]
+HEADERS = ['mm_kernel.cuh', 'mm_frontend.cuh', 'mm_ptx.cuh', 'mm_prep.cuh', os.path.join('..', '..', 'include', 'megamoe_b200.h')]
 
 
 def _stale() -> bool:

@@ -8,6 +8,7 @@
 #include "../../include/megamoe_b200.h"
 #include "mm_kernel.cuh"
 #include "mm_frontend.cuh"
+#include "mm_prep.cuh"
 
 namespace {
 
@@ -295,6 +296,16 @@ int mm_mega_moe_launch(const mm_config_t* cfg, const mm_launch_args_t* a, void* 
     return umma ? launch_variant<16, true>(p, grid, smem_bytes, s) : launch_variant<16, false>(p, grid, smem_bytes, s);
 }
 
+int mm_read_sm_phases(const mm_config_t* cfg, const void* buffer, uint64_t* out, void* stream) {
+    mm_layout_t L;
+    const int st = mm_get_layout(cfg, &L);
+    if (st != MM_OK) return st;
+    if (buffer == nullptr || out == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    MM_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+    MM_CUDA(cudaMemcpy(out, static_cast<const uint8_t*>(buffer) + L.off_ctrl + mm::kCtrlSmPhase, 256 * mm::kSmPhaseSlots * 8, cudaMemcpyDeviceToHost));
+    return MM_OK;
+}
+
 int64_t mm_frontend_workspace_bytes(const mm_config_t* cfg) {
     if (cfg == nullptr) return -1;
     return static_cast<int64_t>(cfg->num_max_tokens_per_rank) * cfg->num_experts * 4 + 256;
@@ -337,13 +348,96 @@ int mm_frontend_launch(const mm_config_t* cfg, void* buffer, const mm_frontend_a
     return MM_OK;
 }
 
+int mm_transform_weights(const void* w_packed, const void* sf, int32_t sf_is_fp32, int64_t sf_stride_e, int64_t sf_stride_n,
+                         int64_t sf_stride_k, int32_t num_groups, int32_t n, int32_t k, int32_t sf_vec, int32_t interleave_gate_up,
+                         void* out_stream, void* stream) {
+    if (w_packed == nullptr || sf == nullptr || out_stream == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (num_groups <= 0 || n <= 0 || k <= 0 || n % 128 != 0 || k % 256 != 0) return MM_ERR_INVALID_ARGUMENT;
+    if (sf_vec != 16 && sf_vec != 32) return MM_ERR_UNSUPPORTED;
+    if (interleave_gate_up && n % 16 != 0) return MM_ERR_INVALID_ARGUMENT;
+    mm::PrepParams q;
+    memset(&q, 0, sizeof(q));
+    q.w = static_cast<const uint8_t*>(w_packed); q.sf = sf;
+    q.sf_stride_e = sf_stride_e; q.sf_stride_n = sf_stride_n; q.sf_stride_k = sf_stride_k;
+    q.sf_is_fp32 = sf_is_fp32; q.E = num_groups; q.N = n; q.K = k; q.vec = sf_vec; q.interleave = interleave_gate_up;
+    q.out = static_cast<uint8_t*>(out_stream);
+    q.planes = mm::kUnitK / (4 * sf_vec);
+    q.unit_bytes = mm::kUnitWBytes + q.planes * 512;
+    const long long units = static_cast<long long>(num_groups) * (n / 128) * (k / 256);
+    if (units > 0x7FFFFFFFll) return MM_ERR_UNSUPPORTED;
+    mm::pretile_weights_kernel<<<static_cast<unsigned>(units), 256, 0, static_cast<cudaStream_t>(stream)>>>(q);
+    MM_CUDA(cudaGetLastError());
+    return MM_OK;
+}
+
+int mm_cast_rows_to_fp4(const void* x, int32_t x_is_bf16, int32_t m, int32_t k, int32_t gran_k, int32_t use_ue8m0,
+                        void* packed_out, float* sf_out, void* stream) {
+    if (x == nullptr || packed_out == nullptr || sf_out == nullptr || m < 0 || k <= 0) return MM_ERR_INVALID_ARGUMENT;
+    if ((gran_k != 16 && gran_k != 32 && gran_k != 64 && gran_k != 128) || k % gran_k != 0) return MM_ERR_UNSUPPORTED;
+    if (m == 0) return MM_OK;
+    const long long threads = static_cast<long long>(m) * (k / 8);
+    const unsigned blocks = static_cast<unsigned>((threads + 255) / 256);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (x_is_bf16)
+        mm::cast_rows_fp4_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), m, k, gran_k, use_ue8m0,
+                                                                      static_cast<uint8_t*>(packed_out), sf_out);
+    else
+        mm::cast_rows_fp4_kernel<float><<<blocks, 256, 0, s>>>(static_cast<const float*>(x), m, k, gran_k, use_ue8m0,
+                                                              static_cast<uint8_t*>(packed_out), sf_out);
+    MM_CUDA(cudaGetLastError());
+    return MM_OK;
+}
+
+int64_t mm_fe_workspace_bytes(int32_t e) { return e > 0 ? 256 + static_cast<int64_t>(4) * 64 * e * 4 : -1; }
+
+int32_t mm_fe_router_ctas(int32_t m, int32_t h, int32_t e, int32_t topk) {
+    (void)m; (void)h; (void)e; (void)topk;
+    int dev = 0, g = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&g, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) return -1;
+    return g;                              // the logits kernel runs one CTA per SM whatever the shape
+}
+
+int mm_fe_forward(const void* hidden, const void* router_weight, void* x, void* x_sf, void* topk_idx, void* topk_weights,
+                  void* workspace, int64_t workspace_bytes, int32_t m, int32_t h, int32_t e, int32_t topk, int32_t mode,
+                  int32_t l2_persist, void* stream) {
+    (void)l2_persist;                      // accepted for the reference's argument list; the router matrix is read once per launch
+    if (hidden == nullptr || router_weight == nullptr || x == nullptr || x_sf == nullptr || topk_idx == nullptr ||
+        topk_weights == nullptr || workspace == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (m < 1 || m > 64 || h <= 0 || h % 256 != 0 || h > 4096) return MM_ERR_INVALID_ARGUMENT;
+    if (topk != 8 || e > 1024) return MM_ERR_UNSUPPORTED;
+    if (e < topk) return MM_ERR_INVALID_ARGUMENT;
+    if (mode < 2 || mode > 4) return MM_ERR_UNSUPPORTED;          // 2 FP8 / 3 MXFP4 / 4 NVFP4 (0 and 1 are Hopper formats)
+    if (workspace_bytes < 256 + static_cast<int64_t>(m) * e * 4) return MM_ERR_INVALID_ARGUMENT;
+    int dev = 0, grid = 0;
+    MM_CUDA(cudaGetDevice(&dev));
+    MM_CUDA(cudaDeviceGetAttribute(&grid, cudaDevAttrMultiProcessorCount, dev));
+    const int fmt = mode == 2 ? MM_FMT_FP8 : (mode == 3 ? MM_FMT_MXFP4 : MM_FMT_NVFP4);
+    mm::FeParams q;
+    memset(&q, 0, sizeof(q));
+    q.hidden = static_cast<const __nv_bfloat16*>(hidden);
+    q.router_w = static_cast<const __nv_bfloat16*>(router_weight);
+    q.logits = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + 256);
+    q.arrive = reinterpret_cast<uint32_t*>(workspace);
+    q.T = m; q.H = h; q.E = e; q.topk = topk; q.score_mode = 0; q.fmt = fmt; q.x_gs = 1.f;
+    q.x = static_cast<uint8_t*>(x); q.x_sf = static_cast<uint8_t*>(x_sf);
+    q.topk_idx = static_cast<long long*>(topk_idx); q.topk_w = static_cast<float*>(topk_weights);
+    q.x_row_bytes = fmt == MM_FMT_FP8 ? h : h / 2;
+    q.x_sf_row_bytes = h / sf_vec_of(fmt);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    mm::frontend_logits_kernel<<<grid, 256, 0, s>>>(q);
+    MM_CUDA(cudaGetLastError());
+    mm::frontend_select_quant_kernel<<<(m + 3) / 4, 128, q.E * 4 * 4, s>>>(q);
+    MM_CUDA(cudaGetLastError());
+    return MM_OK;
+}
+
 int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_t* a, const mm_frontend_args_t* fe, void* stream) {
     mm::KParams p;
     int grid = 0;
     size_t smem_bytes = 0;
     int st = fill_params(cfg, a, &p, &grid, &smem_bytes);
     if (st != MM_OK) return st;
-    if (fe == nullptr || fe->hidden_states == nullptr || fe->router_weight == nullptr || fe->workspace == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    if (fe == nullptr || (fe->hidden_states == nullptr && fe->num_tokens > 0) || fe->router_weight == nullptr || fe->workspace == nullptr) return MM_ERR_INVALID_ARGUMENT;
     if (fe->num_tokens != a->num_tokens) return MM_ERR_INVALID_ARGUMENT;
     if (cfg->num_topk != 8 || cfg->num_experts > 1024) return MM_ERR_UNSUPPORTED;
     if (cfg->num_experts < cfg->num_topk) return MM_ERR_INVALID_ARGUMENT;      // fewer experts than routes per token

@@ -47,13 +47,19 @@ constexpr int kUnitWBytes = kTileRows * 128;
 constexpr int kNumEpiThreads = 128;
 constexpr uint32_t kBarEpi = 1;          // named barrier of the four epilogue warps
 constexpr uint32_t kBarCopy = 2;         // named barrier of the warps that dispatch
+// The scout warp runs beside the other warps of the CTA from kernel entry to the start of the roles; it meets them at
+// four named barriers, each used once per launch: kBarPrologue (the scout arrives without waiting, the others wait),
+// kBarOwn (the scout arrives when its list of own rows is written; the others wait for it), kBarGo (the others arrive
+// after the prologue; the scout waits before it uses the launch number), kBarSched (the others arrive when the task
+// list is written; the scout waits, then takes up its role). kBarMain synchronises the other warps among themselves.
+constexpr uint32_t kBarOwn = 3, kBarGo = 4, kBarSched = 5, kBarMain = 6, kBarPrologue = 7;
 constexpr int kNumExpThreads = 256;      // FP8-activation variant: warps 8..15 widen the packed E2M1 weights to 8-bit containers
 constexpr uint32_t kXbufBytes = 2 * kUnitWBytes + 1024;   // one widened unit + its two scale planes
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kOtileBytes = 4096;
 constexpr uint32_t kVtBytes = kTileTokens * kTileRows * 4;   // fp32 accumulators of one task, token-major
 
-constexpr int kOwnCap = 256;            // routed rows of this rank's own tokens that every SM lists for itself (see the scout)
+constexpr int kOwnCap = 128;            // routed rows of this rank's own tokens that every SM lists for itself (see the scout)
 
 // control-block offsets (bytes from off_ctrl)
 constexpr int kCtrlEpoch = 0;           // u32[256] one launch counter per SM
@@ -62,7 +68,9 @@ constexpr int kCtrlStamps = 2048;       // u64[32] phase stamps
 constexpr int kCtrlFeWords = 3072;      // u32[256] per-SM word: launch number once the SM has published its router logits
 constexpr int kCtrlSmEntry = 4096;      // u64[256] per-SM time of the kernel's first instruction
 constexpr int kCtrlSmWFirst = 6144;     // u64[256] per-SM time of the first weight request (prefetch or load); ~0: none
-constexpr int kCtrlBytes = 8192;
+constexpr int kSmPhaseSlots = 32;       // per SM: 16 phase times, then the landing times of its first 16 weight units
+constexpr int kCtrlSmPhase = 8192;      // u64[256][kSmPhaseSlots] per-SM phase times (see SmPhase)
+constexpr int kCtrlBytes = 8192 + 256 * kSmPhaseSlots * 8;
 
 // tuning bits (KParams::knobs)
 enum : uint32_t {
@@ -84,6 +92,13 @@ enum : int {
     kStampExit = 7, kStampLastExit = 8 /* max over SMs */,
     kStampFrontend = 9, kStampLastTasksDone = 10 /* max over SMs */, kStampLastScheduled = 11 /* max over SMs */,
     kStampLastWeight = 14 /* max over SMs: the last streamed unit has landed */
+};
+
+// per-SM phase times (globaltimer ns), slot index inside the SM's 16 records
+enum SmPhase : int {
+    kSmEntry = 0, kSmPrologue = 1, kSmOwnListed = 2, kSmCountsKnown = 3, kSmScheduled = 4, kSmFirstIssue = 5,
+    kSmFirstLanded = 6, kSmFirstStaged = 7, kSmFirstMmaDone = 8, kSmFirstEpilogue = 9, kSmLastL1Epilogue = 10,
+    kSmFirstL2Staged = 11, kSmTasksDone = 12, kSmFirstCombined = 13, kSmCombineDone = 14, kSmExit = 15
 };
 
 struct RowMeta { int32_t src, token, slot; float weight; };
@@ -156,7 +171,7 @@ struct Ctx {
     uint8_t* buf;         // this rank's buffer
     uint8_t* smem;        // dynamic shared memory (1024 B aligned)
     uint64_t deadline;
-    uint32_t par;         // launch parity: which half of the receive pool this launch uses
+    uint32_t par;         // launch parity: which half of the receive pool this launch uses (set once the launch number is known)
     __device__ __forceinline__ bool aborted() const { return *reinterpret_cast<volatile uint32_t*>(&c.abort_flag) != 0u; }
     __device__ __noinline__ void fail(uint32_t code, uint32_t detail = 0) const {      // cold: keep it out of the callers' code
         uint32_t* st = reinterpret_cast<uint32_t*>(buf + p.off_ctrl + kCtrlStatus);
@@ -186,6 +201,9 @@ struct Ctx {
     }
     __device__ __forceinline__ void stamp(int slot) const {
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[slot] = globaltimer_ns();
+    }
+    __device__ __forceinline__ void sm_phase(int slot) const {
+        reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmPhase)[blockIdx.x * kSmPhaseSlots + slot] = globaltimer_ns();
     }
     __device__ __forceinline__ void stamp_max(int slot, unsigned long long t) const {
         atomicMax(reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps) + slot, t);
@@ -245,7 +263,7 @@ __device__ void role_loader(const Ctx& cx) {
                 mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
                 bulk_g2s(cx.smem + static_cast<size_t>(s) * p.unit_bytes, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
                 c.issued = it + 1u;
-                if (it == 0u) cx.note_first_weight_request();
+                if (it == 0u) { cx.note_first_weight_request(); cx.sm_phase(kSmFirstIssue); }
             }
             __syncwarp();
             if (++s == static_cast<uint32_t>(p.nstage)) { s = 0; ph ^= 1u; }
@@ -281,6 +299,10 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
             if (!cx.warp_wait(ready, kA8 ? (it >> 1) & 1u : ph, kErrWaitFull)) return;
             tc_fence_after();
             t_landed = globaltimer_ns();
+            if (lane == 0) {
+                if (it == 0u) cx.sm_phase(kSmFirstLanded);
+                if (it < 16u) cx.sm_phase(16 + static_cast<int>(it));
+            }
             if (elect_one()) {
               {
                 const uint32_t wsm = kA8 ? smem_u32(cx.smem + p.sm_xbuf + (it & 1u) * kXbufBytes)
@@ -399,6 +421,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
     uint32_t* rowref = c.rowref[sw];
     uint32_t* rowidx = c.rowidx[sw];
     if (sw >= c.nab) return;
+    bool seen_l2 = false;
     #pragma unroll 1
     for (uint32_t ti = sw; ti < c.ntasks; ti += c.nab) {      // with one staging buffer, stager 0 takes every task
         const uint32_t t = c.tasks[ti];
@@ -502,7 +525,11 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
         if (__any_sync(0xffffffffu, bad)) return;
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&c.acts_full[ab]);
+        if (lane == 0) {
+            mbar_arrive(&c.acts_full[ab]);
+            if (ti == 0u) cx.sm_phase(kSmFirstStaged);
+            if (type != 0u && !seen_l2) { seen_l2 = true; cx.sm_phase(kSmFirstL2Staged); }
+        }
     }
 }
 
@@ -569,6 +596,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             ok = cx.warp_wait(&c.tmem_full[acc], use, kErrWaitTmemFull);
             if (ok) {
                 tc_fence_after();
+                if (ti == 0u && etid == 0u) cx.sm_phase(kSmFirstMmaDone);
                 if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
                 nv = c.nvalid[ring];
                 uint32_t raw[kTileTokens];
@@ -729,6 +757,10 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 st_ll_16B(dst, val, c.epoch + 1u);
             }
         }
+        if (etid == 0u) {
+            if (ti == 0u) cx.sm_phase(kSmFirstEpilogue);
+            if (type == 0u) cx.sm_phase(kSmLastL1Epilogue);
+        }
     }
 }
 
@@ -841,34 +873,39 @@ __device__ __forceinline__ uint64_t warp_or_u64(uint64_t v) {
     return (static_cast<uint64_t>(hi) << 32) | lo;
 }
 
-__device__ __noinline__ void role_scout(const Ctx& cx, const ScoutRegs& reg, bool own_ok, uint32_t lane, uint32_t G) {
-    const KParams& p = cx.p; Ctl& c = cx.c;
-    const uint32_t bid = blockIdx.x, R = p.R, flag = c.epoch + 1u;
-    const bool pf = (p.knobs & kKnobPrefetch) != 0u;
-    uint64_t known = 0ull;
-    uint32_t asked = 0;
-    // this SM's share of the weights of the experts in `fresh`: W1 of all of them first (the L1 phase needs it first)
-    auto ask = [&](uint64_t fresh) {
-        if (!pf || fresh == 0ull) return;
-        if (asked == 0u && lane == 0) cx.note_first_weight_request();
-        #pragma unroll 1
-        for (uint32_t layer = 0; layer < 2; ++layer) {
-            const uint32_t per = layer ? p.n2_tiles * p.k2_units : p.n1_tiles * p.k1_units;
-            const uint32_t limit = layer ? p.pf_w2_max : p.pf_w1_max;
-            const uint8_t* base = layer ? p.w2 : p.w1;
-            uint64_t m = fresh;
-            uint32_t n = asked;
-            while (m != 0ull && n < limit) {
-                const uint32_t e = static_cast<uint32_t>(__ffsll(static_cast<long long>(m))) - 1u;
-                m &= m - 1ull;
-                ++n;
-                #pragma unroll 1
-                for (uint32_t u = bid + lane * G; u < per; u += 32u * G)
-                    bulk_prefetch_l2(base + (static_cast<size_t>(e) * per + u) * p.unit_bytes, p.unit_bytes);
-            }
+struct ScoutState { uint64_t known; uint32_t asked; };
+
+// this SM's share of the weights of the experts in `fresh`: W1 of all of them first (the L1 phase needs it first)
+__device__ __forceinline__ void scout_ask(const Ctx& cx, ScoutState& st, uint64_t fresh, uint32_t lane, uint32_t G) {
+    const KParams& p = cx.p;
+    if ((p.knobs & kKnobPrefetch) == 0u || fresh == 0ull) return;
+    const uint32_t bid = blockIdx.x;
+    if (st.asked == 0u && lane == 0) { cx.note_first_weight_request(); }
+    #pragma unroll 1
+    for (uint32_t layer = 0; layer < 2; ++layer) {
+        const uint32_t per = layer ? p.n2_tiles * p.k2_units : p.n1_tiles * p.k1_units;
+        const uint32_t limit = layer ? p.pf_w2_max : p.pf_w1_max;
+        const uint8_t* base = layer ? p.w2 : p.w1;
+        uint64_t m = fresh;
+        uint32_t n = st.asked;
+        while (m != 0ull && n < limit) {
+            const uint32_t e = static_cast<uint32_t>(__ffsll(static_cast<long long>(m))) - 1u;
+            m &= m - 1ull;
+            ++n;
+            #pragma unroll 1
+            for (uint32_t u = bid + lane * G; u < per; u += 32u * G)
+                bulk_prefetch_l2(base + (static_cast<size_t>(e) * per + u) * p.unit_bytes, p.unit_bytes);
         }
-        asked += static_cast<uint32_t>(__popcll(fresh));
-    };
+    }
+    st.asked += static_cast<uint32_t>(__popcll(fresh));
+}
+
+// Phase 1 (needs nothing of the prologue): list this rank's own routed rows from the routing entries the warp loaded
+// at kernel entry, publish the list (named barrier kBarOwn: the scout arrives, the other warps wait there when they
+// need the list), then ask for those experts' weights.
+__device__ __noinline__ void scout_own_rows(const Ctx& cx, ScoutState& st, const ScoutRegs& reg, bool own_ok, uint32_t nthreads,
+                                            uint32_t lane, uint32_t G) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
     if (own_ok) {
         const uint32_t n = static_cast<uint32_t>(p.T) * p.topk;
         uint32_t cnt = 0;
@@ -891,11 +928,20 @@ __device__ __noinline__ void role_scout(const Ctx& cx, const ScoutRegs& reg, boo
                 cnt += __popc(b);
             }
         }
-        if (lane == 0) c.own_cnt = cnt;
-        known = warp_or_u64(m);
-        ask(known);
+        if (lane == 0) { c.own_cnt = cnt; cx.sm_phase(kSmOwnListed); }
+        st.known = warp_or_u64(m);
     }
-    if (!pf) return;
+    __threadfence_block();
+    bar_arrive(kBarOwn, nthreads);
+    scout_ask(cx, st, st.known, lane, G);
+}
+
+// Phase 2 (after the prologue: launch number and receive-pool parity are known): watch the other ranks' header lines and
+// records arrive, asking for every newly seen expert's weights, until every source has been seen.
+__device__ __noinline__ void scout_watch_peers(const Ctx& cx, ScoutState& st, bool own_ok, uint32_t lane, uint32_t G) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    if ((p.knobs & kKnobPrefetch) == 0u) return;
+    const uint32_t R = p.R, flag = c.epoch + 1u;
     uint32_t pending = (R >= 32u ? 0xFFFFFFFFu : (1u << R) - 1u);
     if (own_ok) pending &= ~(1u << p.rank);
     uint32_t passes = 0;
@@ -918,17 +964,18 @@ __device__ __noinline__ void role_scout(const Ctx& cx, const ScoutRegs& reg, boo
                     const uint8_t* src = cx.rx_row(r, i) + 2u * (p.rx_row_bytes - 16);
                     const uint4 a = ld_volatile_v4(src), b = ld_volatile_v4(src + 16);
                     ok = ll_valid(a, b, flag);
-                    if (ok && (a.x & 0xFFu) < static_cast<uint32_t>(p.e_local)) m |= 1ull << (a.x & 63u);      // only experts this rank holds: the prefetch address must lie inside the weights
+                    // only experts this rank holds: the prefetch address must lie inside the weights
+                    if (ok && (a.x & 0xFFu) < static_cast<uint32_t>(p.e_local)) m |= 1ull << (a.x & 63u);
                 }
                 all = __all_sync(0xffffffffu, ok) && all;
             }
             fresh |= warp_or_u64(m);
             if (all) pending &= ~(1u << r);
         }
-        fresh &= ~known;
-        ask(fresh);
-        known |= fresh;
-        if ((++passes & 0xFu) == 0u && (cx.aborted() || cx.expired())) break;   // the header wait of the main path reports the failure
+        fresh &= ~st.known;
+        scout_ask(cx, st, fresh, lane, G);
+        st.known |= fresh;
+        if ((++passes & 0xFu) == 0u && (cx.aborted() || cx.expired())) break;   // the header wait of the other warps reports the failure
     }
 }
 
@@ -947,15 +994,25 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     // the spare warp: the last one (it takes no part in the dispatch copies); with the fused frontend every warp is busy
     constexpr uint32_t kCopyWarps = kFe ? kNT / 32 : kNT / 32 - 1;
     constexpr bool kScout = !kFe;
-    const bool own_ok = kScout && (p.knobs & kKnobOwnRows) != 0u && static_cast<uint32_t>(p.T) * p.topk <= kOwnCap;
+    const bool own_ok = kScout && (p.knobs & kKnobOwnRows) != 0u && static_cast<uint32_t>(p.T) * p.topk <= kOwnCap &&
+                        p.inp == buf;      // (inputs in mapped host memory are read by the dispatching SMs only)
 
     // ---- prologue
+    constexpr uint32_t kO = kScout ? kNT - 32u : kNT;        // threads of the warps other than the scout
+    const bool is_scout = kScout && warp == kCopyWarps;
     ScoutRegs sreg;
-    if constexpr (kScout) { if (warp == kCopyWarps && own_ok) scout_load_own(p, inp, lane, sreg); }
+    ScoutState sst{0ull, 0u};
+    if constexpr (kScout) {
+        if (is_scout) {
+            if (own_ok) scout_load_own(p, inp, lane, sreg);
+            if (lane == 0) reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmWFirst)[bid] = ~0ull;
+        }
+    }
     if (tid == 0) {
         const uint32_t ep = ctrl32[kCtrlEpoch / 4 + bid];
         ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
-        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.own_cnt = 0u; c.comb_next = 0u; c.issued = 0u;
+        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u;
+        if constexpr (!kScout) c.own_cnt = 0u;
         for (int s = 0; s < p.nstage; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
         #pragma unroll 1
         for (int i = 0; i < 2; ++i) {
@@ -965,30 +1022,49 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         }
         mbar_fence_init();
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmEntry)[bid] = t_first;
-        reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmWFirst)[bid] = ~0ull;
+        if constexpr (!kScout) reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmWFirst)[bid] = ~0ull;
     }
     // the token staging area starts from zero (the dispatch lists and the frontend's scratch that pass through it later
     // leave finite bytes; whatever sits in rows beyond a task's valid tokens only reaches accumulator columns nobody reads)
-    #pragma unroll 1
-    for (uint32_t off = tid * 16u; off < p.stage_region; off += kNT * 16u)
-        *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
+    if (!is_scout) {
+        #pragma unroll 1
+        for (uint32_t off = tid * 16u; off < p.stage_region; off += kO * 16u)
+            *reinterpret_cast<uint4*>(smem + p.sm_act + off) = make_uint4(0, 0, 0, 0);
+    }
     if (warp == 1) { tmem_alloc(&c.tmem_base, kTmemCols); tmem_relinquish(); tc_fence_before(); }
     if (tid < kMaxLocalExperts) c.exp_count[tid] = 0u;
-    __syncthreads();
+    Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, 0u};
+    if (is_scout) {
+        // the scout does not wait for the prologue: it lists the own rows and asks for their experts' weights first
+        bar_arrive(kBarPrologue, kNT);
+        scout_own_rows(cx, sst, sreg, own_ok, kNT, lane, G);
+        bar_sync(kBarGo, kNT);
+    } else {
+        bar_sync(kBarPrologue, kNT);
+        if constexpr (kScout) { __threadfence_block(); bar_arrive(kBarGo, kNT); }
+    }
     tc_fence_after();
-    Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, c.epoch & 1u};
+    cx.par = c.epoch & 1u;
     const uint32_t epoch = c.epoch, par = cx.par;
+    const uint32_t ndisp = static_cast<uint32_t>(p.ndisp);
+    const bool dispatching = bid < static_cast<uint32_t>(p.R) * ndisp;
+
+  if (is_scout) {
+    scout_watch_peers(cx, sst, own_ok, lane, G);
+    bar_sync(kBarSched, kNT);
+  } else {
     if (bid == 0 && tid == 0) {
         ctrl32[kCtrlStatus / 4 + 1] = epoch + 1u;
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[kStampEntry] = t_first;
         cx.stamp(kStampPrologue);
     }
+    if (tid == 0) cx.sm_phase(kSmPrologue);
     // The control block and the split-tile counters are touched late, on the critical dependency chain, and by then
     // they have usually been evicted from the L2 by the weight stream of earlier work: ask for their lines now.
     if (warp == 6) {
         const uint32_t g = bid * 32 + lane, gn = G * 32;
         #pragma unroll 1
-        for (uint32_t off = g * 128u; off < kCtrlBytes; off += gn * 128u) prefetch_l2_line(buf + p.off_ctrl + off);
+        for (uint32_t off = g * 128u; off < 8192u; off += gn * 128u) prefetch_l2_line(buf + p.off_ctrl + off);
         const size_t cnt_bytes = static_cast<size_t>(2) * p.cnt_per_phase * 4;
         #pragma unroll 1
         for (size_t off = static_cast<size_t>(g) * 128u; off < (cnt_bytes < 65536 ? cnt_bytes : 65536); off += gn * 128u) prefetch_l2_line(buf + p.off_cnt + off);
@@ -998,10 +1074,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     //      so it runs the scheduler once on dummy counts (eight experts with one row). The real call, which sits on the
     //      critical path right after the dispatch arrives, then finds its instructions cached and overwrites everything
     //      this writes. (On the dispatching SMs warp 6 copies rows; their schedule runs cold.)
-    const uint32_t ndisp = static_cast<uint32_t>(p.ndisp);
-    const bool dispatching = bid < static_cast<uint32_t>(p.R) * ndisp;
     if constexpr (!kFe) {
-        if (warp == 6 && !dispatching) {
+        if (warp == 6 && !dispatching && (p.R > 1 || !own_ok)) {       // (one rank with own rows listed: nothing to hide it behind)
             for (uint32_t e = lane; e < kMaxLocalExperts; e += 32) c.dry_count[e] = e < 8u ? 1u : 0u;
             __syncwarp();
             build_schedule(p, c, c.dry_count, bid, G, lane);
@@ -1011,7 +1085,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     // ---- router frontend (optional): all SMs compute logits; the dispatching SMs select the top-8 of every token
     if constexpr (kFe) {
         fe_logits_items(p.fe, bid * (kNT / 32) + warp, G * (kNT / 32), lane);
-        __syncthreads();
+        bar_sync(kBarMain, kO);
         // Every SM publishes a word with this launch's number once its logits are written; the selecting SMs wait for
         // all G words (per-launch values: launches of the other variants in between leave nothing to catch up with).
         uint32_t* few = ctrl32 + kCtrlFeWords / 4;
@@ -1029,7 +1103,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                     }
                 }
             }
-            __syncthreads();
+            bar_sync(kBarMain, kO);
             float* sc = reinterpret_cast<float*>(smem + p.sm_act) + warp * p.fe.E;
             #pragma unroll 1
             for (uint32_t t = warp; t < static_cast<uint32_t>(p.T); t += kNT / 32) {
@@ -1037,7 +1111,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 fe_select_token(p.fe, t, sc, nz, lane);
             }
             __threadfence();                 // the routing written above is read by other SMs of this launch (combine)
-            __syncthreads();
+            bar_sync(kBarMain, kO);
         }
         if (bid == 0 && tid == 0) cx.stamp(kStampFrontend);
     }
@@ -1121,27 +1195,26 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (bid == 0 && tid == 0) cx.stamp(kStampDispatched);
 
     // ---- receive: wait for every source rank's header line, then scan the received rows' records. The first 32 records
-    //      of every source are fetched speculatively in the same memory round trip as the headers (thread 32 r + i takes
-    //      record i of source r); a record that was not there yet, and any record beyond the first 32, is polled afterwards.
+    //      of the first sources are fetched speculatively in the same memory round trip as the headers (thread 32 r + i
+    //      takes record i of source r); a record that was not there yet, and any other record, is polled afterwards.
     //      The rows of this rank's own tokens need no header: the scout lists them from topk_idx (`own_ok`).
     const uint32_t flag_rx = epoch + 1u;
     const uint32_t spec_r = tid >> 5, spec_i = tid & 31u;
-    const bool spec = tid < 32u * static_cast<uint32_t>(p.R) && spec_i < static_cast<uint32_t>(p.cap) &&
+    constexpr uint32_t kSpecSources = kO / 32u;                       // sources whose first records have a speculating thread
+    const bool spec = spec_r < static_cast<uint32_t>(p.R) && spec_r < kSpecSources && spec_i < static_cast<uint32_t>(p.cap) &&
                       !(own_ok && spec_r == static_cast<uint32_t>(p.rank));
     uint4 spec_a = make_uint4(0u, 0u, 0u, 0u), spec_b = spec_a;
     if (spec) {
         const uint8_t* src = cx.rx_row(spec_r, spec_i) + 2u * (p.rx_row_bytes - 16);
         spec_a = ld_volatile_v4(src); spec_b = ld_volatile_v4(src + 16);
     }
-    if constexpr (kScout) {
-        if (warp == kCopyWarps) role_scout(cx, sreg, own_ok, lane, G);
-    }
     if (tid < static_cast<uint32_t>(p.R) && !(own_ok && tid == static_cast<uint32_t>(p.rank))) {
         uint4 h = make_uint4(0u, 0u, 0u, 0u);
         cx.ll_read(buf + p.off_rx + static_cast<size_t>(par * p.R + tid) * p.rx_region, flag_rx, h, kErrWaitDispatchFlag, tid);
         c.rx_count[tid] = h.x <= static_cast<uint32_t>(p.cap) ? h.x : 0u;
     }
-    __syncthreads();
+    if constexpr (kScout) bar_sync(kBarOwn, kNT);          // (all other warps + the scout's arrival: its list is written)
+    else bar_sync(kBarMain, kO);
     if constexpr (kFe) __threadfence();
     uint32_t total = 0;
     {
@@ -1156,6 +1229,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         if (tid == 0) {
             if (total > kMetaCap) cx.fail(kErrMetaCapacity, total >> 4);
             if (bid == 0) cx.stamp(kStampFlagsSeen);
+            cx.sm_phase(kSmCountsKnown);
         }
         if (total <= kMetaCap) {
             auto take = [&](uint32_t f, const uint4& m) {
@@ -1172,7 +1246,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 take(pre[spec_r] + spec_i, m);
             }
             #pragma unroll 1
-            for (uint32_t f = tid; f < total; f += kNT) {
+            for (uint32_t f = tid; f < total; f += kO) {
                 uint32_t r = 0;
                 #pragma unroll
                 for (int q = 1; q < kMaxRanks; ++q) r += (q < p.R && f >= pre[q]) ? 1u : 0u;
@@ -1182,14 +1256,14 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                     take(f, make_uint4(c.own_e[i], static_cast<uint32_t>(om.token), static_cast<uint32_t>(om.slot), __float_as_uint(om.weight)));
                     continue;
                 }
-                if (i < 32u) continue;                               // taken by the speculative read above
+                if (i < 32u && r < kSpecSources) continue;           // taken by the speculative read above
                 uint4 m = make_uint4(0u, 0u, 0u, 0u);
                 cx.ll_read(cx.rx_row(r, i) + 2u * (p.rx_row_bytes - 16), flag_rx, m, kErrWaitDispatchFlag, r);
                 take(f, m);
             }
         }
     }
-    __syncthreads();
+    bar_sync(kBarMain, kO);
 
     // ---- schedule. 16-token tiles of the active experts, expert-major: M of them. Every SM derives its own task list
     //      (L1 tasks, then L2 tasks) in closed form from the per-expert counts.
@@ -1203,11 +1277,13 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             else c.ntasks = nmine;
         }
     }
-    __syncthreads();
+    bar_sync(kBarMain, kO);
+    if constexpr (kScout) { __threadfence_block(); bar_arrive(kBarSched, kNT); }
     if (bid == 0 && tid == 0) cx.stamp(kStampScheduled);
-    if (tid == 0) cx.stamp_max(kStampLastScheduled, globaltimer_ns());
+    if (tid == 0) { cx.stamp_max(kStampLastScheduled, globaltimer_ns()); cx.sm_phase(kSmScheduled); }
     if (bid == 0 && tid < static_cast<uint32_t>(p.e_local) && p.stats != nullptr && !cx.aborted())
         p.stats[tid] += static_cast<int>(c.exp_count[tid]);
+  }
 
     // ---- roles
     if (!cx.aborted()) {
@@ -1222,6 +1298,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (tid == 128) {                                   // first epilogue thread: this SM's tasks are finished
         if (bid == 0) cx.stamp(kStampTasksDone);
         cx.stamp_max(kStampLastTasksDone, globaltimer_ns());
+        cx.sm_phase(kSmTasksDone);
     }
 
     // ---- combine. No grid-wide or cross-rank barrier precedes it: the expert outputs arrive as flagged words and every
@@ -1292,6 +1369,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 ow[q] = lo | (hi << 16);
             }
             *reinterpret_cast<uint4*>(reinterpret_cast<uint8_t*>(p.y) + (static_cast<size_t>(tok) * p.H) * 2u + ch * 16u) = o;
+            if (k == 0u) cx.sm_phase(kSmFirstCombined);
+            cx.sm_phase(kSmCombineDone);
         }
     }
 
@@ -1310,6 +1389,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (tid == 0) {
         if (bid == 0) cx.stamp(kStampExit);
         cx.stamp_max(kStampLastExit, globaltimer_ns());
+        cx.sm_phase(kSmExit);
     }
 }
 

@@ -71,6 +71,11 @@ __device__ __forceinline__ void bar_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }
 
+// counts the calling warp in on a named barrier without waiting for it
+__device__ __forceinline__ void bar_arrive(uint32_t id, uint32_t nthreads) {
+    asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+
 // barrier + OR-reduction of a predicate over the participating threads: every participant gets the same answer
 __device__ __forceinline__ bool bar_red_or(uint32_t id, uint32_t nthreads, bool pred) {
     uint32_t r;

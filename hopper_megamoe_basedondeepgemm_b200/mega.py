@@ -174,6 +174,15 @@ class SymmBuffer:
                                             torch.cuda.current_stream().cuda_stream), 'phase_stamps')
         return list(stamps)
 
+    def sm_phases(self):
+        """Per-SM phase times of the last launch: tensor int64 [256, 32] (globaltimer ns, 0 = not reached); the slot
+        meanings are listed beside `mm_read_sm_phases` in the header. Synchronises the stream."""
+        lib = _lib.load()
+        out = (ctypes.c_uint64 * (256 * 32))()
+        _lib.check(lib.mm_read_sm_phases(ctypes.byref(self.cfg), self.buffer.data_ptr(), out,
+                                         torch.cuda.current_stream().cuda_stream), 'sm_phases')
+        return torch.tensor(list(out), dtype=torch.int64).view(256, 32)
+
     def destroy(self):
         self.handle = None
         self.buffer = None
@@ -195,19 +204,37 @@ def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor]
                                    l2_weights: Tuple[torch.Tensor, torch.Tensor]):
     """Load-time weight transform (`sm100_b200/mega___init__.py:102-111`).
 
-    Inputs as the reference takes them: `(packed int8 [E, N, K/2], scales int32 [E, N, K/(4 vec)] MN-major)`.
-    L1 gets the 8-row gate/up interleave; both layers are then pre-tiled into the stream the kernel copies verbatim
-    (see `quant.pretile_weights`). Each result is `(stream uint8 [E, N/128, K/256, unit_bytes], shape int64 [N, K, vec])`.
+    Inputs as the reference takes them: `(packed int8 [E, N, K/2], scales int32 [E, N, K/(4 vec)] MN-major)`; fp32
+    scales `[E, N, K/vec]` (what `transform_sf_into_required_layout` accepts, `csrc/apis/layout.hpp:14-60`) are taken
+    too and turned into scale bytes on the way. L1 gets the 8-row gate/up interleave; both layers are pre-tiled into
+    the stream the kernel copies verbatim, by one CUDA copy kernel (`mm_transform_weights`; `quant.pretile_weights`
+    is its torch restatement, used for host tensors and as the test's reference). Each result is `(stream uint8 [E, N/128, K/256, unit_bytes], shape int64 [N, K, vec])`.
     """
     def one(wt, interleave):
         w, sf = wt
         e, n, kh = w.shape
-        vec = (kh * 2) // (sf.shape[-1] * 4)
+        if sf.dtype == torch.float32:                  # one fp32 scale per block: [E, N, K / vec]
+            vec = (kh * 2) // sf.shape[-1]
+        else:                                          # int32 words of four scale bytes: [E, N, K / (4 vec)]
+            vec = (kh * 2) // (sf.shape[-1] * 4)
         if vec not in (16, 32):
-            raise RuntimeError('weight scale tensor must hold one byte per 16 or 32 elements')
-        if interleave:
-            w, sf = interleave_gate_up(w), interleave_gate_up(sf)
-        return pretile_weights(w, sf, vec), torch.tensor([n, kh * 2, vec], dtype=torch.int64)
+            raise RuntimeError('weight scale tensor must hold one scale per 16 or 32 elements')
+        shape = torch.tensor([n, kh * 2, vec], dtype=torch.int64)
+        if not w.is_cuda:                              # host tensors (layout tests): the torch restatement of the kernel
+            if sf.dtype == torch.float32:
+                raise RuntimeError('fp32 weight scales are converted by the CUDA transform: move the tensors to the GPU')
+            if interleave:
+                w, sf = interleave_gate_up(w), interleave_gate_up(sf)
+            return pretile_weights(w, sf, vec), shape
+        lib = _lib.load()
+        geo = _lib.MMWeightGeometry()
+        lib.mm_get_weight_geometry(_lib.FMT['nvfp4' if vec == 16 else 'mxfp4'], ctypes.byref(geo))
+        w = w.contiguous()
+        out = torch.empty((e, n // 128, (kh * 2) // 256, int(geo.unit_bytes)), dtype=torch.uint8, device=w.device)
+        _lib.check(lib.mm_transform_weights(w.data_ptr(), sf.data_ptr(), int(sf.dtype == torch.float32), sf.stride(0),
+                                            sf.stride(1), sf.stride(2), e, n, kh * 2, vec, int(interleave), out.data_ptr(),
+                                            torch.cuda.current_stream().cuda_stream), 'transform_weights_for_mega_moe')
+        return out, shape
     return one(l1_weights, True), one(l2_weights, False)
 
 
@@ -340,14 +367,53 @@ def set_tuning(**kwargs) -> None:
         _lib.check(lib.mm_set_tuning(_lib.TUNE[k], int(v)), f'set_tuning({k})')
 
 
-def fe_workspace_bytes(sym_buffer: SymmBuffer) -> int:
-    return int(_lib.load().mm_frontend_workspace_bytes(ctypes.byref(sym_buffer.cfg)))
+def fe_workspace_bytes(e) -> int:
+    """`fe_workspace_bytes(e)` of `sm100_b200/fe_sm100/fe_binding.cpp:30`; a `SymmBuffer` is accepted in place of the
+    expert count (then the size covers the buffer's token capacity)."""
+    lib = _lib.load()
+    if isinstance(e, SymmBuffer):
+        return max(int(lib.mm_frontend_workspace_bytes(ctypes.byref(e.cfg))), int(lib.mm_fe_workspace_bytes(e.num_experts)))
+    return int(lib.mm_fe_workspace_bytes(int(e)))
 
 
-def fe_forward(hidden: torch.Tensor, router_weight: torch.Tensor, sym_buffer: SymmBuffer, workspace: torch.Tensor,
-               score_mode: int = 0, expert_bias: Optional[torch.Tensor] = None, x_global_scale: float = 1.0):
-    """Router frontend (`sm100_b200/fe_sm100/fe_binding.cpp:8-35`): router GEMM, top-8, routing weights and the token
-    quantisation, written into `sym_buffer.x / x_sf / topk_idx / topk_weights[:hidden.size(0)]`."""
+def fe_router_ctas(m: int, h: int, e: int, topk: int) -> int:
+    """`fe_router_ctas(m, h, e, topk)` of `sm100_b200/fe_sm100/fe_binding.cpp:31`."""
+    return int(_lib.load().mm_fe_router_ctas(int(m), int(h), int(e), int(topk)))
+
+
+def fe_forward(hidden: torch.Tensor, router_weight: torch.Tensor, x: torch.Tensor, x_sf: torch.Tensor,
+               topk_idx: torch.Tensor, topk_weights: torch.Tensor, workspace: torch.Tensor, mode: int, l2_persist: int = 1):
+    """Router frontend with the reference's argument list (`sm100_b200/fe_sm100/fe_binding.cpp:8-28`): router GEMM,
+    top-8 + softmax over the selected logits, and the token quantisation (mode 2 FP8 / 3 MXFP4 / 4 NVFP4), written into
+    the given views (normally `sym_buffer.x / x_sf / topk_idx / topk_weights`). The checks are the reference's."""
+    lib = _lib.load()
+    if hidden.dim() != 2 or hidden.dtype != torch.bfloat16 or not hidden.is_contiguous():
+        raise RuntimeError('hidden must be a contiguous bf16 [m, h] tensor')
+    if router_weight.dim() != 2 or router_weight.dtype != torch.bfloat16 or not router_weight.is_contiguous():
+        raise RuntimeError('router_weight must be a contiguous bf16 [e, h] tensor')
+    m, h = hidden.shape
+    e, topk = router_weight.size(0), topk_idx.size(1)
+    if router_weight.size(1) != h or not (1 <= m <= 64):
+        raise RuntimeError('router shapes do not match (1 <= m <= 64)')
+    if topk_idx.dtype != torch.int64 or topk_weights.dtype != torch.float32:
+        raise RuntimeError('topk_idx must be int64 and topk_weights float32')
+    if topk_idx.size(0) < m or topk_weights.size(0) < m or x.size(0) < m or x_sf.size(0) < m:
+        raise RuntimeError('output views hold fewer than m rows')
+    row = h if mode == 2 else h // 2
+    sf_row = h // (16 if mode == 4 else 32)
+    if x.stride(0) * x.element_size() != row or x_sf.stride(0) * x_sf.element_size() != sf_row or \
+            not (topk_idx[:m].is_contiguous() and topk_weights[:m].is_contiguous()):
+        raise RuntimeError('output views do not have the row strides of the activation format')
+    nbytes = workspace.numel() * workspace.element_size()
+    _lib.check(lib.mm_fe_forward(hidden.data_ptr(), router_weight.data_ptr(), x.data_ptr(), x_sf.data_ptr(),
+                                 topk_idx.data_ptr(), topk_weights.data_ptr(), workspace.data_ptr(), nbytes, m, h, e, topk,
+                                 int(mode), int(l2_persist), torch.cuda.current_stream().cuda_stream), 'fe_forward')
+
+
+def fe_forward_into_buffer(hidden: torch.Tensor, router_weight: torch.Tensor, sym_buffer: SymmBuffer, workspace: torch.Tensor,
+                           score_mode: int = 0, expert_bias: Optional[torch.Tensor] = None, x_global_scale: float = 1.0):
+    """The frontend with this build's extensions (sigmoid + bias scores, NVFP4 global scale, any token count up to the
+    buffer's capacity), written into `sym_buffer.x / x_sf / topk_idx / topk_weights[:hidden.size(0)]`."""
     lib = _lib.load()
     b = sym_buffer
     if hidden.dtype != torch.bfloat16 or router_weight.dtype != torch.bfloat16:
@@ -360,4 +426,4 @@ def fe_forward(hidden: torch.Tensor, router_weight: torch.Tensor, sym_buffer: Sy
                                expert_bias.data_ptr() if expert_bias is not None else None,
                                hidden.size(0), score_mode, workspace.data_ptr(), float(x_global_scale))
     _lib.check(lib.mm_frontend_launch(ctypes.byref(b.cfg), b.buffer.data_ptr(), ctypes.byref(args),
-                                      torch.cuda.current_stream().cuda_stream), 'fe_forward')
+                                      torch.cuda.current_stream().cuda_stream), 'fe_forward_into_buffer')

@@ -110,6 +110,19 @@ typedef struct mm_frontend_args {
 int mm_get_layout(const mm_config_t* cfg, mm_layout_t* out);
 /* sm100_b200/mega___init__.py:81-111 (weight layout contract) */
 int mm_get_weight_geometry(int32_t act_format, mm_weight_geometry_t* out);
+/* Load-time weight transform as one CUDA copy kernel: `transform_weights_for_mega_moe` (sm100_b200/mega___init__.py:81-111:
+ * gate/up interleave of L1, 4 x 32 transposition of the scale words) fused with the scale-layout step the reference runs
+ * before it (`transform_sf_into_required_layout`, csrc/apis/layout.hpp:14-60: int32 MN-major scale words, or fp32 scales
+ * that are first turned into UE8M0 / E4M3 bytes). w_packed: E2M1 pairs [groups][n][k/2]; sf: int32 words (4 scale bytes of
+ * consecutive K blocks each) or fp32 scales, addressed as sf[g * stride_e + row * stride_n + i * stride_k] in elements of
+ * its type; out_stream: [groups][n/128][k/256][mm_weight_geometry.unit_bytes]. */
+int mm_transform_weights(const void* w_packed, const void* sf, int32_t sf_is_fp32, int64_t sf_stride_e, int64_t sf_stride_n,
+                         int64_t sf_stride_k, int32_t num_groups, int32_t n, int32_t k, int32_t sf_vec, int32_t interleave_gate_up,
+                         void* out_stream, void* stream);
+/* Row-wise cast to packed E2M1 with one fp32 scale per gran_k elements, the arithmetic of `per_token_cast_to_fp4`
+ * (deep_gemm/utils/math.py:85-111). x: bf16 or fp32 [m][k]; packed_out [m][k/2]; sf_out fp32 [m][k/gran_k]. */
+int mm_cast_rows_to_fp4(const void* x, int32_t x_is_bf16, int32_t m, int32_t k, int32_t gran_k, int32_t use_ue8m0,
+                        void* packed_out, float* sf_out, void* stream);
 /* sm100_b200/apis_mega.hpp:544-552 (`get_token_alignment_for_mega_moe`) */
 int32_t mm_get_token_alignment(void);
 /* sm100_b200/apis_mega.hpp:173-358 (`fp8_fp4_mega_moe`, `fp4_fp4_mega_moe`): asynchronous launch on `stream` */
@@ -118,6 +131,18 @@ int mm_mega_moe_launch(const mm_config_t* cfg, const mm_launch_args_t* args, voi
 int mm_frontend_launch(const mm_config_t* cfg, void* buffer, const mm_frontend_args_t* args, void* stream);
 /* sm100_b200/fe_sm100/fe_binding.cpp:8-35 (`fe_workspace_bytes`) */
 int64_t mm_frontend_workspace_bytes(const mm_config_t* cfg);
+/* sm100_b200/fe_sm100/fe_binding.cpp:8-35 (`fe_forward`) over `launch_router_quant_topk_frontend`
+ * (sm100_b200/fe_sm100/fable_frontend.h:48-52), with the reference's argument list: bf16 hidden [m][h], bf16 router
+ * weight [e][h] -> quantised rows x [m][h/2] (mode 3 MXFP4, 4 NVFP4) or [m][h] (mode 2 FP8), scale bytes x_sf
+ * [m][h/32] (h/16 for NVFP4), topk_idx int64 [m][topk], topk_weights float [m][topk]; softmax over the selected
+ * logits, an all-zero row is left unrouted (idx -1, weight 0). m <= 64, topk = 8. `l2_persist` is accepted and ignored. */
+int mm_fe_forward(const void* hidden, const void* router_weight, void* x, void* x_sf, void* topk_idx, void* topk_weights,
+                  void* workspace, int64_t workspace_bytes, int32_t m, int32_t h, int32_t e, int32_t topk, int32_t mode,
+                  int32_t l2_persist, void* stream);
+/* sm100_b200/fe_sm100/fe_binding.cpp:30 (`fe_workspace_bytes(e)`): 256 + 4 * 64 * e * 4 */
+int64_t mm_fe_workspace_bytes(int32_t e);
+/* sm100_b200/fe_sm100/fe_binding.cpp:31 (`fe_router_ctas(m, h, e, topk)`): CTAs of the router-logits kernel */
+int32_t mm_fe_router_ctas(int32_t m, int32_t h, int32_t e, int32_t topk);
 /* Router frontend and layer as ONE persistent kernel (the frontend's outputs still land in the buffer views). */
 int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_t* args,
                                    const mm_frontend_args_t* fe, void* stream);
@@ -134,6 +159,13 @@ int mm_read_device_status(const mm_config_t* cfg, const void* buffer, uint32_t o
  * streamed weight unit found in shared memory by any SM (8, 10, 11, 14: maxima over the SMs; 12, 13: minima).
  * Replaces the `DG_SM100_PHASE_STAMPS_PTR` facility (sm100_b200/sm100_fp4_fp4_mega_moe.cuh:97-128). */
 int mm_read_phase_stamps(const mm_config_t* cfg, const void* buffer, uint64_t out_stamps[32], void* stream);
+/* Synchronises `stream`, then copies the per-SM phase times of the last launch: out[sm * 32 + slot], globaltimer ns,
+ * 0 = not reached. Slots: 0 first instruction, 1 prologue done, 2 own rows listed, 3 row counts known, 4 scheduled,
+ * 5 first weight copy issued, 6 first weight unit landed, 7 first task's tokens staged, 8 first task's MMAs done,
+ * 9 first epilogue done, 10 last L1 epilogue done, 11 first L2 task's rows staged, 12 tasks done, 13 first combine
+ * item written, 14 last combine item written, 15 exit, 16..31 when the SM's weight units 0..15 were found landed. The reference's per-CTA frontend stamps are the model
+ * (sm100_b200/fe_sm100/fable_frontend_device.cuh:46-54). */
+int mm_read_sm_phases(const mm_config_t* cfg, const void* buffer, uint64_t* out_256x32, void* stream);
 /* Development knobs, process-wide, read at every launch. The reference reads its own from DG_SM100_* environment
  * variables (sm100_b200/sm100_fp4_fp4_mega_moe.hpp:215-248). MM_TUNE_KNOBS is a bit mask: 1 the spare warp asks for a
  * live expert's weights (L2 prefetch) as soon as it learns of the expert, 2 every SM lists the rows of this rank's own

@@ -69,8 +69,8 @@ def test_frontend_matches_oracle(fmt, score_mode):
         bias = (0.2 / ranks ** 1.2)[torch.randperm(num_experts, generator=torch.Generator().manual_seed(5))]
     ws = torch.zeros(mm.fe_workspace_bytes(buf), dtype=torch.uint8, device='cuda')
     x_gs = 1.0 / 64.0 if fmt == 'nvfp4' else 1.0
-    mm.fe_forward(x.cuda(), wr.cuda(), buf, ws, score_mode=score_mode,
-                  expert_bias=bias.cuda() if bias is not None else None, x_global_scale=x_gs)
+    mm.fe_forward_into_buffer(x.cuda(), wr.cuda(), buf, ws, score_mode=score_mode,
+                              expert_bias=bias.cuda() if bias is not None else None, x_global_scale=x_gs)
     torch.cuda.synchronize()
     logits_gpu = ws[256:256 + tokens * num_experts * 4].view(torch.float32).view(tokens, num_experts).cpu()
     logits = O.router_logits_device_order(x, wr)
@@ -99,7 +99,8 @@ def test_frontend_then_layer_matches_oracle():
     buf = mm.get_symm_buffer_for_mega_moe(None, e_local, 16, 8, hidden, inter, act_format=fmt)
     l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(w, fmt, 'cuda'))
     ws = torch.zeros(mm.fe_workspace_bytes(buf), dtype=torch.uint8, device='cuda')
-    mm.fe_forward(x.cuda(), wr.cuda(), buf, ws)
+    # the reference's call, argument for argument (`sm100_b200/fe_sm100/test_e2e_b200.py:204-231`): mode 3 = MXFP4
+    mm.fe_forward(x.cuda(), wr.cuda(), buf.x, buf.x_sf, buf.topk_idx, buf.topk_weights, ws, 3, 1)
     y = torch.empty((tokens, hidden), dtype=torch.bfloat16, device='cuda')
     mm.fp4_fp4_mega_moe(y, l1, l2, buf, activation_clamp=10.0, timeout_ms=500.0)
     assert buf.device_status()[0] == 0

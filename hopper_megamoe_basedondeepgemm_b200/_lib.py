@@ -2,7 +2,7 @@
 import ctypes
 import os
 
-from .build import LIB_PATH
+from .build import CHECK_LIB_PATH, LIB_PATH
 
 MM_OK = 0
 FMT = {'mxfp4': 0, 'nvfp4': 1, 'fp8': 2}
@@ -67,18 +67,19 @@ EXPORTS = ('mm_get_layout', 'mm_get_weight_geometry', 'mm_get_token_alignment', 
            'mm_read_device_status', 'mm_read_phase_stamps', 'mm_status_string', 'mm_last_cuda_error',
            'mm_mega_moe_launch_static_scratch', 'mm_set_tuning', 'mm_get_tuning', 'mm_read_sm_phases', 'mm_fe_forward', 'mm_fe_workspace_bytes', 'mm_fe_router_ctas', 'mm_transform_weights', 'mm_cast_rows_to_fp4')
 
-_lib = None
+_libs = {}
 
 
-def load() -> ctypes.CDLL:
-    """Load the compiled library; raises if it has not been built (`python -m <package>.build`)."""
-    global _lib
-    if _lib is not None:
-        return _lib
-    if not os.path.exists(LIB_PATH):
-        raise RuntimeError(f'{LIB_PATH} is missing: build it with `python -m hopper_megamoe_basedondeepgemm_b200.build` '
+def load(check: bool = False) -> ctypes.CDLL:
+    """Load the compiled library; raises if it has not been built (`python -m <package>.build`). `check=True` loads the
+    test build that also carries the CUDA-core cross-check engine."""
+    if check in _libs:
+        return _libs[check]
+    path = CHECK_LIB_PATH if check else LIB_PATH
+    if not os.path.exists(path):
+        raise RuntimeError(f'{path} is missing: build it with `python -m hopper_megamoe_basedondeepgemm_b200.build` '
                            '(nvcc, sm_100a). There is no CPU or eager fallback for this operator.')
-    lib = ctypes.CDLL(LIB_PATH)
+    lib = ctypes.CDLL(path)
     P = ctypes.POINTER
     lib.mm_get_layout.argtypes = [P(MMConfig), P(MMLayout)]
     lib.mm_get_weight_geometry.argtypes = [ctypes.c_int32, P(MMWeightGeometry)]
@@ -107,7 +108,7 @@ def load() -> ctypes.CDLL:
     lib.mm_status_string.argtypes = [ctypes.c_int]
     lib.mm_status_string.restype = ctypes.c_char_p
     lib.mm_last_cuda_error.restype = ctypes.c_char_p
-    _lib = lib
+    _libs[check] = lib
     return lib
 
 

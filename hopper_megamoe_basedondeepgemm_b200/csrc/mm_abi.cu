@@ -291,9 +291,14 @@ int mm_mega_moe_launch(const mm_config_t* cfg, const mm_launch_args_t* a, void* 
     const bool umma = a->engine == MM_ENGINE_UMMA;
     if (cfg->act_format == MM_FMT_FP8)                                     // tensor-core engine only
         return umma ? launch_variant<32, true, false, true>(p, grid, smem_bytes, s) : MM_ERR_UNSUPPORTED;
-    if (cfg->act_format == MM_FMT_MXFP4)
-        return umma ? launch_variant<32, true>(p, grid, smem_bytes, s) : launch_variant<32, false>(p, grid, smem_bytes, s);
-    return umma ? launch_variant<16, true>(p, grid, smem_bytes, s) : launch_variant<16, false>(p, grid, smem_bytes, s);
+#ifdef MM_WITH_CHECK_ENGINE
+    // the CUDA-core cross-check engine is test infrastructure: only the test build of the library carries it
+    if (!umma)
+        return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, false>(p, grid, smem_bytes, s) : launch_variant<16, false>(p, grid, smem_bytes, s);
+#else
+    if (!umma) return MM_ERR_UNSUPPORTED;
+#endif
+    return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, true>(p, grid, smem_bytes, s) : launch_variant<16, true>(p, grid, smem_bytes, s);
 }
 
 int mm_read_sm_phases(const mm_config_t* cfg, const void* buffer, uint64_t* out, void* stream) {

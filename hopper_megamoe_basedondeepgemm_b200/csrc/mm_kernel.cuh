@@ -1058,7 +1058,10 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlStamps)[kStampEntry] = t_first;
         cx.stamp(kStampPrologue);
     }
-    if (tid == 0) cx.sm_phase(kSmPrologue);
+    if (tid == 0) {
+        reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmPhase)[bid * kSmPhaseSlots + kSmEntry] = t_first;
+        cx.sm_phase(kSmPrologue);
+    }
     // The control block and the split-tile counters are touched late, on the critical dependency chain, and by then
     // they have usually been evicted from the L2 by the weight stream of earlier work: ask for their lines now.
     if (warp == 6) {

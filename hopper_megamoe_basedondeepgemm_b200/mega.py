@@ -251,7 +251,7 @@ def _input_region_ptr(sym_buffer: 'SymmBuffer', host_inputs):
 
 def _launch(y, l1_weights, l2_weights, sym_buffer: SymmBuffer, stats, recipe, activation, activation_clamp, fast_math,
             engine='umma', global_scales=(1.0, 1.0, 1.0, 1.0), timeout_ms=0.0, host_inputs=None):
-    lib = _lib.load()
+    lib = _lib.load(check=(engine == 'check'))          # the cross-check engine lives in the test build of the library
     if activation != 'swiglu':
         raise RuntimeError('only the swiglu activation is supported')
     b = sym_buffer

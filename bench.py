@@ -326,6 +326,27 @@ def main():
         phases = {name: round((stamps[i] - stamps[12]) / 1e3, 2) for i, name in sorted(STAMP_NAMES.items()) if stamps[i]}
         return statistics.median(spans), (statistics.median(windows) if windows else None), phases
 
+    SM_PHASE_NAMES = ['entry', 'prologue', 'own_listed', 'counts_known', 'scheduled', 'first_issue', 'first_landed', 'first_staged',
+                      'first_mma_done', 'first_epilogue', 'last_l1_epilogue', 'first_l2_staged', 'tasks_done', 'first_combined',
+                      'combine_done', 'exit']
+
+    def sm_phase_summary():
+        """Per-SM phase times of the latest launch on this rank, relative to its earliest SM entry: {phase: [min, median, max]} us."""
+        ph = buf.sm_phases()[:, :16].double()
+        live = ph[:, 0] > 0
+        if not bool(live.any()):
+            return None
+        ph = ph[live]
+        t0 = ph[:, 0].min()
+        out = {}
+        for i, name in enumerate(SM_PHASE_NAMES):
+            col = ph[:, i]
+            col = col[col >= t0]                           # (a slot no launch has written yet, or a stale earlier one: left out)
+            if col.numel():
+                v = ((col - t0) / 1e3)
+                out[name] = [round(float(v.min()), 2), round(float(v.median()), 2), round(float(v.max()), 2)]
+        return out
+
     def reduce_max(values):
         t = torch.tensor([(-1.0 if v is None else float(v)) for v in values], device='cuda', dtype=torch.float64)
         if world > 1:
@@ -442,6 +463,7 @@ def main():
     check_status('timed region')
     span_us, window_us, phases = device_spans(main_case)
     check_status('span launches')
+    sm_summary = sm_phase_summary()
 
     # event-timing floor: two events with nothing / with a one-element kernel between them (what any launch pays)
     floor = timed(lambda: None, None, 20, 3, 'floor_empty')
@@ -542,7 +564,7 @@ def main():
                 'timing': 'CUDA events around each launch, mean of the timed steps, max over ranks',
                 'median_us': med_us, 'device_span_us_median': span_us,
                 'device_span_definition': 'first instruction of the earliest SM to the exit of the last SM (globaltimer), median of 10 launches, max over ranks',
-                'phases_us_last_launch_rank0': phases, 'wall_s': t_wall,
+                'phases_us_last_launch_rank0': phases, 'sm_phases_us_rank0_min_median_max': sm_summary, 'wall_s': t_wall,
                 'event_floor_us': {'nothing_between_events': statistics.median(floor), 'one_element_kernel': statistics.median(floor_k)},
                 'clocks': clocks, 'gpu_launches': args.steps,
                 'tuning': {k: mm._lib.load().mm_get_tuning(v) for k, v in mm._lib.TUNE.items()},

@@ -59,7 +59,7 @@ class MMStaticArgs(ctypes.Structure):
 
 
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
-TUNE = {'knobs': 0, 'stages': 1, 'prefetch_w1_experts': 2, 'prefetch_w2_experts': 3}
+TUNE = {'knobs': 0, 'stages': 1, 'prefetch_w1_experts': 2, 'prefetch_w2_experts': 3, 'row_cache': 4}
 KNOB_PREFETCH, KNOB_OWN_ROWS, KNOB_EARLY_COMBINE = 1, 2, 4
 
 EXPORTS = ('mm_get_layout', 'mm_get_weight_geometry', 'mm_get_token_alignment', 'mm_mega_moe_launch',

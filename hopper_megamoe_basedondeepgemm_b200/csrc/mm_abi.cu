@@ -26,7 +26,7 @@ int sf_vec_of(int fmt) { return fmt == MM_FMT_NVFP4 ? 16 : 32; }
 
 // development knobs (mm_set_tuning): kernel feature bits, ring depth (0 = chosen from the shared-memory plan), and how
 // many experts' W1 / W2 the scout may prefetch into the L2 in one launch
-int g_tuning[MM_TUNE_COUNT] = {mm::kKnobPrefetch | mm::kKnobOwnRows | mm::kKnobEarlyCombine, 0, 14, 14};
+int g_tuning[MM_TUNE_COUNT] = {mm::kKnobPrefetch | mm::kKnobOwnRows | mm::kKnobEarlyCombine, 0, 14, 14, 1};
 
 int check_config(const mm_config_t* c) {
     if (c == nullptr) return MM_ERR_INVALID_ARGUMENT;
@@ -258,7 +258,16 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.stage_region = p.sm_otile - p.sm_act;
     p.sm_vt = p.sm_otile + mm::kOtileBytes;
     p.sm_xbuf = static_cast<uint32_t>(align_up(p.sm_vt + mm::kVtBytes, 1024));
-    *smem_bytes = (a8 ? p.sm_xbuf + xbytes : p.sm_vt + mm::kVtBytes) + 1024 + 256;
+    size_t used = a8 ? p.sm_xbuf + xbytes : p.sm_vt + mm::kVtBytes;
+    // row cache: up to 16 received rows (tokens + scale bytes) in what the plan leaves free
+    p.rc_row_bytes = static_cast<uint32_t>(L.x_row_bytes + L.x_sf_row_bytes);
+    p.sm_rcache = static_cast<uint32_t>(align_up(used, 128));
+    p.rc_rows = 0;
+    if (g_tuning[MM_TUNE_ROW_CACHE] != 0 && p.sm_rcache + 16ull * p.rc_row_bytes + 1024 + 256 <= 232448 - sizeof(mm::Ctl) - 768) {
+        p.rc_rows = 16;
+        used = p.sm_rcache + 16ull * p.rc_row_bytes;
+    }
+    *smem_bytes = used + 1024 + 256;
     if (static_cast<size_t>(p.T) * p.topk * 4 > p.stage_region) return MM_ERR_UNSUPPORTED;
     return MM_OK;
 }

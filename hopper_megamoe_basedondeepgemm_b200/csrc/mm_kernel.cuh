@@ -76,7 +76,8 @@ constexpr int kCtrlBytes = 8192 + 256 * kSmPhaseSlots * 8;
 enum : uint32_t {
     kKnobPrefetch = 1u,                 // the scout asks for the weights of every expert it learns to be live (L2 prefetch)
     kKnobOwnRows = 2u,                  // rows of this rank's own tokens are listed from topk_idx by every SM (no header wait)
-    kKnobEarlyCombine = 4u              // warps start on the combine as soon as their role ends
+    kKnobEarlyCombine = 4u,             // warps start on the combine as soon as their role ends
+    kKnobRehearse = 8u                  // idle role warps run their code once on made-up tasks before the roles start
 };
 
 // device status codes (low byte of status word 0)
@@ -123,6 +124,7 @@ struct KParams {
     int ndisp;                           // SMs that share the dispatch to one destination rank (1 with the fused frontend)
     uint32_t sm_xbuf; int nab;           // widened-unit buffers (FP8 variant); number of 16-row token staging buffers (1 or 2)
     uint32_t stage_region;               // bytes of the token staging area (tiles + scale slots)
+    uint32_t sm_rcache, rc_rows, rc_row_bytes;   // row cache: received rows (tokens + scale bytes) fetched before the weight stream starts
     unsigned long long timeout_ns;
     uint32_t knobs;                      // kKnob* bits
     uint32_t pf_w1_max, pf_w2_max;       // experts whose W1 / W2 the scout may prefetch in one launch (L2 capacity)
@@ -151,6 +153,7 @@ struct Ctl {
     uint32_t nvalid[4];
     uint32_t rowref[2][kTileTokens];
     uint32_t rowidx[2][kTileTokens];
+    uint32_t rcslot[2][kTileTokens];     // row-cache slot of each row of the task being staged (0xFFFFFFFF: not cached)
     float amax_x[4][kTileTokens];
     uint32_t dry_count[kMaxLocalExperts];   // dummy per-expert counts of the schedule's warm-up call
     uint32_t sfb[4][kTileTokens];        // L1 epilogue: one scale byte per (warp, token), gathered into one flagged word
@@ -215,6 +218,15 @@ struct Ctx {
     // received row i of source rank `src_rank` (flagged words: payload byte b sits at 2 * (b & ~3) + (b & 3))
     __device__ __forceinline__ uint8_t* rx_row(uint32_t src_rank, uint32_t i) const {
         return buf + p.off_rx + static_cast<size_t>(par * p.R + src_rank) * p.rx_region + 32u + static_cast<size_t>(i) * 2u * p.rx_row_bytes;
+    }
+    // Row cache: slots [0, tc) hold this rank's own tokens by token index (fetched at kernel entry), the slots behind
+    // them the rows received from other ranks in receive order. Slot of received row f (source r, token `token`), or
+    // 0xFFFFFFFF when the row is not cached.
+    __device__ __forceinline__ uint32_t rc_slot(uint32_t f, uint32_t r, int32_t token, bool own_cached) const {
+        const uint32_t tc = own_cached ? (static_cast<uint32_t>(p.T) < p.rc_rows ? static_cast<uint32_t>(p.T) : p.rc_rows) : 0u;
+        if (own_cached && r == static_cast<uint32_t>(p.rank)) return static_cast<uint32_t>(token) < tc ? static_cast<uint32_t>(token) : 0xFFFFFFFFu;
+        const uint32_t g = (own_cached && f >= c.rx_prefix[p.rank]) ? f - c.own_cnt : f;     // the own rows are contiguous in receive order
+        return tc + g < p.rc_rows ? tc + g : 0xFFFFFFFFu;
     }
     // one 16 B payload chunk of flagged words at `src` (32 B): polls until both halves carry this launch's flag
     __device__ __forceinline__ bool ll_read(const uint8_t* src, uint32_t flag, uint4& out, uint32_t code, uint32_t detail) const {
@@ -415,29 +427,37 @@ __device__ __forceinline__ void find_rows(Ctl& c, uint32_t* rowref, uint32_t tot
 
 // Two stager warps; warp w stages the tasks with index parity w into staging buffer w, so that two consecutive tasks
 // (e.g. a split tile's share and the whole tile that follows) are fetched concurrently.
-__device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
+// `dry`: a rehearsal on two made-up tasks (one of each type, one row, read from row 0 of the own-rank region of the
+// receive pool and row 0 of the intermediate pool, whatever they hold; every word accepted, no barrier touched): run
+// before the roles start, it leaves this code in the SM's instruction cache, so that the first real task, which sits on
+// the launch's critical path, does not pay for fetching it. What it writes into the staging buffer is overwritten later.
+__device__ __noinline__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane, bool dry, bool own_cached) {
     const KParams& p = cx.p; Ctl& c = cx.c;
-    const uint32_t total = c.rx_prefix[p.R];
+    const uint32_t total = dry ? 0u : c.rx_prefix[p.R];
     uint32_t* rowref = c.rowref[sw];
     uint32_t* rowidx = c.rowidx[sw];
-    if (sw >= c.nab) return;
+    uint32_t* rcslot = c.rcslot[sw];
+    if (!dry && sw >= c.nab) return;
     bool seen_l2 = false;
+    const uint32_t ntasks = dry ? 2u : c.ntasks, step = dry ? 1u : c.nab;
+    const uint32_t act_stride = dry ? 0u : c.act_stride, atom_stride = dry ? kTileTokens * 128u : c.atom_stride;
     #pragma unroll 1
-    for (uint32_t ti = sw; ti < c.ntasks; ti += c.nab) {      // with one staging buffer, stager 0 takes every task
-        const uint32_t t = c.tasks[ti];
+    for (uint32_t ti = dry ? 0u : sw; ti < ntasks; ti += step) {      // with one staging buffer, stager 0 takes every task
+        const uint32_t t = dry ? task_pack(ti, 0u, 0u, 0u) : c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
-        const uint32_t ab = c.nab == 2u ? (ti & 1u) : 0u, use = c.nab == 2u ? (ti >> 1) & 1u : (ti & 1u), ring = ti & 3u;
-        if (!cx.warp_wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty)) return;
+        const uint32_t ab = (!dry && c.nab == 2u) ? (ti & 1u) : 0u, use = c.nab == 2u ? (ti >> 1) & 1u : (ti & 1u), ring = ti & 3u;
+        if (!dry && !cx.warp_wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty)) return;
         find_rows(c, rowref, total, e, mt, lane);
         const uint32_t left = c.exp_count[e] - mt * kTileTokens;
-        const uint32_t nv = left < kTileTokens ? left : kTileTokens;
-        if (lane == 0) c.nvalid[ring] = nv;
+        const uint32_t nv = dry ? 1u : (left < kTileTokens ? left : kTileTokens);
+        if (lane == 0 && !dry) c.nvalid[ring] = nv;
         __syncwarp();
         if (lane < nv) {
-            const uint32_t f = rowref[lane];
+            const uint32_t f = dry ? 0u : rowref[lane];
             uint32_t r = 0;
-            while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
-            const uint32_t i = f - c.rx_prefix[r];
+            while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1] && !dry) ++r;
+            if (dry) r = static_cast<uint32_t>(p.rank);
+            const uint32_t i = dry ? 0u : f - c.rx_prefix[r];
             RowMeta m;
             if (f < kMetaSmemRows) m = c.rx_meta[f];
             else {
@@ -446,21 +466,46 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                 m = RowMeta{0, static_cast<int32_t>(q.y), static_cast<int32_t>(q.z), __uint_as_float(q.w)};
             }
             m.src = static_cast<int32_t>(r);
-            c.row_meta[ring][lane] = m;
+            if (!dry) c.row_meta[ring][lane] = m;
             rowidx[lane] = (r << 24) | i;
+            rcslot[lane] = (dry || p.rc_rows == 0u) ? 0xFFFFFFFFu : cx.rc_slot(f, r, m.token, own_cached);
         }
-        uint8_t* act = cx.smem + p.sm_act + ab * c.act_stride;
+        __syncwarp();
+        uint8_t* act = cx.smem + p.sm_act + ab * act_stride;
         uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
         // Both kinds of rows are flagged words that may still be on their way (received tokens for L1, the L1 epilogues'
         // output of other SMs for L2): a chunk is re-read until its flags match. Received rows carry their scale bytes
         // behind the tokens; intermediate rows keep theirs as one flagged word per (row, L1 tile).
         const uint32_t nchunk = (type ? p.mid_row_bytes : p.x_row_bytes) / 16;             // 16 B chunks of one token row
         const uint32_t per_row = nchunk + (type ? 0u : p.x_sf_row_bytes / 16);
-        const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
+        const uint32_t midrow0 = dry ? 0u : c.mid_base[e] + mt * kTileTokens;
         const uint32_t flag = c.epoch + 1u, wait_code = type ? kErrWaitL1Done : kErrWaitDispatchFlag;
         bool bad = false;
+        // one 16 B payload chunk of row n: token bytes into the swizzled tile, scale bytes into their slots
+        auto put = [&](uint32_t n, uint32_t ci, const uint4& v) {
+            if (ci < nchunk) {
+                *reinterpret_cast<uint4*>(act + (ci >> 3) * atom_stride + sw128_off(n, ci & 7u)) = v;
+            } else {
+                // four scale words: one 16 B slot per (scale word, token), word g of the row at slot g
+                uint8_t* dst = asf + (ci - nchunk) * 4u * 256u + n * 16u;
+                *reinterpret_cast<uint32_t*>(dst) = v.x;
+                *reinterpret_cast<uint32_t*>(dst + 256u) = v.y;
+                *reinterpret_cast<uint32_t*>(dst + 512u) = v.z;
+                *reinterpret_cast<uint32_t*>(dst + 768u) = v.w;
+            }
+        };
         #pragma unroll 1
         for (uint32_t n = 0; n < nv; ++n) {
+            if (type == 0u && !dry && p.rc_rows != 0u) {
+                // a row that was fetched into the row cache before the weight stream started: shared memory to shared memory
+                const uint32_t slot = rcslot[n];
+                if (slot != 0xFFFFFFFFu) {
+                    const uint8_t* src = cx.smem + p.sm_rcache + slot * p.rc_row_bytes;
+                    #pragma unroll 1
+                    for (uint32_t ci = lane; ci < per_row; ci += 32) put(n, ci, *reinterpret_cast<const uint4*>(src + ci * 16u));
+                    continue;
+                }
+            }
             const uint8_t* row_src = type ? cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * 2u * p.mid_row_bytes
                                           : cx.rx_row(rowidx[n] >> 24, rowidx[n] & 0xFFFFFFu);
             // four chunks per lane are in flight before the first store: one memory round trip per 128 chunks of a row
@@ -476,7 +521,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                         const uint32_t ci = base + u * 32;
                         if (ci < per_row) {
                             const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
-                            ok = ok && ll_valid(a, b, flag);
+                            ok = ok && (ll_valid(a, b, flag) || dry);
                             v[u] = ll_data(a, b);
                         }
                     }
@@ -488,16 +533,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                 #pragma unroll
                 for (uint32_t u = 0; u < 4; ++u) {
                     const uint32_t ci = base + u * 32;
-                    if (ci < nchunk) {
-                        *reinterpret_cast<uint4*>(act + (ci >> 3) * c.atom_stride + sw128_off(n, ci & 7u)) = v[u];
-                    } else if (ci < per_row) {
-                        // four scale words: one 16 B slot per (scale word, token), word g of the row at slot g
-                        uint8_t* dst = asf + (ci - nchunk) * 4u * 256u + n * 16u;
-                        *reinterpret_cast<uint32_t*>(dst) = v[u].x;
-                        *reinterpret_cast<uint32_t*>(dst + 256u) = v[u].y;
-                        *reinterpret_cast<uint32_t*>(dst + 512u) = v[u].z;
-                        *reinterpret_cast<uint32_t*>(dst + 768u) = v[u].w;
-                    }
+                    if (ci < per_row) put(n, ci, v[u]);
                 }
             }
             if (type) {
@@ -509,7 +545,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
                     uint2 q;
                     for (;;) {
                         q = ld_volatile_v2(sf_src + w * 8u);
-                        if (q.y == flag || bad) break;
+                        if (q.y == flag || bad || dry) break;
                         if ((++spins & 0x3Fu) == 0u) {
                             if (cx.aborted()) bad = true;
                             else if (cx.expired()) { cx.fail(kErrWaitL1Done, e); bad = true; }
@@ -525,7 +561,7 @@ __device__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane) {
         if (__any_sync(0xffffffffu, bad)) return;
         fence_proxy_async_smem();
         __syncwarp();
-        if (lane == 0) {
+        if (lane == 0 && !dry) {
             mbar_arrive(&c.acts_full[ab]);
             if (ti == 0u) cx.sm_phase(kSmFirstStaged);
             if (type != 0u && !seen_l2) { seen_l2 = true; cx.sm_phase(kSmFirstL2Staged); }
@@ -973,7 +1009,9 @@ __device__ __noinline__ void scout_watch_peers(const Ctx& cx, ScoutState& st, bo
             if (all) pending &= ~(1u << r);
         }
         fresh &= ~st.known;
-        scout_ask(cx, st, fresh, lane, G);
+        // (once every source has been seen the other warps are about to fetch the received rows and to start the real
+        // weight copies: a prefetch issued now would only stand in their way)
+        if (pending != 0u) scout_ask(cx, st, fresh, lane, G);
         st.known |= fresh;
         if ((++passes & 0xFu) == 0u && (cx.aborted() || cx.expired())) break;   // the header wait of the other warps reports the failure
     }
@@ -996,6 +1034,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     constexpr bool kScout = !kFe;
     const bool own_ok = kScout && (p.knobs & kKnobOwnRows) != 0u && static_cast<uint32_t>(p.T) * p.topk <= kOwnCap &&
                         p.inp == buf;      // (inputs in mapped host memory are read by the dispatching SMs only)
+
+    const bool own_cached = own_ok && p.rc_rows != 0u;     // the own tokens go into the row cache at kernel entry
 
     // ---- prologue
     constexpr uint32_t kO = kScout ? kNT - 32u : kNT;        // threads of the warps other than the scout
@@ -1033,6 +1073,33 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
     if (warp == 1) { tmem_alloc(&c.tmem_base, kTmemCols); tmem_relinquish(); tc_fence_before(); }
     if (tid < kMaxLocalExperts) c.exp_count[tid] = 0u;
+    if (own_cached && warp >= 1 && warp <= 3) {
+        // this rank's own tokens (packed row + scale bytes) into the row cache, by token index: the memory system is
+        // still idle now; once the weight stream runs, a small load waits behind megabytes of it
+        const uint32_t tc = static_cast<uint32_t>(p.T) < p.rc_rows ? static_cast<uint32_t>(p.T) : p.rc_rows;
+        const uint32_t xq = p.x_row_bytes / 16u, per_row = p.rc_row_bytes / 16u;
+        #pragma unroll 1
+        for (uint32_t t = warp - 1u; t < tc; t += 3u) {
+            const uint8_t* xs = inp + p.off_x + static_cast<size_t>(t) * p.x_row_bytes;
+            const uint8_t* sf = inp + p.off_x_sf + static_cast<size_t>(t) * p.x_sf_row_bytes;
+            uint8_t* dst = smem + p.sm_rcache + t * p.rc_row_bytes;
+            #pragma unroll 1
+            for (uint32_t base = lane; base < per_row; base += 8 * 32) {
+                uint4 v[8];
+                #pragma unroll
+                for (uint32_t u = 0; u < 8; ++u) {
+                    const uint32_t ci = base + u * 32;
+                    if (ci < xq) v[u] = ld_cg_v4(xs + ci * 16u);
+                    else if (ci < per_row) v[u] = ld_cg_v4(sf + (ci - xq) * 16u);
+                }
+                #pragma unroll
+                for (uint32_t u = 0; u < 8; ++u) {
+                    const uint32_t ci = base + u * 32;
+                    if (ci < per_row) *reinterpret_cast<uint4*>(dst + ci * 16u) = v[u];
+                }
+            }
+        }
+    }
     Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, 0u};
     if (is_scout) {
         // the scout does not wait for the prologue: it lists the own rows and asks for their experts' weights first
@@ -1071,6 +1138,10 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         const size_t cnt_bytes = static_cast<size_t>(2) * p.cnt_per_phase * 4;
         #pragma unroll 1
         for (size_t off = static_cast<size_t>(g) * 128u; off < (cnt_bytes < 65536 ? cnt_bytes : 65536); off += gn * 128u) prefetch_l2_line(buf + p.off_cnt + off);
+    }
+
+    if constexpr (!kFe) {
+        if ((p.knobs & kKnobRehearse) != 0u && !dispatching && (warp == 2 || warp == 3)) role_stager(cx, warp - 2, lane, true, false);
     }
 
     // ---- warm-up of the scheduler's instructions: on the SMs that do not dispatch, warp 6 is idle until the roles start,
@@ -1268,6 +1339,55 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
     bar_sync(kBarMain, kO);
 
+    // ---- the rows received from other ranks go into the row cache (one warp per row, warps 1.. of this group) while
+    //      warp 0 builds the schedule: the bulk copies of the weight stream, which start right after, would make these
+    //      small loads wait behind them
+    if (warp != 0 && p.rc_rows != 0u && total <= kMetaCap && !cx.aborted()) {
+        constexpr uint32_t kFillWarps = kO / 32u - 1u;
+        const uint32_t per_row = p.rc_row_bytes / 16u;
+        const uint32_t wi = warp - 1u;                                   // (the scout is the last warp: not in this group)
+        uint32_t k = 0;
+        #pragma unroll 1
+        for (uint32_t f = 0; f < total; ++f) {
+            uint32_t r = 0;
+            while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
+            if (own_cached && r == static_cast<uint32_t>(p.rank)) continue;
+            const uint32_t slot = cx.rc_slot(f, r, 0, own_cached);
+            if (slot == 0xFFFFFFFFu) break;                              // slots grow with f: nothing further fits
+            if (k++ % kFillWarps != wi) continue;
+            const uint8_t* row_src = cx.rx_row(r, f - c.rx_prefix[r]);
+            uint8_t* dst = smem + p.sm_rcache + slot * p.rc_row_bytes;
+            bool bad = false;
+            #pragma unroll 1
+            for (uint32_t base = lane; base < per_row && !bad; base += 4 * 32) {
+                uint4 v[4];
+                uint32_t spins = 0;
+                bool ok;
+                do {
+                    ok = true;
+                    #pragma unroll
+                    for (uint32_t u = 0; u < 4; ++u) {
+                        const uint32_t ci = base + u * 32;
+                        if (ci < per_row) {
+                            const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
+                            ok = ok && ll_valid(a, b, flag_rx);
+                            v[u] = ll_data(a, b);
+                        }
+                    }
+                    if (!ok && (++spins & 0x3Fu) == 0u) {
+                        if (cx.aborted()) bad = true;
+                        else if (cx.expired()) { cx.fail(kErrWaitDispatchFlag, r); bad = true; }
+                    }
+                } while (!ok && !bad);
+                #pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t ci = base + u * 32;
+                    if (ci < per_row && !bad) *reinterpret_cast<uint4*>(dst + ci * 16u) = v[u];
+                }
+            }
+        }
+    }
+
     // ---- schedule. 16-token tiles of the active experts, expert-major: M of them. Every SM derives its own task list
     //      (L1 tasks, then L2 tasks) in closed form from the per-expert counts.
     if (warp == 0 && !cx.aborted()) {
@@ -1292,7 +1412,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (!cx.aborted()) {
         if (warp == 0) role_loader(cx);
         else if (warp == 1) { if constexpr (kUmma) role_mma<kVec, kA8>(cx, lane); }
-        else if (warp < 4) role_stager(cx, warp - 2, lane);
+        else if (warp < 4) role_stager(cx, warp - 2, lane, false, own_cached);
         else if (warp < 8) role_epilogue<kVec, kUmma, kA8>(cx, tid - 128);
         else { if constexpr (kA8) role_expander(cx, tid - kThreads); }
     }

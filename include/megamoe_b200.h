@@ -169,10 +169,12 @@ int mm_read_sm_phases(const mm_config_t* cfg, const void* buffer, uint64_t* out_
 /* Development knobs, process-wide, read at every launch. The reference reads its own from DG_SM100_* environment
  * variables (sm100_b200/sm100_fp4_fp4_mega_moe.hpp:215-248). MM_TUNE_KNOBS is a bit mask: 1 the spare warp asks for a
  * live expert's weights (L2 prefetch) as soon as it learns of the expert, 2 every SM lists the rows of this rank's own
- * tokens from topk_idx instead of waiting for the own-rank header line, 4 warps start the combine when their role ends. */
+ * tokens from topk_idx instead of waiting for the own-rank header line, 4 warps start the combine when their role ends,
+ * 8 the token-staging warps rehearse their code on made-up tasks while the dispatch is in flight. */
 enum mm_tuning_key { MM_TUNE_KNOBS = 0, MM_TUNE_STAGES = 1 /* ring depth, 0 = default */,
                      MM_TUNE_PREFETCH_W1_EXPERTS = 2, MM_TUNE_PREFETCH_W2_EXPERTS = 3 /* experts prefetched per launch at most */,
-                     MM_TUNE_COUNT = 4 };
+                     MM_TUNE_ROW_CACHE = 4 /* 1: received rows are fetched into shared memory before the weight stream starts */,
+                     MM_TUNE_COUNT = 5 };
 int mm_set_tuning(int32_t key, int32_t value);
 int32_t mm_get_tuning(int32_t key);
 

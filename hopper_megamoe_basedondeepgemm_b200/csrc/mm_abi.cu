@@ -126,6 +126,8 @@ int mm_get_layout(const mm_config_t* c, mm_layout_t* out) {
     out->cnt_per_phase = (out->mid_rows / mm::kTileTokens) * n_max;
     out->off_red = take(256 /* SMs */ * 2 /* phases */ * 2 /* slots */ * mm::kTileTokens * mm::kTileRows * 4);
     out->off_cnt = take(2 * out->cnt_per_phase * 4);
+    // partial router logits of the fused frontend: 16 B per (token, expert), flagged with the launch number
+    out->off_logits = take((t_max < mm::kFeMaxFusedTokens ? t_max : mm::kFeMaxFusedTokens) * c->num_experts * 16);
     out->total_bytes = off;
     return MM_OK;
 }
@@ -322,7 +324,7 @@ int mm_read_sm_phases(const mm_config_t* cfg, const void* buffer, uint64_t* out,
 
 int64_t mm_frontend_workspace_bytes(const mm_config_t* cfg) {
     if (cfg == nullptr) return -1;
-    return static_cast<int64_t>(cfg->num_max_tokens_per_rank) * cfg->num_experts * 4 + 256;
+    return static_cast<int64_t>(cfg->num_max_tokens_per_rank) * cfg->num_experts * 16 + 256;
 }
 
 int mm_frontend_launch(const mm_config_t* cfg, void* buffer, const mm_frontend_args_t* fe, void* stream) {
@@ -357,7 +359,7 @@ int mm_frontend_launch(const mm_config_t* cfg, void* buffer, const mm_frontend_a
     mm::frontend_logits_kernel<<<grid, 256, 0, s>>>(q);
     MM_CUDA(cudaGetLastError());
     const int sel_blocks = (q.T + 3) / 4;
-    mm::frontend_select_quant_kernel<<<sel_blocks, 128, q.E * 4 * 4, s>>>(q);
+    mm::frontend_select_quant_kernel<<<sel_blocks, 128, q.E * 2 * 4 * 4, s>>>(q);
     MM_CUDA(cudaGetLastError());
     return MM_OK;
 }
@@ -421,7 +423,7 @@ int mm_fe_forward(const void* hidden, const void* router_weight, void* x, void* 
     if (topk != 8 || e > 1024) return MM_ERR_UNSUPPORTED;
     if (e < topk) return MM_ERR_INVALID_ARGUMENT;
     if (mode < 2 || mode > 4) return MM_ERR_UNSUPPORTED;          // 2 FP8 / 3 MXFP4 / 4 NVFP4 (0 and 1 are Hopper formats)
-    if (workspace_bytes < 256 + static_cast<int64_t>(m) * e * 4) return MM_ERR_INVALID_ARGUMENT;
+    if (workspace_bytes < 256 + static_cast<int64_t>(m) * e * 16) return MM_ERR_INVALID_ARGUMENT;
     int dev = 0, grid = 0;
     MM_CUDA(cudaGetDevice(&dev));
     MM_CUDA(cudaDeviceGetAttribute(&grid, cudaDevAttrMultiProcessorCount, dev));
@@ -440,7 +442,7 @@ int mm_fe_forward(const void* hidden, const void* router_weight, void* x, void* 
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     mm::frontend_logits_kernel<<<grid, 256, 0, s>>>(q);
     MM_CUDA(cudaGetLastError());
-    mm::frontend_select_quant_kernel<<<(m + 3) / 4, 128, q.E * 4 * 4, s>>>(q);
+    mm::frontend_select_quant_kernel<<<(m + 3) / 4, 128, q.E * 2 * 4 * 4, s>>>(q);
     MM_CUDA(cudaGetLastError());
     return MM_OK;
 }
@@ -457,7 +459,8 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     if (cfg->num_experts < cfg->num_topk) return MM_ERR_INVALID_ARGUMENT;      // fewer experts than routes per token
     if (fe->score_mode == 1 && fe->expert_bias == nullptr) return MM_ERR_INVALID_ARGUMENT;
     const bool a8 = cfg->act_format == MM_FMT_FP8;
-    if (static_cast<size_t>(cfg->num_experts) * 4 * ((mm::kThreads + (a8 ? mm::kNumExpThreads : 0)) / 32) > p.stage_region) return MM_ERR_UNSUPPORTED;
+    if (static_cast<size_t>(cfg->num_experts) * 2 * 4 * ((mm::kThreads + (a8 ? mm::kNumExpThreads : 0)) / 32) > p.stage_region) return MM_ERR_UNSUPPORTED;
+    if (fe->num_tokens > mm::kFeMaxFusedTokens) return MM_ERR_UNSUPPORTED;
     mm_layout_t L;
     mm_get_layout(cfg, &L);
     uint8_t* b = static_cast<uint8_t*>(a->buffer);
@@ -465,7 +468,7 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     q.hidden = static_cast<const __nv_bfloat16*>(fe->hidden_states);
     q.router_w = static_cast<const __nv_bfloat16*>(fe->router_weight);
     q.bias = fe->expert_bias;
-    q.logits = reinterpret_cast<float*>(static_cast<uint8_t*>(fe->workspace) + 256);
+    q.logits = reinterpret_cast<float*>(b + L.off_logits);       // inside the buffer: `mm_reset` clears the flagged records with it
     q.arrive = nullptr;
     q.T = fe->num_tokens; q.H = cfg->hidden; q.E = cfg->num_experts; q.topk = cfg->num_topk;
     q.score_mode = fe->score_mode; q.fmt = cfg->act_format;

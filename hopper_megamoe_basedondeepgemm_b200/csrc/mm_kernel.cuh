@@ -65,7 +65,6 @@ constexpr int kOwnCap = 128;            // routed rows of this rank's own tokens
 constexpr int kCtrlEpoch = 0;           // u32[256] one launch counter per SM
 constexpr int kCtrlStatus = 1024;       // u32[16]
 constexpr int kCtrlStamps = 2048;       // u64[32] phase stamps
-constexpr int kCtrlFeWords = 3072;      // u32[256] per-SM word: launch number once the SM has published its router logits
 constexpr int kCtrlSmEntry = 4096;      // u64[256] per-SM time of the kernel's first instruction
 constexpr int kCtrlSmWFirst = 6144;     // u64[256] per-SM time of the first weight request (prefetch or load); ~0: none
 constexpr int kSmPhaseSlots = 32;       // per SM: 16 phase times, then the landing times of its first 16 weight units
@@ -1156,33 +1155,23 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         }
     }
 
-    // ---- router frontend (optional): all SMs compute logits; the dispatching SMs select the top-8 of every token
+    // ---- router frontend (optional): all SMs compute partial logits (one memory round trip per item) and publish them
+    //      as flagged records; the dispatching SMs poll the records of a token, select its top-8 and weights. No barrier
+    //      and no arrival counter in between: the selecting warps wait for exactly the values they read.
     if constexpr (kFe) {
-        fe_logits_items(p.fe, bid * (kNT / 32) + warp, G * (kNT / 32), lane);
-        bar_sync(kBarMain, kO);
-        // Every SM publishes a word with this launch's number once its logits are written; the selecting SMs wait for
-        // all G words (per-launch values: launches of the other variants in between leave nothing to catch up with).
-        uint32_t* few = ctrl32 + kCtrlFeWords / 4;
-        if (tid == 0) st_release_gpu(few + bid, epoch + 1u);
+        const uint32_t fe_flag = epoch + 1u;
+        fe_logits_items(p.fe, bid * (kNT / 32) + warp, G * (kNT / 32), lane, fe_flag);
         if (bid < static_cast<uint32_t>(p.R)) {
-            if (warp == 0) {
-                uint32_t spins = 0;
-                for (;;) {
-                    bool ok = true;
-                    for (uint32_t g = lane; g < G; g += 32) ok = ok && ld_acquire_gpu(few + g) == epoch + 1u;
-                    if (__all_sync(0xffffffffu, ok)) break;
-                    if ((++spins & 0x3Fu) == 0u) {
-                        if (cx.aborted()) break;
-                        if (cx.expired()) { if (lane == 0) cx.fail(kErrWaitFrontend); break; }
-                    }
-                }
-            }
-            bar_sync(kBarMain, kO);
-            float* sc = reinterpret_cast<float*>(smem + p.sm_act) + warp * p.fe.E;
+            float* sc = reinterpret_cast<float*>(smem + p.sm_act) + warp * 2 * p.fe.E;
+            auto give_up = [&]() -> bool {
+                if (cx.aborted()) return true;
+                if (cx.expired()) { cx.fail(kErrWaitFrontend); return true; }
+                return false;
+            };
             #pragma unroll 1
             for (uint32_t t = warp; t < static_cast<uint32_t>(p.T); t += kNT / 32) {
                 const bool nz = fe_row_nonzero(p.fe.hidden + static_cast<size_t>(t) * p.H, p.H, lane);
-                fe_select_token(p.fe, t, sc, nz, lane);
+                if (!fe_select_token(p.fe, t, sc, nz, lane, fe_flag, give_up)) break;
             }
             __threadfence();                 // the routing written above is read by other SMs of this launch (combine)
             bar_sync(kBarMain, kO);
@@ -1230,16 +1219,17 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                       make_uint4(ent & 0xFFu, tok, slot, __float_as_uint(tw[tok * p.topk + slot])), flag);
         }
         if constexpr (kFe) {
-            // quantise the tokens this SM is about to send into the x / x_sf views (the same bytes whichever SM writes them)
+            // quantise the tokens this SM sends: into the x / x_sf views (the same bytes whichever SM writes them) and, from
+            // the same registers, into the destination's receive pool
             #pragma unroll 1
             for (uint32_t i = warp; i < cnt; i += kCopyWarps) {
                 const uint32_t tok = dlist[i] >> 16;
                 fe_quant_token(p.fe.hidden + static_cast<size_t>(tok) * p.H, p.H, kA8 ? 2 : (kVec == 32 ? 0 : 1), p.fe.x_gs,
                                buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes,
-                               buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes, lane);
+                               buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes, lane,
+                               dst_base + static_cast<size_t>(i) * 2u * p.rx_row_bytes, flag, static_cast<uint32_t>(p.x_row_bytes));
             }
-            bar_sync(kBarCopy, kCopyWarps * 32);
-        }
+        } else {
         // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (eight in flight: one memory round trip for
         // a row of up to 4 KB)
         #pragma unroll 1
@@ -1263,6 +1253,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                     if (ci < nchunk) st_ll_16B(dst + ci * 32u, v[u], flag);
                 }
             }
+        }
         }
         bar_sync(kBarCopy, kCopyWarps * 32);
     }

@@ -56,6 +56,7 @@ typedef struct mm_layout {
                                   {2 bf16, launch flag}: 4 bytes per element */
     int64_t off_red;           /* [256 SMs][2 phases][2][16][128] float partial sums of weight tiles split between SMs (local) */
     int64_t off_cnt;           /* [2 phases][cnt_per_phase] uint32 contributors that have parked their part of a tile (local) */
+    int64_t off_logits;        /* [min(T_max, 256)][num_experts] 16 B records {half logit, launch flag} x 2 of the fused router frontend */
     int64_t x_row_bytes, x_sf_row_bytes;
     int64_t rx_row_bytes, rx_cap_rows;
     int64_t mid_rows, mid_row_bytes, mid_sf_row_bytes;
@@ -102,7 +103,8 @@ typedef struct mm_frontend_args {
     const float* expert_bias;        /* optional float [num_experts] (score_mode 1) */
     int32_t num_tokens;
     int32_t score_mode;              /* 0: softmax over the selected logits; 1: sigmoid + bias selection, renormalised */
-    void* workspace;                 /* mm_frontend_workspace_bytes() bytes of device memory */
+    void* workspace;                 /* mm_frontend_workspace_bytes() bytes of device memory (partial logits of the two-kernel frontend;
+                                        the single-kernel path keeps its own inside the buffer and only requires it non-NULL) */
     float x_global_scale;
 } mm_frontend_args_t;
 

@@ -488,12 +488,13 @@ def cosine(a: torch.Tensor, b: torch.Tensor) -> float:
 def router_logits_device_order(x: torch.Tensor, router_w: torch.Tensor) -> torch.Tensor:
     """bf16 router logits with the summation order of this build's frontend kernel, bit for bit.
 
-    The reference's GEMV also fixes an order (fp32 FMA chain per lane, butterfly, one bf16 rounding,
-    `sm100_b200/fe_sm100/fable_frontend_sm100.cu:610-740`); its value-level contract is the torch rule of
-    `router_reference`. Order used here: lane l of 32 owns the 8-element chunks l, l + 32, ... of K and runs one fused
-    multiply-add chain over them; the 32 partial sums are combined by a butterfly (xor 16, 8, 4, 2, 1); one rounding
-    to bf16; -0.0 becomes +0.0. The fused multiply-add is evaluated in float64 (the product of two bf16 values and
-    the sum with an fp32 accumulator are exact there) and rounded once to fp32.
+    The reference's GEMV also fixes an order (fp32 FMA chain per lane, butterfly, K parts summed in order, one bf16
+    rounding, `sm100_b200/fe_sm100/fable_frontend_sm100.cu:610-740`); its value-level contract is the torch rule of
+    `router_reference`. Order used here: K is cut into two halves of ceil(K / 16) 8-element chunks; inside a half,
+    lane l of 32 owns the chunks l, l + 32, ... and runs one fused multiply-add chain over them; the 32 partial sums
+    are combined by a butterfly (xor 16, 8, 4, 2, 1); first half + second half in fp32; one rounding to bf16; -0.0
+    becomes +0.0. The fused multiply-add is evaluated in float64 (the product of two bf16 values and the sum with an
+    fp32 accumulator are exact there) and rounded once to fp32.
     """
     import numpy as np
     xf = x.float().numpy().astype(np.float64)
@@ -501,17 +502,23 @@ def router_logits_device_order(x: torch.Tensor, router_w: torch.Tensor) -> torch
     t, h = xf.shape
     e = wf.shape[0]
     nchunk = h // 8
-    acc = np.zeros((t, e, 32), dtype=np.float32)
-    for c0 in range(0, nchunk, 32):
-        lanes = min(32, nchunk - c0)
-        for k in range(8):
-            cols = (c0 + np.arange(lanes)) * 8 + k
-            prod = xf[:, None, cols] * wf[None, :, cols]
-            acc[:, :, :lanes] = (prod + acc[:, :, :lanes].astype(np.float64)).astype(np.float32)
+    half = (nchunk + 1) // 2
     idx = np.arange(32)
-    for o in (16, 8, 4, 2, 1):
-        acc = (acc + acc[:, :, idx ^ o]).astype(np.float32)
-    logits = torch.from_numpy(acc[:, :, 0].copy()).to(torch.bfloat16)
+    parts = []
+    for c_lo in (0, half):
+        c_hi = min(nchunk, c_lo + half)
+        acc = np.zeros((t, e, 32), dtype=np.float32)
+        for c0 in range(c_lo, c_hi, 32):
+            lanes = min(32, c_hi - c0)
+            for k in range(8):
+                cols = (c0 + np.arange(lanes)) * 8 + k
+                prod = xf[:, None, cols] * wf[None, :, cols]
+                acc[:, :, :lanes] = (prod + acc[:, :, :lanes].astype(np.float64)).astype(np.float32)
+        for o in (16, 8, 4, 2, 1):
+            acc = (acc + acc[:, :, idx ^ o]).astype(np.float32)
+        parts.append(acc[:, :, 0].copy())
+    total = (parts[0] + parts[1]).astype(np.float32)
+    logits = torch.from_numpy(total).to(torch.bfloat16)
     return (logits.float() + 0.0).to(torch.bfloat16)
 
 

@@ -72,7 +72,9 @@ def test_frontend_matches_oracle(fmt, score_mode):
     mm.fe_forward_into_buffer(x.cuda(), wr.cuda(), buf, ws, score_mode=score_mode,
                               expert_bias=bias.cuda() if bias is not None else None, x_global_scale=x_gs)
     torch.cuda.synchronize()
-    logits_gpu = ws[256:256 + tokens * num_experts * 4].view(torch.float32).view(tokens, num_experts).cpu()
+    # the workspace holds 16 B per (token, expert): {first-half sum, flag, second-half sum, flag}
+    parts = ws[256:256 + tokens * num_experts * 16].view(torch.float32).view(tokens, num_experts, 4).cpu()
+    logits_gpu = (parts[..., 0] + parts[..., 2]).to(torch.bfloat16).float() + 0.0
     logits = O.router_logits_device_order(x, wr)
     assert torch.equal(logits_gpu, logits.float())                    # bit-exact logits
     idx, w = O.route_from_logits(logits, x, 8, 'softmax' if score_mode == 0 else 'sigmoid_bias', bias)

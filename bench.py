@@ -328,11 +328,12 @@ def main():
 
     SM_PHASE_NAMES = ['entry', 'prologue', 'own_listed', 'counts_known', 'scheduled', 'first_issue', 'first_landed', 'first_staged',
                       'first_mma_done', 'first_epilogue', 'last_l1_epilogue', 'first_l2_staged', 'tasks_done', 'first_combined',
-                      'combine_done', 'exit']
+                      'combine_done', 'exit', 'rows_cached']
 
     def sm_phase_summary():
         """Per-SM phase times of the latest launch on this rank, relative to its earliest SM entry: {phase: [min, median, max]} us."""
-        ph = buf.sm_phases()[:, :16].double()
+        raw = buf.sm_phases()
+        ph = torch.cat([raw[:, :16], raw[:, 31:32]], dim=1).double()
         live = ph[:, 0] > 0
         if not bool(live.any()):
             return None
@@ -444,6 +445,42 @@ def main():
         rows_back = sum(int((dest[r] == rank).sum()) for r in range(world) if r != rank)
         return int(rows_out * 2 * int(L.rx_row_bytes) + (world - 1) * 32 + rows_back * HIDDEN * 4)
 
+    def steady_state(case, steps=48):
+        """The same workload without the L2 flush, with the routed experts rotating from step to step (six disjoint groups
+        of eight per rank: 300 MB of weights, so a group's weights have left the 126 MB L2 before it comes round again,
+        while the kernel's code stays cached): what consecutive layers of a serving loop see. (event us, span us)."""
+        variants = [W.balanced_routing(case.T, rank, n, num_experts, TOPK, token_offset=8 * k if n > 1 else k, device='cuda')[0]
+                    for k in range(6)]
+        starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        ends = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
+        spans = []
+        for _ in range(20):
+            flush.zero_()
+        for i in range(6 + steps):
+            case.write_inputs()
+            if case.T:
+                buf.topk_idx[:case.T].copy_(variants[i % 6])
+            if world > 1:
+                dist.all_reduce(align)
+            if i >= 6:
+                starts[i - 6].record()
+            case.launch()
+            if i >= 6:
+                ends[i - 6].record()
+        torch.cuda.synchronize()
+        ev = [a.elapsed_time(b) * 1e3 for a, b in zip(starts, ends)]
+        for i in range(8):
+            case.write_inputs()
+            if case.T:
+                buf.topk_idx[:case.T].copy_(variants[i % 6])
+            if world > 1:
+                dist.all_reduce(align)
+            case.launch()
+            st_ = buf.phase_stamps()
+            spans.append((st_[8] - st_[12]) / 1e3)
+        case.write_inputs()
+        return sum(ev) / len(ev), statistics.median(spans)
+
     main_case = HiddenCase(main_tokens) if args.from_hidden else Case(main_tokens)
     main_case.write_inputs()
     sampler = ClockSampler(local)
@@ -503,6 +540,12 @@ def main():
     e2e_copy_us = sum(es_copy) / len(es_copy)
     e2e_map_us = sum(es_map) / len(es_map) if es_map else None
     mean_us, med_us, span_us, window_us, e2e_copy_us, e2e_map_us = reduce_max([mean_us, med_us, span_us, window_us, e2e_copy_us, e2e_map_us])
+
+    ss_ev = ss_span = None
+    if not args.from_hidden:
+        ss_ev, ss_span = steady_state(main_case)
+        check_status('steady-state region')
+        ss_ev, ss_span = reduce_max([ss_ev, ss_span])
 
     par = None if (args.no_parity or args.from_hidden) else parity(main_case)
 
@@ -566,6 +609,10 @@ def main():
                 'device_span_definition': 'first instruction of the earliest SM to the exit of the last SM (globaltimer), median of 10 launches, max over ranks',
                 'phases_us_last_launch_rank0': phases, 'sm_phases_us_rank0_min_median_max': sm_summary, 'wall_s': t_wall,
                 'event_floor_us': {'nothing_between_events': statistics.median(floor), 'one_element_kernel': statistics.median(floor_k)},
+                'steady_state_no_flush': None if ss_ev is None else {
+                    'event_us': ss_ev, 'device_span_us': ss_span,
+                    'what': 'no L2 flush between steps, routed experts rotate over six disjoint groups (300 MB of weights per rank, '
+                            'more than the L2 holds): the weights still come from HBM, the kernel code stays cached'},
                 'clocks': clocks, 'gpu_launches': args.steps,
                 'tuning': {k: mm._lib.load().mm_get_tuning(v) for k, v in mm._lib.TUNE.items()},
                 'e2e': {'value': e2e_us, 'unit': 'us', 'mode': e2e_mode, 'h2d_bytes_per_step': h2d,

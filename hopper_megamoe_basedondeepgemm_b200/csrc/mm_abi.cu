@@ -261,13 +261,18 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.sm_vt = p.sm_otile + mm::kOtileBytes;
     p.sm_xbuf = static_cast<uint32_t>(align_up(p.sm_vt + mm::kVtBytes, 1024));
     size_t used = a8 ? p.sm_xbuf + xbytes : p.sm_vt + mm::kVtBytes;
-    // row cache: up to 16 received rows (tokens + scale bytes) in what the plan leaves free
+    // token region: the first 16 received rows (tokens + scale bytes) are fetched into what the plan leaves free, either as
+    // one swizzled token tile with its scale slots (launches with at most 16 received rows) or as a plain row cache
     p.rc_row_bytes = static_cast<uint32_t>(L.x_row_bytes + L.x_sf_row_bytes);
-    p.sm_rcache = static_cast<uint32_t>(align_up(used, 128));
+    p.sm_rcache = static_cast<uint32_t>(align_up(used, 1024));
     p.rc_rows = 0;
-    if (g_tuning[MM_TUNE_ROW_CACHE] != 0 && p.sm_rcache + 16ull * p.rc_row_bytes + 1024 + 256 <= 232448 - sizeof(mm::Ctl) - 768) {
-        p.rc_rows = 16;
-        used = p.sm_rcache + 16ull * p.rc_row_bytes;
+    {
+        const size_t as_cache = 16ull * p.rc_row_bytes, as_tile = static_cast<size_t>(p.act_bytes) + p.asf_bytes;
+        const size_t region = as_cache > as_tile ? as_cache : as_tile;
+        if (g_tuning[MM_TUNE_ROW_CACHE] != 0 && !a8 && p.sm_rcache + region + 1024 + 256 <= 232448 - sizeof(mm::Ctl) - 768) {
+            p.rc_rows = 16;
+            used = p.sm_rcache + region;
+        }
     }
     *smem_bytes = used + 1024 + 256;
     if (static_cast<size_t>(p.T) * p.topk * 4 > p.stage_region) return MM_ERR_UNSUPPORTED;

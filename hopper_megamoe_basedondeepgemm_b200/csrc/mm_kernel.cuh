@@ -51,11 +51,14 @@ constexpr uint32_t kBarCopy = 2;         // named barrier of the warps that disp
 // four named barriers, each used once per launch: kBarPrologue (the scout arrives without waiting, the others wait),
 // kBarOwn (the scout arrives when its list of own rows is written; the others wait for it), kBarGo (the others arrive
 // after the prologue; the scout waits before it uses the launch number), kBarSched (the others arrive when the task
-// list is written; the scout waits, then takes up its role). kBarMain synchronises the other warps among themselves.
-constexpr uint32_t kBarOwn = 3, kBarGo = 4, kBarSched = 5, kBarMain = 6, kBarPrologue = 7;
+// list is written; the scout waits, then takes up its role). kBarMain synchronises the other warps among themselves;
+// after the received rows' records are scanned, only warps 0 and 1 go on to the schedule (kBarPost is theirs) and arrive
+// on kBarSched, where all other warps wait.
+constexpr uint32_t kBarOwn = 3, kBarGo = 4, kBarSched = 5, kBarMain = 6, kBarPrologue = 7, kBarPost = 8;
 constexpr int kNumExpThreads = 256;      // FP8-activation variant: warps 8..15 widen the packed E2M1 weights to 8-bit containers
 constexpr uint32_t kXbufBytes = 2 * kUnitWBytes + 1024;   // one widened unit + its two scale planes
 constexpr uint32_t kTmemCols = 128;
+constexpr uint32_t kFillWarps = 5;       // warps 2..6 fetch the received rows into shared memory while the schedule is built
 constexpr uint32_t kOtileBytes = 4096;
 constexpr uint32_t kVtBytes = kTileTokens * kTileRows * 4;   // fp32 accumulators of one task, token-major
 
@@ -98,7 +101,8 @@ enum : int {
 enum SmPhase : int {
     kSmEntry = 0, kSmPrologue = 1, kSmOwnListed = 2, kSmCountsKnown = 3, kSmScheduled = 4, kSmFirstIssue = 5,
     kSmFirstLanded = 6, kSmFirstStaged = 7, kSmFirstMmaDone = 8, kSmFirstEpilogue = 9, kSmLastL1Epilogue = 10,
-    kSmFirstL2Staged = 11, kSmTasksDone = 12, kSmFirstCombined = 13, kSmCombineDone = 14, kSmExit = 15
+    kSmFirstL2Staged = 11, kSmTasksDone = 12, kSmFirstCombined = 13, kSmCombineDone = 14, kSmExit = 15,
+    kSmRowsCached = 31 /* a received row has been copied into the row cache (the latest such copy) */
 };
 
 struct RowMeta { int32_t src, token, slot; float weight; };
@@ -134,11 +138,14 @@ struct Ctl {
     uint64_t full[kMaxStages], empty[kMaxStages];
     uint64_t acts_full[2], acts_empty[2], tmem_full[2], tmem_empty[2];
     uint64_t xfull[2], xempty[2];        // FP8-activation variant: widened weight units
+    uint64_t tile_full;                  // decode mode: the shared token tile is complete (one arrival per filling warp)
     uint32_t tmem_base, epoch, abort_flag, ntasks;
     uint32_t rx_count[kMaxRanks], rx_prefix[kMaxRanks + 1];
     uint32_t exp_count[kMaxLocalExperts], mid_base[kMaxLocalExperts];
     uint32_t nt1, nt2, dcount, own_cnt;
-    uint32_t comb_next, issued, pad1, pad2; // next combine item of this SM; weight units the loader has issued
+    uint32_t comb_next, issued, decode, pad2; // next combine item of this SM; weight units the loader has issued; decode mode (see below)
+    uint32_t n1_tasks, padn[3];          // L1 tasks at the head of this SM's list
+    uint32_t epi_nv[2], epi_dcol[2];     // per accumulator: valid rows of the task and (decode mode) the first accumulator column of its expert
     // token staging geometry of this launch: with room for one 16-row buffer only, launches whose experts all have at
     // most 8 rows split it into two 8-row buffers (the MMA then reads rows 8..15 from rows 0..7: stride 0 between the
     // 8-row groups; those accumulator columns are never used)
@@ -218,15 +225,15 @@ struct Ctx {
     __device__ __forceinline__ uint8_t* rx_row(uint32_t src_rank, uint32_t i) const {
         return buf + p.off_rx + static_cast<size_t>(par * p.R + src_rank) * p.rx_region + 32u + static_cast<size_t>(i) * 2u * p.rx_row_bytes;
     }
-    // Row cache: slots [0, tc) hold this rank's own tokens by token index (fetched at kernel entry), the slots behind
-    // them the rows received from other ranks in receive order. Slot of received row f (source r, token `token`), or
-    // 0xFFFFFFFF when the row is not cached.
-    __device__ __forceinline__ uint32_t rc_slot(uint32_t f, uint32_t r, int32_t token, bool own_cached) const {
-        const uint32_t tc = own_cached ? (static_cast<uint32_t>(p.T) < p.rc_rows ? static_cast<uint32_t>(p.T) : p.rc_rows) : 0u;
-        if (own_cached && r == static_cast<uint32_t>(p.rank)) return static_cast<uint32_t>(token) < tc ? static_cast<uint32_t>(token) : 0xFFFFFFFFu;
-        const uint32_t g = (own_cached && f >= c.rx_prefix[p.rank]) ? f - c.own_cnt : f;     // the own rows are contiguous in receive order
-        return tc + g < p.rc_rows ? tc + g : 0xFFFFFFFFu;
-    }
+    // Token rows ahead of the weight stream. The first `rc_rows` received rows (receive order) are fetched into shared
+    // memory while the schedule is being built, before the bulk copies of the weight stream make every small load wait
+    // behind megabytes. Two uses of the same region: with at most 16 received rows in the launch ("decode mode") they
+    // are written straight into ONE swizzled token tile, rows grouped by expert, that every L1 task of the launch
+    // multiplies with (a 16-token MMA costs the same whatever rows are meaningful; the task's epilogue reads its
+    // expert's accumulator columns); otherwise the region is a plain row cache (slot = receive index) that the stager
+    // copies from instead of going to global memory.
+    __device__ __forceinline__ uint8_t* tok_region() const { return smem + p.sm_rcache; }
+    __device__ __forceinline__ uint8_t* tile_asf() const { return smem + p.sm_rcache + p.act_bytes; }
     // one 16 B payload chunk of flagged words at `src` (32 B): polls until both halves carry this launch's flag
     __device__ __forceinline__ bool ll_read(const uint8_t* src, uint32_t flag, uint4& out, uint32_t code, uint32_t detail) const {
         uint32_t spins = 0;
@@ -299,11 +306,18 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         const uint32_t acc = ti & 1u, use = (ti >> 1) & 1u;
-        const uint32_t ab = c.nab == 2u ? acc : 0u, use_a = c.nab == 2u ? use : acc;
-        if (!cx.warp_wait(&c.acts_full[ab], use_a, kErrWaitActsFull)) return;
+        // decode mode: every L1 task multiplies with the launch's shared token tile (written once, before the weight
+        // stream started); nothing is staged for it and the staging barriers count the L2 tasks only
+        const bool shared_tile = !kA8 && c.decode != 0u && (c.tasks[ti] >> 28) == 0u;
+        const uint32_t tis = (!kA8 && c.decode != 0u) ? ti - c.n1_tasks : ti;
+        const uint32_t ab = c.nab == 2u ? (tis & 1u) : 0u, use_a = c.nab == 2u ? (tis >> 1) & 1u : (tis & 1u);
+        if (shared_tile) { if (!cx.warp_wait(&c.tile_full, 0u, kErrWaitActsFull)) return; }
+        else if (!cx.warp_wait(&c.acts_full[ab], use_a, kErrWaitActsFull)) return;
         if (!cx.warp_wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty)) return;
         tc_fence_after();
-        const uint32_t act = smem_u32(cx.smem + p.sm_act + ab * c.act_stride);
+        const uint32_t act = shared_tile ? smem_u32(cx.tok_region()) : smem_u32(cx.smem + p.sm_act + ab * c.act_stride);
+        const uint32_t asf_base = shared_tile ? smem_u32(cx.tile_asf()) : smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes);
+        const uint32_t atom_stride = shared_tile ? kTileTokens * 128u : c.atom_stride, sbo = shared_tile ? 1024u : c.sbo;
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
             uint64_t* ready = kA8 ? &c.xfull[it & 1u] : &c.full[s];
@@ -312,7 +326,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
             t_landed = globaltimer_ns();
             if (lane == 0) {
                 if (it == 0u) cx.sm_phase(kSmFirstLanded);
-                if (it < 16u) cx.sm_phase(16 + static_cast<int>(it));
+                if (it < 15u) cx.sm_phase(16 + static_cast<int>(it));
             }
             if (elect_one()) {
               {
@@ -320,7 +334,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
                                          : smem_u32(cx.smem + static_cast<size_t>(s) * p.unit_bytes);
                 const uint32_t wsf = wsm + (kA8 ? 2u * kUnitWBytes : static_cast<uint32_t>(kUnitWBytes));
                 const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u, sfb = tm + sfb_col + (it & 1u) * 16u;
-                const uint32_t asf = smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes) + static_cast<uint32_t>(u) * kPlanes * 256u;
+                const uint32_t asf = asf_base + static_cast<uint32_t>(u) * kPlanes * 256u;
                 #pragma unroll
                 for (uint32_t pl = 0; pl < kPlanes; ++pl) {
                     // one scale word (4 scale bytes, K span 4 * vec) per row: lane = row % 32, column = row / 32.
@@ -329,13 +343,13 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
                     utccp_32x128b_warpx4(sfb + pl * 4u, smem_desc(asf + pl * 256u, 128u, kLayoutNone));
                 }
                 // token tile: [K atoms][16 rows x 128 B]; an atom holds 256 packed E2M1 or 128 E4M3 elements
-                const uint32_t bsm = act + static_cast<uint32_t>(u) * (kA8 ? 2u : 1u) * c.atom_stride;
+                const uint32_t bsm = act + static_cast<uint32_t>(u) * (kA8 ? 2u : 1u) * atom_stride;
                 #pragma unroll
                 for (uint32_t ks = 0; ks < kUnitK / kStepK; ++ks) {
                     const uint32_t pl = (ks * kStepK) / (4u * kVec), sf_id = ((ks * kStepK) % (4u * kVec)) / kVec;
                     const uint32_t atom = ks / kStepsPerAtom, in_atom = (ks % kStepsPerAtom) * 32u;
                     const uint64_t adesc = smem_desc(wsm + (kA8 ? atom * kUnitWBytes : 0u) + in_atom, 1024u, kLayoutSw128);
-                    const uint64_t bdesc = smem_desc(bsm + (kA8 ? atom * c.atom_stride : 0u) + in_atom, c.sbo, kLayoutSw128);
+                    const uint64_t bdesc = smem_desc(bsm + (kA8 ? atom * atom_stride : 0u) + in_atom, sbo, kLayoutSw128);
                     const uint32_t idesc = idesc_with_sf(kIdesc, sf_id, sf_id);
                     const uint32_t accum = (u > ub || ks > 0) ? 1u : 0u;
                     if constexpr (kA8)
@@ -353,7 +367,7 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         }
         if (elect_one()) {
             tc_commit(&c.tmem_full[acc]);
-            tc_commit(&c.acts_empty[ab]);
+            if (!shared_tile) tc_commit(&c.acts_empty[ab]);
         }
         __syncwarp();
     }
@@ -430,7 +444,7 @@ __device__ __forceinline__ void find_rows(Ctl& c, uint32_t* rowref, uint32_t tot
 // receive pool and row 0 of the intermediate pool, whatever they hold; every word accepted, no barrier touched): run
 // before the roles start, it leaves this code in the SM's instruction cache, so that the first real task, which sits on
 // the launch's critical path, does not pay for fetching it. What it writes into the staging buffer is overwritten later.
-__device__ __noinline__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane, bool dry, bool own_cached) {
+__device__ __noinline__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t lane, bool dry) {
     const KParams& p = cx.p; Ctl& c = cx.c;
     const uint32_t total = dry ? 0u : c.rx_prefix[p.R];
     uint32_t* rowref = c.rowref[sw];
@@ -438,13 +452,19 @@ __device__ __noinline__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t la
     uint32_t* rcslot = c.rcslot[sw];
     if (!dry && sw >= c.nab) return;
     bool seen_l2 = false;
-    const uint32_t ntasks = dry ? 2u : c.ntasks, step = dry ? 1u : c.nab;
+    const uint32_t ntasks = dry ? 2u : c.ntasks;
     const uint32_t act_stride = dry ? 0u : c.act_stride, atom_stride = dry ? kTileTokens * 128u : c.atom_stride;
+    // In decode mode the L1 tasks use neither the staging buffers nor their barriers (they multiply with the launch's
+    // shared token tile and their epilogue lists the rows itself): buffer and phase of a task follow its index among
+    // the tasks that do stage, i.e. the L2 tasks.
+    const uint32_t skip = (!dry && c.decode != 0u) ? c.n1_tasks : 0u;
     #pragma unroll 1
-    for (uint32_t ti = dry ? 0u : sw; ti < ntasks; ti += step) {      // with one staging buffer, stager 0 takes every task
+    for (uint32_t ti = dry ? 0u : skip; ti < ntasks; ++ti) {
+        const uint32_t tis = ti - skip;                               // index among the staging tasks
+        if (!dry && (c.nab == 2u ? (tis & 1u) : 0u) != sw) continue;   // stager w fills buffer w (one buffer: stager 0 takes every task)
         const uint32_t t = dry ? task_pack(ti, 0u, 0u, 0u) : c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
-        const uint32_t ab = (!dry && c.nab == 2u) ? (ti & 1u) : 0u, use = c.nab == 2u ? (ti >> 1) & 1u : (ti & 1u), ring = ti & 3u;
+        const uint32_t ab = (!dry && c.nab == 2u) ? (tis & 1u) : 0u, use = c.nab == 2u ? (tis >> 1) & 1u : (tis & 1u), ring = ti & 3u;
         if (!dry && !cx.warp_wait(&c.acts_empty[ab], use ^ 1u, kErrWaitActsEmpty)) return;
         find_rows(c, rowref, total, e, mt, lane);
         const uint32_t left = c.exp_count[e] - mt * kTileTokens;
@@ -467,7 +487,7 @@ __device__ __noinline__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t la
             m.src = static_cast<int32_t>(r);
             if (!dry) c.row_meta[ring][lane] = m;
             rowidx[lane] = (r << 24) | i;
-            rcslot[lane] = (dry || p.rc_rows == 0u) ? 0xFFFFFFFFu : cx.rc_slot(f, r, m.token, own_cached);
+            rcslot[lane] = (dry || f >= p.rc_rows) ? 0xFFFFFFFFu : f;
         }
         __syncwarp();
         uint8_t* act = cx.smem + p.sm_act + ab * act_stride;
@@ -562,7 +582,7 @@ __device__ __noinline__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t la
         __syncwarp();
         if (lane == 0 && !dry) {
             mbar_arrive(&c.acts_full[ab]);
-            if (ti == 0u) cx.sm_phase(kSmFirstStaged);
+            if (tis == 0u) cx.sm_phase(kSmFirstStaged);
             if (type != 0u && !seen_l2) { seen_l2 = true; cx.sm_phase(kSmFirstL2Staged); }
         }
     }
@@ -624,29 +644,53 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF, j = t & 0xFF;
         const uint32_t acc = ti & 1u, use = (ti >> 1) & 1u, ring = ti & 3u, ab = c.nab == 2u ? acc : 0u;
+        float* vtt = vt;                                           // this task's accumulators: vtt[n * 128], token n of the task
         // ---- accumulators of the valid tokens -> shared memory (the loops below run over the valid tokens only)
         bool ok;
         uint32_t nv = 0;
         if constexpr (kUmma) {
             ok = cx.warp_wait(&c.tmem_full[acc], use, kErrWaitTmemFull);
+            // decode mode, L1 task: nobody staged anything for this task (its tokens sit in the launch's shared tile). The
+            // first epilogue warp lists the expert's rows itself, in receive order: their records, how many there are, and
+            // how many rows of experts with a smaller index precede them in the tile (= the expert's first column).
+            const bool shared_tile = !kA8 && type == 0u && c.decode != 0u;
             if (ok) {
                 tc_fence_after();
                 if (ti == 0u && etid == 0u) cx.sm_phase(kSmFirstMmaDone);
-                if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
-                nv = c.nvalid[ring];
+                if (shared_tile) {
+                    if (ew == 0u) {
+                        const uint32_t total = c.rx_prefix[p.R];
+                        const uint32_t my_e = lane < total ? c.meta_e[lane] : 0xFFu;
+                        const uint32_t same = __ballot_sync(0xffffffffu, my_e == e), below = __ballot_sync(0xffffffffu, my_e < e);
+                        if (my_e == e) {
+                            uint32_t r = 0;
+                            while (r + 1 < static_cast<uint32_t>(p.R) && lane >= c.rx_prefix[r + 1]) ++r;
+                            RowMeta m = c.rx_meta[lane];
+                            m.src = static_cast<int32_t>(r);
+                            c.epi_meta[acc][__popc(same & ((1u << lane) - 1u))] = m;
+                        }
+                        if (lane == 0) { c.epi_nv[acc] = __popc(same); c.epi_dcol[acc] = __popc(below); }
+                    }
+                } else {
+                    if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
+                    if (etid == 0u) { c.epi_nv[acc] = c.nvalid[ring]; c.epi_dcol[acc] = 0u; }
+                }
                 uint32_t raw[kTileTokens];
                 tmem_ld_32x32b_x16(c.tmem_base + ((ew * 32u) << 16) + acc * 16u, raw);
                 tmem_ld_wait();
                 tc_fence_before();
                 mbar_arrive(&c.tmem_empty[acc]);
+                // all sixteen columns go to shared memory (in decode mode they are every received row of the launch; this
+                // task's expert owns nv of them from its first column on)
                 #pragma unroll
-                for (int n = 0; n < kTileTokens; ++n) if (n < static_cast<int>(nv)) vt[n * kTileRows] = __uint_as_float(raw[n]);
+                for (int n = 0; n < kTileTokens; ++n) vt[n * kTileRows] = __uint_as_float(raw[n]);
             }
         } else {
             ok = cx.warp_wait(&c.acts_full[ab], use, kErrWaitActsFull);
             if (ok) {
                 if (etid < kTileTokens) c.epi_meta[acc][etid] = c.row_meta[ring][etid];
                 nv = c.nvalid[ring];
+                if (etid == 0u) { c.epi_nv[acc] = nv; c.epi_dcol[acc] = 0u; }
                 float v[kTileTokens];
                 #pragma unroll
                 for (int n = 0; n < kTileTokens; ++n) v[n] = 0.f;
@@ -667,7 +711,9 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 for (int n = 0; n < kTileTokens; ++n) if (n < static_cast<int>(nv)) vt[n * kTileRows] = v[n];
             }
         }
-        if (bar_red_or(kBarEpi, kNumEpiThreads, !ok)) return;        // also publishes epi_meta
+        if (bar_red_or(kBarEpi, kNumEpiThreads, !ok)) return;        // also publishes epi_meta, epi_nv, epi_dcol
+        nv = c.epi_nv[acc];
+        vtt = vt + c.epi_dcol[acc] * kTileRows;
         const RowMeta* meta = c.epi_meta[acc];
         const uint32_t midrow0 = c.mid_base[e] + mt * kTileTokens;
         const uint32_t np = (c.tasks2[ti] >> 16) & 0xFFu;
@@ -678,7 +724,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             float* red = reinterpret_cast<float*>(cx.buf + p.off_red);
             float* mine = red + ((static_cast<size_t>(blockIdx.x) * 2u + type) * 2u) * (kTileTokens * kTileRows) + row;
             #pragma unroll 1
-            for (uint32_t n = 0; n < nv; ++n) mine[n * kTileRows] = vt[n * kTileRows];
+            for (uint32_t n = 0; n < nv; ++n) mine[n * kTileRows] = vtt[n * kTileRows];
             bar_sync(kBarEpi, kNumEpiThreads);
             if (etid == 0) {
                 uint32_t* cnt = reinterpret_cast<uint32_t*>(cx.buf + p.off_cnt) + type * p.cnt_per_phase + tile;
@@ -706,7 +752,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                     #pragma unroll
                     for (uint32_t d = 0; d < 4; ++d) if (pc0 + d < np) sum += part_v[d];
                 }
-                vt[n * kTileRows] = sum;
+                vtt[n * kTileRows] = sum;
             }
         }
 
@@ -715,14 +761,14 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             const bool is_up = (lane & 8u) != 0u;
             #pragma unroll 1
             for (uint32_t n = 0; n < nv; ++n) {
-                const float mine = bf16_round(vt[n * kTileRows] * p.l1_scale);
+                const float mine = bf16_round(vtt[n * kTileRows] * p.l1_scale);
                 const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
                 float gate = is_up ? other : mine, up = is_up ? mine : other;
                 if (p.has_clamp) { gate = fminf(gate, p.clamp); up = fminf(fmaxf(up, -p.clamp), p.clamp); }
                 const float sig = p.fast_math ? __frcp_rn(1.0f + __expf(-gate)) : 1.0f / (1.0f + expf(-gate));
                 float av = gate * sig * up * meta[n].weight;
                 if constexpr (kVec == 16) av = __fdiv_rn(av, p.mid_gs);
-                vt[n * kTileRows] = av;
+                vtt[n * kTileRows] = av;
                 float a = fabsf(av);
                 a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
                 a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
@@ -737,7 +783,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 float amax = c.amax_x[ew][n];
                 if constexpr (kVec == 32) amax = fmaxf(amax, c.amax_x[ew ^ 1u][n]);
                 amax = fmaxf(amax, 1e-30f);
-                const float av = vt[n * kTileRows];
+                const float av = vtt[n * kTileRows];
                 uint32_t sf_byte; float scaled;
                 if constexpr (kA8) {
                     sf_byte = ceil_pow2_exp(__fdiv_rn(amax, 448.0f));
@@ -781,15 +827,16 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             // ---- L2: bf16 rows back to the token's source rank, as flagged words: the combine there polls the data itself
             __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(otile);
             #pragma unroll 1
-            for (uint32_t n = 0; n < nv; ++n) ot[n * kTileRows + row] = __float2bfloat16_rn(vt[n * kTileRows] * p.l2_scale);
+            for (uint32_t n = 0; n < nv; ++n) ot[n * kTileRows + row] = __float2bfloat16_rn(vtt[n * kTileRows] * p.l2_scale);
             bar_sync(kBarEpi, kNumEpiThreads);
+            // (two lanes per 16 B chunk, one 16 B half of its flagged image each: full 32 B sectors per store instruction)
             #pragma unroll 1
-            for (uint32_t idx = etid; idx < nv * 16u; idx += kNumEpiThreads) {
-                const uint32_t n = idx >> 4, ch = idx & 15u;
+            for (uint32_t idx = etid; idx < nv * 32u; idx += kNumEpiThreads) {
+                const uint32_t n = idx >> 5, ch = (idx & 31u) >> 1;
                 const uint4 val = *reinterpret_cast<const uint4*>(otile + n * 256u + ch * 16u);
                 uint8_t* dst = p.peer[meta[n].src] + p.off_comb +
                     ((static_cast<size_t>(meta[n].token) * p.topk + meta[n].slot) * p.H + j * kTileRows) * 4u + ch * 32u;
-                st_ll_16B(dst, val, c.epoch + 1u);
+                st_ll_half(dst, val, c.epoch + 1u, idx & 1u);
             }
         }
         if (etid == 0u) {
@@ -876,6 +923,7 @@ __device__ __noinline__ uint32_t build_schedule(const KParams& p, Ctl& c, const 
             }
         }
         __syncwarp();
+        if (lane == 0) c.n1_tasks = cnt0;
         nmine = cnt0 + cnt1;
     }    return (M << 16) | (nmine < 0xFFFFu ? nmine : 0xFFFFu);
 }
@@ -1034,8 +1082,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     const bool own_ok = kScout && (p.knobs & kKnobOwnRows) != 0u && static_cast<uint32_t>(p.T) * p.topk <= kOwnCap &&
                         p.inp == buf;      // (inputs in mapped host memory are read by the dispatching SMs only)
 
-    const bool own_cached = own_ok && p.rc_rows != 0u;     // the own tokens go into the row cache at kernel entry
-
     // ---- prologue
     constexpr uint32_t kO = kScout ? kNT - 32u : kNT;        // threads of the warps other than the scout
     const bool is_scout = kScout && warp == kCopyWarps;
@@ -1050,7 +1096,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (tid == 0) {
         const uint32_t ep = ctrl32[kCtrlEpoch / 4 + bid];
         ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
-        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u;
+        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u; c.decode = 0u;
         if constexpr (!kScout) c.own_cnt = 0u;
         for (int s = 0; s < p.nstage; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
         #pragma unroll 1
@@ -1059,6 +1105,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             mbar_init(&c.tmem_full[i], 1); mbar_init(&c.tmem_empty[i], kNumEpiThreads);
             mbar_init(&c.xfull[i], kNumExpThreads / 64); mbar_init(&c.xempty[i], 1);
         }
+        mbar_init(&c.tile_full, kFillWarps);
         mbar_fence_init();
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmEntry)[bid] = t_first;
         if constexpr (!kScout) reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmWFirst)[bid] = ~0ull;
@@ -1072,33 +1119,6 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
     if (warp == 1) { tmem_alloc(&c.tmem_base, kTmemCols); tmem_relinquish(); tc_fence_before(); }
     if (tid < kMaxLocalExperts) c.exp_count[tid] = 0u;
-    if (own_cached && warp >= 1 && warp <= 3) {
-        // this rank's own tokens (packed row + scale bytes) into the row cache, by token index: the memory system is
-        // still idle now; once the weight stream runs, a small load waits behind megabytes of it
-        const uint32_t tc = static_cast<uint32_t>(p.T) < p.rc_rows ? static_cast<uint32_t>(p.T) : p.rc_rows;
-        const uint32_t xq = p.x_row_bytes / 16u, per_row = p.rc_row_bytes / 16u;
-        #pragma unroll 1
-        for (uint32_t t = warp - 1u; t < tc; t += 3u) {
-            const uint8_t* xs = inp + p.off_x + static_cast<size_t>(t) * p.x_row_bytes;
-            const uint8_t* sf = inp + p.off_x_sf + static_cast<size_t>(t) * p.x_sf_row_bytes;
-            uint8_t* dst = smem + p.sm_rcache + t * p.rc_row_bytes;
-            #pragma unroll 1
-            for (uint32_t base = lane; base < per_row; base += 8 * 32) {
-                uint4 v[8];
-                #pragma unroll
-                for (uint32_t u = 0; u < 8; ++u) {
-                    const uint32_t ci = base + u * 32;
-                    if (ci < xq) v[u] = ld_cg_v4(xs + ci * 16u);
-                    else if (ci < per_row) v[u] = ld_cg_v4(sf + (ci - xq) * 16u);
-                }
-                #pragma unroll
-                for (uint32_t u = 0; u < 8; ++u) {
-                    const uint32_t ci = base + u * 32;
-                    if (ci < per_row) *reinterpret_cast<uint4*>(dst + ci * 16u) = v[u];
-                }
-            }
-        }
-    }
     Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, 0u};
     if (is_scout) {
         // the scout does not wait for the prologue: it lists the own rows and asks for their experts' weights first
@@ -1140,7 +1160,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
 
     if constexpr (!kFe) {
-        if ((p.knobs & kKnobRehearse) != 0u && !dispatching && (warp == 2 || warp == 3)) role_stager(cx, warp - 2, lane, true, false);
+        if ((p.knobs & kKnobRehearse) != 0u && !dispatching && (warp == 2 || warp == 3)) role_stager(cx, warp - 2, lane, true);
     }
 
     // ---- warm-up of the scheduler's instructions: on the SMs that do not dispatch, warp 6 is idle until the roles start,
@@ -1238,19 +1258,21 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             const uint8_t* xs_src = inp + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
             const uint8_t* sf_src = inp + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
             uint8_t* dst = dst_base + static_cast<size_t>(i) * 2u * p.rx_row_bytes;
+            // a pair of lanes per 16 B payload chunk: each stores one 16 B half of its 32 B flagged image, so that a warp
+            // instruction writes 512 contiguous bytes in full sectors (the packets that cross NVLink)
             #pragma unroll 1
-            for (uint32_t base = lane; base < nchunk; base += 8 * 32) {
+            for (uint32_t base = lane; base < 2u * nchunk; base += 8 * 32) {
                 uint4 v[8];
                 #pragma unroll
                 for (uint32_t u = 0; u < 8; ++u) {
-                    const uint32_t ci = base + u * 32;
+                    const uint32_t ci = (base + u * 32) >> 1;
                     if (ci < xq) v[u] = *reinterpret_cast<const uint4*>(xs_src + ci * 16u);
                     else if (ci < nchunk) v[u] = *reinterpret_cast<const uint4*>(sf_src + (ci - xq) * 16u);
                 }
                 #pragma unroll
                 for (uint32_t u = 0; u < 8; ++u) {
-                    const uint32_t ci = base + u * 32;
-                    if (ci < nchunk) st_ll_16B(dst + ci * 32u, v[u], flag);
+                    const uint32_t hc = base + u * 32, ci = hc >> 1;
+                    if (ci < nchunk) st_ll_half(dst + ci * 32u, v[u], flag, hc & 1u);
                 }
             }
         }
@@ -1295,6 +1317,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             if (total > kMetaCap) cx.fail(kErrMetaCapacity, total >> 4);
             if (bid == 0) cx.stamp(kStampFlagsSeen);
             cx.sm_phase(kSmCountsKnown);
+            c.decode = (kUmma && !kA8 && p.rc_rows != 0u && total != 0u && total <= kTileTokens) ? 1u : 0u;     // (the cross-check engine reads the per-task staging buffers)
         }
         if (total <= kMetaCap) {
             auto take = [&](uint32_t f, const uint4& m) {
@@ -1330,80 +1353,128 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
     bar_sync(kBarMain, kO);
 
-    // ---- the rows received from other ranks go into the row cache (one warp per row, warps 1.. of this group) while
-    //      warp 0 builds the schedule: the bulk copies of the weight stream, which start right after, would make these
-    //      small loads wait behind them
-    if (warp != 0 && p.rc_rows != 0u && total <= kMetaCap && !cx.aborted()) {
-        constexpr uint32_t kFillWarps = kO / 32u - 1u;
-        const uint32_t per_row = p.rc_row_bytes / 16u;
-        const uint32_t wi = warp - 1u;                                   // (the scout is the last warp: not in this group)
-        uint32_t k = 0;
+    // ---- the rows received from other ranks go into the row cache (one warp per row, warps 2..6) while warp 0 builds the
+    //      schedule and then starts the weight stream without waiting for them: these warps' roles (token staging,
+    //      epilogue) are not needed before the first weights have landed, and the rows' payload may still be on its way
+    //      (a sender pushes its header line and records first). The loads are in flight before the bulk copies of the
+    //      weight stream start, which would otherwise make them wait behind megabytes.
+    const bool is_ctl = warp < 2u;                       // warps 0 and 1 build the schedule and start the weight stream
+    if (warp >= 2u && warp < 2u + kFillWarps && p.rc_rows != 0u && total <= kMetaCap && !cx.aborted()) {
+        const bool decode = c.decode != 0u;
+        const uint32_t per_row = p.rc_row_bytes / 16u, xq = p.x_row_bytes / 16u;
+        const uint32_t limit = total < p.rc_rows ? total : p.rc_rows;
+        const uint32_t my_e = lane < total ? c.meta_e[lane] : 0xFFu;      // (decode mode: at most 16 rows, one per lane)
+        uint8_t* region = cx.tok_region();
         #pragma unroll 1
-        for (uint32_t f = 0; f < total; ++f) {
+        for (uint32_t f = warp - 2u; f < limit; f += kFillWarps) {
             uint32_t r = 0;
             while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
-            if (own_cached && r == static_cast<uint32_t>(p.rank)) continue;
-            const uint32_t slot = cx.rc_slot(f, r, 0, own_cached);
-            if (slot == 0xFFFFFFFFu) break;                              // slots grow with f: nothing further fits
-            if (k++ % kFillWarps != wi) continue;
-            const uint8_t* row_src = cx.rx_row(r, f - c.rx_prefix[r]);
-            uint8_t* dst = smem + p.sm_rcache + slot * p.rc_row_bytes;
+            const uint32_t i = f - c.rx_prefix[r];
+            const bool own = own_ok && r == static_cast<uint32_t>(p.rank);  // this rank's own token: read it where the caller put it
+            // decode mode: row position in the shared tile = rows of experts with a smaller index, then the earlier rows
+            // of the same expert (receive order)
+            const uint32_t e = c.meta_e[f];
+            const uint32_t pos = __popc(__ballot_sync(0xffffffffu, my_e < e)) +
+                                 __popc(__ballot_sync(0xffffffffu, my_e == e) & ((1u << f) - 1u));
+            const uint8_t* xs = nullptr;
+            const uint8_t* sf = nullptr;
+            const uint8_t* row_src = nullptr;
+            if (own) {
+                const uint32_t tok = static_cast<uint32_t>(c.own_meta[i].token);
+                xs = inp + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
+                sf = inp + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
+            } else {
+                row_src = cx.rx_row(r, i);
+            }
+            uint8_t* raw_dst = region + f * p.rc_row_bytes;
             bool bad = false;
             #pragma unroll 1
             for (uint32_t base = lane; base < per_row && !bad; base += 4 * 32) {
                 uint4 v[4];
-                uint32_t spins = 0;
-                bool ok;
-                do {
-                    ok = true;
+                if (own) {
                     #pragma unroll
                     for (uint32_t u = 0; u < 4; ++u) {
                         const uint32_t ci = base + u * 32;
-                        if (ci < per_row) {
-                            const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
-                            ok = ok && ll_valid(a, b, flag_rx);
-                            v[u] = ll_data(a, b);
+                        if (ci < xq) v[u] = ld_cg_v4(xs + ci * 16u);
+                        else if (ci < per_row) v[u] = ld_cg_v4(sf + (ci - xq) * 16u);
+                    }
+                } else {
+                    uint32_t spins = 0;
+                    bool ok;
+                    do {
+                        ok = true;
+                        #pragma unroll
+                        for (uint32_t u = 0; u < 4; ++u) {
+                            const uint32_t ci = base + u * 32;
+                            if (ci < per_row) {
+                                const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
+                                ok = ok && ll_valid(a, b, flag_rx);
+                                v[u] = ll_data(a, b);
+                            }
                         }
-                    }
-                    if (!ok && (++spins & 0x3Fu) == 0u) {
-                        if (cx.aborted()) bad = true;
-                        else if (cx.expired()) { cx.fail(kErrWaitDispatchFlag, r); bad = true; }
-                    }
-                } while (!ok && !bad);
+                        if (!ok && (++spins & 0x3Fu) == 0u) {
+                            if (cx.aborted()) bad = true;
+                            else if (cx.expired()) { cx.fail(kErrWaitDispatchFlag, r); bad = true; }
+                        }
+                    } while (!ok && !bad);
+                }
                 #pragma unroll
                 for (uint32_t u = 0; u < 4; ++u) {
                     const uint32_t ci = base + u * 32;
-                    if (ci < per_row && !bad) *reinterpret_cast<uint4*>(dst + ci * 16u) = v[u];
+                    if (ci >= per_row || bad) continue;
+                    if (!decode) {
+                        *reinterpret_cast<uint4*>(raw_dst + ci * 16u) = v[u];
+                    } else if (ci < xq) {
+                        *reinterpret_cast<uint4*>(region + (ci >> 3) * (kTileTokens * 128u) + sw128_off(pos, ci & 7u)) = v[u];
+                    } else {
+                        uint8_t* dst = cx.tile_asf() + (ci - xq) * 4u * 256u + pos * 16u;
+                        *reinterpret_cast<uint32_t*>(dst) = v[u].x;
+                        *reinterpret_cast<uint32_t*>(dst + 256u) = v[u].y;
+                        *reinterpret_cast<uint32_t*>(dst + 512u) = v[u].z;
+                        *reinterpret_cast<uint32_t*>(dst + 768u) = v[u].w;
+                    }
                 }
             }
+            if (lane == 0) cx.sm_phase(kSmRowsCached);
+        }
+        if (decode) {
+            fence_proxy_async_smem();                     // the tensor core reads the tile through the async proxy
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&c.tile_full);
         }
     }
 
     // ---- schedule. 16-token tiles of the active experts, expert-major: M of them. Every SM derives its own task list
-    //      (L1 tasks, then L2 tasks) in closed form from the per-expert counts.
-    if (warp == 0 && !cx.aborted()) {
-        const uint32_t res = build_schedule(p, c, c.exp_count, bid, G, lane);
-        const uint32_t M = res >> 16, nmine = res & 0xFFFFu;
-        const uint32_t nt1 = M * p.n1_tiles, nt2 = M * p.n2_tiles;
-        if (lane == 0) {
-            c.nt1 = nt1; c.nt2 = nt2;
-            if (M > kMaxMTiles || nmine > kMaxTasks) cx.fail(kErrTaskCapacity, nmine);
-            else c.ntasks = nmine;
+    //      (L1 tasks, then L2 tasks) in closed form from the per-expert counts. Warps 0 and 1 publish it on kBarSched
+    //      without waiting there; every other warp (the scout included) waits on that barrier before it takes up its role.
+    if (is_ctl) {
+        if (warp == 0 && !cx.aborted()) {
+            const uint32_t res = build_schedule(p, c, c.exp_count, bid, G, lane);
+            const uint32_t M = res >> 16, nmine = res & 0xFFFFu;
+            const uint32_t nt1 = M * p.n1_tiles, nt2 = M * p.n2_tiles;
+            if (lane == 0) {
+                c.nt1 = nt1; c.nt2 = nt2;
+                if (M > kMaxMTiles || nmine > kMaxTasks) cx.fail(kErrTaskCapacity, nmine);
+                else c.ntasks = nmine;
+            }
         }
+        bar_sync(kBarPost, 64);
+        __threadfence_block();
+        bar_arrive(kBarSched, kNT);
+        if (bid == 0 && tid == 0) cx.stamp(kStampScheduled);
+        if (tid == 0) { cx.stamp_max(kStampLastScheduled, globaltimer_ns()); cx.sm_phase(kSmScheduled); }
+        if (bid == 0 && tid < static_cast<uint32_t>(p.e_local) && p.stats != nullptr && !cx.aborted())
+            p.stats[tid] += static_cast<int>(c.exp_count[tid]);
+    } else {
+        bar_sync(kBarSched, kNT);
     }
-    bar_sync(kBarMain, kO);
-    if constexpr (kScout) { __threadfence_block(); bar_arrive(kBarSched, kNT); }
-    if (bid == 0 && tid == 0) cx.stamp(kStampScheduled);
-    if (tid == 0) { cx.stamp_max(kStampLastScheduled, globaltimer_ns()); cx.sm_phase(kSmScheduled); }
-    if (bid == 0 && tid < static_cast<uint32_t>(p.e_local) && p.stats != nullptr && !cx.aborted())
-        p.stats[tid] += static_cast<int>(c.exp_count[tid]);
   }
 
     // ---- roles
     if (!cx.aborted()) {
         if (warp == 0) role_loader(cx);
         else if (warp == 1) { if constexpr (kUmma) role_mma<kVec, kA8>(cx, lane); }
-        else if (warp < 4) role_stager(cx, warp - 2, lane, false, own_cached);
+        else if (warp < 4) role_stager(cx, warp - 2, lane, false);
         else if (warp < 8) role_epilogue<kVec, kUmma, kA8>(cx, tid - 128);
         else { if constexpr (kA8) role_expander(cx, tid - kThreads); }
     }

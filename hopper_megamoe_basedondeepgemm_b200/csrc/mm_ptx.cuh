@@ -208,6 +208,13 @@ __device__ __forceinline__ void st_ll_16B(void* dst, uint4 data, uint32_t flag) 
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" :: "l"(dst), "r"(data.x), "r"(flag), "r"(data.y), "r"(flag) : "memory");
     asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" :: "l"(static_cast<uint8_t*>(dst) + 16), "r"(data.z), "r"(flag), "r"(data.w), "r"(flag) : "memory");
 }
+// One 16 B half of a flagged 32 B chunk: half 0 carries payload words x, y, half 1 words z, w. Two neighbouring lanes
+// that store the two halves of a chunk write one full 32 B sector with one instruction; a lane that stores both halves
+// itself (st_ll_16B) touches every sector twice, half at a time, which costs twice the packets on NVLink.
+__device__ __forceinline__ void st_ll_half(void* chunk_dst, const uint4& data, uint32_t flag, uint32_t half) {
+    const uint32_t a = half ? data.z : data.x, b = half ? data.w : data.y;
+    asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" :: "l"(static_cast<uint8_t*>(chunk_dst) + half * 16u), "r"(a), "r"(flag), "r"(b), "r"(flag) : "memory");
+}
 __device__ __forceinline__ uint2 ld_volatile_v2(const void* p) {
     uint2 v;
     asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");

@@ -165,7 +165,7 @@ int mm_read_phase_stamps(const mm_config_t* cfg, const void* buffer, uint64_t ou
  * 0 = not reached. Slots: 0 first instruction, 1 prologue done, 2 own rows listed, 3 row counts known, 4 scheduled,
  * 5 first weight copy issued, 6 first weight unit landed, 7 first task's tokens staged, 8 first task's MMAs done,
  * 9 first epilogue done, 10 last L1 epilogue done, 11 first L2 task's rows staged, 12 tasks done, 13 first combine
- * item written, 14 last combine item written, 15 exit, 16..31 when the SM's weight units 0..15 were found landed. The reference's per-CTA frontend stamps are the model
+ * item written, 14 last combine item written, 15 exit, 16..30 when the SM's weight units 0..14 were found landed, 31 latest copy of a received row into the row cache. The reference's per-CTA frontend stamps are the model
  * (sm100_b200/fe_sm100/fable_frontend_device.cuh:46-54). */
 int mm_read_sm_phases(const mm_config_t* cfg, const void* buffer, uint64_t* out_256x32, void* stream);
 /* Development knobs, process-wide, read at every launch. The reference reads its own from DG_SM100_* environment

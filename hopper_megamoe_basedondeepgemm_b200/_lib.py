@@ -61,11 +61,12 @@ class MMStaticArgs(ctypes.Structure):
 STATIC_SCRATCH_BYTES = 16 * 1024 * 1024
 TUNE = {'knobs': 0, 'stages': 1, 'prefetch_w1_experts': 2, 'prefetch_w2_experts': 3, 'row_cache': 4}
 KNOB_PREFETCH, KNOB_OWN_ROWS, KNOB_EARLY_COMBINE = 1, 2, 4
+WINDOW_HANDLE_BYTES = 64
 
 EXPORTS = ('mm_get_layout', 'mm_get_weight_geometry', 'mm_get_token_alignment', 'mm_mega_moe_launch',
            'mm_frontend_launch', 'mm_frontend_workspace_bytes', 'mm_mega_moe_from_hidden_launch', 'mm_reset',
            'mm_read_device_status', 'mm_read_phase_stamps', 'mm_status_string', 'mm_last_cuda_error',
-           'mm_mega_moe_launch_static_scratch', 'mm_set_tuning', 'mm_get_tuning', 'mm_read_sm_phases', 'mm_fe_forward', 'mm_fe_workspace_bytes', 'mm_fe_router_ctas', 'mm_transform_weights', 'mm_cast_rows_to_fp4')
+           'mm_mega_moe_launch_static_scratch', 'mm_set_tuning', 'mm_get_tuning', 'mm_read_sm_phases', 'mm_fe_forward', 'mm_fe_workspace_bytes', 'mm_fe_router_ctas', 'mm_transform_weights', 'mm_cast_rows_to_fp4', 'mm_window_alloc', 'mm_window_open', 'mm_window_close')
 
 _libs = {}
 
@@ -105,6 +106,9 @@ def load(check: bool = False) -> ctypes.CDLL:
     lib.mm_transform_weights.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64,
                                          ctypes.c_int64] + [ctypes.c_int32] * 5 + [ctypes.c_void_p, ctypes.c_void_p]
     lib.mm_cast_rows_to_fp4.argtypes = [ctypes.c_void_p] + [ctypes.c_int32] * 5 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
+    lib.mm_window_alloc.argtypes = [ctypes.c_int64, P(ctypes.c_void_p), ctypes.c_char_p]
+    lib.mm_window_open.argtypes = [ctypes.c_char_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, P(ctypes.c_void_p)]
+    lib.mm_window_close.argtypes = [P(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p]
     lib.mm_status_string.argtypes = [ctypes.c_int]
     lib.mm_status_string.restype = ctypes.c_char_p
     lib.mm_last_cuda_error.restype = ctypes.c_char_p

@@ -26,7 +26,9 @@ int sf_vec_of(int fmt) { return fmt == MM_FMT_NVFP4 ? 16 : 32; }
 
 // development knobs (mm_set_tuning): kernel feature bits, ring depth (0 = chosen from the shared-memory plan), and how
 // many experts' W1 / W2 the scout may prefetch into the L2 in one launch
-int g_tuning[MM_TUNE_COUNT] = {mm::kKnobPrefetch | mm::kKnobOwnRows | mm::kKnobEarlyCombine, 0, 14, 14, 1};
+// (the L2 prefetch of live experts' weights is off by default: measured, it does not shorten the weight stream - bulk
+// copies from the L2 are barely faster than from HBM here - and its traffic delays the launch's small critical loads)
+int g_tuning[MM_TUNE_COUNT] = {mm::kKnobOwnRows | mm::kKnobEarlyCombine, 0, 14, 14, 1};
 
 int check_config(const mm_config_t* c) {
     if (c == nullptr) return MM_ERR_INVALID_ARGUMENT;
@@ -129,6 +131,47 @@ int mm_get_layout(const mm_config_t* c, mm_layout_t* out) {
     // partial router logits of the fused frontend: 16 B per (token, expert), flagged with the launch number
     out->off_logits = take((t_max < mm::kFeMaxFusedTokens ? t_max : mm::kFeMaxFusedTokens) * c->num_experts * 16);
     out->total_bytes = off;
+    return MM_OK;
+}
+
+// ----------------------------------------------------------------------------- symmetric window without torch
+int mm_window_alloc(int64_t bytes, void** ptr_out, uint8_t handle_out[MM_WINDOW_HANDLE_BYTES]) {
+    static_assert(sizeof(cudaIpcMemHandle_t) <= MM_WINDOW_HANDLE_BYTES, "handle size");
+    if (bytes <= 0 || ptr_out == nullptr || handle_out == nullptr) return MM_ERR_INVALID_ARGUMENT;
+    void* p = nullptr;
+    MM_CUDA(cudaMalloc(&p, static_cast<size_t>(bytes)));
+    cudaError_t e = cudaMemset(p, 0, static_cast<size_t>(bytes));
+    cudaIpcMemHandle_t h;
+    if (e == cudaSuccess) e = cudaIpcGetMemHandle(&h, p);
+    if (e != cudaSuccess) { cudaFree(p); return cuda_fail(e, "mm_window_alloc"); }
+    memset(handle_out, 0, MM_WINDOW_HANDLE_BYTES);
+    memcpy(handle_out, &h, sizeof(h));
+    *ptr_out = p;
+    return MM_OK;
+}
+
+int mm_window_open(const uint8_t* handles, int32_t num_ranks, int32_t rank, void* own_ptr, void** peer_ptrs_out) {
+    if (handles == nullptr || peer_ptrs_out == nullptr || own_ptr == nullptr || num_ranks < 1 || num_ranks > mm::kMaxRanks ||
+        rank < 0 || rank >= num_ranks) return MM_ERR_INVALID_ARGUMENT;
+    for (int r = 0; r < num_ranks; ++r) peer_ptrs_out[r] = nullptr;
+    for (int r = 0; r < num_ranks; ++r) {
+        if (r == rank) { peer_ptrs_out[r] = own_ptr; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handles + static_cast<size_t>(r) * MM_WINDOW_HANDLE_BYTES, sizeof(h));
+        const cudaError_t e = cudaIpcOpenMemHandle(&peer_ptrs_out[r], h, cudaIpcMemLazyEnablePeerAccess);
+        if (e != cudaSuccess) {
+            for (int q = 0; q < r; ++q) if (q != rank && peer_ptrs_out[q] != nullptr) cudaIpcCloseMemHandle(peer_ptrs_out[q]);
+            return cuda_fail(e, "mm_window_open");
+        }
+    }
+    return MM_OK;
+}
+
+int mm_window_close(void* const* peer_ptrs, int32_t num_ranks, int32_t rank, void* own_ptr_to_free) {
+    if (peer_ptrs != nullptr)
+        for (int r = 0; r < num_ranks; ++r)
+            if (r != rank && peer_ptrs[r] != nullptr) MM_CUDA(cudaIpcCloseMemHandle(peer_ptrs[r]));
+    if (own_ptr_to_free != nullptr) MM_CUDA(cudaFree(own_ptr_to_free));
     return MM_OK;
 }
 

@@ -181,6 +181,7 @@ struct Ctx {
     uint8_t* smem;        // dynamic shared memory (1024 B aligned)
     uint64_t deadline;
     uint32_t par;         // launch parity: which half of the receive pool this launch uses (set once the launch number is known)
+    bool own_direct;      // rows of this rank's own tokens are read from the caller's input views, not from the receive pool
     __device__ __forceinline__ bool aborted() const { return *reinterpret_cast<volatile uint32_t*>(&c.abort_flag) != 0u; }
     __device__ __noinline__ void fail(uint32_t code, uint32_t detail = 0) const {      // cold: keep it out of the callers' code
         uint32_t* st = reinterpret_cast<uint32_t*>(buf + p.off_ctrl + kCtrlStatus);
@@ -524,6 +525,16 @@ __device__ __noinline__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t la
                     for (uint32_t ci = lane; ci < per_row; ci += 32) put(n, ci, *reinterpret_cast<const uint4*>(src + ci * 16u));
                     continue;
                 }
+            }
+            if (type == 0u && !dry && cx.own_direct && (rowidx[n] >> 24) == static_cast<uint32_t>(p.rank)) {
+                // a row of this rank's own token (not in the row cache): the token where the caller put it, plain loads
+                const uint32_t tok = static_cast<uint32_t>(c.row_meta[ring][n].token);
+                const uint8_t* xs = p.inp + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
+                const uint8_t* sf = p.inp + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
+                #pragma unroll 1
+                for (uint32_t ci = lane; ci < per_row; ci += 32)
+                    put(n, ci, ld_cg_v4(ci < nchunk ? xs + ci * 16u : sf + (ci - nchunk) * 16u));
+                continue;
             }
             const uint8_t* row_src = type ? cx.buf + p.off_mid + static_cast<size_t>(midrow0 + n) * 2u * p.mid_row_bytes
                                           : cx.rx_row(rowidx[n] >> 24, rowidx[n] & 0xFFFFFFu);
@@ -1119,7 +1130,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
     if (warp == 1) { tmem_alloc(&c.tmem_base, kTmemCols); tmem_relinquish(); tc_fence_before(); }
     if (tid < kMaxLocalExperts) c.exp_count[tid] = 0u;
-    Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, 0u};
+    Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, 0u, own_ok};
     if (is_scout) {
         // the scout does not wait for the prologue: it lists the own rows and asks for their experts' weights first
         bar_arrive(kBarPrologue, kNT);
@@ -1133,9 +1144,24 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     cx.par = c.epoch & 1u;
     const uint32_t epoch = c.epoch, par = cx.par;
     const uint32_t ndisp = static_cast<uint32_t>(p.ndisp);
-    const bool dispatching = bid < static_cast<uint32_t>(p.R) * ndisp;
+    // The rows of this rank's own tokens never travel when `own_ok`: every SM lists them from topk_idx and reads their
+    // tokens where the caller put them. The SM that would have dispatched them only leaves their header line and records
+    // in the receive pool (its scout does, off the critical path), for whoever inspects the pool afterwards.
+    const bool dispatching = bid < static_cast<uint32_t>(p.R) * ndisp &&
+                             !(own_ok && bid - udiv_small(bid, p.R) * p.R == static_cast<uint32_t>(p.rank));
 
   if (is_scout) {
+    if (own_ok && bid == static_cast<uint32_t>(p.rank)) {
+        uint8_t* region = buf + p.off_rx + static_cast<size_t>(par * p.R + p.rank) * p.rx_region;
+        const uint32_t cnt = c.own_cnt, flag = epoch + 1u;
+        if (lane == 0) st_ll_16B(region, make_uint4(cnt, 0u, 0u, 0u), flag);
+        #pragma unroll 1
+        for (uint32_t i = lane; i < cnt; i += 32) {
+            const RowMeta m = c.own_meta[i];
+            st_ll_16B(region + 32u + static_cast<size_t>(i) * 2u * p.rx_row_bytes + 2u * (p.rx_row_bytes - 16),
+                      make_uint4(c.own_e[i], static_cast<uint32_t>(m.token), static_cast<uint32_t>(m.slot), __float_as_uint(m.weight)), flag);
+        }
+    }
     scout_watch_peers(cx, sst, own_ok, lane, G);
     bar_sync(kBarSched, kNT);
   } else {

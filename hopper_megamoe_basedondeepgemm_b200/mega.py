@@ -30,8 +30,8 @@ class SymmBuffer:
 
     def __init__(self, group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int,
                  hidden: int, intermediate_hidden: int, use_fp8_dispatch: bool = True,
-                 activation: str = 'swiglu', act_format: str = 'fp8', num_sms: int = 0):
-        assert act_format in ('fp8', 'mxfp4', 'nvfp4')
+                 activation: str = 'swiglu', act_format: str = 'fp8', num_sms: int = 0, window: str = 'symm_mem'):
+        assert act_format in ('fp8', 'mxfp4', 'nvfp4') and window in ('symm_mem', 'ipc')
         if activation != 'swiglu':
             raise RuntimeError('only the swiglu activation is supported')
         lib = _lib.load()
@@ -50,7 +50,24 @@ class SymmBuffer:
         self.layout = _lib.MMLayout()
         _lib.check(lib.mm_get_layout(ctypes.byref(self.cfg), ctypes.byref(self.layout)), 'get_symm_buffer_for_mega_moe')
         nbytes = int(self.layout.total_bytes)
-        if self.num_ranks > 1:
+        self._ipc = None
+        if self.num_ranks > 1 and window == 'ipc':
+            # the library's own window: device memory + inter-process handles, exchanged once over the group (NCCL)
+            import torch.distributed as dist
+            own = ctypes.c_void_p()
+            handle = ctypes.create_string_buffer(_lib.WINDOW_HANDLE_BYTES)
+            _lib.check(lib.mm_window_alloc(nbytes, ctypes.byref(own), handle), 'mm_window_alloc')
+            mine = torch.frombuffer(bytearray(handle.raw), dtype=torch.uint8).cuda()
+            gathered = [torch.empty_like(mine) for _ in range(self.num_ranks)]
+            dist.all_gather(gathered, mine, group=group)
+            blob = b''.join(bytes(t.cpu().tolist()) for t in gathered)
+            peers = (ctypes.c_void_p * self.num_ranks)()
+            _lib.check(lib.mm_window_open(blob, self.num_ranks, self.rank, own, peers), 'mm_window_open')
+            self._ipc = (own, peers)
+            self.buffer_ptrs = [int(p) for p in peers]
+            self.buffer = _tensor_from_ptr(int(own.value), nbytes)
+            self.handle = SimpleNamespace(buffer_ptrs=list(self.buffer_ptrs), rank=self.rank, world_size=self.num_ranks)
+        elif self.num_ranks > 1:
             import torch.distributed._symmetric_memory as symm_mem
             self.buffer = symm_mem.empty(nbytes, dtype=torch.int8, device='cuda')
             self.handle = symm_mem.rendezvous(self.buffer, group=group)
@@ -184,6 +201,15 @@ class SymmBuffer:
         return torch.tensor(list(out), dtype=torch.int64).view(256, 32)
 
     def destroy(self):
+        if self._ipc is not None:
+            torch.cuda.synchronize()
+            own, peers = self._ipc
+            self.buffer = self.x = self.x_sf = self.topk_idx = self.topk_weights = self.inputs = None
+            self.l1_acts = self.l2_acts = self.l2_acts_sf = self.combine = None
+            if self.group is not None:
+                self.group.barrier()                     # nobody unmaps a buffer a peer's kernel may still write
+            _lib.load().mm_window_close(peers, self.num_ranks, self.rank, own)
+            self._ipc = None
         self.handle = None
         self.buffer = None
         self.group = None
@@ -191,13 +217,21 @@ class SymmBuffer:
         self.x_sf = None
 
 
+def _tensor_from_ptr(ptr: int, nbytes: int) -> torch.Tensor:
+    """An int8 CUDA tensor over memory this process did not allocate through torch (the library's own window)."""
+    class _Mem:
+        __cuda_array_interface__ = {'shape': (nbytes,), 'typestr': '|i1', 'data': (ptr, False), 'version': 3}
+    return torch.as_tensor(_Mem(), device='cuda')
+
+
 def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_rank: int, num_topk: int,
                                  hidden: int, intermediate_hidden: int, use_fp8_dispatch: bool = True,
-                                 activation: str = 'swiglu', act_format: str = 'fp8', num_sms: int = 0) -> SymmBuffer:
+                                 activation: str = 'swiglu', act_format: str = 'fp8', num_sms: int = 0,
+                                 window: str = 'symm_mem') -> SymmBuffer:
     """`sm100_b200/mega___init__.py:63-78`: the token count is rounded up to the operator's alignment."""
     num_max_tokens_per_rank = _align(num_max_tokens_per_rank, get_token_alignment_for_mega_moe())
     return SymmBuffer(group, num_experts, num_max_tokens_per_rank, num_topk, hidden, intermediate_hidden,
-                      use_fp8_dispatch, activation, act_format, num_sms)
+                      use_fp8_dispatch, activation, act_format, num_sms, window)
 
 
 def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor],

@@ -148,6 +148,16 @@ int32_t mm_fe_router_ctas(int32_t m, int32_t h, int32_t e, int32_t topk);
 /* Router frontend and layer as ONE persistent kernel (the frontend's outputs still land in the buffer views). */
 int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_t* args,
                                    const mm_frontend_args_t* fe, void* stream);
+/* The symmetric window without torch: every rank allocates its buffer (device memory, zeroed) and gets a handle of
+ * MM_WINDOW_HANDLE_BYTES that it publishes to the other ranks of the node by whatever the host has (the Python mirror
+ * all-gathers them over its NCCL group); with all handles, mm_window_open maps the peers' buffers and returns the table
+ * of base pointers mm_launch_args.peer_buffers wants. One-time set-up; nothing of it runs per layer. Replaces
+ * `symm_mem.empty` + `symm_mem.rendezvous` (sm100_b200/mega___init__.py:43-47). mm_window_close unmaps the peers and
+ * frees the own buffer (pass NULL to keep it). */
+#define MM_WINDOW_HANDLE_BYTES 64
+int mm_window_alloc(int64_t bytes, void** ptr_out, uint8_t handle_out[MM_WINDOW_HANDLE_BYTES]);
+int mm_window_open(const uint8_t* handles, int32_t num_ranks, int32_t rank, void* own_ptr, void** peer_ptrs_out);
+int mm_window_close(void* const* peer_ptrs, int32_t num_ranks, int32_t rank, void* own_ptr_to_free);
 /* Zero the control block and every flagged region: the launch numbering restarts (after an aborted launch or at
  * creation). The reference's only remedy is re-creating the buffer (sm100_b200/mega___init__.py:43-47). Callers synchronise the ranks around it. */
 int mm_reset(const mm_config_t* cfg, void* buffer, void* stream);

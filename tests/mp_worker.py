@@ -79,7 +79,8 @@ def main():
     if os.environ.get('MP_TOKENS'):                            # many rows per destination: several SMs share a dispatch
         tokens = [int(os.environ['MP_TOKENS']) - 3 * r for r in range(world)]
     ok = True
-    buf = mm.get_symm_buffer_for_mega_moe(group, num_experts, max(16, max(tokens)), topk, hidden, inter, act_format=fmt)
+    buf = mm.get_symm_buffer_for_mega_moe(group, num_experts, max(16, max(tokens)), topk, hidden, inter, act_format=fmt,
+                                          window=os.environ.get('MP_WINDOW', 'symm_mem'))
     weights = [O.make_expert_weights(e_local, hidden, inter, fmt, seed=50 + r, std=0.05)[0] for r in range(world)]
     l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(weights[rank], fmt, 'cuda'))
     for it in range(3):                                          # consecutive launches exercise both parities

@@ -10,8 +10,8 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(nproc, fmt, engine='umma', mode='routed', tokens=None):
-    env = dict(os.environ, MP_FORMAT=fmt, MP_ENGINE=engine, MP_MODE=mode)
+def _run(nproc, fmt, engine='umma', mode='routed', tokens=None, window='symm_mem'):
+    env = dict(os.environ, MP_FORMAT=fmt, MP_ENGINE=engine, MP_MODE=mode, MP_WINDOW=window)
     if tokens:
         env['MP_TOKENS'] = str(tokens)
     cmd = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={nproc}',
@@ -25,6 +25,14 @@ def test_two_ranks(fmt):
     if torch.cuda.device_count() < 2:
         pytest.skip('needs two GPUs')
     _run(2, fmt)
+
+
+def test_two_ranks_over_the_librarys_own_window():
+    """The buffer allocated and mapped through mm_window_alloc / mm_window_open (inter-process memory handles gathered
+    once over the NCCL group) instead of torch's symmetric memory."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip('needs two GPUs')
+    _run(2, 'mxfp4', window='ipc')
 
 
 def test_two_ranks_many_tokens():

@@ -68,3 +68,47 @@ def test_two_gloo_ranks_reproduce_the_single_process_oracle(tmp_path):
         got = torch.load(out + f'.{r}')
         assert torch.equal(got['counts'], ref.counts[r])
         assert torch.equal(got['y'].to(torch.bfloat16), ref.y[r])
+
+
+def _tp_dp_worker(rank, port, out):
+    """4 gloo ranks = 2 data-parallel groups x attention-TP 2; the layer is replaced by a token-wise function with a
+    cross-rank step (an all-reduce of a per-rank checksum over the expert group), so that what is checked is the glue:
+    which tokens each rank feeds, and where its outputs land."""
+    from hopper_megamoe_basedondeepgemm_b200 import tp_dp
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=4)
+    tp_group = tp_dp.make_tp_groups(4, 2, rank)
+    dp_rank, tp_rank = rank // 2, rank % 2
+    m, h = 6, 8
+    g = torch.Generator().manual_seed(100 + dp_rank)
+    full = torch.randn((m, h), generator=g)                              # the TP group's finished hidden states
+    part = torch.randn((m, h), generator=torch.Generator().manual_seed(200 + rank))
+    hidden_partial = part if tp_rank == 0 else full - torch.randn((m, h), generator=torch.Generator().manual_seed(200 + rank - 1))
+    seen = {}
+
+    def layer_fn(y, hloc):
+        seen['h'] = hloc.clone()
+        chk = hloc.sum().reshape(1).clone()
+        dist.all_reduce(chk)                                             # every rank of the expert group takes part
+        y.copy_(hloc * 2.0 + 1.0)
+        seen['chk'] = chk
+    res = {}
+    for mode in (False, True):
+        y = tp_dp.moe_layer_tp_dp(hidden_partial, layer_fn, tp_group, broadcast_output=mode)
+        res[mode] = y.clone()
+    torch.save({'y': res[False], 'y_b': res[True], 'h': seen['h'], 'full': full, 'chk': seen['chk']}, out + f'.{rank}')
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+def test_tp_reduce_scatter_layer_all_gather_glue(tmp_path):
+    out = str(tmp_path / 'tpdp')
+    mp.spawn(_tp_dp_worker, args=(29543, out), nprocs=4, join=True)
+    got = [torch.load(out + f'.{r}') for r in range(4)]
+    total = sum(float(g['full'].sum()) for g in got[::2])
+    for r in range(4):
+        full, tp_rank = got[r]['full'], r % 2
+        assert torch.allclose(got[r]['h'], full[tp_rank * 3:(tp_rank + 1) * 3], atol=1e-5)      # its share of the summed tokens
+        assert torch.allclose(got[r]['y'], full * 2.0 + 1.0, atol=1e-5)                          # all tokens back, in order
+        assert torch.allclose(got[r]['y_b'], got[r]['y'], atol=1e-6)
+        assert abs(float(got[r]['chk']) - total) < 1e-3

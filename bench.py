@@ -203,7 +203,7 @@ def main():
     if args.prefetch_experts >= 0:
         mm.set_tuning(prefetch_w1_experts=args.prefetch_experts, prefetch_w2_experts=args.prefetch_experts)
 
-    buf = mm.get_symm_buffer_for_mega_moe(group, num_experts, T_MAX, TOPK, HIDDEN, INTER, act_format=fmt,
+    buf = mm.get_symm_buffer_for_mega_moe(group, num_experts, max(T_MAX, args.tokens_per_rank), TOPK, HIDDEN, INTER, act_format=fmt,
                                           num_sms=args.num_sms)
     l1, l2, (gs1, gs2), raw_w = W.make_layer_weights(E_LOCAL, HIDDEN, INTER, fmt, seed=1000 + rank, keep_untransformed=True)
     x_gs, mid_gs = (1.0 / 64.0, 1.0 / 512.0) if fmt == 'nvfp4' else (1.0, 1.0)

@@ -20,7 +20,8 @@ class MMLayout(ctypes.Structure):
         'total_bytes', 'off_ctrl', 'off_x', 'off_x_sf', 'off_topk_idx', 'off_topk_weights', 'off_rx',
         'off_mid', 'off_mid_sf', 'off_comb', 'off_red', 'off_cnt', 'off_logits', 'x_row_bytes', 'x_sf_row_bytes', 'rx_row_bytes', 'rx_cap_rows',
         'mid_rows', 'mid_row_bytes', 'mid_sf_row_bytes', 'cnt_per_phase')] + [('sf_vec', ctypes.c_int32), ('ctrl_bytes', ctypes.c_int32),
-                                                   ('rx_region_bytes', ctypes.c_int64)]
+                                                   ('rx_region_bytes', ctypes.c_int64)] + [(n, ctypes.c_int64) for n in (
+        'off_token_tiles', 'off_mid_tiles', 'off_arrive', 'tile_capacity', 'token_tile_bytes', 'mid_tile_bytes')]
 
 
 class MMWeightGeometry(ctypes.Structure):

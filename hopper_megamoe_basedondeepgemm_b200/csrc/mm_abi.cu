@@ -28,7 +28,7 @@ int sf_vec_of(int fmt) { return fmt == MM_FMT_NVFP4 ? 16 : 32; }
 // many experts' W1 / W2 the scout may prefetch into the L2 in one launch
 // (the L2 prefetch of live experts' weights is off by default: measured, it does not shorten the weight stream - bulk
 // copies from the L2 are barely faster than from HBM here - and its traffic delays the launch's small critical loads)
-int g_tuning[MM_TUNE_COUNT] = {mm::kKnobOwnRows | mm::kKnobEarlyCombine, 0, 14, 14, 1};
+int g_tuning[MM_TUNE_COUNT] = {mm::kKnobOwnRows | mm::kKnobEarlyCombine | mm::kKnobTileImages, 0, 14, 14, 1};
 
 int check_config(const mm_config_t* c) {
     if (c == nullptr) return MM_ERR_INVALID_ARGUMENT;
@@ -130,6 +130,13 @@ int mm_get_layout(const mm_config_t* c, mm_layout_t* out) {
     out->off_cnt = take(2 * out->cnt_per_phase * 4);
     // partial router logits of the fused frontend: 16 B per (token, expert), flagged with the launch number
     out->off_logits = take((t_max < mm::kFeMaxFusedTokens ? t_max : mm::kFeMaxFusedTokens) * c->num_experts * 16);
+    // tile images of the launches with more than 16 received rows: token bytes of 16 rows, then one 16 B slot per (scale word, row)
+    out->tile_capacity = out->mid_rows / mm::kTileTokens;
+    out->token_tile_bytes = mm::kTileTokens * out->x_row_bytes + align_up(c->hidden / vec, 16) / 4 * 256;
+    out->mid_tile_bytes = mm::kTileTokens * out->mid_row_bytes + align_up(c->intermediate / vec, 16) / 4 * 256;
+    out->off_token_tiles = take(out->tile_capacity * out->token_tile_bytes);
+    out->off_mid_tiles = take(out->tile_capacity * out->mid_tile_bytes);
+    out->off_arrive = take(2 * 2 * out->tile_capacity * 4);
     out->total_bytes = off;
     return MM_OK;
 }
@@ -263,6 +270,9 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     p.off_topk_idx = L.off_topk_idx; p.off_topk_w = L.off_topk_weights; p.off_rx = L.off_rx;
     p.off_mid = L.off_mid; p.off_mid_sf = L.off_mid_sf; p.off_comb = L.off_comb;
     p.off_red = L.off_red; p.off_cnt = L.off_cnt; p.cnt_per_phase = static_cast<int>(L.cnt_per_phase);
+    p.off_token_tiles = L.off_token_tiles; p.off_mid_tiles = L.off_mid_tiles; p.off_arrive = L.off_arrive;
+    p.tile_capacity = static_cast<uint32_t>(L.tile_capacity);
+    p.token_tile_bytes = static_cast<uint32_t>(L.token_tile_bytes); p.mid_tile_bytes = static_cast<uint32_t>(L.mid_tile_bytes);
     const double tmo = a->timeout_ms > 0.f ? a->timeout_ms : 2000.0;
     p.timeout_ns = static_cast<unsigned long long>(tmo * 1e6);
     // shared memory plan: [stages][token tiles][token scale chunks][output tile][accumulator tile][widened units (FP8)]

@@ -79,7 +79,8 @@ enum : uint32_t {
     kKnobPrefetch = 1u,                 // the scout asks for the weights of every expert it learns to be live (L2 prefetch)
     kKnobOwnRows = 2u,                  // rows of this rank's own tokens are listed from topk_idx by every SM (no header wait)
     kKnobEarlyCombine = 4u,             // warps start on the combine as soon as their role ends
-    kKnobRehearse = 8u                  // idle role warps run their code once on made-up tasks before the roles start
+    kKnobRehearse = 8u,                 // idle role warps run their code once on made-up tasks before the roles start
+    kKnobTileImages = 16u               // launches with more than 16 received rows: operand tiles prepared in global memory, fetched by bulk copies
 };
 
 // device status codes (low byte of status word 0)
@@ -121,6 +122,8 @@ struct KParams {
     const uint8_t* inp;                  // base of the input views: inp + off_x etc. (the buffer itself, or a mapped host mirror of its input region)
     long long off_ctrl, off_x, off_x_sf, off_topk_idx, off_topk_w, off_rx, off_mid, off_mid_sf, off_comb, off_red, off_cnt;
     int cnt_per_phase;
+    long long off_token_tiles, off_mid_tiles, off_arrive;   // operand tile images and their arrival counters (launches with more than 16 rows)
+    uint32_t tile_capacity, token_tile_bytes, mid_tile_bytes;
     long long rx_region;                 // bytes of one (parity, source) region of the receive pool
     uint32_t sm_act, sm_asf, sm_otile, sm_vt;   // dynamic shared memory offsets (stages start at 0)
     uint32_t act_bytes, asf_bytes;
@@ -143,7 +146,7 @@ struct Ctl {
     uint32_t rx_count[kMaxRanks], rx_prefix[kMaxRanks + 1];
     uint32_t exp_count[kMaxLocalExperts], mid_base[kMaxLocalExperts];
     uint32_t nt1, nt2, dcount, own_cnt;
-    uint32_t comb_next, issued, decode, pad2; // next combine item of this SM; weight units the loader has issued; decode mode (see below)
+    uint32_t comb_next, issued, decode, bulk; // next combine item of this SM; weight units the loader has issued; decode mode (see below)
     uint32_t n1_tasks, padn[3];          // L1 tasks at the head of this SM's list
     uint32_t epi_nv[2], epi_dcol[2];     // per accumulator: valid rows of the task and (decode mode) the first accumulator column of its expert
     // token staging geometry of this launch: with room for one 16-row buffer only, launches whose experts all have at
@@ -167,7 +170,7 @@ struct Ctl {
     RowMeta rx_meta[kMetaSmemRows];
     RowMeta own_meta[kOwnCap];           // records of this rank's own routed rows, listed by the scout from topk_idx
     uint8_t own_e[kOwnCap];
-    uint8_t meta_e[kMetaCap];
+    alignas(16) uint8_t meta_e[kMetaCap];
 };
 
 __device__ __forceinline__ uint32_t task_pack(uint32_t type, uint32_t e, uint32_t mt, uint32_t j) {
@@ -493,6 +496,35 @@ __device__ __noinline__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t la
         __syncwarp();
         uint8_t* act = cx.smem + p.sm_act + ab * act_stride;
         uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
+        if (!dry && c.bulk != 0u) {
+            // the task's operand tile is ready-made in global memory: wait until its rows (L1: the tile's received rows,
+            // L2: the outputs of all L1 weight tiles) have been counted in, then fetch tokens and scale slots with two bulk copies
+            const uint32_t tile = (c.mid_base[e] / kTileTokens) + mt;
+            const uint32_t* arr = reinterpret_cast<const uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + type) * p.tile_capacity + tile;
+            const uint32_t need = type ? static_cast<uint32_t>(p.n1_tiles) : nv;
+            uint32_t spins = 0;
+            bool bad = false;
+            while (ld_acquire_gpu(arr) < need) {
+                if ((++spins & 0x3Fu) == 0u) {
+                    if (cx.aborted()) { bad = true; break; }
+                    if (cx.expired()) { cx.fail(type ? kErrWaitL1Done : kErrWaitDispatchFlag, e); bad = true; break; }
+                }
+            }
+            if (bad) return;
+            if (lane == 0) {
+                fence_proxy_async_all();
+                const uint32_t tok_bytes = kTileTokens * static_cast<uint32_t>(type ? p.mid_row_bytes : p.x_row_bytes);
+                const uint32_t img_bytes = type ? p.mid_tile_bytes : p.token_tile_bytes;
+                const uint8_t* img = cx.buf + (type ? p.off_mid_tiles : p.off_token_tiles) + static_cast<size_t>(tile) * img_bytes;
+                mbar_arrive_expect_tx(&c.acts_full[ab], img_bytes);
+                bulk_g2s(act, img, tok_bytes, &c.acts_full[ab]);
+                bulk_g2s(asf, img + tok_bytes, img_bytes - tok_bytes, &c.acts_full[ab]);
+                if (tis == 0u) cx.sm_phase(kSmFirstStaged);
+                if (type != 0u && !seen_l2) { seen_l2 = true; cx.sm_phase(kSmFirstL2Staged); }
+            }
+            __syncwarp();
+            continue;
+        }
         // Both kinds of rows are flagged words that may still be on their way (received tokens for L1, the L1 epilogues'
         // output of other SMs for L2): a chunk is re-read until its flags match. Received rows carry their scale bytes
         // behind the tokens; intermediate rows keep theirs as one flagged word per (row, L1 tile).
@@ -823,6 +855,30 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 // tile's scale bytes.
                 constexpr uint32_t kChunks = kA8 ? 4u : 2u;
                 const uint32_t flag = c.epoch + 1u;
+                if (!kA8 && c.bulk != 0u) {
+                    // operand tile image of the L2 tasks: plain stores into the swizzled tile and the scale-word slots, then
+                    // one count into the tile's arrival word (the L2 token fetch is a bulk copy: it cannot poll flags)
+                    const uint32_t tile = midrow0 / kTileTokens;
+                    uint8_t* img = cx.buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes;
+                    if (etid < nv * kChunks) {
+                        const uint32_t n = etid / kChunks, ci = j * kChunks + etid % kChunks;
+                        const uint4 val = *reinterpret_cast<const uint4*>(otile + etid * 16u);
+                        *reinterpret_cast<uint4*>(img + (ci >> 3) * (kTileTokens * 128u) + sw128_off(n, ci & 7u)) = val;
+                    } else if (etid >= 64u && etid - 64u < nv) {
+                        const uint32_t n = etid - 64u;
+                        uint8_t* slots = img + kTileTokens * p.mid_row_bytes;
+                        if constexpr (kVec == 16)
+                            *reinterpret_cast<uint32_t*>(slots + j * 256u + n * 16u) = c.sfb[0][n] | (c.sfb[1][n] << 8) | (c.sfb[2][n] << 16) | (c.sfb[3][n] << 24);
+                        else
+                            *reinterpret_cast<uint16_t*>(slots + (j >> 1) * 256u + n * 16u + (j & 1u) * 2u) = static_cast<uint16_t>(c.sfb[0][n] | (c.sfb[2][n] << 8));
+                    }
+                    __threadfence();
+                    bar_sync(kBarEpi, kNumEpiThreads);
+                    if (etid == 0u) {
+                        fence_proxy_async_all();
+                        red_release_gpu_add(reinterpret_cast<uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + 1u) * p.tile_capacity + tile, 1u);
+                    }
+                } else
                 if (etid < nv * kChunks) {
                     const uint32_t n = etid / kChunks, q16 = etid % kChunks;
                     const uint4 val = *reinterpret_cast<const uint4*>(otile + (n * kChunks + q16) * 16u);
@@ -1107,7 +1163,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (tid == 0) {
         const uint32_t ep = ctrl32[kCtrlEpoch / 4 + bid];
         ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
-        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u; c.decode = 0u;
+        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u; c.decode = 0u; c.bulk = 0u;
         if constexpr (!kScout) c.own_cnt = 0u;
         for (int s = 0; s < p.nstage; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
         #pragma unroll 1
@@ -1144,6 +1200,13 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     cx.par = c.epoch & 1u;
     const uint32_t epoch = c.epoch, par = cx.par;
     const uint32_t ndisp = static_cast<uint32_t>(p.ndisp);
+    // arrival counters of the operand tile images: this launch counts in the set of its parity and clears the other one
+    // for the next launch (the launch before this one, which used that set, has ended)
+    if (!is_scout) {
+        uint32_t* other = reinterpret_cast<uint32_t*>(buf + p.off_arrive) + (par ^ 1u) * 2u * p.tile_capacity;
+        #pragma unroll 1
+        for (uint32_t i = bid * kO + tid; i < 2u * p.tile_capacity; i += G * kO) other[i] = 0u;
+    }
     // The rows of this rank's own tokens never travel when `own_ok`: every SM lists them from topk_idx and reads their
     // tokens where the caller put them. The SM that would have dispatched them only leaves their header line and records
     // in the receive pool (its scout does, off the critical path), for whoever inspects the pool afterwards.
@@ -1344,6 +1407,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             if (bid == 0) cx.stamp(kStampFlagsSeen);
             cx.sm_phase(kSmCountsKnown);
             c.decode = (kUmma && !kA8 && p.rc_rows != 0u && total != 0u && total <= kTileTokens) ? 1u : 0u;     // (the cross-check engine reads the per-task staging buffers)
+            c.bulk = (kUmma && !kA8 && (p.knobs & kKnobTileImages) != 0u && p.nab == 2 && total > kTileTokens && total <= kMetaCap) ? 1u : 0u;
+            if (bid == 0) ctrl32[kCtrlStatus / 4 + 2] = c.bulk;          // (for whoever inspects the intermediate rows afterwards)
         }
         if (total <= kMetaCap) {
             auto take = [&](uint32_t f, const uint4& m) {
@@ -1385,7 +1450,112 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     //      (a sender pushes its header line and records first). The loads are in flight before the bulk copies of the
     //      weight stream start, which would otherwise make them wait behind megabytes.
     const bool is_ctl = warp < 2u;                       // warps 0 and 1 build the schedule and start the weight stream
-    if (warp >= 2u && warp < 2u + kFillWarps && p.rc_rows != 0u && total <= kMetaCap && !cx.aborted()) {
+    // ---- more than 16 received rows: the rows are sorted into operand tile images in global memory, one image per
+    //      16-token tile of an expert, laid out exactly as the tensor core reads it from shared memory (K atoms of
+    //      16 rows x 128 B with the 128 B swizzle, then the scale-word slots). Row f belongs to SM f mod G; one warp per
+    //      row. A task's token operand is then two bulk copies issued by one thread, which the weight flood does not
+    //      slow down the way it slows thousands of small loads. Every finished row counts into its tile's arrival word.
+    if (warp >= 2u && warp < 2u + kFillWarps && c.bulk != 0u && !cx.aborted()) {
+        const uint32_t el = p.e_local;
+        // first tile of every expert: running sum of ceil(rows / 16), expert-major (the schedule derives the same numbers)
+        const uint32_t m0 = ((lane < el ? c.exp_count[lane] : 0u) + kTileTokens - 1) / kTileTokens;
+        const uint32_t m1 = ((lane + 32 < el ? c.exp_count[lane + 32] : 0u) + kTileTokens - 1) / kTileTokens;
+        uint32_t i0 = m0, i1 = m1;
+        #pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const uint32_t v0 = __shfl_up_sync(0xffffffffu, i0, o), v1 = __shfl_up_sync(0xffffffffu, i1, o);
+            if (static_cast<int>(lane) >= o) { i0 += v0; i1 += v1; }
+        }
+        const uint32_t tbase0 = i0 - m0, tbase1 = __shfl_sync(0xffffffffu, i0, 31) + i1 - m1;
+        const uint32_t per_row = p.rc_row_bytes / 16u, xq = p.x_row_bytes / 16u;
+        uint32_t* arrive = reinterpret_cast<uint32_t*>(buf + p.off_arrive) + par * 2u * p.tile_capacity;
+        #pragma unroll 1
+        for (uint32_t f = bid + (warp - 2u) * G; f < total; f += kFillWarps * G) {
+            const uint32_t e = c.meta_e[f];
+            // position among the expert's rows = rows of the same expert received before this one
+            uint32_t n = 0;
+            #pragma unroll 1
+            for (uint32_t base = 0; base < f; base += 128) {
+                const uint32_t idx = base + lane * 4u;
+                const uint32_t w = *reinterpret_cast<const uint32_t*>(c.meta_e + idx);
+                #pragma unroll
+                for (uint32_t b = 0; b < 4; ++b) n += (idx + b < f && ((w >> (8u * b)) & 0xFFu) == e) ? 1u : 0u;
+            }
+            n = __reduce_add_sync(0xffffffffu, n);
+            const uint32_t tb0 = __shfl_sync(0xffffffffu, tbase0, e & 31u), tb1 = __shfl_sync(0xffffffffu, tbase1, e & 31u);
+            const uint32_t tile = (e < 32u ? tb0 : tb1) + n / kTileTokens, pos = n % kTileTokens;
+            uint32_t r = 0;
+            while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
+            const uint32_t i = f - c.rx_prefix[r];
+            const bool own = own_ok && r == static_cast<uint32_t>(p.rank);
+            const uint8_t* xs = nullptr;
+            const uint8_t* sf = nullptr;
+            const uint8_t* row_src = nullptr;
+            if (own) {
+                const uint32_t tok = static_cast<uint32_t>(c.own_meta[i].token);
+                xs = inp + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
+                sf = inp + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
+            } else {
+                row_src = cx.rx_row(r, i);
+            }
+            uint8_t* img = buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes;
+            uint8_t* img_sf = img + kTileTokens * p.x_row_bytes;
+            bool bad = tile >= p.tile_capacity;
+            #pragma unroll 1
+            for (uint32_t base = lane; base < per_row && !bad; base += 4 * 32) {
+                uint4 v[4];
+                if (own) {
+                    #pragma unroll
+                    for (uint32_t u = 0; u < 4; ++u) {
+                        const uint32_t ci = base + u * 32;
+                        if (ci < xq) v[u] = ld_cg_v4(xs + ci * 16u);
+                        else if (ci < per_row) v[u] = ld_cg_v4(sf + (ci - xq) * 16u);
+                    }
+                } else {
+                    uint32_t spins = 0;
+                    bool ok;
+                    do {
+                        ok = true;
+                        #pragma unroll
+                        for (uint32_t u = 0; u < 4; ++u) {
+                            const uint32_t ci = base + u * 32;
+                            if (ci < per_row) {
+                                const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
+                                ok = ok && ll_valid(a, b, flag_rx);
+                                v[u] = ll_data(a, b);
+                            }
+                        }
+                        if (!ok && (++spins & 0x3Fu) == 0u) {
+                            if (cx.aborted()) bad = true;
+                            else if (cx.expired()) { cx.fail(kErrWaitDispatchFlag, r); bad = true; }
+                        }
+                    } while (!ok && !bad);
+                }
+                #pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t ci = base + u * 32;
+                    if (ci >= per_row || bad) continue;
+                    if (ci < xq) {
+                        *reinterpret_cast<uint4*>(img + (ci >> 3) * (kTileTokens * 128u) + sw128_off(pos, ci & 7u)) = v[u];
+                    } else {
+                        uint8_t* dst = img_sf + (ci - xq) * 4u * 256u + pos * 16u;
+                        *reinterpret_cast<uint32_t*>(dst) = v[u].x;
+                        *reinterpret_cast<uint32_t*>(dst + 256u) = v[u].y;
+                        *reinterpret_cast<uint32_t*>(dst + 512u) = v[u].z;
+                        *reinterpret_cast<uint32_t*>(dst + 768u) = v[u].w;
+                    }
+                }
+            }
+            const bool any_bad = __any_sync(0xffffffffu, bad);      // (also orders the lanes' stores before lane 0's fence)
+            if (lane == 0 && !any_bad) {
+                __threadfence();
+                fence_proxy_async_all();
+                red_release_gpu_add(arrive + tile, 1u);
+                cx.sm_phase(kSmRowsCached);
+            }
+        }
+    }
+    if (warp >= 2u && warp < 2u + kFillWarps && p.rc_rows != 0u && total <= kMetaCap && c.bulk == 0u && !cx.aborted()) {
         const bool decode = c.decode != 0u;
         const uint32_t per_row = p.rc_row_bytes / 16u, xq = p.x_row_bytes / 16u;
         const uint32_t limit = total < p.rc_rows ? total : p.rc_rows;

@@ -67,6 +67,11 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 }
 
 // ----------------------------------------------------------------------------- named barriers
+// orders this thread's earlier accesses through the generic proxy (plain loads, stores, acquires) with its later
+// asynchronous-proxy operations (bulk copies) and the other way round, in every state space
+__device__ __forceinline__ void fence_proxy_async_all() {
+    asm volatile("fence.proxy.async;" ::: "memory");
+}
 __device__ __forceinline__ void bar_sync(uint32_t id, uint32_t nthreads) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

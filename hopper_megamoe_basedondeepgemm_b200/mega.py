@@ -105,6 +105,12 @@ class SymmBuffer:
                             (int(L.mid_rows), 2 * int(L.mid_row_bytes)))
         self.l2_acts_sf = view(L.off_mid_sf, L.mid_rows * (intermediate_hidden // 64) * 8, torch.uint8,
                                (int(L.mid_rows), (intermediate_hidden // 64) * 8))
+        # launches with more than 16 received rows keep the same rows as ready-made operand tiles instead (per 16-row
+        # tile: K atoms of 16 rows x 128 B in the tensor core's swizzled order, then one 16 B slot per (scale word, row))
+        self.token_tiles = view(L.off_token_tiles, L.tile_capacity * L.token_tile_bytes, torch.uint8,
+                                (int(L.tile_capacity), int(L.token_tile_bytes)))
+        self.mid_tiles = view(L.off_mid_tiles, L.tile_capacity * L.mid_tile_bytes, torch.uint8,
+                              (int(L.tile_capacity), int(L.mid_tile_bytes)))
         # expert outputs coming back: per (token, slot) hidden / 2 flagged words {2 bf16, launch flag}
         self.combine = view(L.off_comb, t * num_topk * hidden * 4, torch.int32, (t, num_topk, hidden // 2, 2))
 
@@ -124,13 +130,36 @@ class SymmBuffer:
                  'topk_weights': view(int(L.off_topk_weights), t * self.num_topk * 4, self.topk_weights)}
         return mirror, views
 
+    def used_tile_images(self) -> bool:
+        """Whether the latest launch kept its received and intermediate rows as operand tile images (more than 16
+        received rows) rather than as flagged rows. Synchronises the stream."""
+        return bool(self.device_status()[1][2])
+
+    @staticmethod
+    def _rows_of_tile_images(tiles: torch.Tensor, row_bytes: int):
+        """(rows uint8 [tiles * 16, row_bytes], scale words uint8 [tiles * 16, words, 4]) of operand tile images."""
+        tiles = tiles.cpu()
+        nt, atoms = tiles.size(0), row_bytes // 128
+        tok = tiles[:, :16 * row_bytes].view(nt, atoms, 16, 8, 16)             # [tile][atom][row][stored chunk][16 B]
+        r = torch.arange(16).view(16, 1)
+        stored = (torch.arange(8).view(1, 8) ^ (r & 7)).view(1, 1, 16, 8, 1).expand(nt, atoms, 16, 8, 16)
+        rows = torch.gather(tok, 3, stored).permute(0, 2, 1, 3, 4).reshape(nt * 16, row_bytes)
+        slots = tiles[:, 16 * row_bytes:].view(nt, -1, 16, 16)                  # [tile][scale word][row][16 B slot]
+        words = slots[..., :4].permute(0, 2, 1, 3).reshape(nt * 16, -1, 4)
+        return rows.contiguous(), words.contiguous()
+
     def l2_acts_payload(self) -> torch.Tensor:
-        """The intermediate rows without their flag words: uint8 [mid_rows, mid_row_bytes]."""
+        """The intermediate rows of the latest launch without flag words or swizzle: uint8 [mid_rows, mid_row_bytes]."""
+        if self.used_tile_images():
+            return self._rows_of_tile_images(self.mid_tiles, int(self.layout.mid_row_bytes))[0]
         rows = self.l2_acts.size(0)
         return self.l2_acts.view(torch.int32).view(rows, -1, 2)[..., 0].contiguous().view(torch.uint8).view(rows, -1)
 
     def l2_acts_sf_payload(self) -> torch.Tensor:
         """The intermediate rows' scale bytes, K-major: uint8 [mid_rows, intermediate / vec]."""
+        if self.used_tile_images():
+            words = self._rows_of_tile_images(self.mid_tiles, int(self.layout.mid_row_bytes))[1]
+            return words.reshape(words.size(0), -1)[:, :self.intermediate_hidden // int(self.layout.sf_vec)].contiguous()
         rows = self.l2_acts_sf.size(0)
         words = self.l2_acts_sf.view(torch.int32).view(rows, -1, 2)[..., 0].contiguous().view(torch.uint8).view(rows, -1, 4)
         per_tile = 64 // int(self.layout.sf_vec)
@@ -205,7 +234,7 @@ class SymmBuffer:
             torch.cuda.synchronize()
             own, peers = self._ipc
             self.buffer = self.x = self.x_sf = self.topk_idx = self.topk_weights = self.inputs = None
-            self.l1_acts = self.l2_acts = self.l2_acts_sf = self.combine = None
+            self.l1_acts = self.l2_acts = self.l2_acts_sf = self.combine = self.token_tiles = self.mid_tiles = None
             if self.group is not None:
                 self.group.barrier()                     # nobody unmaps a buffer a peer's kernel may still write
             _lib.load().mm_window_close(peers, self.num_ranks, self.rank, own)

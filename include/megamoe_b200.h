@@ -64,6 +64,12 @@ typedef struct mm_layout {
     int32_t sf_vec;            /* elements per scale byte of the activation format */
     int32_t ctrl_bytes;        /* bytes of the control block at off_ctrl */
     int64_t rx_region_bytes;   /* bytes of one (parity, source) region of the receive pool */
+    /* Launches with more than 16 received rows: rows sorted by expert into ready-made 16-token operand tiles (local). */
+    int64_t off_token_tiles;   /* [tile_capacity][token_tile_bytes] received tokens of one 16-row tile of one expert, in the shared-memory
+                                  image the tensor core reads (K atoms of 16 rows x 128 B, 128 B swizzle), then the scale-word slots */
+    int64_t off_mid_tiles;     /* [tile_capacity][mid_tile_bytes] the same for the requantised SwiGLU output */
+    int64_t off_arrive;        /* [2 parities][2][tile_capacity] uint32: rows of a token tile written / L1 weight tiles of a mid tile written */
+    int64_t tile_capacity, token_tile_bytes, mid_tile_bytes;
 } mm_layout_t;
 
 /* Geometry of the pre-tiled weight stream produced by the load-time transform.
@@ -162,7 +168,8 @@ int mm_window_close(void* const* peer_ptrs, int32_t num_ranks, int32_t rank, voi
  * creation). The reference's only remedy is re-creating the buffer (sm100_b200/mega___init__.py:43-47). Callers synchronise the ranks around it. */
 int mm_reset(const mm_config_t* cfg, void* buffer, void* stream);
 /* Synchronises `stream`, then copies the 16 device status words: [0] first failure (0 = none; code | sm << 8 |
- * detail << 16), [1] launches seen, [2..] diagnostics. The reference traps instead (sm100_b200/layout_mega_moe.cuh:13-19). */
+ * detail << 16), [1] launches seen, [2] 1 when the latest launch kept its rows as operand tile images (more than 16
+ * received rows), [3..] diagnostics. The reference traps instead (sm100_b200/layout_mega_moe.cuh:13-19). */
 int mm_read_device_status(const mm_config_t* cfg, const void* buffer, uint32_t out_words[16], void* stream);
 /* Synchronises `stream`, then copies the 32 phase stamps (globaltimer ns) of the last launch. Slots, SM 0 unless
  * noted: 0 first instruction, 1 dispatched, 2 header lines of all ranks seen, 3 scheduled, 4 tasks done, 5 prologue
@@ -182,7 +189,8 @@ int mm_read_sm_phases(const mm_config_t* cfg, const void* buffer, uint64_t* out_
  * variables (sm100_b200/sm100_fp4_fp4_mega_moe.hpp:215-248). MM_TUNE_KNOBS is a bit mask: 1 the spare warp asks for a
  * live expert's weights (L2 prefetch) as soon as it learns of the expert, 2 every SM lists the rows of this rank's own
  * tokens from topk_idx instead of waiting for the own-rank header line, 4 warps start the combine when their role ends,
- * 8 the token-staging warps rehearse their code on made-up tasks while the dispatch is in flight. */
+ * 8 the token-staging warps rehearse their code on made-up tasks while the dispatch is in flight, 16 launches with more
+ * than 16 received rows sort them into ready-made operand tiles in global memory and fetch a task's tokens by bulk copies. */
 enum mm_tuning_key { MM_TUNE_KNOBS = 0, MM_TUNE_STAGES = 1 /* ring depth, 0 = default */,
                      MM_TUNE_PREFETCH_W1_EXPERTS = 2, MM_TUNE_PREFETCH_W2_EXPERTS = 3 /* experts prefetched per launch at most */,
                      MM_TUNE_ROW_CACHE = 4 /* 1: received rows are fetched into shared memory before the weight stream starts */,

@@ -266,14 +266,15 @@ def test_bounded_wait_reports_timeout_and_buffer_recovers():
 
 @pytest.mark.parametrize('fmt', ['mxfp4', 'fp8'])
 def test_kernel_features_do_not_change_the_result(fmt):
-    """The scout's weight prefetch, the own-row listing and the early combine are scheduling changes only: with all of
-    them off and with all of them on the layer writes the same bits."""
+    """The scout's weight prefetch, the own-row listing, the early combine and the operand tile images (24 received rows
+    here: more than one 16-row tile) are scheduling and data-movement changes only: with all of them off and with all of
+    them on the layer writes the same bits."""
     from hopper_megamoe_basedondeepgemm_b200 import _lib
     lib = _lib.load()
     default = lib.mm_get_tuning(_lib.TUNE['knobs'])
     outs = []
     try:
-        for knobs in (0, 7, 1, 2, 4):
+        for knobs in (0, 7, 1, 2, 4, 16, 22):
             mm.set_tuning(knobs=knobs)
             y, stats, ref, buf, _ = run_layer(fmt, e_local=48, hidden=3072, inter=1280, topk=8, tokens=3, routing='balanced',
                                               engine='umma', std=0.02)

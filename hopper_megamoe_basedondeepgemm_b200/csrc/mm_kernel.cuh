@@ -80,6 +80,7 @@ enum : uint32_t {
     kKnobOwnRows = 2u,                  // rows of this rank's own tokens are listed from topk_idx by every SM (no header wait)
     kKnobEarlyCombine = 4u,             // warps start on the combine as soon as their role ends
     kKnobRehearse = 8u,                 // idle role warps run their code once on made-up tasks before the roles start
+    kKnobWaitProfile = 32u,             // the roles add up the cycles they spend waiting; totals replace the per-unit landing times in the SM records
     kKnobTileImages = 16u               // launches with more than 16 received rows: operand tiles prepared in global memory, fetched by bulk copies
 };
 
@@ -209,6 +210,17 @@ struct Ctx {
         return true;
     }
     // every lane waits; the warp agrees on the outcome
+    // (timed variant: the cycles spent in the wait are added to `acc`)
+    __device__ __forceinline__ bool warp_wait_t(uint64_t* bar, uint32_t parity, uint32_t code, long long& acc) const {
+        const long long t0 = clock64();
+        const bool ok = warp_wait(bar, parity, code);
+        acc += clock64() - t0;
+        return ok;
+    }
+    __device__ __forceinline__ void wait_total(int slot, long long cycles) const {
+        if ((p.knobs & kKnobWaitProfile) != 0u)
+            reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmPhase)[blockIdx.x * kSmPhaseSlots + slot] = static_cast<unsigned long long>(cycles);
+    }
     __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, uint32_t code) const {
         return __all_sync(0xffffffffu, wait(bar, parity, code));
     }
@@ -271,6 +283,7 @@ __device__ __forceinline__ float sf_value(uint32_t byte) {
 __device__ void role_loader(const Ctx& cx) {
     const KParams& p = cx.p; Ctl& c = cx.c;
     uint32_t it = 0, s = 0, ph = 0;                              // units issued; ring stage and its phase bit
+    long long w_empty = 0;
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
@@ -280,7 +293,7 @@ __device__ void role_loader(const Ctx& cx) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
-            if (!cx.warp_wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
+            if (!cx.warp_wait_t(&c.empty[s], ph ^ 1u, kErrWaitEmpty, w_empty)) return;
             if (elect_one()) {
                 mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
                 bulk_g2s(cx.smem + static_cast<size_t>(s) * p.unit_bytes, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
@@ -291,6 +304,7 @@ __device__ void role_loader(const Ctx& cx) {
             if (++s == static_cast<uint32_t>(p.nstage)) { s = 0; ph ^= 1u; }
         }
     }
+    if ((threadIdx.x & 31u) == 0u) cx.wait_total(16, w_empty);
 }
 
 // ============================================================================================= MMA issuer
@@ -306,6 +320,9 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 16
     uint32_t it = 0, s = 0, ph = 0;                             // units consumed so far; ring stage and its phase bit
     unsigned long long t_landed = 0ull;                         // when the latest unit was found in shared memory
+    long long w_acts = 0, w_tmem = 0, w_full = 0;
+    const long long t_role = clock64();
+    const unsigned long long ns_role = globaltimer_ns();
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
@@ -316,8 +333,8 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         const uint32_t tis = (!kA8 && c.decode != 0u) ? ti - c.n1_tasks : ti;
         const uint32_t ab = c.nab == 2u ? (tis & 1u) : 0u, use_a = c.nab == 2u ? (tis >> 1) & 1u : (tis & 1u);
         if (shared_tile) { if (!cx.warp_wait(&c.tile_full, 0u, kErrWaitActsFull)) return; }
-        else if (!cx.warp_wait(&c.acts_full[ab], use_a, kErrWaitActsFull)) return;
-        if (!cx.warp_wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty)) return;
+        else if (!cx.warp_wait_t(&c.acts_full[ab], use_a, kErrWaitActsFull, w_acts)) return;
+        if (!cx.warp_wait_t(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty, w_tmem)) return;
         tc_fence_after();
         const uint32_t act = shared_tile ? smem_u32(cx.tok_region()) : smem_u32(cx.smem + p.sm_act + ab * c.act_stride);
         const uint32_t asf_base = shared_tile ? smem_u32(cx.tile_asf()) : smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes);
@@ -325,12 +342,12 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
             uint64_t* ready = kA8 ? &c.xfull[it & 1u] : &c.full[s];
-            if (!cx.warp_wait(ready, kA8 ? (it >> 1) & 1u : ph, kErrWaitFull)) return;
+            if (!cx.warp_wait_t(ready, kA8 ? (it >> 1) & 1u : ph, kErrWaitFull, w_full)) return;
             tc_fence_after();
             t_landed = globaltimer_ns();
             if (lane == 0) {
                 if (it == 0u) cx.sm_phase(kSmFirstLanded);
-                if (it < 15u) cx.sm_phase(16 + static_cast<int>(it));
+                if (it < 15u && (p.knobs & kKnobWaitProfile) == 0u) cx.sm_phase(16 + static_cast<int>(it));
             }
             if (elect_one()) {
               {
@@ -376,6 +393,10 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         __syncwarp();
     }
     if (lane == 0 && t_landed != 0ull) cx.stamp_max(kStampLastWeight, t_landed);
+    if (lane == 0) {
+        cx.wait_total(17, w_acts); cx.wait_total(18, w_tmem); cx.wait_total(19, w_full); cx.wait_total(20, clock64() - t_role);
+        cx.wait_total(25, static_cast<long long>(globaltimer_ns() - ns_role));
+    }
 }
 
 // ============================================================================================= weight widener (FP8 variant)
@@ -682,6 +703,8 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     uint8_t* otile = cx.smem + p.sm_otile;
     float* vt = reinterpret_cast<float*>(cx.smem + p.sm_vt) + row;      // this thread's accumulators: vt[n * 128], token n
     uint32_t it = 0;
+    long long w_tfull = 0, w_l1 = 0, w_l2 = 0;
+    const long long t_role = clock64();
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
@@ -691,8 +714,10 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
         // ---- accumulators of the valid tokens -> shared memory (the loops below run over the valid tokens only)
         bool ok;
         uint32_t nv = 0;
+        long long t_work = 0;
         if constexpr (kUmma) {
-            ok = cx.warp_wait(&c.tmem_full[acc], use, kErrWaitTmemFull);
+            ok = cx.warp_wait_t(&c.tmem_full[acc], use, kErrWaitTmemFull, w_tfull);
+            t_work = clock64();
             // decode mode, L1 task: nobody staged anything for this task (its tokens sit in the launch's shared tile). The
             // first epilogue warp lists the expert's rows itself, in receive order: their records, how many there are, and
             // how many rows of experts with a smaller index precede them in the tile (= the expert's first column).
@@ -872,8 +897,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                         else
                             *reinterpret_cast<uint16_t*>(slots + (j >> 1) * 256u + n * 16u + (j & 1u) * 2u) = static_cast<uint16_t>(c.sfb[0][n] | (c.sfb[2][n] << 8));
                     }
-                    __threadfence();
-                    bar_sync(kBarEpi, kNumEpiThreads);
+                    bar_sync(kBarEpi, kNumEpiThreads);                    // every thread's stores precede thread 0's release
                     if (etid == 0u) {
                         fence_proxy_async_all();
                         red_release_gpu_add(reinterpret_cast<uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + 1u) * p.tile_capacity + tile, 1u);
@@ -910,7 +934,9 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             if (ti == 0u) cx.sm_phase(kSmFirstEpilogue);
             if (type == 0u) cx.sm_phase(kSmLastL1Epilogue);
         }
+        if constexpr (kUmma) { if (type == 0u) w_l1 += clock64() - t_work; else w_l2 += clock64() - t_work; }
     }
+    if (etid == 0u) { cx.wait_total(21, w_tfull); cx.wait_total(22, clock64() - t_role); cx.wait_total(23, w_l1); cx.wait_total(24, w_l2); }
 }
 
 // ============================================================================================= schedule

@@ -132,8 +132,13 @@ int mm_get_layout(const mm_config_t* c, mm_layout_t* out) {
     out->off_logits = take((t_max < mm::kFeMaxFusedTokens ? t_max : mm::kFeMaxFusedTokens) * c->num_experts * 16);
     // tile images of the launches with more than 16 received rows: token bytes of 16 rows, then one 16 B slot per (scale word, row)
     out->tile_capacity = out->mid_rows / mm::kTileTokens;
-    out->token_tile_bytes = mm::kTileTokens * out->x_row_bytes + align_up(c->hidden / vec, 16) / 4 * 256;
-    out->mid_tile_bytes = mm::kTileTokens * out->mid_row_bytes + align_up(c->intermediate / vec, 16) / 4 * 256;
+    {
+        // per tile: 32 row records of 16 B (token tiles only), then per streamed K unit a record of up to 32 rows x 128 B
+        // and the unit's scale-word slots (16 B per (scale word, row))
+        const int64_t rec32 = mm::kWideTokens * 128 + (mm::kUnitK / (4 * vec)) * mm::kWideTokens * 16;
+        out->token_tile_bytes = mm::kWideTokens * 16 + (c->hidden / mm::kUnitK) * rec32;
+        out->mid_tile_bytes = (c->intermediate / mm::kUnitK) * rec32;
+    }
     out->off_token_tiles = take(out->tile_capacity * out->token_tile_bytes);
     out->off_mid_tiles = take(out->tile_capacity * out->mid_tile_bytes);
     out->off_arrive = take(2 * 2 * out->tile_capacity * 4);
@@ -286,10 +291,12 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     // two token staging buffers when that leaves at least four stream stages, else one
     // (with one, the kernel still runs two 8-row halves when no expert has more than 8 rows: two scale-slot areas always)
     p.nab = 2;
-    size_t fixed = p.nab * p.act_bytes + 2 * p.asf_bytes + mm::kOtileBytes + mm::kVtBytes + xbytes;
+    // output tile and accumulator tile: sized for 32-row token tiles, which only the formats with tile images use
+    const size_t otile_bytes = a8 ? mm::kOtileBytes / 2 : mm::kOtileBytes, vt_bytes = a8 ? mm::kVtBytes / 2 : mm::kVtBytes;
+    size_t fixed = p.nab * p.act_bytes + 2 * p.asf_bytes + otile_bytes + vt_bytes + xbytes;
     if (fixed + 4 * static_cast<size_t>(p.unit_bytes) > budget) {
         p.nab = 1;
-        fixed = p.nab * p.act_bytes + 2 * p.asf_bytes + mm::kOtileBytes + mm::kVtBytes + xbytes;
+        fixed = p.nab * p.act_bytes + 2 * p.asf_bytes + otile_bytes + vt_bytes + xbytes;
     }
     if (fixed + 2 * static_cast<size_t>(p.unit_bytes) > budget) return MM_ERR_UNSUPPORTED;
     int nstage = static_cast<int>((budget - fixed) / p.unit_bytes);
@@ -307,13 +314,17 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
         if (nd > 32) nd = 32;
         p.ndisp = nd < 1 ? 1 : nd;
     }
+    // launches that work from tile images reuse the stages and the token staging area as one ring of wider stages
+    p.wide_stage_bytes = p.unit_bytes + mm::kWideTokens * 128 + (mm::kUnitK / (4 * vec)) * mm::kWideTokens * 16;
     p.sm_act = nstage * p.unit_bytes;
     p.sm_asf = p.sm_act + p.nab * p.act_bytes;
     p.sm_otile = p.sm_asf + 2 * p.asf_bytes;
     p.stage_region = p.sm_otile - p.sm_act;
-    p.sm_vt = p.sm_otile + mm::kOtileBytes;
-    p.sm_xbuf = static_cast<uint32_t>(align_up(p.sm_vt + mm::kVtBytes, 1024));
-    size_t used = a8 ? p.sm_xbuf + xbytes : p.sm_vt + mm::kVtBytes;
+    p.nstage_wide = a8 ? 0u : p.sm_otile / p.wide_stage_bytes;
+    if (p.nstage_wide > static_cast<uint32_t>(mm::kMaxStages)) p.nstage_wide = mm::kMaxStages;
+    p.sm_vt = p.sm_otile + static_cast<uint32_t>(otile_bytes);
+    p.sm_xbuf = static_cast<uint32_t>(align_up(p.sm_vt + vt_bytes, 1024));
+    size_t used = a8 ? p.sm_xbuf + xbytes : p.sm_vt + vt_bytes;
     // token region: the first 16 received rows (tokens + scale bytes) are fetched into what the plan leaves free, either as
     // one swizzled token tile with its scale slots (launches with at most 16 received rows) or as a plain row cache
     p.rc_row_bytes = static_cast<uint32_t>(L.x_row_bytes + L.x_sf_row_bytes);

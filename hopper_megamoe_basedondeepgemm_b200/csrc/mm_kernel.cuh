@@ -59,8 +59,9 @@ constexpr int kNumExpThreads = 256;      // FP8-activation variant: warps 8..15 
 constexpr uint32_t kXbufBytes = 2 * kUnitWBytes + 1024;   // one widened unit + its two scale planes
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kFillWarps = 5;       // warps 2..6 fetch the received rows into shared memory while the schedule is built
-constexpr uint32_t kOtileBytes = 4096;
-constexpr uint32_t kVtBytes = kTileTokens * kTileRows * 4;   // fp32 accumulators of one task, token-major
+constexpr uint32_t kOtileBytes = 8192;
+constexpr uint32_t kWideTokens = 32;      // token tile of the launches whose experts have more than 16 rows
+constexpr uint32_t kVtBytes = kWideTokens * kTileRows * 4;   // fp32 accumulators of one task, token-major
 
 constexpr int kOwnCap = 128;            // routed rows of this rank's own tokens that every SM lists for itself (see the scout)
 
@@ -125,6 +126,7 @@ struct KParams {
     int cnt_per_phase;
     long long off_token_tiles, off_mid_tiles, off_arrive;   // operand tile images and their arrival counters (launches with more than 16 rows)
     uint32_t tile_capacity, token_tile_bytes, mid_tile_bytes;
+    uint32_t wide_stage_bytes, nstage_wide;   // with tile images a ring stage holds a weight unit and a 32-row token record; stages that fit
     long long rx_region;                 // bytes of one (parity, source) region of the receive pool
     uint32_t sm_act, sm_asf, sm_otile, sm_vt;   // dynamic shared memory offsets (stages start at 0)
     uint32_t act_bytes, asf_bytes;
@@ -147,7 +149,8 @@ struct Ctl {
     uint32_t rx_count[kMaxRanks], rx_prefix[kMaxRanks + 1];
     uint32_t exp_count[kMaxLocalExperts], mid_base[kMaxLocalExperts];
     uint32_t nt1, nt2, dcount, own_cnt;
-    uint32_t comb_next, issued, decode, bulk; // next combine item of this SM; weight units the loader has issued; decode mode (see below)
+    uint32_t comb_next, issued, decode, bulk;
+    uint32_t tw, padw[3];                // rows of a token tile in this launch: 16, or 32 when tile images are in use and an expert has more than 16 rows // next combine item of this SM; weight units the loader has issued; decode mode (see below)
     uint32_t n1_tasks, padn[3];          // L1 tasks at the head of this SM's list
     uint32_t epi_nv[2], epi_dcol[2];     // per accumulator: valid rows of the task and (decode mode) the first accumulator column of its expert
     // token staging geometry of this launch: with room for one 16-row buffer only, launches whose experts all have at
@@ -159,14 +162,14 @@ struct Ctl {
     uint32_t tasks3[kMaxTasks];          // tile index inside its phase (counter slot)
     uint32_t red_old;
     RowMeta row_meta[4][kTileTokens];
-    RowMeta epi_meta[2][kTileTokens];
+    RowMeta epi_meta[2][kWideTokens];
     uint32_t nvalid[4];
     uint32_t rowref[2][kTileTokens];
     uint32_t rowidx[2][kTileTokens];
     uint32_t rcslot[2][kTileTokens];     // row-cache slot of each row of the task being staged (0xFFFFFFFF: not cached)
-    float amax_x[4][kTileTokens];
+    float amax_x[4][kWideTokens];
     uint32_t dry_count[kMaxLocalExperts];   // dummy per-expert counts of the schedule's warm-up call
-    uint32_t sfb[4][kTileTokens];        // L1 epilogue: one scale byte per (warp, token), gathered into one flagged word
+    uint32_t sfb[4][kWideTokens];        // L1 epilogue: one scale byte per (warp, token), gathered into one flagged word
     uint32_t mtl[kMaxMTiles];            // (expert << 16 | token tile) of every 16-token tile, expert-major
     RowMeta rx_meta[kMetaSmemRows];
     RowMeta own_meta[kOwnCap];           // records of this rank's own routed rows, listed by the scout from topk_idx
@@ -517,35 +520,6 @@ __device__ __noinline__ void role_stager(const Ctx& cx, uint32_t sw, uint32_t la
         __syncwarp();
         uint8_t* act = cx.smem + p.sm_act + ab * act_stride;
         uint8_t* asf = cx.smem + p.sm_asf + ab * p.asf_bytes;
-        if (!dry && c.bulk != 0u) {
-            // the task's operand tile is ready-made in global memory: wait until its rows (L1: the tile's received rows,
-            // L2: the outputs of all L1 weight tiles) have been counted in, then fetch tokens and scale slots with two bulk copies
-            const uint32_t tile = (c.mid_base[e] / kTileTokens) + mt;
-            const uint32_t* arr = reinterpret_cast<const uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + type) * p.tile_capacity + tile;
-            const uint32_t need = type ? static_cast<uint32_t>(p.n1_tiles) : nv;
-            uint32_t spins = 0;
-            bool bad = false;
-            while (ld_acquire_gpu(arr) < need) {
-                if ((++spins & 0x3Fu) == 0u) {
-                    if (cx.aborted()) { bad = true; break; }
-                    if (cx.expired()) { cx.fail(type ? kErrWaitL1Done : kErrWaitDispatchFlag, e); bad = true; break; }
-                }
-            }
-            if (bad) return;
-            if (lane == 0) {
-                fence_proxy_async_all();
-                const uint32_t tok_bytes = kTileTokens * static_cast<uint32_t>(type ? p.mid_row_bytes : p.x_row_bytes);
-                const uint32_t img_bytes = type ? p.mid_tile_bytes : p.token_tile_bytes;
-                const uint8_t* img = cx.buf + (type ? p.off_mid_tiles : p.off_token_tiles) + static_cast<size_t>(tile) * img_bytes;
-                mbar_arrive_expect_tx(&c.acts_full[ab], img_bytes);
-                bulk_g2s(act, img, tok_bytes, &c.acts_full[ab]);
-                bulk_g2s(asf, img + tok_bytes, img_bytes - tok_bytes, &c.acts_full[ab]);
-                if (tis == 0u) cx.sm_phase(kSmFirstStaged);
-                if (type != 0u && !seen_l2) { seen_l2 = true; cx.sm_phase(kSmFirstL2Staged); }
-            }
-            __syncwarp();
-            continue;
-        }
         // Both kinds of rows are flagged words that may still be on their way (received tokens for L1, the L1 epilogues'
         // output of other SMs for L2): a chunk is re-read until its flags match. Received rows carry their scale bytes
         // behind the tokens; intermediate rows keep theirs as one flagged word per (row, L1 tile).
@@ -880,29 +854,6 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
                 // tile's scale bytes.
                 constexpr uint32_t kChunks = kA8 ? 4u : 2u;
                 const uint32_t flag = c.epoch + 1u;
-                if (!kA8 && c.bulk != 0u) {
-                    // operand tile image of the L2 tasks: plain stores into the swizzled tile and the scale-word slots, then
-                    // one count into the tile's arrival word (the L2 token fetch is a bulk copy: it cannot poll flags)
-                    const uint32_t tile = midrow0 / kTileTokens;
-                    uint8_t* img = cx.buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes;
-                    if (etid < nv * kChunks) {
-                        const uint32_t n = etid / kChunks, ci = j * kChunks + etid % kChunks;
-                        const uint4 val = *reinterpret_cast<const uint4*>(otile + etid * 16u);
-                        *reinterpret_cast<uint4*>(img + (ci >> 3) * (kTileTokens * 128u) + sw128_off(n, ci & 7u)) = val;
-                    } else if (etid >= 64u && etid - 64u < nv) {
-                        const uint32_t n = etid - 64u;
-                        uint8_t* slots = img + kTileTokens * p.mid_row_bytes;
-                        if constexpr (kVec == 16)
-                            *reinterpret_cast<uint32_t*>(slots + j * 256u + n * 16u) = c.sfb[0][n] | (c.sfb[1][n] << 8) | (c.sfb[2][n] << 16) | (c.sfb[3][n] << 24);
-                        else
-                            *reinterpret_cast<uint16_t*>(slots + (j >> 1) * 256u + n * 16u + (j & 1u) * 2u) = static_cast<uint16_t>(c.sfb[0][n] | (c.sfb[2][n] << 8));
-                    }
-                    bar_sync(kBarEpi, kNumEpiThreads);                    // every thread's stores precede thread 0's release
-                    if (etid == 0u) {
-                        fence_proxy_async_all();
-                        red_release_gpu_add(reinterpret_cast<uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + 1u) * p.tile_capacity + tile, 1u);
-                    }
-                } else
                 if (etid < nv * kChunks) {
                     const uint32_t n = etid / kChunks, q16 = etid % kChunks;
                     const uint4 val = *reinterpret_cast<const uint4*>(otile + (n * kChunks + q16) * 16u);
@@ -939,6 +890,318 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     if (etid == 0u) { cx.wait_total(21, w_tfull); cx.wait_total(22, clock64() - t_role); cx.wait_total(23, w_l1); cx.wait_total(24, w_l2); }
 }
 
+// ============================================================================================= roles with tile images
+// Launches with more than 16 received rows. The rows have been sorted into tile images in global memory (token tiles by
+// the sorting pass after the dispatch, intermediate tiles by the L1 epilogues): per tile and per streamed K unit one
+// record = the unit's 128 B of every token row in the tensor core's swizzled order, then the unit's scale-word slots.
+// A record travels with its weight unit: the loader fetches both into the same ring stage (two bulk copies, one
+// barrier), so a task needs no token staging of its own and the token operand costs the loader two instructions per
+// unit, whatever the weight flood does to small loads. A token tile has `c.tw` rows: 16, or 32 when an expert has
+// more than 16 rows (the block-scaled MMA takes the same time for 16 and 32 columns: an expert's weights stream once
+// for up to 32 rows).
+__device__ __forceinline__ uint32_t tile_record_bytes(uint32_t tw, uint32_t planes) { return tw * 128u + planes * tw * 16u; }
+
+__device__ void role_loader_tiles(const Ctx& cx, uint32_t planes) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    const uint32_t tw = c.tw, rec = tile_record_bytes(tw, planes);
+    const uint32_t* arrive = reinterpret_cast<const uint32_t*>(cx.buf + p.off_arrive) + cx.par * 2u * p.tile_capacity;
+    uint32_t it = 0, s = 0, ph = 0;
+    long long w_empty = 0;
+    #pragma unroll 1
+    for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
+        const uint32_t t = c.tasks[ti];
+        const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF, j = t & 0xFF;
+        const int ntiles = type ? p.n2_tiles : p.n1_tiles, kunits = type ? p.k2_units : p.k1_units;
+        const uint8_t* src = (type ? p.w2 : p.w1) + (static_cast<size_t>(e) * ntiles + j) * kunits * p.unit_bytes;
+        const uint32_t tile = udiv_small(c.mid_base[e], tw) + mt;
+        const uint32_t left = c.exp_count[e] - mt * tw;
+        const uint32_t need = type ? static_cast<uint32_t>(p.n1_tiles) : (left < tw ? left : tw);
+        const uint32_t* arr = arrive + type * p.tile_capacity + tile;
+        const uint8_t* img = type ? cx.buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes
+                                  : cx.buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes + kWideTokens * 16u;
+        bool ready = false;
+        const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
+        #pragma unroll 1
+        for (int u = ub; u < ue; ++u, ++it) {
+            if (!cx.warp_wait_t(&c.empty[s], ph ^ 1u, kErrWaitEmpty, w_empty)) return;
+            uint8_t* stage = cx.smem + static_cast<size_t>(s) * p.wide_stage_bytes;
+            const bool leader = elect_one();
+            if (leader) {
+                mbar_arrive_expect_tx(&c.full[s], p.unit_bytes + rec);
+                bulk_g2s(stage, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
+                c.issued = it + 1u;
+                if (it == 0u) { cx.note_first_weight_request(); cx.sm_phase(kSmFirstIssue); }
+            }
+            if (!ready) {
+                // the tile's rows (L1: its received rows, L2: the outputs of all L1 weight tiles) have been counted in
+                uint32_t spins = 0;
+                while (ld_acquire_gpu(arr) < need) {
+                    if ((++spins & 0x3Fu) == 0u) {
+                        if (cx.aborted()) return;
+                        if (cx.expired()) { cx.fail(type ? kErrWaitL1Done : kErrWaitDispatchFlag, e); return; }
+                    }
+                }
+                ready = true;
+            }
+            if (leader) {
+                fence_proxy_async_all();
+                bulk_g2s(stage + p.unit_bytes, img + static_cast<size_t>(u) * rec, rec, &c.full[s]);
+            }
+            __syncwarp();
+            if (++s == p.nstage_wide) { s = 0; ph ^= 1u; }
+        }
+    }
+    if ((threadIdx.x & 31u) == 0u) cx.wait_total(16, w_empty);
+}
+
+template <int kVec>
+__device__ void role_mma_tiles(const Ctx& cx, uint32_t lane) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    constexpr uint32_t kPlanes = kUnitK / (4 * kVec);
+    const uint32_t tw = c.tw;
+    const uint32_t idesc0 = idesc_block_scaled(kFmtMxf4E2M1, kFmtMxf4E2M1, kTileRows, tw, kVec == 32 ? 1u : 0u);
+    const uint32_t tm = c.tmem_base;
+    const uint32_t sfa_col = 64, sfb_col = 96;                  // accumulators 2 x 32 columns, weight scales 2 x 16, token scales 2 x 16
+    uint32_t it = 0, s = 0, ph = 0;
+    unsigned long long t_landed = 0ull;
+    long long w_tmem = 0, w_full = 0;
+    const long long t_role = clock64();
+    const unsigned long long ns_role = globaltimer_ns();
+    #pragma unroll 1
+    for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
+        const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
+        const uint32_t acc = ti & 1u, use = (ti >> 1) & 1u;
+        if (!cx.warp_wait_t(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty, w_tmem)) return;
+        tc_fence_after();
+        #pragma unroll 1
+        for (int u = ub; u < ue; ++u, ++it) {
+            if (!cx.warp_wait_t(&c.full[s], ph, kErrWaitFull, w_full)) return;
+            tc_fence_after();
+            t_landed = globaltimer_ns();
+            if (lane == 0 && it == 0u) cx.sm_phase(kSmFirstLanded);
+            if (elect_one()) {
+                const uint32_t wsm = smem_u32(cx.smem + static_cast<size_t>(s) * p.wide_stage_bytes);
+                const uint32_t wsf = wsm + static_cast<uint32_t>(kUnitWBytes);
+                const uint32_t tok = wsm + p.unit_bytes, tsf = tok + tw * 128u;
+                const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u, sfb = tm + sfb_col + (it & 1u) * 16u;
+                #pragma unroll
+                for (uint32_t pl = 0; pl < kPlanes; ++pl) {
+                    utccp_32x128b_warpx4(sfa + pl * 4u, smem_desc(wsf + pl * 512u, 128u, kLayoutNone));
+                    // (16-row tiles: the copy's upper 16 lanes read the next plane, or the unused tail of the stage)
+                    utccp_32x128b_warpx4(sfb + pl * 4u, smem_desc(tsf + pl * tw * 16u, 128u, kLayoutNone));
+                }
+                #pragma unroll
+                for (uint32_t ks = 0; ks < kUnitK / 64u; ++ks) {
+                    const uint32_t pl = (ks * 64u) / (4u * kVec), sf_id = ((ks * 64u) % (4u * kVec)) / kVec;
+                    const uint64_t adesc = smem_desc(wsm + ks * 32u, 1024u, kLayoutSw128);
+                    const uint64_t bdesc = smem_desc(tok + ks * 32u, 1024u, kLayoutSw128);
+                    const uint32_t idesc = idesc_with_sf(idesc0, sf_id, sf_id);
+                    const uint32_t accum = (u > ub || ks > 0) ? 1u : 0u;
+                    if constexpr (kVec == 32)
+                        umma_mxf4_block32(tm + acc * kWideTokens, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
+                    else
+                        umma_nvf4_block16(tm + acc * kWideTokens, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
+                }
+                tc_commit(&c.empty[s]);
+            }
+            __syncwarp();
+            if (++s == p.nstage_wide) { s = 0; ph ^= 1u; }
+        }
+        if (elect_one()) tc_commit(&c.tmem_full[acc]);
+        __syncwarp();
+    }
+    if (lane == 0 && t_landed != 0ull) cx.stamp_max(kStampLastWeight, t_landed);
+    if (lane == 0) {
+        cx.wait_total(18, w_tmem); cx.wait_total(19, w_full); cx.wait_total(20, clock64() - t_role);
+        cx.wait_total(25, static_cast<long long>(globaltimer_ns() - ns_role));
+    }
+}
+
+template <int kVec>
+__device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    constexpr uint32_t kPlanes = kUnitK / (4 * kVec);
+    const uint32_t ew = etid >> 5, lane = etid & 31u, row = etid, tw = c.tw;
+    const uint32_t rec = tile_record_bytes(tw, kPlanes);
+    uint8_t* otile = cx.smem + p.sm_otile;
+    float* vt = reinterpret_cast<float*>(cx.smem + p.sm_vt) + row;      // this thread's accumulators: vt[n * 128], token n
+    const uint32_t* arrive_tok = reinterpret_cast<const uint32_t*>(cx.buf + p.off_arrive) + cx.par * 2u * p.tile_capacity;
+    uint32_t* arrive_mid = reinterpret_cast<uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + 1u) * p.tile_capacity;
+    long long w_tfull = 0, w_l1 = 0, w_l2 = 0;
+    const long long t_role = clock64();
+    #pragma unroll 1
+    for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
+        const uint32_t t = c.tasks[ti];
+        const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF, j = t & 0xFF;
+        const uint32_t acc = ti & 1u, use = (ti >> 1) & 1u;
+        const uint32_t tile = udiv_small(c.mid_base[e], tw) + mt;
+        const uint32_t left = c.exp_count[e] - mt * tw, nv = left < tw ? left : tw;
+        // the rows' records (source rank, token, slot, top-k weight) head the token tile image; the first warp fetches them
+        // while the task's MMAs run (after its own acquire of the tile's arrival count)
+        RowMeta mrec{0, 0, 0, 0.f};
+        bool ok = true;
+        if (ew == 0u) {
+            uint32_t spins = 0;
+            while (ld_acquire_gpu(arrive_tok + tile) < nv) {
+                if ((++spins & 0x3Fu) == 0u && (cx.aborted() || cx.expired())) { ok = false; break; }
+            }
+            if (ok && lane < nv) {
+                const uint4 q = ld_cg_v4(cx.buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes + lane * 16u);
+                mrec = RowMeta{static_cast<int32_t>(q.x), static_cast<int32_t>(q.y), static_cast<int32_t>(q.z), __uint_as_float(q.w)};
+            }
+        }
+        ok = ok && cx.warp_wait_t(&c.tmem_full[acc], use, kErrWaitTmemFull, w_tfull);
+        const long long t_work = clock64();
+        if (ok) {
+            tc_fence_after();
+            if (ti == 0u && etid == 0u) cx.sm_phase(kSmFirstMmaDone);
+            uint32_t raw[kTileTokens];
+            tmem_ld_32x32b_x16(c.tmem_base + ((ew * 32u) << 16) + acc * kWideTokens, raw);
+            tmem_ld_wait();
+            #pragma unroll
+            for (int n = 0; n < kTileTokens; ++n) vt[n * kTileRows] = __uint_as_float(raw[n]);
+            if (nv > kTileTokens) {
+                tmem_ld_32x32b_x16(c.tmem_base + ((ew * 32u) << 16) + acc * kWideTokens + kTileTokens, raw);
+                tmem_ld_wait();
+                #pragma unroll
+                for (int n = 0; n < kTileTokens; ++n) vt[(kTileTokens + n) * kTileRows] = __uint_as_float(raw[n]);
+            }
+            tc_fence_before();
+            mbar_arrive(&c.tmem_empty[acc]);
+            if (ew == 0u && lane < nv) c.epi_meta[acc][lane] = mrec;
+        }
+        if (bar_red_or(kBarEpi, kNumEpiThreads, !ok)) return;        // also publishes epi_meta
+        const RowMeta* meta = c.epi_meta[acc];
+        const uint32_t np = (c.tasks2[ti] >> 16) & 0xFFu;
+        if (np > 1u) {
+            // this SM covered only part of the tile's K range: park the partial sums, count in, and let the last
+            // contributor add the parts in SM order (a fixed order: the result does not depend on who arrives last)
+            const uint32_t tix = c.tasks3[ti], cfirst = c.tasks2[ti] >> 24;
+            float* red = reinterpret_cast<float*>(cx.buf + p.off_red);
+            constexpr size_t kSlot = 2u * kTileTokens * kTileRows;           // floats: room for 32 rows
+            float* mine = red + (static_cast<size_t>(blockIdx.x) * 2u + type) * kSlot + row;
+            #pragma unroll 1
+            for (uint32_t n = 0; n < nv; ++n) mine[n * kTileRows] = vt[n * kTileRows];
+            bar_sync(kBarEpi, kNumEpiThreads);
+            if (etid == 0) {
+                uint32_t* cnt = reinterpret_cast<uint32_t*>(cx.buf + p.off_cnt) + type * p.cnt_per_phase + tix;
+                const uint32_t old = atom_acq_rel_gpu_add(cnt, 1u);
+                if (old == np - 1u) *cnt = 0u;
+                c.red_old = old;
+            }
+            bar_sync(kBarEpi, kNumEpiThreads);
+            if (c.red_old != np - 1u) continue;
+            #pragma unroll 1
+            for (uint32_t n = 0; n < nv; ++n) {
+                float sum = 0.f;
+                #pragma unroll 1
+                for (uint32_t pc0 = 0; pc0 < np; pc0 += 4) {
+                    float part_v[4];
+                    #pragma unroll
+                    for (uint32_t d = 0; d < 4; ++d) {
+                        part_v[d] = 0.f;
+                        if (pc0 + d < np)
+                            part_v[d] = __uint_as_float(ld_cg_u32(red + (static_cast<size_t>(cfirst + pc0 + d) * 2u + type) * kSlot + n * kTileRows + row));
+                    }
+                    #pragma unroll
+                    for (uint32_t d = 0; d < 4; ++d) if (pc0 + d < np) sum += part_v[d];
+                }
+                vt[n * kTileRows] = sum;
+            }
+        }
+
+        if (type == 0u) {
+            // ---- L1: rows come in groups of 16 = 8 gate rows then the 8 matching up rows
+            const bool is_up = (lane & 8u) != 0u;
+            #pragma unroll 1
+            for (uint32_t n = 0; n < nv; ++n) {
+                const float mine = bf16_round(vt[n * kTileRows] * p.l1_scale);
+                const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
+                float gate = is_up ? other : mine, up = is_up ? mine : other;
+                if (p.has_clamp) { gate = fminf(gate, p.clamp); up = fminf(fmaxf(up, -p.clamp), p.clamp); }
+                const float sig = p.fast_math ? __frcp_rn(1.0f + __expf(-gate)) : 1.0f / (1.0f + expf(-gate));
+                float av = gate * sig * up * meta[n].weight;
+                if constexpr (kVec == 16) av = __fdiv_rn(av, p.mid_gs);
+                vt[n * kTileRows] = av;
+                float a = fabsf(av);
+                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
+                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
+                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
+                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
+                if (lane == 0) c.amax_x[ew][n] = a;
+            }
+            if constexpr (kVec == 32) bar_sync(kBarEpi, kNumEpiThreads);     // a 32-column scale block spans two warps
+            else __syncwarp();
+            #pragma unroll 1
+            for (uint32_t n = 0; n < nv; ++n) {
+                float amax = c.amax_x[ew][n];
+                if constexpr (kVec == 32) amax = fmaxf(amax, c.amax_x[ew ^ 1u][n]);
+                amax = fmaxf(amax, 1e-30f);
+                const float av = vt[n * kTileRows];
+                uint32_t sf_byte; float scaled;
+                if constexpr (kVec == 32) {
+                    sf_byte = ceil_pow2_exp(__fdiv_rn(amax, 6.0f));
+                    scaled = __fdiv_rn(av, __uint_as_float(sf_byte << 23));
+                } else {
+                    sf_byte = cvt_e4m3x2(__fdiv_rn(amax, 6.0f), 0.f) & 0xFFu;
+                    const float sf = e4m3_to_float(sf_byte);
+                    scaled = sf > 0.f ? __fdiv_rn(av, sf) : (av == 0.f ? 0.f : copysignf(6.0f, av));
+                }
+                const float nb = __shfl_down_sync(0xffffffffu, scaled, 1);
+                if (!is_up && (lane & 1u) == 0u)
+                    otile[n * 32 + ew * 8u + (lane >> 4) * 4u + ((lane & 7u) >> 1)] = static_cast<uint8_t>(cvt_e2m1x2(scaled, nb));
+                if (lane == 0) c.sfb[ew][n] = sf_byte;
+            }
+            bar_sync(kBarEpi, kNumEpiThreads);
+            {
+                // the 64 output columns of every row go into the intermediate tile's image: two 16 B chunks at their
+                // swizzled place in the record of their K unit, the scale bytes into that record's slots; then one count
+                // into the tile's arrival word (thread 0's release covers the stores the barrier ordered before it)
+                uint8_t* img = cx.buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes;
+                if (etid < nv * 2u) {
+                    const uint32_t n = etid >> 1, ci = j * 2u + (etid & 1u);
+                    const uint4 val = *reinterpret_cast<const uint4*>(otile + etid * 16u);
+                    *reinterpret_cast<uint4*>(img + (ci >> 3) * rec + sw128_off(n, ci & 7u)) = val;
+                } else if (etid >= 64u && etid - 64u < nv) {
+                    const uint32_t n = etid - 64u;
+                    if constexpr (kVec == 16) {
+                        uint8_t* slots = img + (j >> 2) * rec + tw * 128u + (j & 3u) * tw * 16u;
+                        *reinterpret_cast<uint32_t*>(slots + n * 16u) = c.sfb[0][n] | (c.sfb[1][n] << 8) | (c.sfb[2][n] << 16) | (c.sfb[3][n] << 24);
+                    } else {
+                        uint8_t* slots = img + (j >> 2) * rec + tw * 128u + ((j >> 1) & 1u) * tw * 16u;
+                        *reinterpret_cast<uint16_t*>(slots + n * 16u + (j & 1u) * 2u) = static_cast<uint16_t>(c.sfb[0][n] | (c.sfb[2][n] << 8));
+                    }
+                }
+                bar_sync(kBarEpi, kNumEpiThreads);
+                if (etid == 0u) {
+                    fence_proxy_async_all();
+                    red_release_gpu_add(arrive_mid + tile, 1u);
+                }
+            }
+        } else {
+            // ---- L2: bf16 rows back to the token's source rank, as flagged words: the combine there polls the data itself
+            __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(otile);
+            #pragma unroll 1
+            for (uint32_t n = 0; n < nv; ++n) ot[n * kTileRows + row] = __float2bfloat16_rn(vt[n * kTileRows] * p.l2_scale);
+            bar_sync(kBarEpi, kNumEpiThreads);
+            #pragma unroll 1
+            for (uint32_t idx = etid; idx < nv * 32u; idx += kNumEpiThreads) {
+                const uint32_t n = idx >> 5, ch = (idx & 31u) >> 1;
+                const uint4 val = *reinterpret_cast<const uint4*>(otile + n * 256u + ch * 16u);
+                uint8_t* dst = p.peer[meta[n].src] + p.off_comb +
+                    ((static_cast<size_t>(meta[n].token) * p.topk + meta[n].slot) * p.H + j * kTileRows) * 4u + ch * 32u;
+                st_ll_half(dst, val, c.epoch + 1u, idx & 1u);
+            }
+        }
+        if (etid == 0u) {
+            if (ti == 0u) cx.sm_phase(kSmFirstEpilogue);
+            if (type == 0u) cx.sm_phase(kSmLastL1Epilogue);
+        }
+        if (type == 0u) w_l1 += clock64() - t_work; else w_l2 += clock64() - t_work;
+    }
+    if (etid == 0u) { cx.wait_total(21, w_tfull); cx.wait_total(22, clock64() - t_role); cx.wait_total(23, w_l1); cx.wait_total(24, w_l2); }
+}
+
 // ============================================================================================= schedule
 // One warp derives this SM's task list from the per-expert row counts (16-token tiles of the active experts,
 // expert-major: M of them). Returns M << 16 | number of tasks. Out of line on purpose: a spare warp runs it once on
@@ -947,7 +1210,9 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
 __device__ __noinline__ uint32_t build_schedule(const KParams& p, Ctl& c, const uint32_t* counts, uint32_t bid, uint32_t G, uint32_t lane) {
     const uint32_t el = p.e_local;
     const uint32_t c0 = lane < el ? counts[lane] : 0u, c1 = lane + 32 < el ? counts[lane + 32] : 0u;
-    const uint32_t m0 = (c0 + kTileTokens - 1) / kTileTokens, m1 = (c1 + kTileTokens - 1) / kTileTokens;
+    // rows per token tile: 16, or 32 when the launch works from tile images and an expert has more than 16 rows
+    const uint32_t tw = (c.bulk != 0u && __any_sync(0xffffffffu, c0 > kTileTokens || c1 > kTileTokens)) ? kWideTokens : static_cast<uint32_t>(kTileTokens);
+    const uint32_t m0 = udiv_small(c0 + tw - 1u, tw), m1 = udiv_small(c1 + tw - 1u, tw);
     uint32_t i0 = m0, i1 = m1;
     #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -962,10 +1227,11 @@ __device__ __noinline__ uint32_t build_schedule(const KParams& p, Ctl& c, const 
         c.act_stride = split ? p.act_bytes / 2u : p.act_bytes;
         c.atom_stride = split ? 8u * 128u : kTileTokens * 128u;
         c.sbo = split ? 0u : 1024u;
+        c.tw = tw;
     }
     const uint32_t x0 = i0 - m0, x1 = tot0 + i1 - m1;
-    if (lane < el) c.mid_base[lane] = x0 * kTileTokens;
-    if (lane + 32 < el) c.mid_base[lane + 32] = x1 * kTileTokens;
+    if (lane < el) c.mid_base[lane] = x0 * tw;
+    if (lane + 32 < el) c.mid_base[lane + 32] = x1 * tw;
     if (M <= kMaxMTiles) {
         #pragma unroll 1
         for (uint32_t mt = 0; mt < m0; ++mt) c.mtl[x0 + mt] = (lane << 16) | mt;
@@ -1191,7 +1457,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
         c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u; c.decode = 0u; c.bulk = 0u;
         if constexpr (!kScout) c.own_cnt = 0u;
-        for (int s = 0; s < p.nstage; ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
+        for (int s = 0; s < (p.nstage > static_cast<int>(p.nstage_wide) ? p.nstage : static_cast<int>(p.nstage_wide)); ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
         #pragma unroll 1
         for (int i = 0; i < 2; ++i) {
             mbar_init(&c.acts_full[i], 1); mbar_init(&c.acts_empty[i], kUmma ? 1 : kNumEpiThreads);
@@ -1433,8 +1699,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             if (bid == 0) cx.stamp(kStampFlagsSeen);
             cx.sm_phase(kSmCountsKnown);
             c.decode = (kUmma && !kA8 && p.rc_rows != 0u && total != 0u && total <= kTileTokens) ? 1u : 0u;     // (the cross-check engine reads the per-task staging buffers)
-            c.bulk = (kUmma && !kA8 && (p.knobs & kKnobTileImages) != 0u && p.nab == 2 && total > kTileTokens && total <= kMetaCap) ? 1u : 0u;
-            if (bid == 0) ctrl32[kCtrlStatus / 4 + 2] = c.bulk;          // (for whoever inspects the intermediate rows afterwards)
+            c.bulk = (kUmma && !kA8 && (p.knobs & kKnobTileImages) != 0u && p.nstage_wide >= 3u && total > kTileTokens && total <= kMetaCap) ? 1u : 0u;
         }
         if (total <= kMetaCap) {
             auto take = [&](uint32_t f, const uint4& m) {
@@ -1476,16 +1741,18 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     //      (a sender pushes its header line and records first). The loads are in flight before the bulk copies of the
     //      weight stream start, which would otherwise make them wait behind megabytes.
     const bool is_ctl = warp < 2u;                       // warps 0 and 1 build the schedule and start the weight stream
-    // ---- more than 16 received rows: the rows are sorted into operand tile images in global memory, one image per
-    //      16-token tile of an expert, laid out exactly as the tensor core reads it from shared memory (K atoms of
-    //      16 rows x 128 B with the 128 B swizzle, then the scale-word slots). Row f belongs to SM f mod G; one warp per
-    //      row. A task's token operand is then two bulk copies issued by one thread, which the weight flood does not
-    //      slow down the way it slows thousands of small loads. Every finished row counts into its tile's arrival word.
+    // ---- more than 16 received rows: the rows are sorted into tile images in global memory, one image per token tile
+    //      (16 or 32 rows) of an expert: the rows' records, then per streamed K unit the unit's 128 B of every row in the
+    //      tensor core's swizzled order and the unit's scale-word slots. Row f belongs to SM f mod G; one warp per row.
+    //      Every finished row counts into its tile's arrival word.
     if (warp >= 2u && warp < 2u + kFillWarps && c.bulk != 0u && !cx.aborted()) {
         const uint32_t el = p.e_local;
-        // first tile of every expert: running sum of ceil(rows / 16), expert-major (the schedule derives the same numbers)
-        const uint32_t m0 = ((lane < el ? c.exp_count[lane] : 0u) + kTileTokens - 1) / kTileTokens;
-        const uint32_t m1 = ((lane + 32 < el ? c.exp_count[lane + 32] : 0u) + kTileTokens - 1) / kTileTokens;
+        constexpr uint32_t kPlanes = kUnitK / (4 * kVec);
+        // first tile of every expert: running sum of ceil(rows / tile rows), expert-major (the schedule derives the same numbers)
+        const uint32_t cnt0 = lane < el ? c.exp_count[lane] : 0u, cnt1 = lane + 32 < el ? c.exp_count[lane + 32] : 0u;
+        const uint32_t tw = __any_sync(0xffffffffu, cnt0 > kTileTokens || cnt1 > kTileTokens) ? kWideTokens : static_cast<uint32_t>(kTileTokens);
+        const uint32_t rec = tile_record_bytes(tw, kPlanes);
+        const uint32_t m0 = udiv_small(cnt0 + tw - 1u, tw), m1 = udiv_small(cnt1 + tw - 1u, tw);
         uint32_t i0 = m0, i1 = m1;
         #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -1509,7 +1776,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             }
             n = __reduce_add_sync(0xffffffffu, n);
             const uint32_t tb0 = __shfl_sync(0xffffffffu, tbase0, e & 31u), tb1 = __shfl_sync(0xffffffffu, tbase1, e & 31u);
-            const uint32_t tile = (e < 32u ? tb0 : tb1) + n / kTileTokens, pos = n % kTileTokens;
+            const uint32_t tile = (e < 32u ? tb0 : tb1) + udiv_small(n, tw), pos = n - udiv_small(n, tw) * tw;
             uint32_t r = 0;
             while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
             const uint32_t i = f - c.rx_prefix[r];
@@ -1524,9 +1791,22 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             } else {
                 row_src = cx.rx_row(r, i);
             }
-            uint8_t* img = buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes;
-            uint8_t* img_sf = img + kTileTokens * p.x_row_bytes;
+            uint8_t* head = buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes;
+            uint8_t* img = head + kWideTokens * 16u;
             bool bad = tile >= p.tile_capacity;
+            if (lane == 0 && !bad) {
+                // the row's record for the epilogues: source rank, token, slot, top-k weight
+                RowMeta m;
+                if (own) m = c.own_meta[i];
+                else if (f < kMetaSmemRows) m = c.rx_meta[f];
+                else {
+                    uint4 q = make_uint4(0u, 0u, 0u, 0u);
+                    if (!cx.ll_read(row_src + 2u * (p.rx_row_bytes - 16), flag_rx, q, kErrWaitDispatchFlag, r)) bad = true;
+                    m = RowMeta{0, static_cast<int32_t>(q.y), static_cast<int32_t>(q.z), __uint_as_float(q.w)};
+                }
+                *reinterpret_cast<uint4*>(head + pos * 16u) = make_uint4(r, static_cast<uint32_t>(m.token), static_cast<uint32_t>(m.slot), __float_as_uint(m.weight));
+            }
+            bad = __any_sync(0xffffffffu, bad);
             #pragma unroll 1
             for (uint32_t base = lane; base < per_row && !bad; base += 4 * 32) {
                 uint4 v[4];
@@ -1562,19 +1842,20 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                     const uint32_t ci = base + u * 32;
                     if (ci >= per_row || bad) continue;
                     if (ci < xq) {
-                        *reinterpret_cast<uint4*>(img + (ci >> 3) * (kTileTokens * 128u) + sw128_off(pos, ci & 7u)) = v[u];
+                        *reinterpret_cast<uint4*>(img + (ci >> 3) * rec + sw128_off(pos, ci & 7u)) = v[u];
                     } else {
-                        uint8_t* dst = img_sf + (ci - xq) * 4u * 256u + pos * 16u;
-                        *reinterpret_cast<uint32_t*>(dst) = v[u].x;
-                        *reinterpret_cast<uint32_t*>(dst + 256u) = v[u].y;
-                        *reinterpret_cast<uint32_t*>(dst + 512u) = v[u].z;
-                        *reinterpret_cast<uint32_t*>(dst + 768u) = v[u].w;
+                        // four scale words g .. g + 3 of the row: word g belongs to K unit g / planes, plane g % planes
+                        const uint32_t g = (ci - xq) * 4u;
+                        const uint32_t wv[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                        #pragma unroll
+                        for (uint32_t k = 0; k < 4; ++k)
+                            if ((g + k) * 4u < static_cast<uint32_t>(p.x_sf_row_bytes))
+                                *reinterpret_cast<uint32_t*>(img + ((g + k) / kPlanes) * rec + tw * 128u + ((g + k) % kPlanes) * tw * 16u + pos * 16u) = wv[k];
                     }
                 }
             }
             const bool any_bad = __any_sync(0xffffffffu, bad);      // (also orders the lanes' stores before lane 0's fence)
             if (lane == 0 && !any_bad) {
-                __threadfence();
                 fence_proxy_async_all();
                 red_release_gpu_add(arrive + tile, 1u);
                 cx.sm_phase(kSmRowsCached);
@@ -1675,6 +1956,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             const uint32_t M = res >> 16, nmine = res & 0xFFFFu;
             const uint32_t nt1 = M * p.n1_tiles, nt2 = M * p.n2_tiles;
             if (lane == 0) {
+                if (bid == 0) ctrl32[kCtrlStatus / 4 + 2] = c.bulk != 0u ? c.tw : 0u;      // (for whoever inspects the intermediate rows afterwards)
                 c.nt1 = nt1; c.nt2 = nt2;
                 if (M > kMaxMTiles || nmine > kMaxTasks) cx.fail(kErrTaskCapacity, nmine);
                 else c.ntasks = nmine;
@@ -1693,7 +1975,15 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
   }
 
     // ---- roles
-    if (!cx.aborted()) {
+    bool tiles = false;
+    if constexpr (kUmma && !kA8) tiles = c.bulk != 0u;
+    if (!cx.aborted() && tiles) {
+        if constexpr (kUmma && !kA8) {                     // (launches with more than 16 received rows)
+            if (warp == 0) role_loader_tiles(cx, kUnitK / (4 * kVec));
+            else if (warp == 1) role_mma_tiles<kVec>(cx, lane);
+            else if (warp >= 4 && warp < 8) role_epilogue_tiles<kVec>(cx, tid - 128);
+        }
+    } else if (!cx.aborted()) {
         if (warp == 0) role_loader(cx);
         else if (warp == 1) { if constexpr (kUmma) role_mma<kVec, kA8>(cx, lane); }
         else if (warp < 4) role_stager(cx, warp - 2, lane, false);
@@ -1784,7 +2074,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     // ---- exit: an aborted SM lets the loader's copies in flight land (a bounded wait on the barriers of the stages it
     //      issued last) before the shared memory goes away
     if (warp == 0 && cx.aborted()) {
-        const uint32_t issued = *reinterpret_cast<volatile uint32_t*>(&c.issued), nst = static_cast<uint32_t>(p.nstage);
+        const uint32_t issued = *reinterpret_cast<volatile uint32_t*>(&c.issued), nst = tiles ? p.nstage_wide : static_cast<uint32_t>(p.nstage);
         #pragma unroll 1
         for (uint32_t k = issued > nst ? issued - nst : 0u; k < issued; ++k) {
             const uint32_t s = k % nst, ph = (k / nst) & 1u;

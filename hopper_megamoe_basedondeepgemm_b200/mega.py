@@ -130,35 +130,40 @@ class SymmBuffer:
                  'topk_weights': view(int(L.off_topk_weights), t * self.num_topk * 4, self.topk_weights)}
         return mirror, views
 
-    def used_tile_images(self) -> bool:
-        """Whether the latest launch kept its received and intermediate rows as operand tile images (more than 16
-        received rows) rather than as flagged rows. Synchronises the stream."""
-        return bool(self.device_status()[1][2])
+    def tile_image_rows(self) -> int:
+        """Rows per token tile (16 or 32) if the latest launch kept its received and intermediate rows as tile images
+        (more than 16 received rows), 0 if it kept them as flagged rows. Synchronises the stream."""
+        return int(self.device_status()[1][2])
 
-    @staticmethod
-    def _rows_of_tile_images(tiles: torch.Tensor, row_bytes: int):
-        """(rows uint8 [tiles * 16, row_bytes], scale words uint8 [tiles * 16, words, 4]) of operand tile images."""
-        tiles = tiles.cpu()
-        nt, atoms = tiles.size(0), row_bytes // 128
-        tok = tiles[:, :16 * row_bytes].view(nt, atoms, 16, 8, 16)             # [tile][atom][row][stored chunk][16 B]
-        r = torch.arange(16).view(16, 1)
-        stored = (torch.arange(8).view(1, 8) ^ (r & 7)).view(1, 1, 16, 8, 1).expand(nt, atoms, 16, 8, 16)
-        rows = torch.gather(tok, 3, stored).permute(0, 2, 1, 3, 4).reshape(nt * 16, row_bytes)
-        slots = tiles[:, 16 * row_bytes:].view(nt, -1, 16, 16)                  # [tile][scale word][row][16 B slot]
-        words = slots[..., :4].permute(0, 2, 1, 3).reshape(nt * 16, -1, 4)
+    def _rows_of_tile_images(self, tiles: torch.Tensor, row_bytes: int, tw: int, header: int):
+        """(rows uint8 [tiles * tw, row_bytes], scale words uint8 [tiles * tw, words, 4]) of tile images: per K unit a
+        record of tw rows x 128 B (128 B swizzle) followed by the unit's scale-word slots (16 B per (word, row))."""
+        planes = 256 // (4 * int(self.layout.sf_vec))
+        rec, units = tw * 128 + planes * tw * 16, row_bytes // 128
+        tiles = tiles.cpu()[:, header:header + units * rec]
+        nt = tiles.size(0)
+        recs = tiles.reshape(nt, units, rec)
+        tok = recs[:, :, :tw * 128].reshape(nt, units, tw, 8, 16)                # [tile][unit][row][stored chunk][16 B]
+        r = torch.arange(tw).view(tw, 1)
+        stored = (torch.arange(8).view(1, 8) ^ (r & 7)).view(1, 1, tw, 8, 1).expand(nt, units, tw, 8, 16)
+        rows = torch.gather(tok, 3, stored).permute(0, 2, 1, 3, 4).reshape(nt * tw, row_bytes)
+        slots = recs[:, :, tw * 128:].reshape(nt, units, planes, tw, 16)         # [tile][unit][plane][row][16 B slot]
+        words = slots[..., :4].permute(0, 3, 1, 2, 4).reshape(nt * tw, units * planes, 4)
         return rows.contiguous(), words.contiguous()
 
     def l2_acts_payload(self) -> torch.Tensor:
         """The intermediate rows of the latest launch without flag words or swizzle: uint8 [mid_rows, mid_row_bytes]."""
-        if self.used_tile_images():
-            return self._rows_of_tile_images(self.mid_tiles, int(self.layout.mid_row_bytes))[0]
+        tw = self.tile_image_rows()
+        if tw:
+            return self._rows_of_tile_images(self.mid_tiles, int(self.layout.mid_row_bytes), tw, 0)[0]
         rows = self.l2_acts.size(0)
         return self.l2_acts.view(torch.int32).view(rows, -1, 2)[..., 0].contiguous().view(torch.uint8).view(rows, -1)
 
     def l2_acts_sf_payload(self) -> torch.Tensor:
         """The intermediate rows' scale bytes, K-major: uint8 [mid_rows, intermediate / vec]."""
-        if self.used_tile_images():
-            words = self._rows_of_tile_images(self.mid_tiles, int(self.layout.mid_row_bytes))[1]
+        tw = self.tile_image_rows()
+        if tw:
+            words = self._rows_of_tile_images(self.mid_tiles, int(self.layout.mid_row_bytes), tw, 0)[1]
             return words.reshape(words.size(0), -1)[:, :self.intermediate_hidden // int(self.layout.sf_vec)].contiguous()
         rows = self.l2_acts_sf.size(0)
         words = self.l2_acts_sf.view(torch.int32).view(rows, -1, 2)[..., 0].contiguous().view(torch.uint8).view(rows, -1, 4)

@@ -65,9 +65,10 @@ typedef struct mm_layout {
     int32_t ctrl_bytes;        /* bytes of the control block at off_ctrl */
     int64_t rx_region_bytes;   /* bytes of one (parity, source) region of the receive pool */
     /* Launches with more than 16 received rows: rows sorted by expert into ready-made 16-token operand tiles (local). */
-    int64_t off_token_tiles;   /* [tile_capacity][token_tile_bytes] received tokens of one 16-row tile of one expert, in the shared-memory
-                                  image the tensor core reads (K atoms of 16 rows x 128 B, 128 B swizzle), then the scale-word slots */
-    int64_t off_mid_tiles;     /* [tile_capacity][mid_tile_bytes] the same for the requantised SwiGLU output */
+    int64_t off_token_tiles;   /* [tile_capacity][token_tile_bytes] received rows of one token tile (16 or 32 rows) of one expert: 32 row
+                                  records of 16 B {source rank, token, slot, weight}, then per streamed K unit the unit's 128 B of every
+                                  row in the tensor core's shared-memory order (128 B swizzle) and the unit's scale-word slots */
+    int64_t off_mid_tiles;     /* [tile_capacity][mid_tile_bytes] the same, without the row records, for the requantised SwiGLU output */
     int64_t off_arrive;        /* [2 parities][2][tile_capacity] uint32: rows of a token tile written / L1 weight tiles of a mid tile written */
     int64_t tile_capacity, token_tile_bytes, mid_tile_bytes;
 } mm_layout_t;
@@ -168,8 +169,8 @@ int mm_window_close(void* const* peer_ptrs, int32_t num_ranks, int32_t rank, voi
  * creation). The reference's only remedy is re-creating the buffer (sm100_b200/mega___init__.py:43-47). Callers synchronise the ranks around it. */
 int mm_reset(const mm_config_t* cfg, void* buffer, void* stream);
 /* Synchronises `stream`, then copies the 16 device status words: [0] first failure (0 = none; code | sm << 8 |
- * detail << 16), [1] launches seen, [2] 1 when the latest launch kept its rows as operand tile images (more than 16
- * received rows), [3..] diagnostics. The reference traps instead (sm100_b200/layout_mega_moe.cuh:13-19). */
+ * detail << 16), [1] launches seen, [2] rows per token tile (16 or 32) when the latest launch kept its rows as tile images (more than
+ * 16 received rows), else 0, [3..] diagnostics. The reference traps instead (sm100_b200/layout_mega_moe.cuh:13-19). */
 int mm_read_device_status(const mm_config_t* cfg, const void* buffer, uint32_t out_words[16], void* stream);
 /* Synchronises `stream`, then copies the 32 phase stamps (globaltimer ns) of the last launch. Slots, SM 0 unless
  * noted: 0 first instruction, 1 dispatched, 2 header lines of all ranks seen, 3 scheduled, 4 tasks done, 5 prologue

@@ -348,10 +348,10 @@ def main():
                 out[name] = [round(float(v.min()), 2), round(float(v.median()), 2), round(float(v.max()), 2)]
         if mm._lib.load().mm_get_tuning(mm._lib.TUNE['knobs']) & 32:
             # wait profile (knob 32): cycles the roles spent waiting, as us (cycle length from the MMA role's own two clocks)
-            w = raw[live][:, 16:26].double()
+            w = raw[live][:, 16:30].double()
             ns_per_cycle = (w[:, 9] / w[:, 4].clamp(min=1)).median()
             names = ['loader_waits_free_stage', 'mma_waits_tokens', 'mma_waits_accumulator', 'mma_waits_weights', 'mma_role',
-                     'epilogue_waits_mma', 'epilogue_role', 'epilogue_l1_work', 'epilogue_l2_work']
+                     'epilogue_waits_mma', 'epilogue_role', 'epilogue_l1_work', 'epilogue_l2_work', 'mma_role_ns', 'mma_waits_token_records', 'release_latency_sum', 'release_latency_max', 'release_busy']
             out['wait_profile_us_median_max'] = {n: [round(float((w[:, i] * ns_per_cycle / 1e3).median()), 2),
                                                      round(float((w[:, i] * ns_per_cycle / 1e3).max()), 2)] for i, n in enumerate(names)}
         return out

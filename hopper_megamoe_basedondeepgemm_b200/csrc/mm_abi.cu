@@ -305,6 +305,10 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     const int want = g_tuning[MM_TUNE_STAGES] > 0 ? g_tuning[MM_TUNE_STAGES] : mm::kDefaultStages;
     if (nstage > want) nstage = want;
     if (nstage > mm::kMaxStages) nstage = mm::kMaxStages;
+    // FP8 activations: the two widening warp groups take the units alternately, and a group must see every use of a
+    // stage it waits on (a group that skipped a stage's previous use could take its barrier's older phase for the one it
+    // wants): with an even ring depth a stage always belongs to the same group
+    if (a8) nstage &= ~1;
     if (nstage < 2) return MM_ERR_UNSUPPORTED;
     p.nstage = nstage;
     // dispatching SMs per destination: one per ~16 expected rows, at most G / R (and at most 32)

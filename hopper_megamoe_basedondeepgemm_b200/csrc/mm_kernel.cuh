@@ -38,7 +38,7 @@ constexpr int kMaxTasks = 256;          // tasks one SM can own in one launch
 constexpr int kMetaCap = 4096;          // rows one rank can receive in one launch
 constexpr int kMaxStages = 12;
 constexpr int kDefaultStages = 4;       // stages used when shared memory allows more (see the launch code)
-constexpr int kMetaSmemRows = 256;      // received rows whose (token, slot, weight) records are cached in shared memory
+constexpr int kMetaSmemRows = 128;      // received rows whose (token, slot, weight) records are cached in shared memory
 constexpr int kMaxMTiles = kMetaCap / 16 + kMaxLocalExperts;   // 16-token tiles over all local experts
 constexpr int kTileRows = 128;          // UMMA M: weight rows per task
 constexpr int kTileTokens = 16;         // UMMA N: token rows per task
@@ -60,8 +60,10 @@ constexpr uint32_t kXbufBytes = 2 * kUnitWBytes + 1024;   // one widened unit + 
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kFillWarps = 5;       // warps 2..6 fetch the received rows into shared memory while the schedule is built
 constexpr uint32_t kOtileBytes = 8192;
+constexpr uint32_t kRelQueue = 8;         // entries of the epilogue -> releasing warp queue
 constexpr uint32_t kWideTokens = 32;      // token tile of the launches whose experts have more than 16 rows
-constexpr uint32_t kVtBytes = kWideTokens * kTileRows * 4;   // fp32 accumulators of one task, token-major
+constexpr uint32_t kVtStride = kTileRows + 8;   // floats between the tokens of the accumulator tile (tile-image epilogue: conflict-free 16 B reads)
+constexpr uint32_t kVtBytes = kWideTokens * kVtStride * 4;   // fp32 accumulators of one task, token-major
 
 constexpr int kOwnCap = 128;            // routed rows of this rank's own tokens that every SM lists for itself (see the scout)
 
@@ -142,15 +144,21 @@ struct KParams {
 
 struct Ctl {
     uint64_t full[kMaxStages], empty[kMaxStages];
+    uint64_t rfull[kMaxStages];          // launches with tile images: the token record of a stage has landed
     uint64_t acts_full[2], acts_empty[2], tmem_full[2], tmem_empty[2];
     uint64_t xfull[2], xempty[2];        // FP8-activation variant: widened weight units
+    uint64_t meta_full[4], meta_empty[4];   // launches with tile images: the row records of a task's tile (loader -> epilogue)
     uint64_t tile_full;                  // decode mode: the shared token tile is complete (one arrival per filling warp)
     uint32_t tmem_base, epoch, abort_flag, ntasks;
     uint32_t rx_count[kMaxRanks], rx_prefix[kMaxRanks + 1];
     uint32_t exp_count[kMaxLocalExperts], mid_base[kMaxLocalExperts];
     uint32_t nt1, nt2, dcount, own_cnt;
-    uint32_t comb_next, issued, decode, bulk;
-    uint32_t tw, padw[3];                // rows of a token tile in this launch: 16, or 32 when tile images are in use and an expert has more than 16 rows // next combine item of this SM; weight units the loader has issued; decode mode (see below)
+    uint32_t comb_next, issued, decode, bulk;   // next combine item of this SM; weight units the loader has issued; decode mode and tile-image mode (see below)
+    // rows of a token tile in this launch (16, or 32 when tile images are in use and an expert has more than 16 rows);
+    // queue of finished intermediate tiles, epilogue -> releasing warp
+    uint32_t tw, rel_head, rel_tail, padw;
+    uint32_t rel_q[kRelQueue];
+    long long rel_t[kRelQueue];          // (wait profile: when the entry was queued)
     uint32_t n1_tasks, padn[3];          // L1 tasks at the head of this SM's list
     uint32_t epi_nv[2], epi_dcol[2];     // per accumulator: valid rows of the task and (decode mode) the first accumulator column of its expert
     // token staging geometry of this launch: with room for one 16-row buffer only, launches whose experts all have at
@@ -162,14 +170,15 @@ struct Ctl {
     uint32_t tasks3[kMaxTasks];          // tile index inside its phase (counter slot)
     uint32_t red_old;
     RowMeta row_meta[4][kTileTokens];
-    RowMeta epi_meta[2][kWideTokens];
+    RowMeta epi_meta[2][kTileTokens];
+    alignas(16) RowMeta meta_ring[4][kWideTokens];
     uint32_t nvalid[4];
     uint32_t rowref[2][kTileTokens];
     uint32_t rowidx[2][kTileTokens];
     uint32_t rcslot[2][kTileTokens];     // row-cache slot of each row of the task being staged (0xFFFFFFFF: not cached)
-    float amax_x[4][kWideTokens];
+    float amax_x[4][kTileTokens];
     uint32_t dry_count[kMaxLocalExperts];   // dummy per-expert counts of the schedule's warm-up call
-    uint32_t sfb[4][kWideTokens];        // L1 epilogue: one scale byte per (warp, token), gathered into one flagged word
+    uint32_t sfb[4][kTileTokens];        // L1 epilogue: one scale byte per (warp, token), gathered into one flagged word
     uint32_t mtl[kMaxMTiles];            // (expert << 16 | token tile) of every 16-token tile, expert-major
     RowMeta rx_meta[kMetaSmemRows];
     RowMeta own_meta[kOwnCap];           // records of this rank's own routed rows, listed by the scout from topk_idx
@@ -901,57 +910,104 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
 // for up to 32 rows).
 __device__ __forceinline__ uint32_t tile_record_bytes(uint32_t tw, uint32_t planes) { return tw * 128u + planes * tw * 16u; }
 
-__device__ void role_loader_tiles(const Ctx& cx, uint32_t planes) {
+// Weight units of this SM's tasks into the ring of wide stages (the same stream as `role_loader`, wider stage stride).
+__device__ void role_loader_tiles(const Ctx& cx) {
     const KParams& p = cx.p; Ctl& c = cx.c;
-    const uint32_t tw = c.tw, rec = tile_record_bytes(tw, planes);
-    const uint32_t* arrive = reinterpret_cast<const uint32_t*>(cx.buf + p.off_arrive) + cx.par * 2u * p.tile_capacity;
     uint32_t it = 0, s = 0, ph = 0;
     long long w_empty = 0;
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
-        const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF, j = t & 0xFF;
+        const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, j = t & 0xFF;
         const int ntiles = type ? p.n2_tiles : p.n1_tiles, kunits = type ? p.k2_units : p.k1_units;
         const uint8_t* src = (type ? p.w2 : p.w1) + (static_cast<size_t>(e) * ntiles + j) * kunits * p.unit_bytes;
-        const uint32_t tile = udiv_small(c.mid_base[e], tw) + mt;
-        const uint32_t left = c.exp_count[e] - mt * tw;
-        const uint32_t need = type ? static_cast<uint32_t>(p.n1_tiles) : (left < tw ? left : tw);
-        const uint32_t* arr = arrive + type * p.tile_capacity + tile;
-        const uint8_t* img = type ? cx.buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes
-                                  : cx.buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes + kWideTokens * 16u;
-        bool ready = false;
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
             if (!cx.warp_wait_t(&c.empty[s], ph ^ 1u, kErrWaitEmpty, w_empty)) return;
-            uint8_t* stage = cx.smem + static_cast<size_t>(s) * p.wide_stage_bytes;
-            const bool leader = elect_one();
-            if (leader) {
-                mbar_arrive_expect_tx(&c.full[s], p.unit_bytes + rec);
-                bulk_g2s(stage, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
+            if (elect_one()) {
+                mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
+                bulk_g2s(cx.smem + static_cast<size_t>(s) * p.wide_stage_bytes, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
                 c.issued = it + 1u;
                 if (it == 0u) { cx.note_first_weight_request(); cx.sm_phase(kSmFirstIssue); }
-            }
-            if (!ready) {
-                // the tile's rows (L1: its received rows, L2: the outputs of all L1 weight tiles) have been counted in
-                uint32_t spins = 0;
-                while (ld_acquire_gpu(arr) < need) {
-                    if ((++spins & 0x3Fu) == 0u) {
-                        if (cx.aborted()) return;
-                        if (cx.expired()) { cx.fail(type ? kErrWaitL1Done : kErrWaitDispatchFlag, e); return; }
-                    }
-                }
-                ready = true;
-            }
-            if (leader) {
-                fence_proxy_async_all();
-                bulk_g2s(stage + p.unit_bytes, img + static_cast<size_t>(u) * rec, rec, &c.full[s]);
             }
             __syncwarp();
             if (++s == p.nstage_wide) { s = 0; ph ^= 1u; }
         }
     }
     if ((threadIdx.x & 31u) == 0u) cx.wait_total(16, w_empty);
+}
+
+// The token side of the same stages, by a warp of its own: per task the row records of its tile (for the epilogue), per
+// unit the tile's record. This warp waits for tiles that are not complete yet; the weight loader never does, so the
+// weights of the following units keep coming while a tile is awaited.
+__device__ void role_record_loader(const Ctx& cx, uint32_t planes) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t tw = c.tw, rec = tile_record_bytes(tw, planes);
+    const uint32_t* arrive = reinterpret_cast<const uint32_t*>(cx.buf + p.off_arrive) + cx.par * 2u * p.tile_capacity;
+    uint32_t s = 0, ph = 0;
+    long long w_tiles = 0;
+    // Whether a task's tile is complete (L1: its received rows, L2: the outputs of all L1 weight tiles, counted into the
+    // tile's arrival word) is looked up for 32 tasks at a time, one lane per task: one memory round trip per window.
+    uint32_t win_base = 0, win_ready = 0;
+    auto refresh = [&](uint32_t base) {
+        const uint32_t ti = base + lane;
+        bool r = false;
+        if (ti < c.ntasks) {
+            const uint32_t t = c.tasks[ti], type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
+            const uint32_t tile = udiv_small(c.mid_base[e], tw) + mt, left = c.exp_count[e] - mt * tw;
+            const uint32_t need = type ? static_cast<uint32_t>(p.n1_tiles) : (left < tw ? left : tw);
+            r = ld_acquire_gpu(arrive + type * p.tile_capacity + tile) >= need;
+        }
+        win_base = base;
+        win_ready = __ballot_sync(0xffffffffu, r);
+        fence_proxy_async_all();       // the rows were written through the generic proxy; the bulk copies read them through the async proxy
+    };
+    refresh(0u);
+    #pragma unroll 1
+    for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
+        const uint32_t t = c.tasks[ti];
+        const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
+        const uint32_t tile = udiv_small(c.mid_base[e], tw) + mt;
+        const uint8_t* head = cx.buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes;
+        const uint8_t* img = type ? cx.buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes : head + kWideTokens * 16u;
+        if (!(ti - win_base < 32u && ((win_ready >> (ti - win_base)) & 1u) != 0u)) {
+            const long long t0 = clock64();
+            uint32_t spins = 0;
+            for (;;) {
+                refresh(ti);
+                if (win_ready & 1u) break;
+                if ((++spins & 0xFu) == 0u) {
+                    if (cx.aborted()) return;
+                    if (cx.expired()) { cx.fail(type ? kErrWaitL1Done : kErrWaitDispatchFlag, e); return; }
+                }
+            }
+            w_tiles += clock64() - t0;
+        }
+        {
+            // the rows' records (source rank, token, slot, top-k weight) of the task's tile, for its epilogue: slot ti mod 4
+            const uint32_t ms = ti & 3u;
+            if (!cx.warp_wait(&c.meta_empty[ms], ((ti >> 2) & 1u) ^ 1u, kErrWaitEmpty)) return;
+            if (elect_one()) {
+                mbar_arrive_expect_tx(&c.meta_full[ms], kWideTokens * 16u);
+                bulk_g2s(c.meta_ring[ms], head, kWideTokens * 16u, &c.meta_full[ms]);
+            }
+            __syncwarp();
+        }
+        const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
+        #pragma unroll 1
+        for (int u = ub; u < ue; ++u) {
+            if (!cx.warp_wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
+            if (elect_one()) {
+                mbar_arrive_expect_tx(&c.rfull[s], rec);
+                bulk_g2s(cx.smem + static_cast<size_t>(s) * p.wide_stage_bytes + p.unit_bytes, img + static_cast<size_t>(u) * rec, rec, &c.rfull[s]);
+            }
+            __syncwarp();
+            if (++s == p.nstage_wide) { s = 0; ph ^= 1u; }
+        }
+    }
+    if (lane == 0u) cx.wait_total(17, w_tiles);
 }
 
 template <int kVec>
@@ -964,7 +1020,7 @@ __device__ void role_mma_tiles(const Ctx& cx, uint32_t lane) {
     const uint32_t sfa_col = 64, sfb_col = 96;                  // accumulators 2 x 32 columns, weight scales 2 x 16, token scales 2 x 16
     uint32_t it = 0, s = 0, ph = 0;
     unsigned long long t_landed = 0ull;
-    long long w_tmem = 0, w_full = 0;
+    long long w_tmem = 0, w_full = 0, w_tok = 0;
     const long long t_role = clock64();
     const unsigned long long ns_role = globaltimer_ns();
     #pragma unroll 1
@@ -976,6 +1032,7 @@ __device__ void role_mma_tiles(const Ctx& cx, uint32_t lane) {
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
             if (!cx.warp_wait_t(&c.full[s], ph, kErrWaitFull, w_full)) return;
+            if (!cx.warp_wait_t(&c.rfull[s], ph, kErrWaitActsFull, w_tok)) return;
             tc_fence_after();
             t_landed = globaltimer_ns();
             if (lane == 0 && it == 0u) cx.sm_phase(kSmFirstLanded);
@@ -1013,7 +1070,7 @@ __device__ void role_mma_tiles(const Ctx& cx, uint32_t lane) {
     if (lane == 0 && t_landed != 0ull) cx.stamp_max(kStampLastWeight, t_landed);
     if (lane == 0) {
         cx.wait_total(18, w_tmem); cx.wait_total(19, w_full); cx.wait_total(20, clock64() - t_role);
-        cx.wait_total(25, static_cast<long long>(globaltimer_ns() - ns_role));
+        cx.wait_total(25, static_cast<long long>(globaltimer_ns() - ns_role)); cx.wait_total(26, w_tok);
     }
 }
 
@@ -1024,7 +1081,8 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
     const uint32_t ew = etid >> 5, lane = etid & 31u, row = etid, tw = c.tw;
     const uint32_t rec = tile_record_bytes(tw, kPlanes);
     uint8_t* otile = cx.smem + p.sm_otile;
-    float* vt = reinterpret_cast<float*>(cx.smem + p.sm_vt) + row;      // this thread's accumulators: vt[n * 128], token n
+    float* vt_all = reinterpret_cast<float*>(cx.smem + p.sm_vt);
+    float* vt = vt_all + row;      // this thread's accumulators: vt[n * kVtStride], token n
     const uint32_t* arrive_tok = reinterpret_cast<const uint32_t*>(cx.buf + p.off_arrive) + cx.par * 2u * p.tile_capacity;
     uint32_t* arrive_mid = reinterpret_cast<uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + 1u) * p.tile_capacity;
     long long w_tfull = 0, w_l1 = 0, w_l2 = 0;
@@ -1036,20 +1094,8 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
         const uint32_t acc = ti & 1u, use = (ti >> 1) & 1u;
         const uint32_t tile = udiv_small(c.mid_base[e], tw) + mt;
         const uint32_t left = c.exp_count[e] - mt * tw, nv = left < tw ? left : tw;
-        // the rows' records (source rank, token, slot, top-k weight) head the token tile image; the first warp fetches them
-        // while the task's MMAs run (after its own acquire of the tile's arrival count)
-        RowMeta mrec{0, 0, 0, 0.f};
-        bool ok = true;
-        if (ew == 0u) {
-            uint32_t spins = 0;
-            while (ld_acquire_gpu(arrive_tok + tile) < nv) {
-                if ((++spins & 0x3Fu) == 0u && (cx.aborted() || cx.expired())) { ok = false; break; }
-            }
-            if (ok && lane < nv) {
-                const uint4 q = ld_cg_v4(cx.buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes + lane * 16u);
-                mrec = RowMeta{static_cast<int32_t>(q.x), static_cast<int32_t>(q.y), static_cast<int32_t>(q.z), __uint_as_float(q.w)};
-            }
-        }
+        // the rows' records (source rank, token, slot, top-k weight): the loader copied the tile's header into slot ti mod 4
+        bool ok = cx.warp_wait(&c.meta_full[ti & 3u], (ti >> 2) & 1u, kErrWaitActsFull);
         ok = ok && cx.warp_wait_t(&c.tmem_full[acc], use, kErrWaitTmemFull, w_tfull);
         const long long t_work = clock64();
         if (ok) {
@@ -1059,19 +1105,19 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
             tmem_ld_32x32b_x16(c.tmem_base + ((ew * 32u) << 16) + acc * kWideTokens, raw);
             tmem_ld_wait();
             #pragma unroll
-            for (int n = 0; n < kTileTokens; ++n) vt[n * kTileRows] = __uint_as_float(raw[n]);
+            for (int n = 0; n < kTileTokens; ++n) vt[n * kVtStride] = __uint_as_float(raw[n]);
             if (nv > kTileTokens) {
                 tmem_ld_32x32b_x16(c.tmem_base + ((ew * 32u) << 16) + acc * kWideTokens + kTileTokens, raw);
                 tmem_ld_wait();
                 #pragma unroll
-                for (int n = 0; n < kTileTokens; ++n) vt[(kTileTokens + n) * kTileRows] = __uint_as_float(raw[n]);
+                for (int n = 0; n < kTileTokens; ++n) vt[(kTileTokens + n) * kVtStride] = __uint_as_float(raw[n]);
             }
             tc_fence_before();
             mbar_arrive(&c.tmem_empty[acc]);
-            if (ew == 0u && lane < nv) c.epi_meta[acc][lane] = mrec;
         }
-        if (bar_red_or(kBarEpi, kNumEpiThreads, !ok)) return;        // also publishes epi_meta
-        const RowMeta* meta = c.epi_meta[acc];
+        if (bar_red_or(kBarEpi, kNumEpiThreads, !ok)) return;
+        if (etid == 0u && ti > 0u) mbar_arrive(&c.meta_empty[(ti - 1u) & 3u]);      // every thread is past the previous task's records
+        const RowMeta* meta = c.meta_ring[ti & 3u];
         const uint32_t np = (c.tasks2[ti] >> 16) & 0xFFu;
         if (np > 1u) {
             // this SM covered only part of the tile's K range: park the partial sums, count in, and let the last
@@ -1081,7 +1127,7 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
             constexpr size_t kSlot = 2u * kTileTokens * kTileRows;           // floats: room for 32 rows
             float* mine = red + (static_cast<size_t>(blockIdx.x) * 2u + type) * kSlot + row;
             #pragma unroll 1
-            for (uint32_t n = 0; n < nv; ++n) mine[n * kTileRows] = vt[n * kTileRows];
+            for (uint32_t n = 0; n < nv; ++n) mine[n * kTileRows] = vt[n * kVtStride];
             bar_sync(kBarEpi, kNumEpiThreads);
             if (etid == 0) {
                 uint32_t* cnt = reinterpret_cast<uint32_t*>(cx.buf + p.off_cnt) + type * p.cnt_per_phase + tix;
@@ -1106,83 +1152,115 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
                     #pragma unroll
                     for (uint32_t d = 0; d < 4; ++d) if (pc0 + d < np) sum += part_v[d];
                 }
-                vt[n * kTileRows] = sum;
+                vt[n * kVtStride] = sum;
             }
+            bar_sync(kBarEpi, kNumEpiThreads);                    // the sums are read across threads below
         }
 
         if (type == 0u) {
-            // ---- L1: rows come in groups of 16 = 8 gate rows then the 8 matching up rows
-            const bool is_up = (lane & 8u) != 0u;
-            #pragma unroll 1
-            for (uint32_t n = 0; n < nv; ++n) {
-                const float mine = bf16_round(vt[n * kTileRows] * p.l1_scale);
-                const float other = __shfl_xor_sync(0xffffffffu, mine, 8);
-                float gate = is_up ? other : mine, up = is_up ? mine : other;
-                if (p.has_clamp) { gate = fminf(gate, p.clamp); up = fminf(fmaxf(up, -p.clamp), p.clamp); }
-                const float sig = p.fast_math ? __frcp_rn(1.0f + __expf(-gate)) : 1.0f / (1.0f + expf(-gate));
-                float av = gate * sig * up * meta[n].weight;
-                if constexpr (kVec == 16) av = __fdiv_rn(av, p.mid_gs);
-                vt[n * kTileRows] = av;
-                float a = fabsf(av);
+            // ---- L1. Weight rows come in groups of 16 = 8 gate rows then the 8 matching up rows: 64 output columns per
+            //      token. Thread (token n = t / 4, q = t % 4) takes the columns [16 k + 4 q, 16 k + 4 q + 4), k = 0..3, of
+            //      its token from the accumulator tile in shared memory: all tokens at once, sixteen independent values
+            //      per thread, whatever the number of rows.
+            const uint32_t n = etid >> 2, q = etid & 3u;
+            const bool live = n < nv;
+            const float* vrow = vt_all + (live ? n : 0u) * kVtStride;
+            const float wgt = meta[live ? n : 0u].weight;
+            float o[16];
+            #pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+                const uint32_t base = 32u * k + 16u * (q >> 1) + 4u * (q & 1u);
+                const float4 g4 = *reinterpret_cast<const float4*>(vrow + base), u4 = *reinterpret_cast<const float4*>(vrow + base + 8u);
+                const float gs[4] = {g4.x, g4.y, g4.z, g4.w}, us[4] = {u4.x, u4.y, u4.z, u4.w};
+                #pragma unroll
+                for (uint32_t i = 0; i < 4; ++i) {
+                    float gate = bf16_round(gs[i] * p.l1_scale), up = bf16_round(us[i] * p.l1_scale);
+                    if (p.has_clamp) { gate = fminf(gate, p.clamp); up = fminf(fmaxf(up, -p.clamp), p.clamp); }
+                    const float sig = p.fast_math ? __frcp_rn(1.0f + __expf(-gate)) : 1.0f / (1.0f + expf(-gate));
+                    float av = gate * sig * up * wgt;
+                    if constexpr (kVec == 16) av = __fdiv_rn(av, p.mid_gs);
+                    o[4 * k + i] = av;
+                }
+            }
+            // block maxima: a block of 16 columns is one k over the four q threads; a block of 32 columns is two k
+            float am[4];
+            #pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+                float a = fmaxf(fmaxf(fabsf(o[4 * k]), fabsf(o[4 * k + 1])), fmaxf(fabsf(o[4 * k + 2]), fabsf(o[4 * k + 3])));
                 a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 1));
                 a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 2));
-                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 4));
-                a = fmaxf(a, __shfl_xor_sync(0xffffffffu, a, 16));
-                if (lane == 0) c.amax_x[ew][n] = a;
+                am[k] = a;
             }
-            if constexpr (kVec == 32) bar_sync(kBarEpi, kNumEpiThreads);     // a 32-column scale block spans two warps
-            else __syncwarp();
-            #pragma unroll 1
-            for (uint32_t n = 0; n < nv; ++n) {
-                float amax = c.amax_x[ew][n];
-                if constexpr (kVec == 32) amax = fmaxf(amax, c.amax_x[ew ^ 1u][n]);
+            uint32_t sfw = 0u, packed[4];
+            #pragma unroll
+            for (uint32_t k = 0; k < 4; ++k) {
+                float amax = kVec == 32 ? fmaxf(am[k & 2u], am[(k & 2u) + 1u]) : am[k];
                 amax = fmaxf(amax, 1e-30f);
-                const float av = vt[n * kTileRows];
-                uint32_t sf_byte; float scaled;
+                uint32_t sf_byte; float sc[4];
                 if constexpr (kVec == 32) {
                     sf_byte = ceil_pow2_exp(__fdiv_rn(amax, 6.0f));
-                    scaled = __fdiv_rn(av, __uint_as_float(sf_byte << 23));
+                    const float sf = __uint_as_float(sf_byte << 23);
+                    #pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) sc[i] = __fdiv_rn(o[4 * k + i], sf);
+                    if ((k & 1u) == 0u) sfw |= sf_byte << (4u * k);          // blocks 0 and 1 -> bytes 0 and 1
                 } else {
                     sf_byte = cvt_e4m3x2(__fdiv_rn(amax, 6.0f), 0.f) & 0xFFu;
                     const float sf = e4m3_to_float(sf_byte);
-                    scaled = sf > 0.f ? __fdiv_rn(av, sf) : (av == 0.f ? 0.f : copysignf(6.0f, av));
-                }
-                const float nb = __shfl_down_sync(0xffffffffu, scaled, 1);
-                if (!is_up && (lane & 1u) == 0u)
-                    otile[n * 32 + ew * 8u + (lane >> 4) * 4u + ((lane & 7u) >> 1)] = static_cast<uint8_t>(cvt_e2m1x2(scaled, nb));
-                if (lane == 0) c.sfb[ew][n] = sf_byte;
-            }
-            bar_sync(kBarEpi, kNumEpiThreads);
-            {
-                // the 64 output columns of every row go into the intermediate tile's image: two 16 B chunks at their
-                // swizzled place in the record of their K unit, the scale bytes into that record's slots; then one count
-                // into the tile's arrival word (thread 0's release covers the stores the barrier ordered before it)
-                uint8_t* img = cx.buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes;
-                if (etid < nv * 2u) {
-                    const uint32_t n = etid >> 1, ci = j * 2u + (etid & 1u);
-                    const uint4 val = *reinterpret_cast<const uint4*>(otile + etid * 16u);
-                    *reinterpret_cast<uint4*>(img + (ci >> 3) * rec + sw128_off(n, ci & 7u)) = val;
-                } else if (etid >= 64u && etid - 64u < nv) {
-                    const uint32_t n = etid - 64u;
-                    if constexpr (kVec == 16) {
-                        uint8_t* slots = img + (j >> 2) * rec + tw * 128u + (j & 3u) * tw * 16u;
-                        *reinterpret_cast<uint32_t*>(slots + n * 16u) = c.sfb[0][n] | (c.sfb[1][n] << 8) | (c.sfb[2][n] << 16) | (c.sfb[3][n] << 24);
-                    } else {
-                        uint8_t* slots = img + (j >> 2) * rec + tw * 128u + ((j >> 1) & 1u) * tw * 16u;
-                        *reinterpret_cast<uint16_t*>(slots + n * 16u + (j & 1u) * 2u) = static_cast<uint16_t>(c.sfb[0][n] | (c.sfb[2][n] << 8));
+                    #pragma unroll
+                    for (uint32_t i = 0; i < 4; ++i) {
+                        const float av = o[4 * k + i];
+                        sc[i] = sf > 0.f ? __fdiv_rn(av, sf) : (av == 0.f ? 0.f : copysignf(6.0f, av));
                     }
+                    sfw |= sf_byte << (8u * k);
+                }
+                packed[k] = cvt_e2m1x2(sc[0], sc[1]) | (cvt_e2m1x2(sc[2], sc[3]) << 8);
+            }
+            // the token's 32 output bytes = two 16 B chunks: chunk c holds k = 2c, 2c + 1, each as the 2-byte pieces of q = 0..3
+            const uint32_t v01 = packed[0] | (packed[1] << 16), v23 = packed[2] | (packed[3] << 16);
+            uint32_t w01[4], w23[4];
+            #pragma unroll
+            for (uint32_t d = 0; d < 4; ++d) {
+                w01[d] = __shfl_sync(0xffffffffu, v01, (lane & ~3u) + d);
+                w23[d] = __shfl_sync(0xffffffffu, v23, (lane & ~3u) + d);
+            }
+            {
+                // into the intermediate tile's image: the chunks at their swizzled place in the record of their K unit, the
+                // scale bytes into that record's slots; then one count into the tile's arrival word (thread 0's release
+                // covers the stores the barrier ordered before it)
+                uint8_t* img = cx.buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes;
+                if (live && q < 2u) {
+                    const uint32_t* w = q == 0u ? w01 : w23;
+                    const uint4 val = make_uint4((w[0] & 0xFFFFu) | (w[1] << 16), (w[2] & 0xFFFFu) | (w[3] << 16),
+                                                 (w[0] >> 16) | (w[1] & 0xFFFF0000u), (w[2] >> 16) | (w[3] & 0xFFFF0000u));
+                    const uint32_t ci = j * 2u + q;
+                    *reinterpret_cast<uint4*>(img + (ci >> 3) * rec + sw128_off(n, ci & 7u)) = val;
+                } else if (live && q == 2u) {
+                    if constexpr (kVec == 16)
+                        *reinterpret_cast<uint32_t*>(img + (j >> 2) * rec + tw * 128u + (j & 3u) * tw * 16u + n * 16u) = sfw;
+                    else
+                        *reinterpret_cast<uint16_t*>(img + (j >> 2) * rec + tw * 128u + ((j >> 1) & 1u) * tw * 16u + n * 16u + (j & 1u) * 2u) = static_cast<uint16_t>(sfw);
                 }
                 bar_sync(kBarEpi, kNumEpiThreads);
                 if (etid == 0u) {
-                    fence_proxy_async_all();
-                    red_release_gpu_add(arrive_mid + tile, 1u);
+                    // The count needs a release, and under the weight flood a release takes microseconds: it is handed to
+                    // the releasing warp through a queue in shared memory (done here only if that queue is full).
+                    const uint32_t head = c.rel_head;
+                    if (head - *reinterpret_cast<volatile uint32_t*>(&c.rel_tail) < kRelQueue) {
+                        c.rel_q[head % kRelQueue] = tile;
+                        c.rel_t[head % kRelQueue] = clock64();
+                        __threadfence_block();
+                        *reinterpret_cast<volatile uint32_t*>(&c.rel_head) = head + 1u;
+                    } else {
+                        fence_proxy_async_all();
+                        red_release_gpu_add(arrive_mid + tile, 1u);
+                    }
                 }
             }
         } else {
             // ---- L2: bf16 rows back to the token's source rank, as flagged words: the combine there polls the data itself
             __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(otile);
             #pragma unroll 1
-            for (uint32_t n = 0; n < nv; ++n) ot[n * kTileRows + row] = __float2bfloat16_rn(vt[n * kTileRows] * p.l2_scale);
+            for (uint32_t n = 0; n < nv; ++n) ot[n * kTileRows + row] = __float2bfloat16_rn(vt[n * kVtStride] * p.l2_scale);
             bar_sync(kBarEpi, kNumEpiThreads);
             #pragma unroll 1
             for (uint32_t idx = etid; idx < nv * 32u; idx += kNumEpiThreads) {
@@ -1199,7 +1277,51 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
         }
         if (type == 0u) w_l1 += clock64() - t_work; else w_l2 += clock64() - t_work;
     }
-    if (etid == 0u) { cx.wait_total(21, w_tfull); cx.wait_total(22, clock64() - t_role); cx.wait_total(23, w_l1); cx.wait_total(24, w_l2); }
+    if (etid == 0u) {
+        // the releasing warp ends when it finds this entry
+        uint32_t head = c.rel_head, spins = 0;
+        while (head - *reinterpret_cast<volatile uint32_t*>(&c.rel_tail) >= kRelQueue && ++spins < 4000000u) { }
+        c.rel_q[head % kRelQueue] = 0xFFFFFFFFu;
+        __threadfence_block();
+        *reinterpret_cast<volatile uint32_t*>(&c.rel_head) = head + 1u;
+        cx.wait_total(21, w_tfull); cx.wait_total(22, clock64() - t_role); cx.wait_total(23, w_l1); cx.wait_total(24, w_l2);
+    }
+}
+
+// The releasing warp: counts finished intermediate tiles in for the L1 epilogue (queue of tile numbers in shared memory,
+// written by the epilogue's first thread after the barrier that follows the tile's stores). The release orders those
+// stores, which the queue hand-off made visible to this warp, before the count.
+__device__ void role_releaser(const Ctx& cx) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    const uint32_t lane = threadIdx.x & 31u;
+    uint32_t* arrive_mid = reinterpret_cast<uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + 1u) * p.tile_capacity;
+    uint32_t tail = 0, spins = 0;
+    long long lat_sum = 0, lat_max = 0, busy = 0;
+    // (the whole warp stays in this loop: lanes that left it would spin in the combine and take the issue slots of the lane that works here)
+    for (;;) {
+        uint32_t tile = 0xFFFFFFFEu;
+        if (lane == 0) {
+            if (*reinterpret_cast<volatile uint32_t*>(&c.rel_head) != tail) {
+                __threadfence_block();
+                tile = *reinterpret_cast<volatile uint32_t*>(&c.rel_q[tail % kRelQueue]);
+                const long long t_q = *reinterpret_cast<volatile long long*>(&c.rel_t[tail % kRelQueue]);
+                ++tail;
+                *reinterpret_cast<volatile uint32_t*>(&c.rel_tail) = tail;
+                if (tile != 0xFFFFFFFFu) {
+                    const long long t0 = clock64();
+                    fence_proxy_async_all();
+                    red_release_gpu_add(arrive_mid + tile, 1u);
+                    const long long t1 = clock64();
+                    busy += t1 - t0; lat_sum += t1 - t_q; lat_max = lat_max > t1 - t_q ? lat_max : t1 - t_q;
+                }
+            } else if ((++spins & 0xFFFu) == 0u && (cx.aborted() || cx.expired())) {
+                tile = 0xFFFFFFFFu;
+            }
+        }
+        tile = __shfl_sync(0xffffffffu, tile, 0);
+        if (tile == 0xFFFFFFFFu) break;
+    }
+    if (lane == 0) { cx.wait_total(27, lat_sum); cx.wait_total(28, lat_max); cx.wait_total(29, busy); }
 }
 
 // ============================================================================================= schedule
@@ -1455,9 +1577,9 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (tid == 0) {
         const uint32_t ep = ctrl32[kCtrlEpoch / 4 + bid];
         ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
-        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u; c.decode = 0u; c.bulk = 0u;
+        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u; c.decode = 0u; c.bulk = 0u; c.rel_head = 0u; c.rel_tail = 0u;
         if constexpr (!kScout) c.own_cnt = 0u;
-        for (int s = 0; s < (p.nstage > static_cast<int>(p.nstage_wide) ? p.nstage : static_cast<int>(p.nstage_wide)); ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
+        for (int s = 0; s < (p.nstage > static_cast<int>(p.nstage_wide) ? p.nstage : static_cast<int>(p.nstage_wide)); ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.rfull[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
         #pragma unroll 1
         for (int i = 0; i < 2; ++i) {
             mbar_init(&c.acts_full[i], 1); mbar_init(&c.acts_empty[i], kUmma ? 1 : kNumEpiThreads);
@@ -1465,6 +1587,8 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             mbar_init(&c.xfull[i], kNumExpThreads / 64); mbar_init(&c.xempty[i], 1);
         }
         mbar_init(&c.tile_full, kFillWarps);
+        #pragma unroll 1
+        for (int i = 0; i < 4; ++i) { mbar_init(&c.meta_full[i], 1); mbar_init(&c.meta_empty[i], 1); }
         mbar_fence_init();
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmEntry)[bid] = t_first;
         if constexpr (!kScout) reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmWFirst)[bid] = ~0ull;
@@ -1794,21 +1918,15 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             uint8_t* head = buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes;
             uint8_t* img = head + kWideTokens * 16u;
             bool bad = tile >= p.tile_capacity;
-            if (lane == 0 && !bad) {
-                // the row's record for the epilogues: source rank, token, slot, top-k weight
-                RowMeta m;
-                if (own) m = c.own_meta[i];
-                else if (f < kMetaSmemRows) m = c.rx_meta[f];
-                else {
-                    uint4 q = make_uint4(0u, 0u, 0u, 0u);
-                    if (!cx.ll_read(row_src + 2u * (p.rx_row_bytes - 16), flag_rx, q, kErrWaitDispatchFlag, r)) bad = true;
-                    m = RowMeta{0, static_cast<int32_t>(q.y), static_cast<int32_t>(q.z), __uint_as_float(q.w)};
-                }
+            // (chunk `per_row` of a received row is its record {expert, token, slot, top-k weight}: it becomes the row's
+            //  record {source rank, token, slot, weight} in the tile's header; an own row's record comes from the scout's list)
+            if (own && lane == 0 && !bad) {
+                const RowMeta m = c.own_meta[i];
                 *reinterpret_cast<uint4*>(head + pos * 16u) = make_uint4(r, static_cast<uint32_t>(m.token), static_cast<uint32_t>(m.slot), __float_as_uint(m.weight));
             }
-            bad = __any_sync(0xffffffffu, bad);
+            const uint32_t nread = own ? per_row : per_row + 1u;
             #pragma unroll 1
-            for (uint32_t base = lane; base < per_row && !bad; base += 4 * 32) {
+            for (uint32_t base = lane; base < nread && !bad; base += 4 * 32) {
                 uint4 v[4];
                 if (own) {
                     #pragma unroll
@@ -1825,7 +1943,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                         #pragma unroll
                         for (uint32_t u = 0; u < 4; ++u) {
                             const uint32_t ci = base + u * 32;
-                            if (ci < per_row) {
+                            if (ci < nread) {
                                 const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
                                 ok = ok && ll_valid(a, b, flag_rx);
                                 v[u] = ll_data(a, b);
@@ -1840,8 +1958,10 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                 #pragma unroll
                 for (uint32_t u = 0; u < 4; ++u) {
                     const uint32_t ci = base + u * 32;
-                    if (ci >= per_row || bad) continue;
-                    if (ci < xq) {
+                    if (ci >= nread || bad) continue;
+                    if (ci == per_row) {
+                        *reinterpret_cast<uint4*>(head + pos * 16u) = make_uint4(r, v[u].y, v[u].z, v[u].w);
+                    } else if (ci < xq) {
                         *reinterpret_cast<uint4*>(img + (ci >> 3) * rec + sw128_off(pos, ci & 7u)) = v[u];
                     } else {
                         // four scale words g .. g + 3 of the row: word g belongs to K unit g / planes, plane g % planes
@@ -1979,8 +2099,10 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if constexpr (kUmma && !kA8) tiles = c.bulk != 0u;
     if (!cx.aborted() && tiles) {
         if constexpr (kUmma && !kA8) {                     // (launches with more than 16 received rows)
-            if (warp == 0) role_loader_tiles(cx, kUnitK / (4 * kVec));
+            if (warp == 0) role_loader_tiles(cx);
             else if (warp == 1) role_mma_tiles<kVec>(cx, lane);
+            else if (warp == 2) role_record_loader(cx, kUnitK / (4 * kVec));
+            else if (warp == 3) role_releaser(cx);
             else if (warp >= 4 && warp < 8) role_epilogue_tiles<kVec>(cx, tid - 128);
         }
     } else if (!cx.aborted()) {

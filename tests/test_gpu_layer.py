@@ -43,7 +43,7 @@ def run_layer(fmt, e_local, hidden, inter, topk, tokens, routing, engine, seed=0
                             fast_math=True, engine=engine, x_global_scale=x_gs, l1_global_scale=gs1,
                             l2_global_scale=gs2, mid_global_scale=mid_gs, timeout_ms=500.0)
     st, words = buf.device_status()
-    assert st == 0, f'device status {st}: {[hex(v) for v in words[:4]]}'
+    assert st == 0, f'device status {st}: {[hex(v) for v in words[:4]]} {U.last_cuda_error()}'
     return y.cpu(), stats.cpu(), ref, buf, inp
 
 

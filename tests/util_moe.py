@@ -48,3 +48,13 @@ def write_inputs(buf, inp: O.RankInput, sfb: torch.Tensor):
     buf.x_sf[:t].copy_(sfb.contiguous().view(torch.int32))
     buf.topk_idx[:t].copy_(inp.topk_idx)
     buf.topk_weights[:t].copy_(inp.topk_weights)
+
+
+def last_cuda_error() -> str:
+    """Text of the latest CUDA runtime failure the library recorded (empty if none)."""
+    import ctypes
+    from hopper_megamoe_basedondeepgemm_b200 import _lib
+    lib = _lib.load()
+    lib.mm_last_cuda_error.restype = ctypes.c_char_p
+    msg = lib.mm_last_cuda_error()
+    return msg.decode() if msg else ''

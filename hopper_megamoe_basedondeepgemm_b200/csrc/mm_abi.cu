@@ -311,11 +311,10 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     if (a8) nstage &= ~1;
     if (nstage < 2) return MM_ERR_UNSUPPORTED;
     p.nstage = nstage;
-    // dispatching SMs per destination: one per ~16 expected rows, at most G / R (and at most 32)
+    // dispatching SMs per destination: one per ~8 expected rows (one row per copying warp), at most G / R
     {
-        int nd = (p.T * p.topk) / (p.R * 16);
+        int nd = (p.T * p.topk) / (p.R * 8);
         if (nd > *grid / p.R) nd = *grid / p.R;
-        if (nd > 32) nd = 32;
         p.ndisp = nd < 1 ? 1 : nd;
     }
     // launches that work from tile images reuse the stages and the token staging area as one ring of wider stages

@@ -1080,10 +1080,8 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
     constexpr uint32_t kPlanes = kUnitK / (4 * kVec);
     const uint32_t ew = etid >> 5, lane = etid & 31u, row = etid, tw = c.tw;
     const uint32_t rec = tile_record_bytes(tw, kPlanes);
-    uint8_t* otile = cx.smem + p.sm_otile;
     float* vt_all = reinterpret_cast<float*>(cx.smem + p.sm_vt);
     float* vt = vt_all + row;      // this thread's accumulators: vt[n * kVtStride], token n
-    const uint32_t* arrive_tok = reinterpret_cast<const uint32_t*>(cx.buf + p.off_arrive) + cx.par * 2u * p.tile_capacity;
     uint32_t* arrive_mid = reinterpret_cast<uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + 1u) * p.tile_capacity;
     long long w_tfull = 0, w_l1 = 0, w_l2 = 0;
     const long long t_role = clock64();
@@ -1257,19 +1255,24 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
                 }
             }
         } else {
-            // ---- L2: bf16 rows back to the token's source rank, as flagged words: the combine there polls the data itself
-            __nv_bfloat16* ot = reinterpret_cast<__nv_bfloat16*>(otile);
-            #pragma unroll 1
-            for (uint32_t n = 0; n < nv; ++n) ot[n * kTileRows + row] = __float2bfloat16_rn(vt[n * kVtStride] * p.l2_scale);
-            bar_sync(kBarEpi, kNumEpiThreads);
+            // ---- L2: bf16 rows back to the token's source rank, as flagged words: the combine there polls the data itself.
+            //      A pair of lanes per 16 B chunk (8 weight rows of one token, read from the accumulator tile in shared
+            //      memory): each lane stores one 16 B half of the chunk's flagged image, full 32 B sectors per instruction.
             #pragma unroll 1
             for (uint32_t idx = etid; idx < nv * 32u; idx += kNumEpiThreads) {
                 const uint32_t n = idx >> 5, ch = (idx & 31u) >> 1;
-                const uint4 val = *reinterpret_cast<const uint4*>(otile + n * 256u + ch * 16u);
+                const float* v = vt_all + n * kVtStride + ch * 8u;
+                const float4 lo = *reinterpret_cast<const float4*>(v), hi = *reinterpret_cast<const float4*>(v + 4);
+                auto pack = [&](float x0, float x1) -> uint32_t {
+                    return static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(x0 * p.l2_scale))) |
+                           (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(x1 * p.l2_scale))) << 16);
+                };
+                const uint4 val = make_uint4(pack(lo.x, lo.y), pack(lo.z, lo.w), pack(hi.x, hi.y), pack(hi.z, hi.w));
                 uint8_t* dst = p.peer[meta[n].src] + p.off_comb +
                     ((static_cast<size_t>(meta[n].token) * p.topk + meta[n].slot) * p.H + j * kTileRows) * 4u + ch * 32u;
                 st_ll_half(dst, val, c.epoch + 1u, idx & 1u);
             }
+            bar_sync(kBarEpi, kNumEpiThreads);            // the accumulator tile is read across threads: nobody refills it before all are done
         }
         if (etid == 0u) {
             if (ti == 0u) cx.sm_phase(kSmFirstEpilogue);
@@ -1714,15 +1717,24 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             const uint32_t n = static_cast<uint32_t>(p.T) * p.topk;
             uint32_t cnt = 0;
             #pragma unroll 1
-            for (uint32_t base = 0; base < n; base += 32) {
-                const uint32_t i = base + lane;
-                const long long ex = i < n ? tk[i] : -1;
-                const uint32_t ex32 = ex >= 0 && ex < 0x10000 ? static_cast<uint32_t>(ex) : 0u;
-                const uint32_t dest = udiv_small(ex32, p.e_local), tok = udiv_small(i, p.topk);
-                const bool m = ex >= 0 && ex < 0x10000 && dest == d;
-                const uint32_t b = __ballot_sync(0xffffffffu, m);
-                if (m) dlist[cnt + __popc(b & ((1u << lane) - 1u))] = (tok << 16) | ((i - tok * p.topk) << 8) | (ex32 - dest * p.e_local);
-                cnt += __popc(b);
+            for (uint32_t base0 = 0; base0 < n; base0 += 4 * 32) {
+                long long exs[4];                                  // four loads in flight: one memory round trip per 128 routing entries
+                #pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t i = base0 + u * 32 + lane;
+                    exs[u] = i < n ? tk[i] : -1;
+                }
+                #pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t i = base0 + u * 32 + lane;
+                    const long long ex = exs[u];
+                    const uint32_t ex32 = ex >= 0 && ex < 0x10000 ? static_cast<uint32_t>(ex) : 0u;
+                    const uint32_t dest = udiv_small(ex32, p.e_local), tok = udiv_small(i, p.topk);
+                    const bool m = ex >= 0 && ex < 0x10000 && dest == d;
+                    const uint32_t b = __ballot_sync(0xffffffffu, m);
+                    if (m) dlist[cnt + __popc(b & ((1u << lane) - 1u))] = (tok << 16) | ((i - tok * p.topk) << 8) | (ex32 - dest * p.e_local);
+                    cnt += __popc(b);
+                }
             }
             if (lane == 0) c.dcount = cnt;
         }
@@ -1839,21 +1851,39 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                     cx.ll_read(cx.rx_row(spec_r, spec_i) + 2u * (p.rx_row_bytes - 16), flag_rx, m, kErrWaitDispatchFlag, spec_r);
                 take(pre[spec_r] + spec_i, m);
             }
+            // (four records per thread in flight together: one memory round trip per four records of a large batch)
             #pragma unroll 1
-            for (uint32_t f = tid; f < total; f += kO) {
-                uint32_t r = 0;
+            for (uint32_t f0 = tid; f0 < total; f0 += 4u * kO) {
+                const uint8_t* src[4];
+                uint4 ra[4], rb[4];
+                uint32_t rr[4];
                 #pragma unroll
-                for (int q = 1; q < kMaxRanks; ++q) r += (q < p.R && f >= pre[q]) ? 1u : 0u;
-                const uint32_t i = f - pre[r];
-                if (own_ok && r == static_cast<uint32_t>(p.rank)) {
-                    const RowMeta om = c.own_meta[i];
-                    take(f, make_uint4(c.own_e[i], static_cast<uint32_t>(om.token), static_cast<uint32_t>(om.slot), __float_as_uint(om.weight)));
-                    continue;
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t f = f0 + u * kO;
+                    src[u] = nullptr;
+                    rr[u] = 0u;
+                    if (f >= total) continue;
+                    uint32_t r = 0;
+                    #pragma unroll
+                    for (int q = 1; q < kMaxRanks; ++q) r += (q < p.R && f >= pre[q]) ? 1u : 0u;
+                    const uint32_t i = f - pre[r];
+                    if (own_ok && r == static_cast<uint32_t>(p.rank)) {
+                        const RowMeta om = c.own_meta[i];
+                        take(f, make_uint4(c.own_e[i], static_cast<uint32_t>(om.token), static_cast<uint32_t>(om.slot), __float_as_uint(om.weight)));
+                        continue;
+                    }
+                    if (i < 32u && r < kSpecSources) continue;           // taken by the speculative read above
+                    src[u] = cx.rx_row(r, i) + 2u * (p.rx_row_bytes - 16);
+                    rr[u] = r;
+                    ra[u] = ld_volatile_v4(src[u]); rb[u] = ld_volatile_v4(src[u] + 16);
                 }
-                if (i < 32u && r < kSpecSources) continue;           // taken by the speculative read above
-                uint4 m = make_uint4(0u, 0u, 0u, 0u);
-                cx.ll_read(cx.rx_row(r, i) + 2u * (p.rx_row_bytes - 16), flag_rx, m, kErrWaitDispatchFlag, r);
-                take(f, m);
+                #pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    if (src[u] == nullptr) continue;
+                    uint4 m = ll_data(ra[u], rb[u]);
+                    if (!ll_valid(ra[u], rb[u], flag_rx)) cx.ll_read(src[u], flag_rx, m, kErrWaitDispatchFlag, rr[u]);
+                    take(f0 + u * kO, m);
+                }
             }
         }
     }

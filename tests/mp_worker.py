@@ -126,7 +126,7 @@ def main():
         # and the intermediate rows sit in that order
         vec = O.SF_VEC[fmt]
         mid, mid_sf = buf.l2_acts_payload().cpu(), buf.l2_acts_sf_payload().cpu()
-        base = 0
+        base, step = 0, buf.tile_image_rows() or 16        # rows of an expert start on a tile boundary (16 or 32 rows)
         for e, cnt in enumerate(ref.counts[rank].tolist()):
             if cnt == 0:
                 continue
@@ -136,7 +136,7 @@ def main():
             if any(O.rel_rmse(got[n], want[n]) > 0.05 for n in range(cnt)):
                 print(f'rank {rank} it {it}: expert {e} intermediate rows differ ({O.rel_rmse(got, want):.3f})', flush=True)
                 ok = False
-            base += (cnt + 15) // 16 * 16
+            base += (cnt + step - 1) // step * step
         torch.cuda.synchronize()
         dist.barrier()
     flag = torch.tensor([1 if ok else 0], device='cuda')

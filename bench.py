@@ -175,6 +175,8 @@ def main():
     ap.add_argument('--knobs', type=int, default=-1, help='kernel feature bit mask (mm_set_tuning), default: library default')
     ap.add_argument('--stages', type=int, default=0)
     ap.add_argument('--prefetch-experts', type=int, default=-1)
+    ap.add_argument('--skewed', action='store_true',
+                    help='with --from-hidden: sigmoid scores + Zipf(1.2) expert bias instead of softmax scores (hot experts)')
     ap.add_argument('--from-hidden', action='store_true',
                     help='time the single-kernel layer from bf16 hidden states (router + top-8 + quantisation fused in)')
     args = ap.parse_args()
@@ -262,6 +264,12 @@ def main():
             self.hidden_dev = self.hidden_src.clone()
             self.h_hidden = self.hidden_src.cpu().pin_memory()
             self.ws = torch.zeros(mm.fe_workspace_bytes(buf), dtype=torch.uint8, device='cuda')
+            # --skewed: sigmoid scores + Zipf(1.2) expert bias (a random permutation of 1 / rank^1.2 over all experts),
+            # renormalised top-8: hot experts receive many rows, most experts few or none
+            self.bias = None
+            if args.skewed:
+                gb = torch.Generator().manual_seed(11)
+                self.bias = (1.0 / torch.arange(1, num_experts + 1, dtype=torch.float32) ** 1.2)[torch.randperm(num_experts, generator=gb)].cuda()
             if world > 1:
                 dist.barrier()
             self.launch(stats=self.stats)
@@ -281,7 +289,7 @@ def main():
         def launch(self, y=None, host_inputs=None, stats=None):
             mm.mega_moe_from_hidden(self.y if y is None else y, self.hidden_dev, self.wr, l1, l2, buf, self.ws,
                                     cumulative_local_expert_recv_stats=stats, activation_clamp=10.0, fast_math=True,
-                                    x_global_scale=x_gs, l1_global_scale=gs1, l2_global_scale=gs2, mid_global_scale=mid_gs)
+                                    score_mode=1 if self.bias is not None else 0, expert_bias=self.bias, x_global_scale=x_gs, l1_global_scale=gs1, l2_global_scale=gs2, mid_global_scale=mid_gs)
 
     def timed(step_fn, prep_fn, steps, warm, tag):
         starts = [torch.cuda.Event(enable_timing=True) for _ in range(steps)]
@@ -432,11 +440,24 @@ def main():
                 for (e, t, s, _) in rows:
                     got[e].append((src, t, s))
             slots_ok = got == [list(v) for v in smap]
-        flags = torch.tensor([rel, -cos, 0.0 if counts_ok else 1.0, 0.0 if slots_ok else 1.0], device='cuda', dtype=torch.float64)
+        # from bf16 hidden states: the routing the kernel's frontend wrote against the oracle's router on the same tokens
+        # (bf16 logits in the kernel's summation order, top-8 by value then expert index): exact
+        top8_ok = True
+        if isinstance(case, HiddenCase) and case.T:
+            hx, wr = case.hidden_src.cpu(), case.wr.cpu()
+            mode = 'sigmoid_bias' if case.bias is not None else 'softmax'
+            idx_ref, _ = O.route_from_logits(O.router_logits_device_order(hx, wr), hx, TOPK, mode,
+                                             None if case.bias is None else case.bias.cpu())
+            top8_ok = bool(torch.equal(inputs[rank].topk_idx, idx_ref))
+        flags = torch.tensor([rel, -cos, 0.0 if counts_ok else 1.0, 0.0 if slots_ok else 1.0, 0.0 if top8_ok else 1.0],
+                             device='cuda', dtype=torch.float64)
         if world > 1:
             dist.all_reduce(flags, op=dist.ReduceOp.MAX)
-        rel, ncos, cbad, sbad = flags.tolist()
-        return {'rel_rmse_max_over_ranks': rel, 'cosine_min_over_ranks': -ncos, 'counts_exact': cbad == 0.0,
+        rel, ncos, cbad, sbad, tbad = flags.tolist()
+        extra = {'top8_exact': tbad == 0.0, 'rows_per_expert_max_this_rank': int(counts.max())} if isinstance(case, HiddenCase) else {}
+        if tbad != 0.0:
+            cbad = 1.0
+        return {**extra, 'rel_rmse_max_over_ranks': rel, 'cosine_min_over_ranks': -ncos, 'counts_exact': cbad == 0.0,
                 'slot_map_exact': sbad == 0.0, 'tolerance': {'rel_rmse': REL_RMSE_TOL, 'cosine': COS_TOL},
                 'shape': f'E={num_experts}, H={HIDDEN}, I={INTER}, top-{TOPK}, tokens per rank {T_all}, {fmt}',
                 'checker': 'CPU oracle (pure-torch quantised MoE), every rank its own experts, partial outputs all-reduced',
@@ -555,7 +576,7 @@ def main():
         check_status('steady-state region')
         ss_ev, ss_span = reduce_max([ss_ev, ss_span])
 
-    par = None if (args.no_parity or args.from_hidden) else parity(main_case)
+    par = None if args.no_parity else parity(main_case)
 
     sweep = None
     if not args.no_sweep and not args.from_hidden and world > 1 and not args.active_ranks and args.tokens_per_rank == 1:
@@ -579,6 +600,35 @@ def main():
                            'frac_of_hbm_roofline_span': alg / (sp * 1e-6) / 1e9 / peaks()[0],
                            'parity_ok': None if pr is None else pr['ok'],
                            'rel_rmse': None if pr is None else pr['rel_rmse_max_over_ranks']}
+
+    # one rank: larger batches (16 .. 128 tokens, forced-balanced over the 48 experts: every expert active, up to 22 rows
+    # per expert), on a buffer of their own sized for 128 tokens; same timing recipe, each case checked against the oracle
+    tokens_sweep = None
+    if not args.no_sweep and not args.from_hidden and world == 1 and args.tokens_per_rank == 1:
+        tokens_sweep = {}
+        saved = (buf, h_in, h_views)
+        buf = mm.get_symm_buffer_for_mega_moe(group, num_experts, 128, TOPK, HIDDEN, INTER, act_format=fmt, num_sms=args.num_sms)
+        h_in, h_views = buf.host_inputs()
+        try:
+            for t in (16, 32, 64, 128):
+                case = Case([t])
+                case.write_inputs()
+                ev = timed(case.launch, case.write_inputs, 30, 3, f'tokens_{t}')
+                sp, win, _ = device_spans(case, reps=8)
+                check_status(f'tokens sweep {t}')
+                pr = parity(case) if not args.no_parity else None
+                alg = max(case.active) * W.weight_bytes_per_expert(HIDDEN, INTER, fmt)
+                ev_mean = sum(ev) / len(ev)
+                tokens_sweep[f'T{t}'] = {'tokens': t, 'rows': t * TOPK, 'event_us': ev_mean, 'span_us': sp, 'active_experts': max(case.active),
+                                         'token_tile_rows': buf.tile_image_rows(),
+                                         'frac_of_hbm_roofline_events': alg / (ev_mean * 1e-6) / 1e9 / peaks()[0],
+                                         'frac_of_hbm_roofline_span': alg / (sp * 1e-6) / 1e9 / peaks()[0],
+                                         'parity_ok': None if pr is None else pr['ok'],
+                                         'rel_rmse': None if pr is None else pr['rel_rmse_max_over_ranks']}
+                if pr is not None and not pr['ok']:
+                    par = dict(par or {}, ok=False, failed_case=f'tokens sweep T{t}')
+        finally:
+            buf, h_in, h_views = saved
 
     fail = par is not None and not par['ok']
     if rank == 0:
@@ -629,6 +679,8 @@ def main():
                 'roofline': roofline, 'parity': par}
         if sweep is not None:
             line['m_sweep'] = sweep
+        if tokens_sweep is not None:
+            line['tokens_sweep'] = tokens_sweep
         if not args.no_cpu_baseline and n == 1:
             us, us_pre, cores = cpu_reference_us(main_tokens[0], fmt, 5)
             line['cpu_baseline'] = {'value': us, 'unit': 'us', 'cores': cores, 'kind': 'port',

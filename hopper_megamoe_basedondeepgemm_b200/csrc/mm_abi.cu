@@ -346,9 +346,13 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
     return MM_OK;
 }
 
-template <int kVec, bool kUmma, bool kFe = false, bool kA8 = false>
+static bool wants_tile_images(const mm::KParams& p) {
+    return (p.knobs & mm::kKnobTileImages) != 0u && p.nstage_wide >= 3u && static_cast<long long>(p.T) * p.topk > mm::kTileTokens;
+}
+
+template <int kVec, bool kUmma, bool kFe = false, bool kA8 = false, bool kTiles = false>
 static int launch_variant(const mm::KParams& p, int grid, size_t smem_bytes, cudaStream_t stream) {
-    auto kern = mm::mega_moe_kernel<kVec, kUmma, kFe, kA8>;
+    auto kern = mm::mega_moe_kernel<kVec, kUmma, kFe, kA8, kTiles>;
     // the opt-in shared-memory size is a per-device function attribute: set once per (variant, device), raised on demand
     static int attr_bytes[64] = {};
     int dev = 0;
@@ -381,6 +385,12 @@ int mm_mega_moe_launch(const mm_config_t* cfg, const mm_launch_args_t* a, void* 
 #else
     if (!umma) return MM_ERR_UNSUPPORTED;
 #endif
+    // Two builds of the tensor-core kernel for the 4-bit activation formats: one that can work from tile images (launches
+    // with more than 16 received rows) and one without that code, whose start-up path is shorter. Either is correct for
+    // any input; a rank with at most 16 routed rows of its own takes the lean one (the decode-size launches).
+    if (wants_tile_images(p))
+        return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, true, false, false, true>(p, grid, smem_bytes, s)
+                                               : launch_variant<16, true, false, false, true>(p, grid, smem_bytes, s);
     return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, true>(p, grid, smem_bytes, s) : launch_variant<16, true>(p, grid, smem_bytes, s);
 }
 
@@ -557,6 +567,9 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
                                        : launch_variant<32, true, true, true>(p, grid, smem_bytes, s);
     if (fe->num_tokens == 0) return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, true>(p, grid, smem_bytes, s)
                                                                     : launch_variant<16, true>(p, grid, smem_bytes, s);
+    if (wants_tile_images(p))
+        return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, true, true, false, true>(p, grid, smem_bytes, s)
+                                               : launch_variant<16, true, true, false, true>(p, grid, smem_bytes, s);
     return cfg->act_format == MM_FMT_MXFP4 ? launch_variant<32, true, true>(p, grid, smem_bytes, s)
                                            : launch_variant<16, true, true>(p, grid, smem_bytes, s);
 }

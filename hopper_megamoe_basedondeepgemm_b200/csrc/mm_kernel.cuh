@@ -222,13 +222,6 @@ struct Ctx {
         return true;
     }
     // every lane waits; the warp agrees on the outcome
-    // (timed variant: the cycles spent in the wait are added to `acc`)
-    __device__ __forceinline__ bool warp_wait_t(uint64_t* bar, uint32_t parity, uint32_t code, long long& acc) const {
-        const long long t0 = clock64();
-        const bool ok = warp_wait(bar, parity, code);
-        acc += clock64() - t0;
-        return ok;
-    }
     __device__ __forceinline__ void wait_total(int slot, long long cycles) const {
         if ((p.knobs & kKnobWaitProfile) != 0u)
             reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmPhase)[blockIdx.x * kSmPhaseSlots + slot] = static_cast<unsigned long long>(cycles);
@@ -295,7 +288,6 @@ __device__ __forceinline__ float sf_value(uint32_t byte) {
 __device__ void role_loader(const Ctx& cx) {
     const KParams& p = cx.p; Ctl& c = cx.c;
     uint32_t it = 0, s = 0, ph = 0;                              // units issued; ring stage and its phase bit
-    long long w_empty = 0;
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
@@ -305,7 +297,7 @@ __device__ void role_loader(const Ctx& cx) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
-            if (!cx.warp_wait_t(&c.empty[s], ph ^ 1u, kErrWaitEmpty, w_empty)) return;
+            if (!cx.warp_wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
             if (elect_one()) {
                 mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
                 bulk_g2s(cx.smem + static_cast<size_t>(s) * p.unit_bytes, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
@@ -316,7 +308,6 @@ __device__ void role_loader(const Ctx& cx) {
             if (++s == static_cast<uint32_t>(p.nstage)) { s = 0; ph ^= 1u; }
         }
     }
-    if ((threadIdx.x & 31u) == 0u) cx.wait_total(16, w_empty);
 }
 
 // ============================================================================================= MMA issuer
@@ -332,9 +323,6 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
     const uint32_t acc_col = 0, sfa_col = 32, sfb_col = 64;     // accumulators 2 x 16, weight scales 2 x 16, token scales 2 x 16
     uint32_t it = 0, s = 0, ph = 0;                             // units consumed so far; ring stage and its phase bit
     unsigned long long t_landed = 0ull;                         // when the latest unit was found in shared memory
-    long long w_acts = 0, w_tmem = 0, w_full = 0;
-    const long long t_role = clock64();
-    const unsigned long long ns_role = globaltimer_ns();
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
@@ -345,8 +333,8 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         const uint32_t tis = (!kA8 && c.decode != 0u) ? ti - c.n1_tasks : ti;
         const uint32_t ab = c.nab == 2u ? (tis & 1u) : 0u, use_a = c.nab == 2u ? (tis >> 1) & 1u : (tis & 1u);
         if (shared_tile) { if (!cx.warp_wait(&c.tile_full, 0u, kErrWaitActsFull)) return; }
-        else if (!cx.warp_wait_t(&c.acts_full[ab], use_a, kErrWaitActsFull, w_acts)) return;
-        if (!cx.warp_wait_t(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty, w_tmem)) return;
+        else if (!cx.warp_wait(&c.acts_full[ab], use_a, kErrWaitActsFull)) return;
+        if (!cx.warp_wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty)) return;
         tc_fence_after();
         const uint32_t act = shared_tile ? smem_u32(cx.tok_region()) : smem_u32(cx.smem + p.sm_act + ab * c.act_stride);
         const uint32_t asf_base = shared_tile ? smem_u32(cx.tile_asf()) : smem_u32(cx.smem + p.sm_asf + ab * p.asf_bytes);
@@ -354,12 +342,12 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
             uint64_t* ready = kA8 ? &c.xfull[it & 1u] : &c.full[s];
-            if (!cx.warp_wait_t(ready, kA8 ? (it >> 1) & 1u : ph, kErrWaitFull, w_full)) return;
+            if (!cx.warp_wait(ready, kA8 ? (it >> 1) & 1u : ph, kErrWaitFull)) return;
             tc_fence_after();
             t_landed = globaltimer_ns();
             if (lane == 0) {
                 if (it == 0u) cx.sm_phase(kSmFirstLanded);
-                if (it < 15u && (p.knobs & kKnobWaitProfile) == 0u) cx.sm_phase(16 + static_cast<int>(it));
+                if (it < 15u) cx.sm_phase(16 + static_cast<int>(it));
             }
             if (elect_one()) {
               {
@@ -405,10 +393,6 @@ __device__ void role_mma(const Ctx& cx, uint32_t lane) {
         __syncwarp();
     }
     if (lane == 0 && t_landed != 0ull) cx.stamp_max(kStampLastWeight, t_landed);
-    if (lane == 0) {
-        cx.wait_total(17, w_acts); cx.wait_total(18, w_tmem); cx.wait_total(19, w_full); cx.wait_total(20, clock64() - t_role);
-        cx.wait_total(25, static_cast<long long>(globaltimer_ns() - ns_role));
-    }
 }
 
 // ============================================================================================= weight widener (FP8 variant)
@@ -686,8 +670,6 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
     uint8_t* otile = cx.smem + p.sm_otile;
     float* vt = reinterpret_cast<float*>(cx.smem + p.sm_vt) + row;      // this thread's accumulators: vt[n * 128], token n
     uint32_t it = 0;
-    long long w_tfull = 0, w_l1 = 0, w_l2 = 0;
-    const long long t_role = clock64();
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
@@ -697,10 +679,8 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
         // ---- accumulators of the valid tokens -> shared memory (the loops below run over the valid tokens only)
         bool ok;
         uint32_t nv = 0;
-        long long t_work = 0;
         if constexpr (kUmma) {
-            ok = cx.warp_wait_t(&c.tmem_full[acc], use, kErrWaitTmemFull, w_tfull);
-            t_work = clock64();
+            ok = cx.warp_wait(&c.tmem_full[acc], use, kErrWaitTmemFull);
             // decode mode, L1 task: nobody staged anything for this task (its tokens sit in the launch's shared tile). The
             // first epilogue warp lists the expert's rows itself, in receive order: their records, how many there are, and
             // how many rows of experts with a smaller index precede them in the tile (= the expert's first column).
@@ -894,9 +874,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
             if (ti == 0u) cx.sm_phase(kSmFirstEpilogue);
             if (type == 0u) cx.sm_phase(kSmLastL1Epilogue);
         }
-        if constexpr (kUmma) { if (type == 0u) w_l1 += clock64() - t_work; else w_l2 += clock64() - t_work; }
     }
-    if (etid == 0u) { cx.wait_total(21, w_tfull); cx.wait_total(22, clock64() - t_role); cx.wait_total(23, w_l1); cx.wait_total(24, w_l2); }
 }
 
 // ============================================================================================= roles with tile images
@@ -908,11 +886,45 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
 // unit, whatever the weight flood does to small loads. A token tile has `c.tw` rows: 16, or 32 when an expert has
 // more than 16 rows (the block-scaled MMA takes the same time for 16 and 32 columns: an expert's weights stream once
 // for up to 32 rows).
+// The launch parameters the tile-image roles use, handed to them by value (in registers).
+struct TileP {
+    uint32_t unit_bytes, wide_stage_bytes, nstage_wide, tile_capacity, token_tile_bytes, mid_tile_bytes, sm_vt, knobs;
+    int n1_tiles, n2_tiles, k1_units, k2_units, topk, H, has_clamp, fast_math, cnt_per_phase;
+    float clamp, l1_scale, l2_scale, mid_gs;
+    long long off_mid_tiles, off_token_tiles, off_arrive, off_red, off_cnt, off_comb;
+    const uint8_t* w1; const uint8_t* w2;
+};
+__device__ __forceinline__ TileP make_tile_params(const KParams& p) {
+    TileP t;
+    t.unit_bytes = p.unit_bytes; t.wide_stage_bytes = p.wide_stage_bytes; t.nstage_wide = p.nstage_wide; t.tile_capacity = p.tile_capacity;
+    t.token_tile_bytes = p.token_tile_bytes; t.mid_tile_bytes = p.mid_tile_bytes; t.sm_vt = p.sm_vt; t.knobs = p.knobs;
+    t.n1_tiles = p.n1_tiles; t.n2_tiles = p.n2_tiles; t.k1_units = p.k1_units; t.k2_units = p.k2_units; t.topk = p.topk; t.H = p.H;
+    t.has_clamp = p.has_clamp; t.fast_math = p.fast_math; t.cnt_per_phase = p.cnt_per_phase;
+    t.clamp = p.clamp; t.l1_scale = p.l1_scale; t.l2_scale = p.l2_scale; t.mid_gs = p.mid_gs;
+    t.off_mid_tiles = p.off_mid_tiles; t.off_token_tiles = p.off_token_tiles; t.off_arrive = p.off_arrive; t.off_red = p.off_red;
+    t.off_cnt = p.off_cnt; t.off_comb = p.off_comb; t.w1 = p.w1; t.w2 = p.w2;
+    return t;
+}
+// the roles' own wait (first probe inline, timed only when the wait profile is on) and profile helpers
+struct TileCtx {
+    const Ctx& cx; bool prof;
+    __device__ __forceinline__ long long clk() const { return prof ? clock64() : 0ll; }
+    __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, uint32_t code, long long& acc) const {
+        if (!prof) return cx.warp_wait(bar, parity, code);
+        const long long t0 = clock64();
+        const bool ok = cx.warp_wait(bar, parity, code);
+        acc += clock64() - t0;
+        return ok;
+    }
+    __device__ __forceinline__ void total(int slot, long long cycles) const { if (prof) cx.wait_total(slot, cycles); }
+};
 __device__ __forceinline__ uint32_t tile_record_bytes(uint32_t tw, uint32_t planes) { return tw * 128u + planes * tw * 16u; }
 
 // Weight units of this SM's tasks into the ring of wide stages (the same stream as `role_loader`, wider stage stride).
-__device__ void role_loader_tiles(const Ctx& cx) {
-    const KParams& p = cx.p; Ctl& c = cx.c;
+__device__ void role_loader_tiles(const Ctx& cx, const TileP p) {
+    Ctl& c = cx.c;
+    uint8_t* const smem = cx.smem;
+    const TileCtx tc{cx, (p.knobs & kKnobWaitProfile) != 0u};
     uint32_t it = 0, s = 0, ph = 0;
     long long w_empty = 0;
     #pragma unroll 1
@@ -924,10 +936,10 @@ __device__ void role_loader_tiles(const Ctx& cx) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
-            if (!cx.warp_wait_t(&c.empty[s], ph ^ 1u, kErrWaitEmpty, w_empty)) return;
+            if (!tc.wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty, w_empty)) return;
             if (elect_one()) {
                 mbar_arrive_expect_tx(&c.full[s], p.unit_bytes);
-                bulk_g2s(cx.smem + static_cast<size_t>(s) * p.wide_stage_bytes, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
+                bulk_g2s(smem + static_cast<size_t>(s) * p.wide_stage_bytes, src + static_cast<size_t>(u) * p.unit_bytes, p.unit_bytes, &c.full[s]);
                 c.issued = it + 1u;
                 if (it == 0u) { cx.note_first_weight_request(); cx.sm_phase(kSmFirstIssue); }
             }
@@ -935,17 +947,19 @@ __device__ void role_loader_tiles(const Ctx& cx) {
             if (++s == p.nstage_wide) { s = 0; ph ^= 1u; }
         }
     }
-    if ((threadIdx.x & 31u) == 0u) cx.wait_total(16, w_empty);
+    if ((threadIdx.x & 31u) == 0u) tc.total(16, w_empty);
 }
 
 // The token side of the same stages, by a warp of its own: per task the row records of its tile (for the epilogue), per
 // unit the tile's record. This warp waits for tiles that are not complete yet; the weight loader never does, so the
 // weights of the following units keep coming while a tile is awaited.
-__device__ void role_record_loader(const Ctx& cx, uint32_t planes) {
-    const KParams& p = cx.p; Ctl& c = cx.c;
+__device__ void role_record_loader(const Ctx& cx, const TileP p, uint32_t planes) {
+    Ctl& c = cx.c;
+    uint8_t* const smem = cx.smem; uint8_t* const buf = cx.buf; const uint32_t par = cx.par;
+    const TileCtx tc{cx, (p.knobs & kKnobWaitProfile) != 0u};
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t tw = c.tw, rec = tile_record_bytes(tw, planes);
-    const uint32_t* arrive = reinterpret_cast<const uint32_t*>(cx.buf + p.off_arrive) + cx.par * 2u * p.tile_capacity;
+    const uint32_t* arrive = reinterpret_cast<const uint32_t*>(buf + p.off_arrive) + par * 2u * p.tile_capacity;
     uint32_t s = 0, ph = 0;
     long long w_tiles = 0;
     // Whether a task's tile is complete (L1: its received rows, L2: the outputs of all L1 weight tiles, counted into the
@@ -970,10 +984,10 @@ __device__ void role_record_loader(const Ctx& cx, uint32_t planes) {
         const uint32_t t = c.tasks[ti];
         const uint32_t type = t >> 28, e = (t >> 20) & 0xFF, mt = (t >> 8) & 0xFFF;
         const uint32_t tile = udiv_small(c.mid_base[e], tw) + mt;
-        const uint8_t* head = cx.buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes;
-        const uint8_t* img = type ? cx.buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes : head + kWideTokens * 16u;
+        const uint8_t* head = buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes;
+        const uint8_t* img = type ? buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes : head + kWideTokens * 16u;
         if (!(ti - win_base < 32u && ((win_ready >> (ti - win_base)) & 1u) != 0u)) {
-            const long long t0 = clock64();
+            const long long t0 = tc.clk();
             uint32_t spins = 0;
             for (;;) {
                 refresh(ti);
@@ -983,7 +997,7 @@ __device__ void role_record_loader(const Ctx& cx, uint32_t planes) {
                     if (cx.expired()) { cx.fail(type ? kErrWaitL1Done : kErrWaitDispatchFlag, e); return; }
                 }
             }
-            w_tiles += clock64() - t0;
+            w_tiles += tc.clk() - t0;
         }
         {
             // the rows' records (source rank, token, slot, top-k weight) of the task's tile, for its epilogue: slot ti mod 4
@@ -1001,18 +1015,20 @@ __device__ void role_record_loader(const Ctx& cx, uint32_t planes) {
             if (!cx.warp_wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
             if (elect_one()) {
                 mbar_arrive_expect_tx(&c.rfull[s], rec);
-                bulk_g2s(cx.smem + static_cast<size_t>(s) * p.wide_stage_bytes + p.unit_bytes, img + static_cast<size_t>(u) * rec, rec, &c.rfull[s]);
+                bulk_g2s(smem + static_cast<size_t>(s) * p.wide_stage_bytes + p.unit_bytes, img + static_cast<size_t>(u) * rec, rec, &c.rfull[s]);
             }
             __syncwarp();
             if (++s == p.nstage_wide) { s = 0; ph ^= 1u; }
         }
     }
-    if (lane == 0u) cx.wait_total(17, w_tiles);
+    if (lane == 0u) tc.total(17, w_tiles);
 }
 
 template <int kVec>
-__device__ void role_mma_tiles(const Ctx& cx, uint32_t lane) {
-    const KParams& p = cx.p; Ctl& c = cx.c;
+__device__ void role_mma_tiles(const Ctx& cx, const TileP p, uint32_t lane) {
+    Ctl& c = cx.c;
+    uint8_t* const smem = cx.smem;
+    const TileCtx tc{cx, (p.knobs & kKnobWaitProfile) != 0u};
     constexpr uint32_t kPlanes = kUnitK / (4 * kVec);
     const uint32_t tw = c.tw;
     const uint32_t idesc0 = idesc_block_scaled(kFmtMxf4E2M1, kFmtMxf4E2M1, kTileRows, tw, kVec == 32 ? 1u : 0u);
@@ -1021,23 +1037,23 @@ __device__ void role_mma_tiles(const Ctx& cx, uint32_t lane) {
     uint32_t it = 0, s = 0, ph = 0;
     unsigned long long t_landed = 0ull;
     long long w_tmem = 0, w_full = 0, w_tok = 0;
-    const long long t_role = clock64();
-    const unsigned long long ns_role = globaltimer_ns();
+    const long long t_role = tc.clk();
+    const unsigned long long ns_role = tc.prof ? globaltimer_ns() : 0ull;
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         const uint32_t acc = ti & 1u, use = (ti >> 1) & 1u;
-        if (!cx.warp_wait_t(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty, w_tmem)) return;
+        if (!tc.wait(&c.tmem_empty[acc], use ^ 1u, kErrWaitTmemEmpty, w_tmem)) return;
         tc_fence_after();
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
-            if (!cx.warp_wait_t(&c.full[s], ph, kErrWaitFull, w_full)) return;
-            if (!cx.warp_wait_t(&c.rfull[s], ph, kErrWaitActsFull, w_tok)) return;
+            if (!tc.wait(&c.full[s], ph, kErrWaitFull, w_full)) return;
+            if (!tc.wait(&c.rfull[s], ph, kErrWaitActsFull, w_tok)) return;
             tc_fence_after();
             t_landed = globaltimer_ns();
             if (lane == 0 && it == 0u) cx.sm_phase(kSmFirstLanded);
             if (elect_one()) {
-                const uint32_t wsm = smem_u32(cx.smem + static_cast<size_t>(s) * p.wide_stage_bytes);
+                const uint32_t wsm = smem_u32(smem + static_cast<size_t>(s) * p.wide_stage_bytes);
                 const uint32_t wsf = wsm + static_cast<uint32_t>(kUnitWBytes);
                 const uint32_t tok = wsm + p.unit_bytes, tsf = tok + tw * 128u;
                 const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u, sfb = tm + sfb_col + (it & 1u) * 16u;
@@ -1069,22 +1085,24 @@ __device__ void role_mma_tiles(const Ctx& cx, uint32_t lane) {
     }
     if (lane == 0 && t_landed != 0ull) cx.stamp_max(kStampLastWeight, t_landed);
     if (lane == 0) {
-        cx.wait_total(18, w_tmem); cx.wait_total(19, w_full); cx.wait_total(20, clock64() - t_role);
-        cx.wait_total(25, static_cast<long long>(globaltimer_ns() - ns_role)); cx.wait_total(26, w_tok);
+        tc.total(18, w_tmem); tc.total(19, w_full); tc.total(20, tc.clk() - t_role);
+        if (tc.prof) tc.total(25, static_cast<long long>(globaltimer_ns() - ns_role)); tc.total(26, w_tok);
     }
 }
 
 template <int kVec>
-__device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
-    const KParams& p = cx.p; Ctl& c = cx.c;
+__device__ void role_epilogue_tiles(const Ctx& cx, const TileP p, uint32_t etid) {
+    Ctl& c = cx.c;
+    uint8_t* const smem = cx.smem; uint8_t* const buf = cx.buf; const uint32_t par = cx.par;
+    const TileCtx tc{cx, (p.knobs & kKnobWaitProfile) != 0u};
     constexpr uint32_t kPlanes = kUnitK / (4 * kVec);
     const uint32_t ew = etid >> 5, lane = etid & 31u, row = etid, tw = c.tw;
     const uint32_t rec = tile_record_bytes(tw, kPlanes);
-    float* vt_all = reinterpret_cast<float*>(cx.smem + p.sm_vt);
+    float* vt_all = reinterpret_cast<float*>(smem + p.sm_vt);
     float* vt = vt_all + row;      // this thread's accumulators: vt[n * kVtStride], token n
-    uint32_t* arrive_mid = reinterpret_cast<uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + 1u) * p.tile_capacity;
+    uint32_t* arrive_mid = reinterpret_cast<uint32_t*>(buf + p.off_arrive) + (par * 2u + 1u) * p.tile_capacity;
     long long w_tfull = 0, w_l1 = 0, w_l2 = 0;
-    const long long t_role = clock64();
+    const long long t_role = tc.clk();
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
@@ -1094,8 +1112,8 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
         const uint32_t left = c.exp_count[e] - mt * tw, nv = left < tw ? left : tw;
         // the rows' records (source rank, token, slot, top-k weight): the loader copied the tile's header into slot ti mod 4
         bool ok = cx.warp_wait(&c.meta_full[ti & 3u], (ti >> 2) & 1u, kErrWaitActsFull);
-        ok = ok && cx.warp_wait_t(&c.tmem_full[acc], use, kErrWaitTmemFull, w_tfull);
-        const long long t_work = clock64();
+        ok = ok && tc.wait(&c.tmem_full[acc], use, kErrWaitTmemFull, w_tfull);
+        const long long t_work = tc.clk();
         if (ok) {
             tc_fence_after();
             if (ti == 0u && etid == 0u) cx.sm_phase(kSmFirstMmaDone);
@@ -1121,14 +1139,14 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
             // this SM covered only part of the tile's K range: park the partial sums, count in, and let the last
             // contributor add the parts in SM order (a fixed order: the result does not depend on who arrives last)
             const uint32_t tix = c.tasks3[ti], cfirst = c.tasks2[ti] >> 24;
-            float* red = reinterpret_cast<float*>(cx.buf + p.off_red);
+            float* red = reinterpret_cast<float*>(buf + p.off_red);
             constexpr size_t kSlot = 2u * kTileTokens * kTileRows;           // floats: room for 32 rows
             float* mine = red + (static_cast<size_t>(blockIdx.x) * 2u + type) * kSlot + row;
             #pragma unroll 1
             for (uint32_t n = 0; n < nv; ++n) mine[n * kTileRows] = vt[n * kVtStride];
             bar_sync(kBarEpi, kNumEpiThreads);
             if (etid == 0) {
-                uint32_t* cnt = reinterpret_cast<uint32_t*>(cx.buf + p.off_cnt) + type * p.cnt_per_phase + tix;
+                uint32_t* cnt = reinterpret_cast<uint32_t*>(buf + p.off_cnt) + type * p.cnt_per_phase + tix;
                 const uint32_t old = atom_acq_rel_gpu_add(cnt, 1u);
                 if (old == np - 1u) *cnt = 0u;
                 c.red_old = old;
@@ -1225,7 +1243,7 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
                 // into the intermediate tile's image: the chunks at their swizzled place in the record of their K unit, the
                 // scale bytes into that record's slots; then one count into the tile's arrival word (thread 0's release
                 // covers the stores the barrier ordered before it)
-                uint8_t* img = cx.buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes;
+                uint8_t* img = buf + p.off_mid_tiles + static_cast<size_t>(tile) * p.mid_tile_bytes;
                 if (live && q < 2u) {
                     const uint32_t* w = q == 0u ? w01 : w23;
                     const uint4 val = make_uint4((w[0] & 0xFFFFu) | (w[1] << 16), (w[2] & 0xFFFFu) | (w[3] << 16),
@@ -1245,7 +1263,7 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
                     const uint32_t head = c.rel_head;
                     if (head - *reinterpret_cast<volatile uint32_t*>(&c.rel_tail) < kRelQueue) {
                         c.rel_q[head % kRelQueue] = tile;
-                        c.rel_t[head % kRelQueue] = clock64();
+                        c.rel_t[head % kRelQueue] = tc.clk();
                         __threadfence_block();
                         *reinterpret_cast<volatile uint32_t*>(&c.rel_head) = head + 1u;
                     } else {
@@ -1268,7 +1286,7 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
                            (static_cast<uint32_t>(__bfloat16_as_ushort(__float2bfloat16_rn(x1 * p.l2_scale))) << 16);
                 };
                 const uint4 val = make_uint4(pack(lo.x, lo.y), pack(lo.z, lo.w), pack(hi.x, hi.y), pack(hi.z, hi.w));
-                uint8_t* dst = p.peer[meta[n].src] + p.off_comb +
+                uint8_t* dst = cx.p.peer[meta[n].src] + p.off_comb +
                     ((static_cast<size_t>(meta[n].token) * p.topk + meta[n].slot) * p.H + j * kTileRows) * 4u + ch * 32u;
                 st_ll_half(dst, val, c.epoch + 1u, idx & 1u);
             }
@@ -1278,7 +1296,7 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
             if (ti == 0u) cx.sm_phase(kSmFirstEpilogue);
             if (type == 0u) cx.sm_phase(kSmLastL1Epilogue);
         }
-        if (type == 0u) w_l1 += clock64() - t_work; else w_l2 += clock64() - t_work;
+        if (type == 0u) w_l1 += tc.clk() - t_work; else w_l2 += tc.clk() - t_work;
     }
     if (etid == 0u) {
         // the releasing warp ends when it finds this entry
@@ -1287,17 +1305,19 @@ __device__ void role_epilogue_tiles(const Ctx& cx, uint32_t etid) {
         c.rel_q[head % kRelQueue] = 0xFFFFFFFFu;
         __threadfence_block();
         *reinterpret_cast<volatile uint32_t*>(&c.rel_head) = head + 1u;
-        cx.wait_total(21, w_tfull); cx.wait_total(22, clock64() - t_role); cx.wait_total(23, w_l1); cx.wait_total(24, w_l2);
+        tc.total(21, w_tfull); tc.total(22, tc.clk() - t_role); tc.total(23, w_l1); tc.total(24, w_l2);
     }
 }
 
 // The releasing warp: counts finished intermediate tiles in for the L1 epilogue (queue of tile numbers in shared memory,
 // written by the epilogue's first thread after the barrier that follows the tile's stores). The release orders those
 // stores, which the queue hand-off made visible to this warp, before the count.
-__device__ void role_releaser(const Ctx& cx) {
-    const KParams& p = cx.p; Ctl& c = cx.c;
+__device__ void role_releaser(const Ctx& cx, const TileP p) {
+    Ctl& c = cx.c;
+    uint8_t* const buf = cx.buf; const uint32_t par = cx.par;
+    const TileCtx tc{cx, (p.knobs & kKnobWaitProfile) != 0u};
     const uint32_t lane = threadIdx.x & 31u;
-    uint32_t* arrive_mid = reinterpret_cast<uint32_t*>(cx.buf + p.off_arrive) + (cx.par * 2u + 1u) * p.tile_capacity;
+    uint32_t* arrive_mid = reinterpret_cast<uint32_t*>(buf + p.off_arrive) + (par * 2u + 1u) * p.tile_capacity;
     uint32_t tail = 0, spins = 0;
     long long lat_sum = 0, lat_max = 0, busy = 0;
     // (the whole warp stays in this loop: lanes that left it would spin in the combine and take the issue slots of the lane that works here)
@@ -1311,10 +1331,10 @@ __device__ void role_releaser(const Ctx& cx) {
                 ++tail;
                 *reinterpret_cast<volatile uint32_t*>(&c.rel_tail) = tail;
                 if (tile != 0xFFFFFFFFu) {
-                    const long long t0 = clock64();
+                    const long long t0 = tc.clk();
                     fence_proxy_async_all();
                     red_release_gpu_add(arrive_mid + tile, 1u);
-                    const long long t1 = clock64();
+                    const long long t1 = tc.clk();
                     busy += t1 - t0; lat_sum += t1 - t_q; lat_max = lat_max > t1 - t_q ? lat_max : t1 - t_q;
                 }
             } else if ((++spins & 0xFFFu) == 0u && (cx.aborted() || cx.expired())) {
@@ -1324,7 +1344,131 @@ __device__ void role_releaser(const Ctx& cx) {
         tile = __shfl_sync(0xffffffffu, tile, 0);
         if (tile == 0xFFFFFFFFu) break;
     }
-    if (lane == 0) { cx.wait_total(27, lat_sum); cx.wait_total(28, lat_max); cx.wait_total(29, busy); }
+    if (lane == 0) { tc.total(27, lat_sum); tc.total(28, lat_max); tc.total(29, busy); }
+}
+
+// Out of line on purpose: launches with at most 16 received rows never run it, and inline it would sit in the middle of
+// the start-up code they do run.
+// ---- more than 16 received rows: the rows are sorted into tile images in global memory, one image per token tile
+//      (16 or 32 rows) of an expert: the rows' records, then per streamed K unit the unit's 128 B of every row in the
+//      tensor core's swizzled order and the unit's scale-word slots. Row f belongs to SM f mod G; one warp per row.
+//      Every finished row counts into its tile's arrival word.
+template <int kVec>
+__device__ __noinline__ void sort_rows_into_tiles(const Ctx& cx, const uint8_t* inp, uint32_t total, bool own_ok, uint32_t flag_rx, uint32_t warp, uint32_t lane) {
+    const KParams& p = cx.p; Ctl& c = cx.c;
+    uint8_t* buf = cx.buf;
+    const uint32_t bid = blockIdx.x, G = gridDim.x, par = cx.par;
+    const uint32_t el = p.e_local;
+    constexpr uint32_t kPlanes = kUnitK / (4 * kVec);
+    // first tile of every expert: running sum of ceil(rows / tile rows), expert-major (the schedule derives the same numbers)
+    const uint32_t cnt0 = lane < el ? c.exp_count[lane] : 0u, cnt1 = lane + 32 < el ? c.exp_count[lane + 32] : 0u;
+    const uint32_t tw = __any_sync(0xffffffffu, cnt0 > kTileTokens || cnt1 > kTileTokens) ? kWideTokens : static_cast<uint32_t>(kTileTokens);
+    const uint32_t rec = tile_record_bytes(tw, kPlanes);
+    const uint32_t m0 = udiv_small(cnt0 + tw - 1u, tw), m1 = udiv_small(cnt1 + tw - 1u, tw);
+    uint32_t i0 = m0, i1 = m1;
+    #pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t v0 = __shfl_up_sync(0xffffffffu, i0, o), v1 = __shfl_up_sync(0xffffffffu, i1, o);
+        if (static_cast<int>(lane) >= o) { i0 += v0; i1 += v1; }
+    }
+    const uint32_t tbase0 = i0 - m0, tbase1 = __shfl_sync(0xffffffffu, i0, 31) + i1 - m1;
+    const uint32_t per_row = p.rc_row_bytes / 16u, xq = p.x_row_bytes / 16u;
+    uint32_t* arrive = reinterpret_cast<uint32_t*>(buf + p.off_arrive) + par * 2u * p.tile_capacity;
+    #pragma unroll 1
+    for (uint32_t f = bid + (warp - 2u) * G; f < total; f += kFillWarps * G) {
+        const uint32_t e = c.meta_e[f];
+        // position among the expert's rows = rows of the same expert received before this one
+        uint32_t n = 0;
+        #pragma unroll 1
+        for (uint32_t base = 0; base < f; base += 128) {
+            const uint32_t idx = base + lane * 4u;
+            const uint32_t w = *reinterpret_cast<const uint32_t*>(c.meta_e + idx);
+            #pragma unroll
+            for (uint32_t b = 0; b < 4; ++b) n += (idx + b < f && ((w >> (8u * b)) & 0xFFu) == e) ? 1u : 0u;
+        }
+        n = __reduce_add_sync(0xffffffffu, n);
+        const uint32_t tb0 = __shfl_sync(0xffffffffu, tbase0, e & 31u), tb1 = __shfl_sync(0xffffffffu, tbase1, e & 31u);
+        const uint32_t tile = (e < 32u ? tb0 : tb1) + udiv_small(n, tw), pos = n - udiv_small(n, tw) * tw;
+        uint32_t r = 0;
+        while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
+        const uint32_t i = f - c.rx_prefix[r];
+        const bool own = own_ok && r == static_cast<uint32_t>(p.rank);
+        const uint8_t* xs = nullptr;
+        const uint8_t* sf = nullptr;
+        const uint8_t* row_src = nullptr;
+        if (own) {
+            const uint32_t tok = static_cast<uint32_t>(c.own_meta[i].token);
+            xs = inp + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
+            sf = inp + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
+        } else {
+            row_src = cx.rx_row(r, i);
+        }
+        uint8_t* head = buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes;
+        uint8_t* img = head + kWideTokens * 16u;
+        bool bad = tile >= p.tile_capacity;
+        // (chunk `per_row` of a received row is its record {expert, token, slot, top-k weight}: it becomes the row's
+        //  record {source rank, token, slot, weight} in the tile's header; an own row's record comes from the scout's list)
+        if (own && lane == 0 && !bad) {
+            const RowMeta m = c.own_meta[i];
+            *reinterpret_cast<uint4*>(head + pos * 16u) = make_uint4(r, static_cast<uint32_t>(m.token), static_cast<uint32_t>(m.slot), __float_as_uint(m.weight));
+        }
+        const uint32_t nread = own ? per_row : per_row + 1u;
+        #pragma unroll 1
+        for (uint32_t base = lane; base < nread && !bad; base += 4 * 32) {
+            uint4 v[4];
+            if (own) {
+                #pragma unroll
+                for (uint32_t u = 0; u < 4; ++u) {
+                    const uint32_t ci = base + u * 32;
+                    if (ci < xq) v[u] = ld_cg_v4(xs + ci * 16u);
+                    else if (ci < per_row) v[u] = ld_cg_v4(sf + (ci - xq) * 16u);
+                }
+            } else {
+                uint32_t spins = 0;
+                bool ok;
+                do {
+                    ok = true;
+                    #pragma unroll
+                    for (uint32_t u = 0; u < 4; ++u) {
+                        const uint32_t ci = base + u * 32;
+                        if (ci < nread) {
+                            const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
+                            ok = ok && ll_valid(a, b, flag_rx);
+                            v[u] = ll_data(a, b);
+                        }
+                    }
+                    if (!ok && (++spins & 0x3Fu) == 0u) {
+                        if (cx.aborted()) bad = true;
+                        else if (cx.expired()) { cx.fail(kErrWaitDispatchFlag, r); bad = true; }
+                    }
+                } while (!ok && !bad);
+            }
+            #pragma unroll
+            for (uint32_t u = 0; u < 4; ++u) {
+                const uint32_t ci = base + u * 32;
+                if (ci >= nread || bad) continue;
+                if (ci == per_row) {
+                    *reinterpret_cast<uint4*>(head + pos * 16u) = make_uint4(r, v[u].y, v[u].z, v[u].w);
+                } else if (ci < xq) {
+                    *reinterpret_cast<uint4*>(img + (ci >> 3) * rec + sw128_off(pos, ci & 7u)) = v[u];
+                } else {
+                    // four scale words g .. g + 3 of the row: word g belongs to K unit g / planes, plane g % planes
+                    const uint32_t g = (ci - xq) * 4u;
+                    const uint32_t wv[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
+                    #pragma unroll
+                    for (uint32_t k = 0; k < 4; ++k)
+                        if ((g + k) * 4u < static_cast<uint32_t>(p.x_sf_row_bytes))
+                            *reinterpret_cast<uint32_t*>(img + ((g + k) / kPlanes) * rec + tw * 128u + ((g + k) % kPlanes) * tw * 16u + pos * 16u) = wv[k];
+                }
+            }
+        }
+        const bool any_bad = __any_sync(0xffffffffu, bad);      // (also orders the lanes' stores before lane 0's fence)
+        if (lane == 0 && !any_bad) {
+            fence_proxy_async_all();
+            red_release_gpu_add(arrive + tile, 1u);
+            cx.sm_phase(kSmRowsCached);
+        }
+    }
 }
 
 // ============================================================================================= schedule
@@ -1337,7 +1481,8 @@ __device__ __noinline__ uint32_t build_schedule(const KParams& p, Ctl& c, const 
     const uint32_t c0 = lane < el ? counts[lane] : 0u, c1 = lane + 32 < el ? counts[lane + 32] : 0u;
     // rows per token tile: 16, or 32 when the launch works from tile images and an expert has more than 16 rows
     const uint32_t tw = (c.bulk != 0u && __any_sync(0xffffffffu, c0 > kTileTokens || c1 > kTileTokens)) ? kWideTokens : static_cast<uint32_t>(kTileTokens);
-    const uint32_t m0 = udiv_small(c0 + tw - 1u, tw), m1 = udiv_small(c1 + tw - 1u, tw);
+    const uint32_t sh = tw == kWideTokens ? 5u : 4u;
+    const uint32_t m0 = (c0 + tw - 1u) >> sh, m1 = (c1 + tw - 1u) >> sh;
     uint32_t i0 = m0, i1 = m1;
     #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
@@ -1549,7 +1694,7 @@ __device__ __noinline__ void scout_watch_peers(const Ctx& cx, ScoutState& st, bo
 }
 
 // ============================================================================================= the kernel
-template <int kVec, bool kUmma, bool kFe, bool kA8>
+template <int kVec, bool kUmma, bool kFe, bool kA8, bool kTiles>
 __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1) mega_moe_kernel(const __grid_constant__ KParams p) {
     constexpr uint32_t kNT = kA8 ? kThreads + kNumExpThreads : kThreads;       // threads of this instantiation
     const unsigned long long t_first = globaltimer_ns();
@@ -1582,7 +1727,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
         c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u; c.decode = 0u; c.bulk = 0u; c.rel_head = 0u; c.rel_tail = 0u;
         if constexpr (!kScout) c.own_cnt = 0u;
-        for (int s = 0; s < (p.nstage > static_cast<int>(p.nstage_wide) ? p.nstage : static_cast<int>(p.nstage_wide)); ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.rfull[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
+        for (int s = 0; s < (p.nstage > static_cast<int>(p.nstage_wide) ? p.nstage : static_cast<int>(p.nstage_wide)); ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
         #pragma unroll 1
         for (int i = 0; i < 2; ++i) {
             mbar_init(&c.acts_full[i], 1); mbar_init(&c.acts_empty[i], kUmma ? 1 : kNumEpiThreads);
@@ -1590,11 +1735,17 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             mbar_init(&c.xfull[i], kNumExpThreads / 64); mbar_init(&c.xempty[i], 1);
         }
         mbar_init(&c.tile_full, kFillWarps);
-        #pragma unroll 1
-        for (int i = 0; i < 4; ++i) { mbar_init(&c.meta_full[i], 1); mbar_init(&c.meta_empty[i], 1); }
         mbar_fence_init();
         reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmEntry)[bid] = t_first;
         if constexpr (!kScout) reinterpret_cast<unsigned long long*>(buf + p.off_ctrl + kCtrlSmWFirst)[bid] = ~0ull;
+    }
+    if (kTiles && tid == 64) {
+        // (the barriers only the tile-image roles use, set up by another thread than the one that does the rest)
+        #pragma unroll 1
+        for (uint32_t s2 = 0; s2 < p.nstage_wide; ++s2) mbar_init(&c.rfull[s2], 1);
+        #pragma unroll 1
+        for (int i = 0; i < 4; ++i) { mbar_init(&c.meta_full[i], 1); mbar_init(&c.meta_empty[i], 1); }
+        mbar_fence_init();
     }
     // the token staging area starts from zero (the dispatch lists and the frontend's scratch that pass through it later
     // leave finite bytes; whatever sits in rows beyond a task's valid tokens only reaches accumulator columns nobody reads)
@@ -1716,16 +1867,17 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             const long long* tk = reinterpret_cast<const long long*>(inp + p.off_topk_idx);
             const uint32_t n = static_cast<uint32_t>(p.T) * p.topk;
             uint32_t cnt = 0;
+            constexpr uint32_t kDl = kTiles ? 4u : 1u;             // (large batches: four loads in flight, one memory round trip per 128 routing entries)
             #pragma unroll 1
-            for (uint32_t base0 = 0; base0 < n; base0 += 4 * 32) {
-                long long exs[4];                                  // four loads in flight: one memory round trip per 128 routing entries
+            for (uint32_t base0 = 0; base0 < n; base0 += kDl * 32) {
+                long long exs[kDl];
                 #pragma unroll
-                for (uint32_t u = 0; u < 4; ++u) {
+                for (uint32_t u = 0; u < kDl; ++u) {
                     const uint32_t i = base0 + u * 32 + lane;
                     exs[u] = i < n ? tk[i] : -1;
                 }
                 #pragma unroll
-                for (uint32_t u = 0; u < 4; ++u) {
+                for (uint32_t u = 0; u < kDl; ++u) {
                     const uint32_t i = base0 + u * 32 + lane;
                     const long long ex = exs[u];
                     const uint32_t ex32 = ex >= 0 && ex < 0x10000 ? static_cast<uint32_t>(ex) : 0u;
@@ -1835,7 +1987,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             if (bid == 0) cx.stamp(kStampFlagsSeen);
             cx.sm_phase(kSmCountsKnown);
             c.decode = (kUmma && !kA8 && p.rc_rows != 0u && total != 0u && total <= kTileTokens) ? 1u : 0u;     // (the cross-check engine reads the per-task staging buffers)
-            c.bulk = (kUmma && !kA8 && (p.knobs & kKnobTileImages) != 0u && p.nstage_wide >= 3u && total > kTileTokens && total <= kMetaCap) ? 1u : 0u;
+            c.bulk = (kTiles && kUmma && !kA8 && (p.knobs & kKnobTileImages) != 0u && p.nstage_wide >= 3u && total > kTileTokens && total <= kMetaCap) ? 1u : 0u;
         }
         if (total <= kMetaCap) {
             auto take = [&](uint32_t f, const uint4& m) {
@@ -1851,6 +2003,24 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                     cx.ll_read(cx.rx_row(spec_r, spec_i) + 2u * (p.rx_row_bytes - 16), flag_rx, m, kErrWaitDispatchFlag, spec_r);
                 take(pre[spec_r] + spec_i, m);
             }
+            if (!kTiles || total <= kO) {
+                // one record per thread and pass
+                #pragma unroll 1
+                for (uint32_t f = tid; f < total; f += kO) {
+                    uint32_t r = 0;
+                    #pragma unroll
+                    for (int q = 1; q < kMaxRanks; ++q) r += (q < p.R && f >= pre[q]) ? 1u : 0u;
+                    const uint32_t i = f - pre[r];
+                    if (own_ok && r == static_cast<uint32_t>(p.rank)) {
+                        const RowMeta om = c.own_meta[i];
+                        take(f, make_uint4(c.own_e[i], static_cast<uint32_t>(om.token), static_cast<uint32_t>(om.slot), __float_as_uint(om.weight)));
+                    } else if (!(i < 32u && r < kSpecSources)) {         // (else: taken by the speculative read above)
+                        uint4 m = make_uint4(0u, 0u, 0u, 0u);
+                        cx.ll_read(cx.rx_row(r, i) + 2u * (p.rx_row_bytes - 16), flag_rx, m, kErrWaitDispatchFlag, r);
+                        take(f, m);
+                    }
+                }
+            } else
             // (four records per thread in flight together: one memory round trip per four records of a large batch)
             #pragma unroll 1
             for (uint32_t f0 = tid; f0 < total; f0 += 4u * kO) {
@@ -1895,122 +2065,9 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     //      (a sender pushes its header line and records first). The loads are in flight before the bulk copies of the
     //      weight stream start, which would otherwise make them wait behind megabytes.
     const bool is_ctl = warp < 2u;                       // warps 0 and 1 build the schedule and start the weight stream
-    // ---- more than 16 received rows: the rows are sorted into tile images in global memory, one image per token tile
-    //      (16 or 32 rows) of an expert: the rows' records, then per streamed K unit the unit's 128 B of every row in the
-    //      tensor core's swizzled order and the unit's scale-word slots. Row f belongs to SM f mod G; one warp per row.
-    //      Every finished row counts into its tile's arrival word.
+    // ---- more than 16 received rows: the rows are sorted into tile images in global memory (see sort_rows_into_tiles)
     if (warp >= 2u && warp < 2u + kFillWarps && c.bulk != 0u && !cx.aborted()) {
-        const uint32_t el = p.e_local;
-        constexpr uint32_t kPlanes = kUnitK / (4 * kVec);
-        // first tile of every expert: running sum of ceil(rows / tile rows), expert-major (the schedule derives the same numbers)
-        const uint32_t cnt0 = lane < el ? c.exp_count[lane] : 0u, cnt1 = lane + 32 < el ? c.exp_count[lane + 32] : 0u;
-        const uint32_t tw = __any_sync(0xffffffffu, cnt0 > kTileTokens || cnt1 > kTileTokens) ? kWideTokens : static_cast<uint32_t>(kTileTokens);
-        const uint32_t rec = tile_record_bytes(tw, kPlanes);
-        const uint32_t m0 = udiv_small(cnt0 + tw - 1u, tw), m1 = udiv_small(cnt1 + tw - 1u, tw);
-        uint32_t i0 = m0, i1 = m1;
-        #pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const uint32_t v0 = __shfl_up_sync(0xffffffffu, i0, o), v1 = __shfl_up_sync(0xffffffffu, i1, o);
-            if (static_cast<int>(lane) >= o) { i0 += v0; i1 += v1; }
-        }
-        const uint32_t tbase0 = i0 - m0, tbase1 = __shfl_sync(0xffffffffu, i0, 31) + i1 - m1;
-        const uint32_t per_row = p.rc_row_bytes / 16u, xq = p.x_row_bytes / 16u;
-        uint32_t* arrive = reinterpret_cast<uint32_t*>(buf + p.off_arrive) + par * 2u * p.tile_capacity;
-        #pragma unroll 1
-        for (uint32_t f = bid + (warp - 2u) * G; f < total; f += kFillWarps * G) {
-            const uint32_t e = c.meta_e[f];
-            // position among the expert's rows = rows of the same expert received before this one
-            uint32_t n = 0;
-            #pragma unroll 1
-            for (uint32_t base = 0; base < f; base += 128) {
-                const uint32_t idx = base + lane * 4u;
-                const uint32_t w = *reinterpret_cast<const uint32_t*>(c.meta_e + idx);
-                #pragma unroll
-                for (uint32_t b = 0; b < 4; ++b) n += (idx + b < f && ((w >> (8u * b)) & 0xFFu) == e) ? 1u : 0u;
-            }
-            n = __reduce_add_sync(0xffffffffu, n);
-            const uint32_t tb0 = __shfl_sync(0xffffffffu, tbase0, e & 31u), tb1 = __shfl_sync(0xffffffffu, tbase1, e & 31u);
-            const uint32_t tile = (e < 32u ? tb0 : tb1) + udiv_small(n, tw), pos = n - udiv_small(n, tw) * tw;
-            uint32_t r = 0;
-            while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
-            const uint32_t i = f - c.rx_prefix[r];
-            const bool own = own_ok && r == static_cast<uint32_t>(p.rank);
-            const uint8_t* xs = nullptr;
-            const uint8_t* sf = nullptr;
-            const uint8_t* row_src = nullptr;
-            if (own) {
-                const uint32_t tok = static_cast<uint32_t>(c.own_meta[i].token);
-                xs = inp + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
-                sf = inp + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
-            } else {
-                row_src = cx.rx_row(r, i);
-            }
-            uint8_t* head = buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes;
-            uint8_t* img = head + kWideTokens * 16u;
-            bool bad = tile >= p.tile_capacity;
-            // (chunk `per_row` of a received row is its record {expert, token, slot, top-k weight}: it becomes the row's
-            //  record {source rank, token, slot, weight} in the tile's header; an own row's record comes from the scout's list)
-            if (own && lane == 0 && !bad) {
-                const RowMeta m = c.own_meta[i];
-                *reinterpret_cast<uint4*>(head + pos * 16u) = make_uint4(r, static_cast<uint32_t>(m.token), static_cast<uint32_t>(m.slot), __float_as_uint(m.weight));
-            }
-            const uint32_t nread = own ? per_row : per_row + 1u;
-            #pragma unroll 1
-            for (uint32_t base = lane; base < nread && !bad; base += 4 * 32) {
-                uint4 v[4];
-                if (own) {
-                    #pragma unroll
-                    for (uint32_t u = 0; u < 4; ++u) {
-                        const uint32_t ci = base + u * 32;
-                        if (ci < xq) v[u] = ld_cg_v4(xs + ci * 16u);
-                        else if (ci < per_row) v[u] = ld_cg_v4(sf + (ci - xq) * 16u);
-                    }
-                } else {
-                    uint32_t spins = 0;
-                    bool ok;
-                    do {
-                        ok = true;
-                        #pragma unroll
-                        for (uint32_t u = 0; u < 4; ++u) {
-                            const uint32_t ci = base + u * 32;
-                            if (ci < nread) {
-                                const uint4 a = ld_volatile_v4(row_src + ci * 32u), b = ld_volatile_v4(row_src + ci * 32u + 16u);
-                                ok = ok && ll_valid(a, b, flag_rx);
-                                v[u] = ll_data(a, b);
-                            }
-                        }
-                        if (!ok && (++spins & 0x3Fu) == 0u) {
-                            if (cx.aborted()) bad = true;
-                            else if (cx.expired()) { cx.fail(kErrWaitDispatchFlag, r); bad = true; }
-                        }
-                    } while (!ok && !bad);
-                }
-                #pragma unroll
-                for (uint32_t u = 0; u < 4; ++u) {
-                    const uint32_t ci = base + u * 32;
-                    if (ci >= nread || bad) continue;
-                    if (ci == per_row) {
-                        *reinterpret_cast<uint4*>(head + pos * 16u) = make_uint4(r, v[u].y, v[u].z, v[u].w);
-                    } else if (ci < xq) {
-                        *reinterpret_cast<uint4*>(img + (ci >> 3) * rec + sw128_off(pos, ci & 7u)) = v[u];
-                    } else {
-                        // four scale words g .. g + 3 of the row: word g belongs to K unit g / planes, plane g % planes
-                        const uint32_t g = (ci - xq) * 4u;
-                        const uint32_t wv[4] = {v[u].x, v[u].y, v[u].z, v[u].w};
-                        #pragma unroll
-                        for (uint32_t k = 0; k < 4; ++k)
-                            if ((g + k) * 4u < static_cast<uint32_t>(p.x_sf_row_bytes))
-                                *reinterpret_cast<uint32_t*>(img + ((g + k) / kPlanes) * rec + tw * 128u + ((g + k) % kPlanes) * tw * 16u + pos * 16u) = wv[k];
-                    }
-                }
-            }
-            const bool any_bad = __any_sync(0xffffffffu, bad);      // (also orders the lanes' stores before lane 0's fence)
-            if (lane == 0 && !any_bad) {
-                fence_proxy_async_all();
-                red_release_gpu_add(arrive + tile, 1u);
-                cx.sm_phase(kSmRowsCached);
-            }
-        }
+        if constexpr (kTiles && kUmma && !kA8) sort_rows_into_tiles<kVec>(cx, inp, total, own_ok, flag_rx, warp, lane);
     }
     if (warp >= 2u && warp < 2u + kFillWarps && p.rc_rows != 0u && total <= kMetaCap && c.bulk == 0u && !cx.aborted()) {
         const bool decode = c.decode != 0u;
@@ -2126,14 +2183,15 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
 
     // ---- roles
     bool tiles = false;
-    if constexpr (kUmma && !kA8) tiles = c.bulk != 0u;
+    if constexpr (kTiles && kUmma && !kA8) tiles = c.bulk != 0u;
     if (!cx.aborted() && tiles) {
-        if constexpr (kUmma && !kA8) {                     // (launches with more than 16 received rows)
-            if (warp == 0) role_loader_tiles(cx);
-            else if (warp == 1) role_mma_tiles<kVec>(cx, lane);
-            else if (warp == 2) role_record_loader(cx, kUnitK / (4 * kVec));
-            else if (warp == 3) role_releaser(cx);
-            else if (warp >= 4 && warp < 8) role_epilogue_tiles<kVec>(cx, tid - 128);
+        if constexpr (kTiles && kUmma && !kA8) {                     // (launches with more than 16 received rows)
+            const TileP tp = make_tile_params(p);
+            if (warp == 0) role_loader_tiles(cx, tp);
+            else if (warp == 1) role_mma_tiles<kVec>(cx, tp, lane);
+            else if (warp == 2) role_record_loader(cx, tp, kUnitK / (4 * kVec));
+            else if (warp == 3) role_releaser(cx, tp);
+            else if (warp >= 4 && warp < 8) role_epilogue_tiles<kVec>(cx, tp, tid - 128);
         }
     } else if (!cx.aborted()) {
         if (warp == 0) role_loader(cx);

@@ -17,13 +17,18 @@ from oracle import megamoe_oracle as O                     # noqa: E402
 from tests import util_moe as U                            # noqa: E402
 
 
-def run_from_hidden(rank, world, group, fmt):
-    """The whole layer from bf16 hidden states (router + top-8 + quantisation fused at the head of the kernel)."""
+def run_from_hidden(rank, world, group, fmt, skewed=False):
+    """The whole layer from bf16 hidden states (router + top-8 + quantisation fused at the head of the kernel).
+    `skewed`: sigmoid scores + Zipf(1.2) expert bias, renormalised top-8, 16 tokens per rank: the hot experts receive
+    more than 16 rows (32-row token tiles), most experts few or none."""
     e_local, hidden, inter, topk = 8, 1024, 512, 8
     num_experts = e_local * world
-    tokens = [5 + 2 * r for r in range(world)]
+    tokens = [16 - r for r in range(world)] if skewed else [5 + 2 * r for r in range(world)]
     ok = True
     buf = mm.get_symm_buffer_for_mega_moe(group, num_experts, 16, topk, hidden, inter, act_format=fmt)
+    gb = torch.Generator().manual_seed(11)
+    bias = (1.0 / torch.arange(1, num_experts + 1, dtype=torch.float32) ** 1.2)[torch.randperm(num_experts, generator=gb)] if skewed else None
+    mode = 'sigmoid_bias' if skewed else 'softmax'
     weights = [O.make_expert_weights(e_local, hidden, inter, fmt, seed=70 + r, std=0.05)[0] for r in range(world)]
     l1, l2 = mm.transform_weights_for_mega_moe(*U.to_operator_weights(weights[rank], fmt, 'cuda'))
     ws = torch.zeros(mm.fe_workspace_bytes(buf), dtype=torch.uint8, device='cuda')
@@ -34,17 +39,26 @@ def run_from_hidden(rank, world, group, fmt):
         for r in range(world):
             gx = torch.Generator().manual_seed(1000 * it + r)
             x = torch.randn((tokens[r], hidden), generator=gx).to(torch.bfloat16)
-            idx, tw = O.route_from_logits(O.router_logits_device_order(x, wr), x, topk)
+            idx, tw = O.route_from_logits(O.router_logits_device_order(x, wr), x, topk, mode, bias)
             q, sf, _ = O.quantise_tokens(x, fmt, rounding='rne', sf_rule='mul')
             xs.append(x); inputs.append(O.RankInput(q, sf, idx, tw))
         ref = O.moe_layer_reference(inputs, weights, fmt, num_experts, clamp=10.0)
         y = torch.empty((tokens[rank], hidden), dtype=torch.bfloat16, device='cuda')
+        stats = torch.zeros(e_local, dtype=torch.int32, device='cuda')
         dist.barrier()
-        mm.mega_moe_from_hidden(y, xs[rank].cuda(), wr.cuda(), l1, l2, buf, ws, activation_clamp=10.0, timeout_ms=2000.0)
+        mm.mega_moe_from_hidden(y, xs[rank].cuda(), wr.cuda(), l1, l2, buf, ws, cumulative_local_expert_recv_stats=stats,
+                                activation_clamp=10.0, score_mode=1 if skewed else 0,
+                                expert_bias=bias.cuda() if skewed else None, timeout_ms=2000.0)
         st, words = buf.device_status()
         if st != 0:
             print(f'rank {rank}: device status {st} {[hex(v) for v in words[:4]]}', flush=True)
             return False
+        if not torch.equal(stats.cpu(), ref.counts[rank]):
+            print(f'rank {rank} it {it}: counts {stats.cpu().tolist()} != {ref.counts[rank].tolist()}', flush=True)
+            ok = False
+        if skewed and rank == 0 and it == 0 and max(int(c.max()) for c in ref.counts) <= 16:
+            print('the skewed case has no expert with more than 16 rows', flush=True)
+            ok = False
         if not torch.equal(buf.topk_idx[:tokens[rank]].cpu(), inputs[rank].topk_idx):
             print(f'rank {rank} it {it}: top-8 differs from the oracle', flush=True)
             ok = False
@@ -64,8 +78,9 @@ def main():
     group = dist.group.WORLD
     fmt = os.environ.get('MP_FORMAT', 'mxfp4')
     engine = os.environ.get('MP_ENGINE', 'umma')
-    if os.environ.get('MP_MODE', 'routed') == 'from_hidden':
-        flag = torch.tensor([1 if run_from_hidden(rank, world, group, fmt) else 0], device='cuda')
+    if os.environ.get('MP_MODE', 'routed') in ('from_hidden', 'from_hidden_skewed'):
+        skewed = os.environ['MP_MODE'] == 'from_hidden_skewed'
+        flag = torch.tensor([1 if run_from_hidden(rank, world, group, fmt, skewed) else 0], device='cuda')
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         if rank == 0:
             print('MP_OK' if int(flag) == 1 else 'MP_FAIL', flush=True)

@@ -48,6 +48,15 @@ def test_two_ranks_from_hidden_states():
     _run(2, 'mxfp4', mode='from_hidden')
 
 
+def test_skewed_routing_from_hidden_states_on_all_gpus():
+    """Sigmoid scores + Zipf(1.2) expert bias over all ranks' experts, 16 tokens per rank, router fused into the launch:
+    hot experts receive more than 16 rows from several source ranks (32-row token tiles), counts and top-8 exact."""
+    n = torch.cuda.device_count()
+    if n < 2:
+        pytest.skip('needs two GPUs')
+    _run(8 if n >= 8 else (4 if n >= 4 else 2), 'mxfp4', mode='from_hidden_skewed')
+
+
 def test_all_ranks_of_the_node():
     n = torch.cuda.device_count()
     if n < 4:

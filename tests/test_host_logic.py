@@ -34,8 +34,17 @@ def test_layout_regions_are_ordered_and_sized():
     st, L = _layout()
     assert st == 0
     offs = [L.off_ctrl, L.off_x, L.off_x_sf, L.off_topk_idx, L.off_topk_weights, L.off_rx, L.off_mid,
-            L.off_mid_sf, L.off_comb, L.off_red, L.off_cnt, L.total_bytes]
+            L.off_mid_sf, L.off_comb, L.off_red, L.off_cnt, L.off_logits, L.off_token_tiles, L.off_mid_tiles, L.off_arrive,
+            L.total_bytes]
     assert offs == sorted(offs) and all(o % 1024 == 0 for o in offs)
+    # tile images (launches with more than 16 received rows): one per 16 rows of the intermediate pool at most; per tile 32
+    # row records of 16 B (token tiles), then per 256-element K unit a record of 32 rows x 128 B + two scale-word slot planes
+    rec32 = 32 * 128 + 2 * 32 * 16
+    assert L.tile_capacity == L.mid_rows // 16
+    assert L.token_tile_bytes == 32 * 16 + (3072 // 256) * rec32 and L.mid_tile_bytes == (1280 // 256) * rec32
+    assert L.off_mid_tiles - L.off_token_tiles >= L.tile_capacity * L.token_tile_bytes
+    assert L.off_arrive - L.off_mid_tiles >= L.tile_capacity * L.mid_tile_bytes
+    assert L.total_bytes - L.off_arrive >= 2 * 2 * L.tile_capacity * 4
     assert L.x_row_bytes == 1536 and L.x_sf_row_bytes == 96 and L.rx_row_bytes == 1536 + 96 + 16
     assert L.rx_cap_rows == 128 * 8 and L.mid_row_bytes == 640 and L.mid_sf_row_bytes == 48
     assert L.rx_region_bytes >= 32 + 2 * L.rx_cap_rows * L.rx_row_bytes

@@ -1347,14 +1347,12 @@ __device__ void role_releaser(const Ctx& cx, const TileP p) {
     if (lane == 0) { tc.total(27, lat_sum); tc.total(28, lat_max); tc.total(29, busy); }
 }
 
-// Out of line on purpose: launches with at most 16 received rows never run it, and inline it would sit in the middle of
-// the start-up code they do run.
 // ---- more than 16 received rows: the rows are sorted into tile images in global memory, one image per token tile
 //      (16 or 32 rows) of an expert: the rows' records, then per streamed K unit the unit's 128 B of every row in the
 //      tensor core's swizzled order and the unit's scale-word slots. Row f belongs to SM f mod G; one warp per row.
 //      Every finished row counts into its tile's arrival word.
 template <int kVec>
-__device__ __noinline__ void sort_rows_into_tiles(const Ctx& cx, const uint8_t* inp, uint32_t total, bool own_ok, uint32_t flag_rx, uint32_t warp, uint32_t lane) {
+__device__ __forceinline__ void sort_rows_into_tiles(const Ctx& cx, const uint8_t* inp, uint32_t total, bool own_ok, uint32_t flag_rx, uint32_t warp, uint32_t lane) {
     const KParams& p = cx.p; Ctl& c = cx.c;
     uint8_t* buf = cx.buf;
     const uint32_t bid = blockIdx.x, G = gridDim.x, par = cx.par;
@@ -1374,8 +1372,24 @@ __device__ __noinline__ void sort_rows_into_tiles(const Ctx& cx, const uint8_t* 
     const uint32_t tbase0 = i0 - m0, tbase1 = __shfl_sync(0xffffffffu, i0, 31) + i1 - m1;
     const uint32_t per_row = p.rc_row_bytes / 16u, xq = p.x_row_bytes / 16u;
     uint32_t* arrive = reinterpret_cast<uint32_t*>(buf + p.off_arrive) + par * 2u * p.tile_capacity;
+    // Records of this warp's first 32 rows that are own rows without an entry in the scout's list or in shared memory:
+    // lane k fetches the record of the warp's k-th row, all in one memory round trip (the row's token index is in it).
+    const uint32_t f_first = bid + (warp - 2u) * G, f_step = kFillWarps * G;
+    uint4 my_rec = make_uint4(0u, 0u, 0u, 0u);
+    bool my_rec_bad = false;
+    if (cx.own_direct && !own_ok) {
+        const uint32_t f = f_first + lane * f_step;
+        if (f < total && f >= kMetaSmemRows) {
+            uint32_t r = 0;
+            while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
+            if (r == static_cast<uint32_t>(p.rank))
+                my_rec_bad = !cx.ll_read(cx.rx_row(r, f - c.rx_prefix[r]) + 2u * (p.rx_row_bytes - 16), flag_rx, my_rec, kErrWaitDispatchFlag, r);
+        }
+    }
+    uint32_t done_tiles[4];                                 // tiles of the rows written since the last release (one release per four rows)
+    uint32_t ndone = 0, krow = 0;
     #pragma unroll 1
-    for (uint32_t f = bid + (warp - 2u) * G; f < total; f += kFillWarps * G) {
+    for (uint32_t f = f_first; f < total; f += f_step, ++krow) {
         const uint32_t e = c.meta_e[f];
         // position among the expert's rows = rows of the same expert received before this one
         uint32_t n = 0;
@@ -1392,12 +1406,30 @@ __device__ __noinline__ void sort_rows_into_tiles(const Ctx& cx, const uint8_t* 
         uint32_t r = 0;
         while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
         const uint32_t i = f - c.rx_prefix[r];
-        const bool own = own_ok && r == static_cast<uint32_t>(p.rank);
+        const bool own = cx.own_direct && r == static_cast<uint32_t>(p.rank);
         const uint8_t* xs = nullptr;
         const uint8_t* sf = nullptr;
         const uint8_t* row_src = nullptr;
+        RowMeta own_m{0, 0, 0, 0.f};
+        bool rec_bad = false;
         if (own) {
-            const uint32_t tok = static_cast<uint32_t>(c.own_meta[i].token);
+            // the row's record: from the scout's list, or (a batch too large for that list) from the receive pool, where the
+            // dispatch left the records of the own rows without their payload
+            if (own_ok) own_m = c.own_meta[i];
+            else if (f < kMetaSmemRows) own_m = c.rx_meta[f];
+            else {
+                uint4 q = my_rec;
+                bool qbad = my_rec_bad;
+                if (krow >= 32u) {                                  // (beyond the prefetched records: fetch it now)
+                    q = make_uint4(0u, 0u, 0u, 0u);
+                    if (lane == 0) qbad = !cx.ll_read(cx.rx_row(r, i) + 2u * (p.rx_row_bytes - 16), flag_rx, q, kErrWaitDispatchFlag, r);
+                }
+                const uint32_t src_lane = krow < 32u ? krow : 0u;
+                rec_bad = __shfl_sync(0xffffffffu, qbad ? 1u : 0u, src_lane) != 0u;
+                own_m = RowMeta{0, static_cast<int32_t>(__shfl_sync(0xffffffffu, q.y, src_lane)), static_cast<int32_t>(__shfl_sync(0xffffffffu, q.z, src_lane)),
+                                __uint_as_float(__shfl_sync(0xffffffffu, q.w, src_lane))};
+            }
+            const uint32_t tok = static_cast<uint32_t>(own_m.token);
             xs = inp + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
             sf = inp + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
         } else {
@@ -1405,11 +1437,11 @@ __device__ __noinline__ void sort_rows_into_tiles(const Ctx& cx, const uint8_t* 
         }
         uint8_t* head = buf + p.off_token_tiles + static_cast<size_t>(tile) * p.token_tile_bytes;
         uint8_t* img = head + kWideTokens * 16u;
-        bool bad = tile >= p.tile_capacity;
+        bool bad = tile >= p.tile_capacity || __any_sync(0xffffffffu, rec_bad);
         // (chunk `per_row` of a received row is its record {expert, token, slot, top-k weight}: it becomes the row's
-        //  record {source rank, token, slot, weight} in the tile's header; an own row's record comes from the scout's list)
+        //  record {source rank, token, slot, weight} in the tile's header)
         if (own && lane == 0 && !bad) {
-            const RowMeta m = c.own_meta[i];
+            const RowMeta m = own_m;
             *reinterpret_cast<uint4*>(head + pos * 16u) = make_uint4(r, static_cast<uint32_t>(m.token), static_cast<uint32_t>(m.slot), __float_as_uint(m.weight));
         }
         const uint32_t nread = own ? per_row : per_row + 1u;
@@ -1463,10 +1495,20 @@ __device__ __noinline__ void sort_rows_into_tiles(const Ctx& cx, const uint8_t* 
             }
         }
         const bool any_bad = __any_sync(0xffffffffu, bad);      // (also orders the lanes' stores before lane 0's fence)
-        if (lane == 0 && !any_bad) {
-            fence_proxy_async_all();
-            red_release_gpu_add(arrive + tile, 1u);
-            cx.sm_phase(kSmRowsCached);
+        if (any_bad) break;
+        // the rows' arrival counts: one release fence per four rows (under the weight flood a release takes microseconds),
+        // then one relaxed count per row
+        done_tiles[ndone & 3u] = tile;
+        ++ndone;
+        if ((ndone & 3u) == 0u || f + f_step >= total) {
+            if (lane == 0) {
+                fence_proxy_async_all();
+                __threadfence();
+                const uint32_t nrel = (ndone & 3u) == 0u ? 4u : (ndone & 3u);
+                for (uint32_t k = 0; k < nrel; ++k) atomicAdd(arrive + done_tiles[k], 1u);
+                cx.sm_phase(kSmRowsCached);
+            }
+            ndone = 0;
         }
     }
 }
@@ -1756,7 +1798,11 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     }
     if (warp == 1) { tmem_alloc(&c.tmem_base, kTmemCols); tmem_relinquish(); tc_fence_before(); }
     if (tid < kMaxLocalExperts) c.exp_count[tid] = 0u;
-    Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, 0u, own_ok};
+    // Larger batches (the build with tile images): the rows of this rank's own tokens still get their header line and
+    // records in the receive pool, but their payload does not travel: whoever needs such a row reads the token where the
+    // caller put it (its index is in the record).
+    const bool own_skip = kTiles && !kFe && !own_ok && p.inp == buf && static_cast<uint32_t>(p.T) * p.topk > kOwnCap;
+    Ctx cx{p, c, buf, smem, globaltimer_ns() + p.timeout_ns, 0u, own_ok || own_skip};
     if (is_scout) {
         // the scout does not wait for the prologue: it lists the own rows and asks for their experts' weights first
         bar_arrive(kBarPrologue, kNT);
@@ -1918,7 +1964,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
                                buf + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes, lane,
                                dst_base + static_cast<size_t>(i) * 2u * p.rx_row_bytes, flag, static_cast<uint32_t>(p.x_row_bytes));
             }
-        } else {
+        } else if (!(own_skip && d == static_cast<uint32_t>(p.rank))) {
         // warp w copies rows w, w + 8, ...: lane l moves chunks l, l + 32, ... (eight in flight: one memory round trip for
         // a row of up to 4 KB)
         #pragma unroll 1
@@ -2080,7 +2126,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             uint32_t r = 0;
             while (r + 1 < static_cast<uint32_t>(p.R) && f >= c.rx_prefix[r + 1]) ++r;
             const uint32_t i = f - c.rx_prefix[r];
-            const bool own = own_ok && r == static_cast<uint32_t>(p.rank);  // this rank's own token: read it where the caller put it
+            const bool own = cx.own_direct && r == static_cast<uint32_t>(p.rank);  // this rank's own token: read it where the caller put it
             // decode mode: row position in the shared tile = rows of experts with a smaller index, then the earlier rows
             // of the same expert (receive order)
             const uint32_t e = c.meta_e[f];
@@ -2090,7 +2136,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             const uint8_t* sf = nullptr;
             const uint8_t* row_src = nullptr;
             if (own) {
-                const uint32_t tok = static_cast<uint32_t>(c.own_meta[i].token);
+                const uint32_t tok = static_cast<uint32_t>(own_ok ? c.own_meta[i].token : c.rx_meta[f].token);   // (f < 16: its record is in shared memory)
                 xs = inp + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes;
                 sf = inp + p.off_x_sf + static_cast<size_t>(tok) * p.x_sf_row_bytes;
             } else {

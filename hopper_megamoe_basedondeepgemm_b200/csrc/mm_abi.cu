@@ -318,13 +318,14 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
         p.ndisp = nd < 1 ? 1 : nd;
     }
     // launches that work from tile images reuse the stages and the token staging area as one ring of wider stages
-    p.wide_stage_bytes = p.unit_bytes + mm::kWideTokens * 128 + (mm::kUnitK / (4 * vec)) * mm::kWideTokens * 16;
+    p.wide_stage_bytes = p.unit_bytes;
+    p.rec_slot_bytes = mm::kWideTokens * 128 + (mm::kUnitK / (4 * vec)) * mm::kWideTokens * 16;
     p.sm_act = nstage * p.unit_bytes;
     p.sm_asf = p.sm_act + p.nab * p.act_bytes;
     p.sm_otile = p.sm_asf + 2 * p.asf_bytes;
     p.stage_region = p.sm_otile - p.sm_act;
     p.nstage_wide = a8 ? 0u : p.sm_otile / p.wide_stage_bytes;
-    if (p.nstage_wide > static_cast<uint32_t>(mm::kMaxStages)) p.nstage_wide = mm::kMaxStages;
+    if (p.nstage_wide > 6u) p.nstage_wide = 6u;
     p.sm_vt = p.sm_otile + static_cast<uint32_t>(otile_bytes);
     p.sm_xbuf = static_cast<uint32_t>(align_up(p.sm_vt + vt_bytes, 1024));
     size_t used = a8 ? p.sm_xbuf + xbytes : p.sm_vt + vt_bytes;
@@ -338,7 +339,13 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
         const size_t region = as_cache > as_tile ? as_cache : as_tile;
         if (g_tuning[MM_TUNE_ROW_CACHE] != 0 && !a8 && p.sm_rcache + region + 1024 + 256 <= 232448 - sizeof(mm::Ctl) - 768) {
             p.rc_rows = 16;
-            used = p.sm_rcache + region;
+            // launches with tile images keep their ring of token records here: as many slots as fit, eight at most
+            const size_t room = 232448 - sizeof(mm::Ctl) - 768 - 1024 - 256 - p.sm_rcache;
+            p.sm_rec = p.sm_rcache;
+            p.nrec = static_cast<uint32_t>(room / p.rec_slot_bytes);
+            if (p.nrec > mm::kMaxRecSlots) p.nrec = mm::kMaxRecSlots;
+            const size_t rec_region = static_cast<size_t>(p.nrec) * p.rec_slot_bytes;
+            used = p.sm_rcache + (region > rec_region ? region : rec_region);
         }
     }
     *smem_bytes = used + 1024 + 256;
@@ -347,7 +354,7 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
 }
 
 static bool wants_tile_images(const mm::KParams& p) {
-    return (p.knobs & mm::kKnobTileImages) != 0u && p.nstage_wide >= 3u && static_cast<long long>(p.T) * p.topk > mm::kTileTokens;
+    return (p.knobs & mm::kKnobTileImages) != 0u && p.nstage_wide >= 3u && p.nrec >= 2u && static_cast<long long>(p.T) * p.topk > mm::kTileTokens;
 }
 
 template <int kVec, bool kUmma, bool kFe = false, bool kA8 = false, bool kTiles = false>
@@ -619,7 +626,8 @@ int mm_mega_moe_launch_static_scratch(const mm_config_t* cfg, const mm_static_ar
     // (the split-tile partial sums between them are always written before they are read: not cleared)
     MM_CUDA(cudaMemsetAsync(scratch + L.off_ctrl, 0, L.off_x - L.off_ctrl, s));
     MM_CUDA(cudaMemsetAsync(scratch + L.off_rx, 0, L.off_red - L.off_rx, s));
-    MM_CUDA(cudaMemsetAsync(scratch + L.off_cnt, 0, L.total_bytes - L.off_cnt, s));
+    MM_CUDA(cudaMemsetAsync(scratch + L.off_cnt, 0, L.off_token_tiles - L.off_cnt, s));
+    MM_CUDA(cudaMemsetAsync(scratch + L.off_arrive, 0, L.total_bytes - L.off_arrive, s));      // (the tile images need no clearing)
     const size_t t = static_cast<size_t>(a->num_tokens);
     if (t > 0) {
         MM_CUDA(cudaMemcpyAsync(scratch + L.off_x, a->x, t * L.x_row_bytes, cudaMemcpyDeviceToDevice, s));

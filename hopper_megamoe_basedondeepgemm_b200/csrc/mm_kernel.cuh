@@ -60,6 +60,7 @@ constexpr uint32_t kXbufBytes = 2 * kUnitWBytes + 1024;   // one widened unit + 
 constexpr uint32_t kTmemCols = 128;
 constexpr uint32_t kFillWarps = 5;       // warps 2..6 fetch the received rows into shared memory while the schedule is built
 constexpr uint32_t kOtileBytes = 8192;
+constexpr uint32_t kMaxRecSlots = 8;      // slots of the token-record ring
 constexpr uint32_t kRelQueue = 8;         // entries of the epilogue -> releasing warp queue
 constexpr uint32_t kWideTokens = 32;      // token tile of the launches whose experts have more than 16 rows
 constexpr uint32_t kVtStride = kTileRows + 8;   // floats between the tokens of the accumulator tile (tile-image epilogue: conflict-free 16 B reads)
@@ -128,7 +129,8 @@ struct KParams {
     int cnt_per_phase;
     long long off_token_tiles, off_mid_tiles, off_arrive;   // operand tile images and their arrival counters (launches with more than 16 rows)
     uint32_t tile_capacity, token_tile_bytes, mid_tile_bytes;
-    uint32_t wide_stage_bytes, nstage_wide;   // with tile images a ring stage holds a weight unit and a 32-row token record; stages that fit
+    uint32_t wide_stage_bytes, nstage_wide;   // launches with tile images: stride and depth of the weight ring (it takes over the token staging buffers)
+    uint32_t sm_rec, nrec, rec_slot_bytes;    // and a ring of token records of its own (in the token region): offset, slots, bytes of a 32-row record
     long long rx_region;                 // bytes of one (parity, source) region of the receive pool
     uint32_t sm_act, sm_asf, sm_otile, sm_vt;   // dynamic shared memory offsets (stages start at 0)
     uint32_t act_bytes, asf_bytes;
@@ -144,7 +146,7 @@ struct KParams {
 
 struct Ctl {
     uint64_t full[kMaxStages], empty[kMaxStages];
-    uint64_t rfull[kMaxStages];          // launches with tile images: the token record of a stage has landed
+    uint64_t rfull[kMaxRecSlots], rempty[kMaxRecSlots];   // launches with tile images: ring of token records (record loader -> MMA issuer)
     uint64_t acts_full[2], acts_empty[2], tmem_full[2], tmem_empty[2];
     uint64_t xfull[2], xempty[2];        // FP8-activation variant: widened weight units
     uint64_t meta_full[4], meta_empty[4];   // launches with tile images: the row records of a task's tile (loader -> epilogue)
@@ -156,7 +158,7 @@ struct Ctl {
     uint32_t comb_next, issued, decode, bulk;   // next combine item of this SM; weight units the loader has issued; decode mode and tile-image mode (see below)
     // rows of a token tile in this launch (16, or 32 when tile images are in use and an expert has more than 16 rows);
     // queue of finished intermediate tiles, epilogue -> releasing warp
-    uint32_t tw, rel_head, rel_tail, padw;
+    uint32_t tw, rel_head, rel_tail, rissued;   // (rissued: token records and tile headers the record loader has issued, for the aborted exit)
     uint32_t rel_q[kRelQueue];
     long long rel_t[kRelQueue];          // (wait profile: when the entry was queued)
     uint32_t n1_tasks, padn[3];          // L1 tasks at the head of this SM's list
@@ -888,7 +890,7 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
 // for up to 32 rows).
 // The launch parameters the tile-image roles use, handed to them by value (in registers).
 struct TileP {
-    uint32_t unit_bytes, wide_stage_bytes, nstage_wide, tile_capacity, token_tile_bytes, mid_tile_bytes, sm_vt, knobs;
+    uint32_t unit_bytes, wide_stage_bytes, nstage_wide, tile_capacity, token_tile_bytes, mid_tile_bytes, sm_vt, knobs, sm_rec, nrec, rec_slot_bytes;
     int n1_tiles, n2_tiles, k1_units, k2_units, topk, H, has_clamp, fast_math, cnt_per_phase;
     float clamp, l1_scale, l2_scale, mid_gs;
     long long off_mid_tiles, off_token_tiles, off_arrive, off_red, off_cnt, off_comb;
@@ -896,6 +898,7 @@ struct TileP {
 };
 __device__ __forceinline__ TileP make_tile_params(const KParams& p) {
     TileP t;
+    t.sm_rec = p.sm_rec; t.nrec = p.nrec; t.rec_slot_bytes = p.rec_slot_bytes;
     t.unit_bytes = p.unit_bytes; t.wide_stage_bytes = p.wide_stage_bytes; t.nstage_wide = p.nstage_wide; t.tile_capacity = p.tile_capacity;
     t.token_tile_bytes = p.token_tile_bytes; t.mid_tile_bytes = p.mid_tile_bytes; t.sm_vt = p.sm_vt; t.knobs = p.knobs;
     t.n1_tiles = p.n1_tiles; t.n2_tiles = p.n2_tiles; t.k1_units = p.k1_units; t.k2_units = p.k2_units; t.topk = p.topk; t.H = p.H;
@@ -960,7 +963,7 @@ __device__ void role_record_loader(const Ctx& cx, const TileP p, uint32_t planes
     const uint32_t lane = threadIdx.x & 31u;
     const uint32_t tw = c.tw, rec = tile_record_bytes(tw, planes);
     const uint32_t* arrive = reinterpret_cast<const uint32_t*>(buf + p.off_arrive) + par * 2u * p.tile_capacity;
-    uint32_t s = 0, ph = 0;
+    uint32_t s = 0, ph = 0, nissued = 0;
     long long w_tiles = 0;
     // Whether a task's tile is complete (L1: its received rows, L2: the outputs of all L1 weight tiles, counted into the
     // tile's arrival word) is looked up for 32 tasks at a time, one lane per task: one memory round trip per window.
@@ -1012,13 +1015,14 @@ __device__ void role_record_loader(const Ctx& cx, const TileP p, uint32_t planes
         const int ub = c.tasks2[ti] & 0xFF, ue = (c.tasks2[ti] >> 8) & 0xFF;
         #pragma unroll 1
         for (int u = ub; u < ue; ++u) {
-            if (!cx.warp_wait(&c.empty[s], ph ^ 1u, kErrWaitEmpty)) return;
+            if (!cx.warp_wait(&c.rempty[s], ph ^ 1u, kErrWaitEmpty)) return;
             if (elect_one()) {
                 mbar_arrive_expect_tx(&c.rfull[s], rec);
-                bulk_g2s(smem + static_cast<size_t>(s) * p.wide_stage_bytes + p.unit_bytes, img + static_cast<size_t>(u) * rec, rec, &c.rfull[s]);
+                bulk_g2s(smem + p.sm_rec + static_cast<size_t>(s) * p.rec_slot_bytes, img + static_cast<size_t>(u) * rec, rec, &c.rfull[s]);
+                c.rissued = ++nissued;
             }
             __syncwarp();
-            if (++s == p.nstage_wide) { s = 0; ph ^= 1u; }
+            if (++s == p.nrec) { s = 0; ph ^= 1u; }
         }
     }
     if (lane == 0u) tc.total(17, w_tiles);
@@ -1034,7 +1038,7 @@ __device__ void role_mma_tiles(const Ctx& cx, const TileP p, uint32_t lane) {
     const uint32_t idesc0 = idesc_block_scaled(kFmtMxf4E2M1, kFmtMxf4E2M1, kTileRows, tw, kVec == 32 ? 1u : 0u);
     const uint32_t tm = c.tmem_base;
     const uint32_t sfa_col = 64, sfb_col = 96;                  // accumulators 2 x 32 columns, weight scales 2 x 16, token scales 2 x 16
-    uint32_t it = 0, s = 0, ph = 0;
+    uint32_t it = 0, s = 0, ph = 0, rs = 0, rph = 0;             // units consumed; weight stage and record slot with their phase bits
     unsigned long long t_landed = 0ull;
     long long w_tmem = 0, w_full = 0, w_tok = 0;
     const long long t_role = tc.clk();
@@ -1048,14 +1052,14 @@ __device__ void role_mma_tiles(const Ctx& cx, const TileP p, uint32_t lane) {
         #pragma unroll 1
         for (int u = ub; u < ue; ++u, ++it) {
             if (!tc.wait(&c.full[s], ph, kErrWaitFull, w_full)) return;
-            if (!tc.wait(&c.rfull[s], ph, kErrWaitActsFull, w_tok)) return;
+            if (!tc.wait(&c.rfull[rs], rph, kErrWaitActsFull, w_tok)) return;
             tc_fence_after();
             t_landed = globaltimer_ns();
             if (lane == 0 && it == 0u) cx.sm_phase(kSmFirstLanded);
             if (elect_one()) {
                 const uint32_t wsm = smem_u32(smem + static_cast<size_t>(s) * p.wide_stage_bytes);
                 const uint32_t wsf = wsm + static_cast<uint32_t>(kUnitWBytes);
-                const uint32_t tok = wsm + p.unit_bytes, tsf = tok + tw * 128u;
+                const uint32_t tok = smem_u32(smem + p.sm_rec + static_cast<size_t>(rs) * p.rec_slot_bytes), tsf = tok + tw * 128u;
                 const uint32_t sfa = tm + sfa_col + (it & 1u) * 16u, sfb = tm + sfb_col + (it & 1u) * 16u;
                 #pragma unroll
                 for (uint32_t pl = 0; pl < kPlanes; ++pl) {
@@ -1076,9 +1080,11 @@ __device__ void role_mma_tiles(const Ctx& cx, const TileP p, uint32_t lane) {
                         umma_nvf4_block16(tm + acc * kWideTokens, adesc, bdesc, idesc, sfa + pl * 4u, sfb + pl * 4u, accum);
                 }
                 tc_commit(&c.empty[s]);
+                tc_commit(&c.rempty[rs]);
             }
             __syncwarp();
             if (++s == p.nstage_wide) { s = 0; ph ^= 1u; }
+            if (++rs == p.nrec) { rs = 0; rph ^= 1u; }
         }
         if (elect_one()) tc_commit(&c.tmem_full[acc]);
         __syncwarp();
@@ -1767,7 +1773,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (tid == 0) {
         const uint32_t ep = ctrl32[kCtrlEpoch / 4 + bid];
         ctrl32[kCtrlEpoch / 4 + bid] = ep + 1u;
-        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u; c.decode = 0u; c.bulk = 0u; c.rel_head = 0u; c.rel_tail = 0u;
+        c.epoch = ep; c.abort_flag = 0u; c.ntasks = 0u; c.dcount = 0u; c.comb_next = 0u; c.issued = 0u; c.decode = 0u; c.bulk = 0u; c.rel_head = 0u; c.rel_tail = 0u; c.rissued = 0u;
         if constexpr (!kScout) c.own_cnt = 0u;
         for (int s = 0; s < (p.nstage > static_cast<int>(p.nstage_wide) ? p.nstage : static_cast<int>(p.nstage_wide)); ++s) { mbar_init(&c.full[s], 1); mbar_init(&c.empty[s], kA8 ? kNumExpThreads / 64 : (kUmma ? 1 : kNumEpiThreads)); }
         #pragma unroll 1
@@ -1784,7 +1790,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if (kTiles && tid == 64) {
         // (the barriers only the tile-image roles use, set up by another thread than the one that does the rest)
         #pragma unroll 1
-        for (uint32_t s2 = 0; s2 < p.nstage_wide; ++s2) mbar_init(&c.rfull[s2], 1);
+        for (uint32_t s2 = 0; s2 < p.nrec; ++s2) { mbar_init(&c.rfull[s2], 1); mbar_init(&c.rempty[s2], 1); }
         #pragma unroll 1
         for (int i = 0; i < 4; ++i) { mbar_init(&c.meta_full[i], 1); mbar_init(&c.meta_empty[i], 1); }
         mbar_fence_init();
@@ -2033,7 +2039,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             if (bid == 0) cx.stamp(kStampFlagsSeen);
             cx.sm_phase(kSmCountsKnown);
             c.decode = (kUmma && !kA8 && p.rc_rows != 0u && total != 0u && total <= kTileTokens) ? 1u : 0u;     // (the cross-check engine reads the per-task staging buffers)
-            c.bulk = (kTiles && kUmma && !kA8 && (p.knobs & kKnobTileImages) != 0u && p.nstage_wide >= 3u && total > kTileTokens && total <= kMetaCap) ? 1u : 0u;
+            c.bulk = (kTiles && kUmma && !kA8 && (p.knobs & kKnobTileImages) != 0u && p.nstage_wide >= 3u && p.nrec >= 2u && total > kTileTokens && total <= kMetaCap) ? 1u : 0u;
         }
         if (total <= kMetaCap) {
             auto take = [&](uint32_t f, const uint4& m) {
@@ -2335,6 +2341,15 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
         for (uint32_t k = issued > nst ? issued - nst : 0u; k < issued; ++k) {
             const uint32_t s = k % nst, ph = (k / nst) & 1u;
             for (uint32_t spin = 0; spin < 400000u && !mbar_try_wait(&c.full[s], ph); ++spin) { }
+        }
+        if (tiles) {                                       // likewise the token records (and the last tile header) still on their way
+            const uint32_t rissued = *reinterpret_cast<volatile uint32_t*>(&c.rissued), nr = p.nrec;
+            #pragma unroll 1
+            for (uint32_t k = rissued > nr ? rissued - nr : 0u; k < rissued; ++k) {
+                const uint32_t s = k % nr, ph = (k / nr) & 1u;
+                for (uint32_t spin = 0; spin < 400000u && !mbar_try_wait(&c.rfull[s], ph); ++spin) { }
+            }
+            for (uint32_t spin = 0; spin < 2000u; ++spin) __nanosleep(100);      // (a 512 B header copy: microseconds at most)
         }
     }
     __syncthreads();

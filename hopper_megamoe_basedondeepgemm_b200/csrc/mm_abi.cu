@@ -567,7 +567,7 @@ int mm_mega_moe_from_hidden_launch(const mm_config_t* cfg, const mm_launch_args_
     q.topk_w = reinterpret_cast<float*>(b + L.off_topk_weights);
     q.x_row_bytes = static_cast<int>(L.x_row_bytes); q.x_sf_row_bytes = static_cast<int>(L.x_sf_row_bytes);
     p.fe_enabled = 1;
-    p.ndisp = 1;                          // the dispatching SMs also select the routes: one per destination
+    // (the dispatching SMs also select the routes, each of them for all tokens: `fill_params` chose one SM per eight rows)
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (a->engine != MM_ENGINE_UMMA) return MM_ERR_UNSUPPORTED;     // the cross-check engine takes pre-routed inputs only
     if (a8) return fe->num_tokens == 0 ? launch_variant<32, true, false, true>(p, grid, smem_bytes, s)

@@ -134,7 +134,7 @@ struct KParams {
     long long rx_region;                 // bytes of one (parity, source) region of the receive pool
     uint32_t sm_act, sm_asf, sm_otile, sm_vt;   // dynamic shared memory offsets (stages start at 0)
     uint32_t act_bytes, asf_bytes;
-    int ndisp;                           // SMs that share the dispatch to one destination rank (1 with the fused frontend)
+    int ndisp;                           // SMs that share the dispatch to one destination rank
     uint32_t sm_xbuf; int nab;           // widened-unit buffers (FP8 variant); number of 16-row token staging buffers (1 or 2)
     uint32_t stage_region;               // bytes of the token staging area (tiles + scale slots)
     uint32_t sm_rcache, rc_rows, rc_row_bytes;   // row cache: received rows (tokens + scale bytes) fetched before the weight stream starts
@@ -1892,7 +1892,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
     if constexpr (kFe) {
         const uint32_t fe_flag = epoch + 1u;
         fe_logits_items(p.fe, bid * (kNT / 32) + warp, G * (kNT / 32), lane, fe_flag);
-        if (bid < static_cast<uint32_t>(p.R)) {
+        if (dispatching) {                       // (every dispatching SM selects all tokens: it needs the whole routing for its row list)
             float* sc = reinterpret_cast<float*>(smem + p.sm_act) + warp * 2 * p.fe.E;
             auto give_up = [&]() -> bool {
                 if (cx.aborted()) return true;
@@ -1963,7 +1963,7 @@ __global__ void __launch_bounds__(kA8 ? kThreads + kNumExpThreads : kThreads, 1)
             // quantise the tokens this SM sends: into the x / x_sf views (the same bytes whichever SM writes them) and, from
             // the same registers, into the destination's receive pool
             #pragma unroll 1
-            for (uint32_t i = warp; i < cnt; i += kCopyWarps) {
+            for (uint32_t i = part + warp * ndisp; i < cnt; i += kCopyWarps * ndisp) {
                 const uint32_t tok = dlist[i] >> 16;
                 fe_quant_token(p.fe.hidden + static_cast<size_t>(tok) * p.H, p.H, kA8 ? 2 : (kVec == 32 ? 0 : 1), p.fe.x_gs,
                                buf + p.off_x + static_cast<size_t>(tok) * p.x_row_bytes,

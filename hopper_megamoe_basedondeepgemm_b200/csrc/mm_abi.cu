@@ -317,7 +317,8 @@ static int fill_params(const mm_config_t* cfg, const mm_launch_args_t* a, mm::KP
         if (nd > *grid / p.R) nd = *grid / p.R;
         p.ndisp = nd < 1 ? 1 : nd;
     }
-    // launches that work from tile images reuse the stages and the token staging area as one ring of wider stages
+    // launches that work from tile images use the stages and the token staging area as one longer weight ring, and the
+    // token region as a ring of token records (32 rows x 128 B + scale-word slots per slot)
     p.wide_stage_bytes = p.unit_bytes;
     p.rec_slot_bytes = mm::kWideTokens * 128 + (mm::kUnitK / (4 * vec)) * mm::kWideTokens * 16;
     p.sm_act = nstage * p.unit_bytes;

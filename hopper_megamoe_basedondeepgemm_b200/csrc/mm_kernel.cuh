@@ -883,11 +883,12 @@ __device__ void role_epilogue(const Ctx& cx, uint32_t etid) {
 // Launches with more than 16 received rows. The rows have been sorted into tile images in global memory (token tiles by
 // the sorting pass after the dispatch, intermediate tiles by the L1 epilogues): per tile and per streamed K unit one
 // record = the unit's 128 B of every token row in the tensor core's swizzled order, then the unit's scale-word slots.
-// A record travels with its weight unit: the loader fetches both into the same ring stage (two bulk copies, one
-// barrier), so a task needs no token staging of its own and the token operand costs the loader two instructions per
-// unit, whatever the weight flood does to small loads. A token tile has `c.tw` rows: 16, or 32 when an expert has
-// more than 16 rows (the block-scaled MMA takes the same time for 16 and 32 columns: an expert's weights stream once
-// for up to 32 rows).
+// A record travels beside its weight unit: one warp streams the weight units into the weight ring (which takes over the
+// space of the token staging buffers), another the records into a ring of record slots in the token region; the MMA
+// issuer waits for both copies of a unit. A task needs no token staging of its own and the token operand costs one bulk
+// copy per unit, whatever the weight flood does to small loads. A token tile has `c.tw` rows: 16, or 32 when an expert
+// has more than 16 rows (the block-scaled MMA takes the same time for 16 and 32 columns: an expert's weights stream
+// once for up to 32 rows).
 // The launch parameters the tile-image roles use, handed to them by value (in registers).
 struct TileP {
     uint32_t unit_bytes, wide_stage_bytes, nstage_wide, tile_capacity, token_tile_bytes, mid_tile_bytes, sm_vt, knobs, sm_rec, nrec, rec_slot_bytes;
@@ -923,7 +924,7 @@ struct TileCtx {
 };
 __device__ __forceinline__ uint32_t tile_record_bytes(uint32_t tw, uint32_t planes) { return tw * 128u + planes * tw * 16u; }
 
-// Weight units of this SM's tasks into the ring of wide stages (the same stream as `role_loader`, wider stage stride).
+// Weight units of this SM's tasks into the weight ring of the tile-image launches (the same stream as `role_loader`, more stages).
 __device__ void role_loader_tiles(const Ctx& cx, const TileP p) {
     Ctl& c = cx.c;
     uint8_t* const smem = cx.smem;
@@ -979,9 +980,9 @@ __device__ void role_record_loader(const Ctx& cx, const TileP p, uint32_t planes
         }
         win_base = base;
         win_ready = __ballot_sync(0xffffffffu, r);
-        fence_proxy_async_all();       // the rows were written through the generic proxy; the bulk copies read them through the async proxy
     };
     refresh(0u);
+    fence_proxy_async_all();           // the rows were written through the generic proxy; the bulk copies read them through the async proxy
     #pragma unroll 1
     for (uint32_t ti = 0; ti < c.ntasks; ++ti) {
         const uint32_t t = c.tasks[ti];
@@ -1000,6 +1001,7 @@ __device__ void role_record_loader(const Ctx& cx, const TileP p, uint32_t planes
                     if (cx.expired()) { cx.fail(type ? kErrWaitL1Done : kErrWaitDispatchFlag, e); return; }
                 }
             }
+            fence_proxy_async_all();
             w_tiles += tc.clk() - t0;
         }
         {

@@ -206,10 +206,25 @@ template <typename GiveUp>
 __device__ __forceinline__ bool fe_select_token(const FeParams& q, uint32_t t, float* sc, bool nonzero, uint32_t lane, uint32_t flag, GiveUp give_up) {
     float* lgv = sc + q.E;
     bool ok = true;
-    for (int e = lane; e < q.E; e += 32) {
-        const float v = fe_read_logit(q, t, e, flag, ok, give_up);
-        lgv[e] = v;
-        sc[e] = q.score_mode == 1 ? (1.0f / (1.0f + expf(-v))) + q.bias[e] : v;
+    // the token's logit records, eight per lane in flight at a time (one memory round trip per 256 experts when they have
+    // all arrived); a record that is not complete yet is polled on its own afterwards
+    for (int e0 = lane; e0 < q.E; e0 += 32 * 8) {
+        uint4 rec[8];
+        #pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            const int e = e0 + 32 * b;
+            if (e < q.E) rec[b] = ld_volatile_v4(reinterpret_cast<const uint8_t*>(q.logits) + (static_cast<size_t>(t) * q.E + e) * 16u);
+        }
+        #pragma unroll
+        for (int b = 0; b < 8; ++b) {
+            const int e = e0 + 32 * b;
+            if (e >= q.E) continue;
+            float v;
+            if (flag == 0u || (rec[b].y == flag && rec[b].w == flag)) v = bf16_round(__uint_as_float(rec[b].x) + __uint_as_float(rec[b].z)) + 0.0f;
+            else v = fe_read_logit(q, t, static_cast<uint32_t>(e), flag, ok, give_up);
+            lgv[e] = v;
+            sc[e] = q.score_mode == 1 ? (1.0f / (1.0f + expf(-v))) + q.bias[e] : v;
+        }
     }
     if (!__all_sync(0xffffffffu, ok)) return false;
     __syncwarp();

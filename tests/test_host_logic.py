@@ -173,3 +173,31 @@ def test_tuning_values_round_trip():
     assert lib.mm_set_tuning(_lib.TUNE['stages'], 6) == 0 and lib.mm_get_tuning(_lib.TUNE['stages']) == 6
     assert lib.mm_set_tuning(_lib.TUNE['stages'], old) == 0
     assert lib.mm_set_tuning(99, 1) == 1 and lib.mm_set_tuning(0, -1) == 1 and lib.mm_get_tuning(99) == -1
+
+
+@pytest.mark.parametrize('tw,vec', [(16, 32), (32, 32), (32, 16)])
+def test_tile_image_reader_inverts_the_documented_layout(tw, vec):
+    """Tile images (launches with more than 16 received rows): per 256-element K unit a record of `tw` rows x 128 B in
+    the 128 B swizzle (16 B chunk c of row r at chunk c ^ (r & 7) of the row's 128 B, rows in groups of 8 x 128 B), then
+    per scale word of the unit `tw` slots of 16 B with the word in the first 4 bytes. Images written with that address
+    arithmetic are read back row by row by `SymmBuffer._rows_of_tile_images`."""
+    from types import SimpleNamespace
+    from hopper_megamoe_basedondeepgemm_b200.mega import SymmBuffer
+    torch.manual_seed(tw + vec)
+    row_bytes, tiles, header = 640, 3, 512
+    units, planes = row_bytes // 128, 256 // (4 * vec)
+    rec = tw * 128 + planes * tw * 16
+    rows = torch.randint(0, 256, (tiles * tw, row_bytes), dtype=torch.uint8)
+    words = torch.randint(0, 256, (tiles * tw, units * planes, 4), dtype=torch.uint8)
+    img = torch.zeros((tiles, header + units * rec), dtype=torch.uint8)
+    for t in range(tiles):
+        for r in range(tw):
+            for ci in range(row_bytes // 16):
+                off = header + (ci >> 3) * rec + (r >> 3) * 1024 + (r & 7) * 128 + (((ci & 7) ^ (r & 7)) << 4)
+                img[t, off:off + 16] = rows[t * tw + r, ci * 16:ci * 16 + 16]
+            for g in range(units * planes):
+                off = header + (g // planes) * rec + tw * 128 + (g % planes) * tw * 16 + r * 16
+                img[t, off:off + 4] = words[t * tw + r, g]
+    fake = SimpleNamespace(layout=SimpleNamespace(sf_vec=vec))
+    got_rows, got_words = SymmBuffer._rows_of_tile_images(fake, img, row_bytes, tw, header)
+    assert torch.equal(got_rows, rows) and torch.equal(got_words, words)

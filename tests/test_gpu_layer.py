@@ -274,7 +274,7 @@ def test_kernel_features_do_not_change_the_result(fmt):
     default = lib.mm_get_tuning(_lib.TUNE['knobs'])
     outs = []
     try:
-        for knobs in (0, 7, 1, 2, 4, 16, 22):
+        for knobs in (0, 7, 1, 2, 4, 16, 22, 54):            # (54 = 22 + the wait profile of the tile roles)
             mm.set_tuning(knobs=knobs)
             y, stats, ref, buf, _ = run_layer(fmt, e_local=48, hidden=3072, inter=1280, topk=8, tokens=3, routing='balanced',
                                               engine='umma', std=0.02)

@@ -67,7 +67,7 @@ WINDOW_HANDLE_BYTES = 64
 EXPORTS = ('mm_get_layout', 'mm_get_weight_geometry', 'mm_get_token_alignment', 'mm_mega_moe_launch',
            'mm_frontend_launch', 'mm_frontend_workspace_bytes', 'mm_mega_moe_from_hidden_launch', 'mm_reset',
            'mm_read_device_status', 'mm_read_phase_stamps', 'mm_status_string', 'mm_last_cuda_error',
-           'mm_mega_moe_launch_static_scratch', 'mm_set_tuning', 'mm_get_tuning', 'mm_read_sm_phases', 'mm_fe_forward', 'mm_fe_workspace_bytes', 'mm_fe_router_ctas', 'mm_transform_weights', 'mm_cast_rows_to_fp4', 'mm_window_alloc', 'mm_window_open', 'mm_window_close')
+           'mm_mega_moe_launch_static_scratch', 'mm_set_tuning', 'mm_get_tuning', 'mm_read_sm_phases', 'mm_fe_forward', 'mm_fe_workspace_bytes', 'mm_fe_router_ctas', 'mm_transform_weights', 'mm_cast_rows_to_fp4', 'mm_tensor_absmax', 'mm_window_alloc', 'mm_window_open', 'mm_window_close')
 
 _libs = {}
 
@@ -106,6 +106,7 @@ def load(check: bool = False) -> ctypes.CDLL:
     lib.mm_fe_router_ctas.restype = ctypes.c_int32
     lib.mm_transform_weights.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64,
                                          ctypes.c_int64] + [ctypes.c_int32] * 5 + [ctypes.c_void_p, ctypes.c_void_p]
+    lib.mm_tensor_absmax.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_void_p, ctypes.c_void_p]
     lib.mm_cast_rows_to_fp4.argtypes = [ctypes.c_void_p] + [ctypes.c_int32] * 5 + [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p]
     lib.mm_window_alloc.argtypes = [ctypes.c_int64, P(ctypes.c_void_p), ctypes.c_char_p]
     lib.mm_window_open.argtypes = [ctypes.c_char_p, ctypes.c_int32, ctypes.c_int32, ctypes.c_void_p, P(ctypes.c_void_p)]

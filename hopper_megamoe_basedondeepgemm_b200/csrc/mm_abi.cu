@@ -494,6 +494,23 @@ int mm_cast_rows_to_fp4(const void* x, int32_t x_is_bf16, int32_t m, int32_t k, 
     return MM_OK;
 }
 
+int mm_tensor_absmax(const void* x, int32_t x_is_bf16, int64_t n, float* absmax_out, void* stream) {
+    if (x == nullptr || absmax_out == nullptr || n < 0) return MM_ERR_INVALID_ARGUMENT;
+    if ((reinterpret_cast<uintptr_t>(x) & 15u) != 0u) return MM_ERR_INVALID_ARGUMENT;      // 16 B loads
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    MM_CUDA(cudaMemsetAsync(absmax_out, 0, sizeof(float), s));
+    if (n == 0) return MM_OK;
+    const long long per = x_is_bf16 ? 8 : 4;
+    long long blocks = (n / per + 255) / 256;
+    blocks = blocks < 1 ? 1 : (blocks > 1184 ? 1184 : blocks);                               // eight blocks per SM at most
+    if (x_is_bf16)
+        mm::absmax_kernel<__nv_bfloat16><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), n, reinterpret_cast<uint32_t*>(absmax_out));
+    else
+        mm::absmax_kernel<float><<<static_cast<unsigned>(blocks), 256, 0, s>>>(static_cast<const float*>(x), n, reinterpret_cast<uint32_t*>(absmax_out));
+    MM_CUDA(cudaGetLastError());
+    return MM_OK;
+}
+
 int64_t mm_fe_workspace_bytes(int32_t e) { return e > 0 ? 256 + static_cast<int64_t>(4) * 64 * e * 4 : -1; }
 
 int32_t mm_fe_router_ctas(int32_t m, int32_t h, int32_t e, int32_t topk) {

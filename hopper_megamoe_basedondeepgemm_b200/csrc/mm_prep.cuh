@@ -103,4 +103,31 @@ __global__ void __launch_bounds__(256) cast_rows_fp4_kernel(const T* __restrict_
     }
 }
 
+// Largest magnitude of a tensor (grid-stride, 16 B loads, one atomic per block): the calibration step of a per-tensor
+// global scale. `out` holds the bit pattern of a non-negative float (such patterns order like unsigned integers) and must
+// start at zero; NaNs are ignored.
+template <typename T>
+__global__ void __launch_bounds__(256) absmax_kernel(const T* __restrict__ x, long long n, uint32_t* __restrict__ out) {
+    constexpr int kPer = 16 / sizeof(T);
+    float m = 0.f;
+    const long long nvec = n / kPer;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec; i += static_cast<long long>(gridDim.x) * blockDim.x) {
+        const uint4 q = ld_cg_v4(reinterpret_cast<const uint4*>(x) + i);
+        const T* v = reinterpret_cast<const T*>(&q);
+        #pragma unroll
+        for (int j = 0; j < kPer; ++j) m = fmaxf(m, fabsf(static_cast<float>(v[j])));
+    }
+    if (blockIdx.x == 0 && threadIdx.x < n - nvec * kPer) m = fmaxf(m, fabsf(static_cast<float>(x[nvec * kPer + threadIdx.x])));
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    __shared__ float part[8];
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        #pragma unroll
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, part[w]);
+        atomicMax(out, __float_as_uint(m));
+    }
+}
+
 }  // namespace mm

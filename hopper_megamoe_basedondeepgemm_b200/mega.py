@@ -268,6 +268,23 @@ def get_symm_buffer_for_mega_moe(group, num_experts: int, num_max_tokens_per_ran
                       use_fp8_dispatch, activation, act_format, num_sms, window)
 
 
+def nvfp4_global_scale(t: torch.Tensor) -> float:
+    """Per-tensor NVFP4 global scale of a CUDA bf16 / fp32 tensor: largest magnitude / (6 * 448), so that the largest
+    per-16 block scale is the largest E4M3 value. The reduction is the library's `mm_tensor_absmax` kernel; the
+    result comes back to the host (load time / calibration, not the hot path)."""
+    if not t.is_cuda or t.dtype not in (torch.bfloat16, torch.float32):
+        raise RuntimeError('nvfp4_global_scale takes a CUDA bf16 or fp32 tensor')
+    if t.numel() == 0:
+        return 0.0
+    t = t.contiguous()
+    if t.data_ptr() % 16:
+        t = t.clone()                                     # (a view that starts inside a 16 B word: the kernel loads 16 B at a time)
+    out = torch.zeros(1, dtype=torch.float32, device=t.device)
+    _lib.check(_lib.load().mm_tensor_absmax(t.data_ptr(), 1 if t.dtype == torch.bfloat16 else 0, t.numel(), out.data_ptr(),
+                                            torch.cuda.current_stream().cuda_stream), 'nvfp4_global_scale')
+    return float(out.item()) / (6.0 * 448.0)
+
+
 def transform_weights_for_mega_moe(l1_weights: Tuple[torch.Tensor, torch.Tensor],
                                    l2_weights: Tuple[torch.Tensor, torch.Tensor]):
     """Load-time weight transform (`sm100_b200/mega___init__.py:102-111`).

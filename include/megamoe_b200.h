@@ -130,6 +130,10 @@ int mm_transform_weights(const void* w_packed, const void* sf, int32_t sf_is_fp3
                          void* out_stream, void* stream);
 /* Row-wise cast to packed E2M1 with one fp32 scale per gran_k elements, the arithmetic of `per_token_cast_to_fp4`
  * (deep_gemm/utils/math.py:85-111). x: bf16 or fp32 [m][k]; packed_out [m][k/2]; sf_out fp32 [m][k/gran_k]. */
+/* Largest magnitude of a bf16 or fp32 tensor of n elements (16-byte aligned), written as one float to device memory: the
+ * calibration step of an NVFP4 per-tensor global scale, `absmax / (6 * 448)` (the rule of the benchmark's NVFP4
+ * configuration; the reference's SM100 operator has no global-scale argument and its tests compute none). */
+int mm_tensor_absmax(const void* x, int32_t x_is_bf16, int64_t n, float* absmax_out, void* stream);
 int mm_cast_rows_to_fp4(const void* x, int32_t x_is_bf16, int32_t m, int32_t k, int32_t gran_k, int32_t use_ue8m0,
                         void* packed_out, float* sf_out, void* stream);
 /* sm100_b200/apis_mega.hpp:544-552 (`get_token_alignment_for_mega_moe`) */

@@ -71,3 +71,17 @@ def test_fp4_cast_kernel_matches_the_reference_helper_vectors():
     assert lib.mm_cast_rows_to_fp4(xf.data_ptr(), 0, m, k, 32, 1, packed.data_ptr(), sf.data_ptr(), torch.cuda.current_stream().cuda_stream) == 0
     torch.cuda.synchronize()
     assert np.array_equal(packed.cpu().numpy(), gold['cast_fp4_packed'])
+
+
+@pytest.mark.parametrize('dtype', [torch.bfloat16, torch.float32])
+def test_global_scale_calibration_matches_torch(dtype):
+    """`mm_tensor_absmax` / `nvfp4_global_scale`: largest magnitude of a tensor (sizes that are not multiples of the 16 B
+    load, the maximum in the ragged tail, an all-zero and an empty tensor), exact against torch."""
+    g = torch.Generator().manual_seed(5)
+    for n in (1, 7, 4096, 48 * 2560 * 96 + 3):
+        x = torch.randn(n, generator=g).to(dtype).cuda()
+        if n > 4:
+            x[-1] = 37.5                                  # in the tail beyond the last full 16 B load
+        assert mm.nvfp4_global_scale(x) == float(x.float().abs().max().item()) / (6.0 * 448.0)
+    assert mm.nvfp4_global_scale(torch.zeros(64, dtype=dtype, device='cuda')) == 0.0
+    assert mm.nvfp4_global_scale(torch.zeros(0, dtype=dtype, device='cuda')) == 0.0

@@ -201,3 +201,53 @@ def test_tile_image_reader_inverts_the_documented_layout(tw, vec):
     fake = SimpleNamespace(layout=SimpleNamespace(sf_vec=vec))
     got_rows, got_words = SymmBuffer._rows_of_tile_images(fake, img, row_bytes, tw, header)
     assert torch.equal(got_rows, rows) and torch.equal(got_words, words)
+
+
+def _closed_form_schedule(nt, k, g):
+    """The kernel's per-SM task list of one phase (`build_schedule` in csrc/mm_kernel.cuh), restated: NT weight-tile
+    tasks of k units on G SMs. The first r = NT mod G tiles are split along K: tile t of them is shared by the SMs
+    [ceil(t G / r), ceil((t + 1) G / r)), each taking one contiguous unit range (sizes differ by at most one); SM b
+    then runs the whole tiles r + b, r + b + G, ... Returns per SM a list of (tile, first unit, end unit, parts)."""
+    r = nt % g
+    out = []
+    for b in range(g):
+        tasks = []
+        if r:
+            t = b * r // g
+            gs, ge = -(-t * g // r), -(-(t + 1) * g // r)
+            s, li = ge - gs, b - gs
+            base, extra = k // s, k % s
+            ub = li * base + min(li, extra)
+            ue = ub + base + (1 if li < extra else 0)
+            if ue > ub:
+                tasks.append((t, ub, ue, min(s, k)))
+        tasks += [(t, 0, k, 1) for t in range(r + b, nt, g)]
+        out.append(tasks)
+    return out
+
+
+@pytest.mark.parametrize('g', [148, 132, 8])
+def test_closed_form_schedule_covers_every_unit_once(g):
+    """Every (tile, unit) of a phase is owned by exactly one SM, the parts of a split tile are contiguous ranges that
+    agree on their count, and the SMs' unit totals differ by at most one tile's units (the arithmetic the kernel's
+    scheduler runs per SM, for 16- and 32-row token tiles alike: only the number of tiles changes)."""
+    for n_tiles, k in ((20, 12), (24, 5), (3, 7)):
+        for m in list(range(1, 20)) + [48, 96, 113]:
+            nt = m * n_tiles
+            sched = _closed_form_schedule(nt, k, g)
+            owner = {}
+            parts = {}
+            for b, tasks in enumerate(sched):
+                assert sum(1 for t in tasks if t[3] > 1) <= 1          # at most one partial task per SM and phase
+                for (t, ub, ue, np_) in tasks:
+                    assert 0 <= ub < ue <= k
+                    parts.setdefault(t, set()).add(np_)
+                    for u in range(ub, ue):
+                        assert (t, u) not in owner, (m, t, u)
+                        owner[(t, u)] = b
+            assert len(owner) == nt * k
+            assert all(len(v) == 1 for v in parts.values())
+            for t, v in parts.items():
+                assert sum(1 for tasks in sched for x in tasks if x[0] == t) == next(iter(v))
+            loads = [sum(ue - ub for (_, ub, ue, _) in tasks) for tasks in sched]
+            assert max(loads) - min(loads) <= k

@@ -251,3 +251,12 @@ def test_closed_form_schedule_covers_every_unit_once(g):
                 assert sum(1 for tasks in sched for x in tasks if x[0] == t) == next(iter(v))
             loads = [sum(ue - ub for (_, ub, ue, _) in tasks) for tasks in sched]
             assert max(loads) - min(loads) <= k
+
+
+def test_global_scale_helper_refuses_host_tensors():
+    """`nvfp4_global_scale` runs the library's reduction kernel: there is no CPU path, a host tensor is an error."""
+    import hopper_megamoe_basedondeepgemm_b200 as mm
+    with pytest.raises(RuntimeError):
+        mm.nvfp4_global_scale(torch.ones(8))
+    lib = _lib.load()
+    assert lib.mm_tensor_absmax(None, 1, 8, None, None) == 1        # invalid argument: null pointers
